@@ -1,0 +1,220 @@
+/*
+ * pariskv_b200 -- C ABI of the B200 (sm_100a) ParisKV retrieval engine.
+ *
+ * Every entry point takes plain tensor descriptors (pointer, shape, strides, dtype tag) and a
+ * CUDA stream handle, launches asynchronously on that stream, allocates nothing on the device
+ * (scratch is passed in by the caller, see pk_*_workspace_bytes) and returns a status code:
+ * 0 on success, non-zero on a rejected argument or a CUDA launch error; pk_last_error() then
+ * holds a message (thread local).  The caller makes the device of the tensors current.
+ *
+ * Each declaration names the reference interface it replaces (path inside the reference
+ * project : line).  Logical tensor shapes are the reference's; strides are free unless stated,
+ * so the reference's plane-major tensors ([bs,H,16,N]) and this library's preferred key-major
+ * storage ([bs,H,N,16] exposed as a permuted view) both work; the key-major form is the fast one.
+ *
+ * Deterministic selection everywhere: ties are broken by the lowest index and outputs have a
+ * fixed order (stated per function); the reference's own kernels leave both to atomics order.
+ */
+#ifndef PARISKV_B200_H
+#define PARISKV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PK_MAX_DIMS 6
+
+enum pk_dtype { PK_U8 = 0, PK_I32 = 1, PK_I64 = 2, PK_F32 = 3, PK_BF16 = 4 };
+
+enum pk_status {
+  PK_OK = 0,
+  PK_ERR_ARG = 1,       /* bad shape / dtype / stride / null pointer */
+  PK_ERR_CUDA = 2,      /* a CUDA runtime call or launch failed */
+  PK_ERR_UNSUPPORTED = 3,
+  PK_ERR_WORKSPACE = 4  /* workspace missing or too small */
+};
+
+/* A strided view.  stride[] is in ELEMENTS of dtype.  data may be a device pointer or, where
+ * a function says "host", a pinned host pointer that the device can read (UVA). */
+typedef struct pk_tensor {
+  void* data;
+  int32_t dtype; /* enum pk_dtype */
+  int32_t ndim;
+  int64_t shape[PK_MAX_DIMS];
+  int64_t stride[PK_MAX_DIMS];
+} pk_tensor;
+
+int pk_version(void);
+const char* pk_last_error(void);
+/* Number of kernels launched by this library in this process (all threads). */
+int64_t pk_launch_count(void);
+
+/* ---- (a) key coding ---------------------------------------------------------------------- */
+
+/* SRHT normalise-rotate + 8-bit sign code + 4-bit (sign | 3-bit level) code + fused rerank weight
+ * for L keys per (batch, head); optionally adds the per-subspace code histogram of those keys.
+ * Replaces polar_cache.batch_encode + _pack_4bit_codes + _count_cluster_keys
+ * (cache_hub/polar_cache.py:924-978, :887-893, :980-996).
+ *   keys          bf16 [bs,H,L,128]   last stride 1
+ *   signs         bf16 [128]          SRHT diagonal (+1/-1)
+ *   codebook      u8   [bs,H,16,L]
+ *   block_weight  bf16 [bs,H,16,L]
+ *   packed_4bit   u8   [bs,H,16,L,4]  last stride 1
+ *   cluster_counts i32 [bs,H,16,256] contiguous, ADDED to; may be NULL */
+int pk_encode_keys(const pk_tensor* keys, const pk_tensor* signs, const pk_tensor* codebook,
+                   const pk_tensor* block_weight, const pk_tensor* packed_4bit,
+                   const pk_tensor* cluster_counts, void* stream);
+
+/* Histogram of codes per (batch, head, subspace): polar_cache._count_cluster_keys
+ * (cache_hub/polar_cache.py:980-996).  counts i32 [bs,H,16,256] contiguous; accumulate != 0 adds
+ * to the existing contents (as :774-775), 0 overwrites (as :600-601). */
+int pk_count_clusters(const pk_tensor* codebook, const pk_tensor* counts, int accumulate, void* stream);
+
+/* ---- query side -------------------------------------------------------------------------- */
+
+/* GQA group mean + normalise + SRHT of the decode query: polar_cache.compute :1027-1031 and
+ * _encode_query_blocks (cache_hub/polar_cache.py:905-922).
+ *   queries  bf16 [bs,1,Hq,128] contiguous;  q_blocks bf16 [bs,H,16,8];  q_norm bf16 [bs,H,1]
+ *   query_avg bf16 [bs,H,128] or NULL (the group mean, needed by the adaptive-k variants) */
+int pk_query_prep(const pk_tensor* queries, const pk_tensor* signs, const pk_tensor* q_blocks,
+                  const pk_tensor* q_norm, const pk_tensor* query_avg, void* stream);
+
+/* Cluster ranking: scores = q_blocks @ sign_table^T, argsort descending
+ * (cache_hub/polar_cache.py:1216-1217).  Ties go to the lower cluster id.
+ *   q_blocks bf16 [bs,H,16,8] contiguous;  sorted_ids i64 [bs,H,16,256] contiguous */
+int pk_rank_clusters(const pk_tensor* q_blocks, const pk_tensor* sorted_ids, void* stream);
+
+/* ---- (b) collision counting --------------------------------------------------------------- */
+
+/* Weighted multi-tier collision count: module update_cache_cnt.update_cache_cnt of
+ * cache_hub/collision_fused/collision.cu:395-416 (Python: collison_interface.py:60-86).
+ *   sorted_cluster_ids i64|i32 [bs,H,B,NC] contiguous, NC <= 256, B <= 32
+ *   cluster_key_counts i32 [bs,H,B,NC] contiguous
+ *   codebook           u8  [bs,H,B,N]  any strides
+ *   tier_counts        host array of n_tiers (1..8) thresholds
+ *   cache_cnt          i32 [bs,H,N] contiguous (output)
+ *   workspace          >= pk_collision_workspace_bytes(bs,H,B,NC) bytes, device */
+int64_t pk_collision_workspace_bytes(int64_t bs, int64_t H, int64_t B, int64_t NC);
+int pk_collision_fused(const pk_tensor* sorted_cluster_ids, const pk_tensor* cluster_key_counts,
+                       const pk_tensor* codebook, const int64_t* tier_counts, int n_tiers,
+                       const pk_tensor* cache_cnt, void* workspace, int64_t workspace_bytes,
+                       void* stream);
+
+/* Single-tier unfused collision count: module update_cache_cnt.update_cache_cnt of
+ * cache_hub/collision/collision.cu:161-281 (Python: collision.py:87-98).
+ *   sorted_cluster_ids i32 [bs,H,B,NC]; topk_cluster_cnt i32 [bs,H,B];
+ *   code_book i32 [bs,H,N,B] contiguous; cache_cnt i32 [bs,H,N]; workspace as above */
+int pk_collision(const pk_tensor* sorted_cluster_ids, const pk_tensor* topk_cluster_cnt,
+                 const pk_tensor* code_book, const pk_tensor* cache_cnt, void* workspace,
+                 int64_t workspace_bytes, void* stream);
+
+/* ---- (c) top-k ------------------------------------------------------------------------------ */
+
+/* Exact top-k of every row of input [rows, L] (i32 or f32, row stride free, last stride 1):
+ * radix_topk_ext.{bucket_topk,radix_topk}[_3d] of cache_hub/topk/radix_topk.cu:258-401.
+ * The selected set is the first k of (value descending, index ascending).
+ *   out    i64 [rows, k] contiguous
+ *   order  0: ascending index;  1: value descending (index ascending among equals), k <= 4096 */
+int pk_topk(const pk_tensor* input, int64_t k, const pk_tensor* out, int order, void* stream);
+
+/* Final select of the retrieval chain: torch.topk + gather of cache_hub/polar_cache.py:1300-1302,
+ * on fp32 scores.  out[i] = cand[position], positions chosen as in pk_topk order 0.
+ *   scores f32 [bs,H,C]; cand i64 [bs,H,C]; out i64 [bs,H,K] */
+int pk_final_topk(const pk_tensor* scores, const pk_tensor* cand, int64_t K, const pk_tensor* out,
+                  void* stream);
+
+/* Fused adaptive-k: module adaptive_topk.adaptive_topk of
+ * cache_hub/adaptive_k_fused/adaptive_topk.cu:272-314, and the varlen call contract of
+ * cache_hub/polar_cache_adaptivek_varlen.py:1741-1753.
+ *   sl_logits   f32 [bs,H,S]   already scaled, last stride 1
+ *   cand_scores f32|bf16 [bs,H,C]; logit = float(score) * cand_scale
+ *   sl_vnorm    f32 [bs,H,S]   last stride 1
+ *   cand_indices i64 [bs,H,C]
+ *   cand_vnorm  f32 [bs,H,C], or NULL with value_norm f32 [bs,H,cap] and sink_size:
+ *               norm of candidate i = value_norm[b,h, cand_indices[i] + sink_size]
+ *   adaptive_k  i64 [bs,H]; topk_indices i64 [bs,H,K_out], benefit descending;
+ *   min_k/max_k clamp the result when max_k > 0 (polar_cache_adaptivek_varlen.py:1759) */
+int pk_adaptive_topk(const pk_tensor* sl_logits, const pk_tensor* cand_scores, float cand_scale,
+                     const pk_tensor* sl_vnorm, const pk_tensor* cand_indices,
+                     const pk_tensor* cand_vnorm, const pk_tensor* value_norm, int64_t sink_size,
+                     float threshold, int64_t K_out, int64_t min_k, int64_t max_k,
+                     const pk_tensor* adaptive_k, const pk_tensor* topk_indices, void* stream);
+
+/* ---- (d) rerank ------------------------------------------------------------------------------ */
+
+/* 4-bit RaBitQ rerank: module rerank.partial_rerank of cache_hub/rerank/rerank.cu:141-224
+ * (Python: rerank.py:214-263).  fp32 accumulation; correct for any batch size.
+ *   coarse_indices i64 [bs,H,C] contiguous
+ *   key_4bit  u8 [bs,H,16,N,4] last stride 1;  key_block_weight bf16 [bs,H,16,N] any strides
+ *   q_blocks bf16 [bs,H,16,8] contiguous; q_norm bf16 [bs,H,1]; mag_centers bf16 [8]
+ *   approx_scores bf16 [bs,H,C]; scores_f32 f32 [bs,H,C] or NULL; v4b bf16 [bs,H,16,C,8] or NULL */
+int pk_rerank(const pk_tensor* coarse_indices, const pk_tensor* key_4bit,
+              const pk_tensor* key_block_weight, const pk_tensor* q_blocks, const pk_tensor* q_norm,
+              const pk_tensor* mag_centers, const pk_tensor* approx_scores,
+              const pk_tensor* scores_f32, const pk_tensor* v4b, void* stream);
+
+/* ---- (e) gather and sparse decode attention ----------------------------------------------------- */
+
+/* UVA gather of selected K/V rows from pinned host memory: module h2d_gather_kv.h2d_gather_kv of
+ * cache_hub/gather_trans/trans_h2d.cu:79-126 (Python: trans_h2d.py:65-105).
+ *   src_k/src_v bf16 [bs,H,N,128] contiguous, pinned HOST (or device) memory
+ *   selected_indices i64 [bs,H,K] contiguous (device); dst_k/dst_v bf16 [bs,H,cap>=K,128] device */
+int pk_h2d_gather_kv(const pk_tensor* src_k, const pk_tensor* src_v, const pk_tensor* selected_indices,
+                     const pk_tensor* dst_k, const pk_tensor* dst_v, void* stream);
+
+/* Packed (varlen) UVA gather: call contract of cache_hub/polar_cache_adaptivek_varlen.py:1634-1644.
+ * For virtual head vh = b*H + h and j < cu_seqlens_topk[vh+1]-cu_seqlens_topk[vh]:
+ *   k_packed[cu_seqlens_k[vh] + sink_local_end + j] = src_k[b,h, indices_packed[cu_seqlens_topk[vh]+j]]
+ *   k_packed/v_packed bf16 [total_k,128]; indices_packed i64 [total_topk]; cu_* i32 [bs*H+1] */
+int pk_h2d_gather_kv_packed(const pk_tensor* src_k, const pk_tensor* src_v, const pk_tensor* k_packed,
+                            const pk_tensor* v_packed, const pk_tensor* indices_packed,
+                            const pk_tensor* cu_seqlens_topk, const pk_tensor* cu_seqlens_k,
+                            int64_t sink_local_end, int64_t global_k, void* stream);
+
+/* Host-side row gather out[b,h,k,:] = src[b,h,index[b,h,k],:] on CPU threads: module
+ * polar_gather_ext.gather_kv_out_cpu of cache_hub/gather/gather_cpu.cpp:116-174.  All host memory;
+ * returns PK_ERR_ARG on an out-of-range index.  n_threads <= 0 uses the hardware concurrency. */
+int pk_gather_kv_out_cpu(const pk_tensor* src, const pk_tensor* index, const pk_tensor* out,
+                         int n_threads);
+
+/* Split-K sparse decode attention with the UVA fetch fused in: replaces h2d_gather_kv + torch.cat +
+ * flash_attn_with_kvcache of cache_hub/polar_cache.py:1075-1105 (and the gather-on-GPU branch
+ * :1090-1095).  Per (batch, KV head) attends, non-causally, the first n_window rows of the GPU
+ * window plus K selected rows of the big store:
+ *   queries   bf16 [bs,1,Hq,128] contiguous
+ *   window_k/window_v bf16 [bs,H,cap_w,128] device, last stride 1, row stride 128
+ *   store_k/store_v   bf16 [bs,H,cap_s,128] contiguous; pinned HOST (UVA) or device
+ *   selected  i64 [bs,H,K] (device) or NULL with K = 0;  row = selected + index_offset
+ *   n_sel     i32 [bs,H] per-head count of valid entries of selected, or NULL (all K)
+ *   out       bf16 [bs,1,Hq,128]
+ *   workspace >= pk_attention_workspace_bytes(bs,Hq,n_window+K) bytes, device */
+int64_t pk_attention_workspace_bytes(int64_t bs, int64_t Hq, int64_t max_rows);
+int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* window_k, const pk_tensor* window_v,
+                        int64_t n_window, const pk_tensor* store_k, const pk_tensor* store_v,
+                        const pk_tensor* selected, const pk_tensor* n_sel, int64_t index_offset,
+                        float scale, const pk_tensor* out, void* workspace, int64_t workspace_bytes,
+                        void* stream);
+
+/* ---- the whole retrieval chain in one call ------------------------------------------------------- */
+
+/* queries -> final top-K key indices for one layer and one decode step: the body of
+ * polar_cache.collision_based_topk_batch (cache_hub/polar_cache.py:1126-1162, :1207-1304).
+ *   codebook / key_block_weight / key_4bit: views of the N searchable keys (as pk_collision_fused /
+ *   pk_rerank); cluster_key_counts i32 [bs,H,16,256]; tier_counts host array (6);
+ *   C candidates, K final; final_indices i64 [bs,H,K] ascending key index.
+ *   Optional outputs (NULL to skip): cand i64 [bs,H,C], scores_f32 f32 [bs,H,C],
+ *   q_blocks bf16 [bs,H,16,8], q_norm bf16 [bs,H,1], query_avg bf16 [bs,H,128]. */
+int64_t pk_retrieve_workspace_bytes(int64_t bs, int64_t H, int64_t N, int64_t C);
+int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, const pk_tensor* mag_centers,
+                const pk_tensor* codebook, const pk_tensor* key_block_weight, const pk_tensor* key_4bit,
+                const pk_tensor* cluster_key_counts, const int64_t* tier_counts, int n_tiers, int64_t C,
+                int64_t K, const pk_tensor* final_indices, const pk_tensor* cand,
+                const pk_tensor* scores_f32, const pk_tensor* q_blocks, const pk_tensor* q_norm,
+                const pk_tensor* query_avg, void* workspace, int64_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PARISKV_B200_H */

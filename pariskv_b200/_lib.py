@@ -1,0 +1,114 @@
+"""ctypes binding of ``libpariskv_b200.so`` (the C ABI declared in ``include/pariskv_b200.h``).
+
+There is no fallback: if the library cannot be loaded every op raises.  Tensors cross the boundary
+as ``pk_tensor`` descriptors (data pointer, dtype tag, shape, strides); nothing torch-specific is
+visible to the C side.
+"""
+import ctypes
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libpariskv_b200.so")
+
+PK_MAX_DIMS = 6
+PK_U8, PK_I32, PK_I64, PK_F32, PK_BF16 = range(5)
+_DTYPES = {torch.uint8: PK_U8, torch.int32: PK_I32, torch.int64: PK_I64, torch.float32: PK_F32,
+           torch.bfloat16: PK_BF16}
+
+
+class PkTensor(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("dtype", ctypes.c_int32), ("ndim", ctypes.c_int32),
+                ("shape", ctypes.c_int64 * PK_MAX_DIMS), ("stride", ctypes.c_int64 * PK_MAX_DIMS)]
+
+
+TP = ctypes.POINTER(PkTensor)
+_I64, _INT, _F32, _VP = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+_I64P = ctypes.POINTER(ctypes.c_int64)
+
+# name -> (restype, argtypes); must list every symbol the header declares
+SIGNATURES = {
+    "pk_version": (_INT, []),
+    "pk_last_error": (ctypes.c_char_p, []),
+    "pk_launch_count": (_I64, []),
+    "pk_encode_keys": (_INT, [TP, TP, TP, TP, TP, TP, _VP]),
+    "pk_count_clusters": (_INT, [TP, TP, _INT, _VP]),
+    "pk_query_prep": (_INT, [TP, TP, TP, TP, TP, _VP]),
+    "pk_rank_clusters": (_INT, [TP, TP, _VP]),
+    "pk_collision_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
+    "pk_collision_fused": (_INT, [TP, TP, TP, _I64P, _INT, TP, _VP, _I64, _VP]),
+    "pk_collision": (_INT, [TP, TP, TP, TP, _VP, _I64, _VP]),
+    "pk_topk": (_INT, [TP, _I64, TP, _INT, _VP]),
+    "pk_final_topk": (_INT, [TP, TP, _I64, TP, _VP]),
+    "pk_adaptive_topk": (_INT, [TP, TP, _F32, TP, TP, TP, TP, _I64, _F32, _I64, _I64, _I64, TP, TP, _VP]),
+    "pk_rerank": (_INT, [TP, TP, TP, TP, TP, TP, TP, TP, TP, _VP]),
+    "pk_h2d_gather_kv": (_INT, [TP, TP, TP, TP, TP, _VP]),
+    "pk_h2d_gather_kv_packed": (_INT, [TP, TP, TP, TP, TP, TP, TP, _I64, _I64, _VP]),
+    "pk_gather_kv_out_cpu": (_INT, [TP, TP, TP, _INT]),
+    "pk_attention_workspace_bytes": (_I64, [_I64, _I64, _I64]),
+    "pk_sparse_attention": (_INT, [TP, TP, TP, _I64, TP, TP, TP, TP, _I64, _F32, TP, _VP, _I64, _VP]),
+    "pk_retrieve_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
+    "pk_retrieve": (_INT, [TP, TP, TP, TP, TP, TP, TP, _I64P, _INT, _I64, _I64, TP, TP, TP, TP, TP, TP, _VP, _I64,
+                           _VP]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the library (once).  Raises RuntimeError with the build hint if it is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m pariskv_b200.build` "
+                "(there is no fallback path for the CUDA kernels)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def desc(t):
+    """torch.Tensor (or None) -> pk_tensor (or None).  Keep the tensor alive while the call runs."""
+    if t is None:
+        return None
+    if t.dim() > PK_MAX_DIMS:
+        raise ValueError("too many dimensions")
+    if t.dtype not in _DTYPES:
+        raise TypeError(f"unsupported dtype {t.dtype}")
+    d = PkTensor()
+    d.data = t.data_ptr()
+    d.dtype = _DTYPES[t.dtype]
+    d.ndim = t.dim()
+    for i in range(t.dim()):
+        d.shape[i] = t.shape[i]
+        d.stride[i] = t.stride(i)
+    return d
+
+
+def ref(d):
+    return ctypes.byref(d) if d is not None else None
+
+
+def stream_ptr(device=None):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def check(rc):
+    if rc != 0:
+        msg = load().pk_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"pariskv_b200 error {rc}: {msg}")
+
+
+def i64_array(values):
+    arr = (ctypes.c_int64 * len(values))(*[int(v) for v in values])
+    return arr
+
+
+def launch_count() -> int:
+    return int(load().pk_launch_count())

@@ -1,0 +1,287 @@
+// Split-K sparse decode attention with the UVA fetch of the selected rows fused in.
+//
+// Per (batch, KV head) the attended rows are the first n_window rows of the GPU window
+// ([sink | local | update buffer]) followed by the K selected rows of the big K/V store, which may
+// live in pinned host memory.  The rows are cut into tiles of 64; one block per (tile, KV head,
+// batch, group of <= 4 query heads) stages its tile of K and V rows into shared memory with
+// asynchronous 16-byte copies (all 64 x 512 bytes of a tile in flight at once, so a grid keeps
+// megabytes outstanding on the host link), then 16 groups of 8 lanes run an online softmax over the
+// rows for up to four query heads sharing the KV head.  Partial (m, l, o) triples go to a workspace and
+// a second small kernel merges the tiles.  Scores are kept in the log2 domain.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace pk {
+namespace {
+
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_TILE = 64;
+constexpr int ATT_GQ = 4;       // query heads per block
+constexpr int ATT_REC = 132;    // floats per partial: o[128], m, l, pad, pad
+
+struct AttParams {
+  const uint16_t* q;  // [bs][Hq][128]
+  const uint16_t* wk;
+  const uint16_t* wv;
+  int64_t w_b, w_h, w_l;  // window strides (elements)
+  int64_t n_window;
+  const uint16_t* sk;
+  const uint16_t* sv;
+  int64_t cap_s;          // rows per (b,h) of the store
+  const int64_t* sel;     // [bs*H][K]
+  const int32_t* n_sel;   // [bs*H] or null
+  int64_t K, index_offset;
+  int H, Hq, G, n_qgroups;
+  int64_t n_tiles;
+  float scale_log2;
+  float* ws;              // [bs*Hq][n_tiles][ATT_REC]
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+
+__device__ __forceinline__ void unpack8f(uint4 v, float* out) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams p) {
+  extern __shared__ __align__(16) unsigned char dyn[];
+  uint16_t* Ks = reinterpret_cast<uint16_t*>(dyn);                       // [64][128]
+  uint16_t* Vs = reinterpret_cast<uint16_t*>(dyn + ATT_TILE * 256);      // [64][128]
+  float* obuf = reinterpret_cast<float*>(dyn);                           // reused: [16][4][128]
+  __shared__ float s_m[16][ATT_GQ], s_l[16][ATT_GQ];
+  __shared__ unsigned char s_valid[ATT_TILE];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tile = blockIdx.x;
+  const int h = blockIdx.y / p.n_qgroups, qg = blockIdx.y % p.n_qgroups;
+  const int b = blockIdx.z;
+  const int64_t bh = (int64_t)b * p.H + h;
+  const int64_t n_sel = p.n_sel ? min((int64_t)p.n_sel[bh], p.K) : p.K;
+  const int64_t n_rows = p.n_window + n_sel;
+  const int64_t r0 = (int64_t)tile * ATT_TILE;
+  const int n_tile = (int)max((int64_t)0, min((int64_t)ATT_TILE, n_rows - r0));
+
+  // ---- stage the tile: warp w copies rows w, w+4, ...; lanes 0-15 the K row, 16-31 the V row ----
+  {
+    const int l = lane & 15;
+    const bool is_v = lane >= 16;
+    for (int i = warp; i < n_tile; i += ATT_THREADS / 32) {
+      const int64_t r = r0 + i;
+      const uint16_t* src;
+      bool ok = true;
+      if (r < p.n_window) {
+        src = (is_v ? p.wv : p.wk) + b * p.w_b + h * p.w_h + r * p.w_l;
+      } else {
+        const int64_t row = p.sel[bh * p.K + (r - p.n_window)] + p.index_offset;
+        ok = row >= 0 && row < p.cap_s;
+        src = (is_v ? p.sv : p.sk) + (bh * p.cap_s + (ok ? row : 0)) * 128;
+      }
+      if (ok) cp_async16((is_v ? Vs : Ks) + i * 128 + l * 8, src + l * 8);
+      if (lane == 0) s_valid[i] = ok;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  // ---- queries of this block's heads: lane s holds dims [16s, 16s+16) ----
+  const int s = tid & 7, grp = tid >> 3;
+  const int n_heads = min(ATT_GQ, p.G - qg * ATT_GQ);
+  float qf[ATT_GQ][16];
+#pragma unroll
+  for (int g = 0; g < ATT_GQ; g++) {
+    if (g < n_heads) {
+      const uint4* qp = reinterpret_cast<const uint4*>(p.q + ((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * 128 + 16 * s);
+      unpack8f(__ldg(qp), qf[g]);
+      unpack8f(__ldg(qp + 1), qf[g] + 8);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; i++) qf[g][i] = 0.0f;
+    }
+  }
+  float m[ATT_GQ], lsum[ATT_GQ], o[ATT_GQ][16];
+#pragma unroll
+  for (int g = 0; g < ATT_GQ; g++) {
+    m[g] = -INFINITY;
+    lsum[g] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) o[g][i] = 0.0f;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+
+  for (int i = grp; i < ATT_TILE; i += 16) {  // uniform trip count per warp: shuffles need all lanes
+    const bool live = i < n_tile && s_valid[i];
+    float kf[16], vf[16];
+    if (live) {
+      const uint4* kp = reinterpret_cast<const uint4*>(Ks + i * 128 + 16 * s);
+      const uint4* vp = reinterpret_cast<const uint4*>(Vs + i * 128 + 16 * s);
+      unpack8f(kp[0], kf);
+      unpack8f(kp[1], kf + 8);
+      unpack8f(vp[0], vf);
+      unpack8f(vp[1], vf + 8);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; j++) kf[j] = 0.0f, vf[j] = 0.0f;
+    }
+#pragma unroll
+    for (int g = 0; g < ATT_GQ; g++) {
+      float d = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 16; j++) d = fmaf(kf[j], qf[g][j], d);
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      d += __shfl_xor_sync(0xffffffffu, d, 4);
+      if (live) {
+        const float sc = d * p.scale_log2;
+        const float mn = fmaxf(m[g], sc);
+        const float corr = exp2f(m[g] - mn);  // m = -inf on the first row gives 0
+        const float pr = exp2f(sc - mn);
+        lsum[g] = lsum[g] * corr + pr;
+#pragma unroll
+        for (int j = 0; j < 16; j++) o[g][j] = o[g][j] * corr + pr * vf[j];
+        m[g] = mn;
+      }
+    }
+  }
+  __syncthreads();  // tile no longer needed: its shared memory becomes the merge buffer
+#pragma unroll
+  for (int g = 0; g < ATT_GQ; g++) {
+#pragma unroll
+    for (int j = 0; j < 16; j++) obuf[(grp * ATT_GQ + g) * 128 + 16 * s + j] = o[g][j];
+    if (s == 0) {
+      s_m[grp][g] = m[g];
+      s_l[grp][g] = lsum[g];
+    }
+  }
+  __syncthreads();
+  for (int g = 0; g < n_heads; g++) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int t = 0; t < 16; t++) M = fmaxf(M, s_m[t][g]);
+    float L = 0.0f, O = 0.0f;
+#pragma unroll
+    for (int t = 0; t < 16; t++) {
+      const float f = (s_m[t][g] == -INFINITY) ? 0.0f : exp2f(s_m[t][g] - M);
+      L += s_l[t][g] * f;
+      O += obuf[(t * ATT_GQ + g) * 128 + tid] * f;
+    }
+    float* rec = p.ws + (((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * p.n_tiles + tile) * ATT_REC;
+    rec[tid] = O;
+    if (tid == 0) {
+      rec[128] = M;
+      rec[129] = L;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) attention_merge_kernel(const float* __restrict__ ws, int64_t n_tiles,
+                                                              uint16_t* __restrict__ out) {
+  const int64_t bq = blockIdx.x;
+  const float* rec = ws + bq * n_tiles * ATT_REC;
+  float M = -INFINITY;
+  for (int64_t t = 0; t < n_tiles; t++) M = fmaxf(M, rec[t * ATT_REC + 128]);
+  float L = 0.0f, O = 0.0f;
+  for (int64_t t = 0; t < n_tiles; t++) {
+    const float mt = rec[t * ATT_REC + 128];
+    const float f = (mt == -INFINITY) ? 0.0f : exp2f(mt - M);
+    L += rec[t * ATT_REC + 129] * f;
+    O += rec[t * ATT_REC + threadIdx.x] * f;
+  }
+  out[bq * 128 + threadIdx.x] = f2bf(L > 0.0f ? O / L : 0.0f);
+}
+
+}  // namespace
+}  // namespace pk
+
+using namespace pk;
+
+extern "C" int64_t pk_attention_workspace_bytes(int64_t bs, int64_t Hq, int64_t max_rows) {
+  const int64_t tiles = (max_rows + ATT_TILE - 1) / ATT_TILE;
+  return bs * Hq * (tiles > 0 ? tiles : 1) * ATT_REC * 4;
+}
+
+extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* window_k, const pk_tensor* window_v,
+                                   int64_t n_window, const pk_tensor* store_k, const pk_tensor* store_v,
+                                   const pk_tensor* selected, const pk_tensor* n_sel, int64_t index_offset,
+                                   float scale, const pk_tensor* out, void* workspace, int64_t workspace_bytes,
+                                   void* stream) {
+  PK_CHECK_TENSOR(queries, PK_BF16, 4);
+  PK_CHECK_TENSOR(out, PK_BF16, 4);
+  const int64_t bs = queries->shape[0], Hq = queries->shape[2];
+  PK_REQUIRE(queries->shape[1] == 1 && queries->shape[3] == 128 && is_contig(queries) &&
+                 (reinterpret_cast<uintptr_t>(queries->data) & 15) == 0,
+             "queries must be contiguous, 16-byte aligned [bs,1,Hq,128]");
+  PK_REQUIRE(is_contig(out) && out->shape[0] == bs && out->shape[1] == 1 && out->shape[2] == Hq && out->shape[3] == 128,
+             "out must be contiguous [bs,1,Hq,128]");
+  AttParams p = {};
+  int64_t H = 0;
+  if (n_window > 0) {
+    PK_CHECK_TENSOR(window_k, PK_BF16, 4);
+    PK_CHECK_TENSOR(window_v, PK_BF16, 4);
+    H = window_k->shape[1];
+    PK_REQUIRE(window_k->shape[0] == bs && window_k->shape[3] == 128 && window_k->stride[3] == 1 &&
+                   window_k->shape[2] >= n_window,
+               "window_k must be [bs,H,cap>=n_window,128] with last stride 1");
+    for (int i = 0; i < 4; i++)
+      PK_REQUIRE(window_k->shape[i] == window_v->shape[i] && window_k->stride[i] == window_v->stride[i],
+                 "window_k and window_v must have the same shape and strides");
+    PK_REQUIRE((reinterpret_cast<uintptr_t>(window_k->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(window_v->data) & 15) == 0 &&
+                   window_k->stride[0] % 8 == 0 && window_k->stride[1] % 8 == 0 && window_k->stride[2] % 8 == 0,
+               "window rows must be 16-byte aligned");
+    p.wk = (const uint16_t*)window_k->data, p.wv = (const uint16_t*)window_v->data;
+    p.w_b = window_k->stride[0], p.w_h = window_k->stride[1], p.w_l = window_k->stride[2];
+  }
+  int64_t K = 0;
+  if (selected) {
+    PK_CHECK_TENSOR(selected, PK_I64, 3);
+    PK_CHECK_TENSOR(store_k, PK_BF16, 4);
+    PK_CHECK_TENSOR(store_v, PK_BF16, 4);
+    K = selected->shape[2];
+    PK_REQUIRE(H == 0 || store_k->shape[1] == H, "window and store disagree on the number of KV heads");
+    H = store_k->shape[1];
+    PK_REQUIRE(is_contig(store_k) && is_contig(store_v) && store_k->shape[0] == bs && store_k->shape[3] == 128 &&
+                   store_v->shape[0] == bs && store_v->shape[1] == H && store_v->shape[2] == store_k->shape[2] &&
+                   store_v->shape[3] == 128,
+               "store_k / store_v must be contiguous [bs,H,cap,128]");
+    PK_REQUIRE((reinterpret_cast<uintptr_t>(store_k->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(store_v->data) & 15) == 0,
+               "store rows must be 16-byte aligned");
+    PK_REQUIRE(is_contig(selected) && selected->shape[0] == bs && selected->shape[1] == H,
+               "selected must be contiguous [bs,H,K]");
+    p.sk = (const uint16_t*)store_k->data, p.sv = (const uint16_t*)store_v->data;
+    p.cap_s = store_k->shape[2];
+    p.sel = (const int64_t*)selected->data;
+    if (n_sel) {
+      PK_CHECK_TENSOR(n_sel, PK_I32, 2);
+      PK_REQUIRE(is_contig(n_sel) && n_sel->shape[0] == bs && n_sel->shape[1] == H, "n_sel must be contiguous [bs,H]");
+      p.n_sel = (const int32_t*)n_sel->data;
+    }
+  }
+  PK_REQUIRE(H > 0 && Hq % H == 0, "need at least one of window / selected rows, and Hq a multiple of H");
+  PK_REQUIRE(n_window >= 0, "n_window must be non-negative");
+  if (bs == 0) return PK_OK;
+  const int64_t max_rows = n_window + K;
+  const int64_t n_tiles = max_rows > 0 ? (max_rows + ATT_TILE - 1) / ATT_TILE : 1;
+  if (!workspace || workspace_bytes < pk_attention_workspace_bytes(bs, Hq, max_rows))
+    return fail(PK_ERR_WORKSPACE, "attention workspace too small: %lld < %lld", (long long)workspace_bytes,
+                (long long)pk_attention_workspace_bytes(bs, Hq, max_rows));
+  p.q = (const uint16_t*)queries->data;
+  p.n_window = n_window;
+  p.K = K, p.index_offset = index_offset;
+  p.H = (int)H, p.Hq = (int)Hq, p.G = (int)(Hq / H);
+  p.n_qgroups = (p.G + ATT_GQ - 1) / ATT_GQ;
+  p.n_tiles = n_tiles;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.ws = (float*)workspace;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid((unsigned)n_tiles, (unsigned)(H * p.n_qgroups), (unsigned)bs);
+  sparse_attention_kernel<<<grid, ATT_THREADS, 2 * ATT_TILE * 256, st>>>(p);
+  int rc = check_launch("sparse_attention");
+  if (rc) return rc;
+  attention_merge_kernel<<<(unsigned)(bs * Hq), 128, 0, st>>>(p.ws, n_tiles, (uint16_t*)out->data);
+  return check_launch("attention_merge");
+}

@@ -1,0 +1,434 @@
+// Cluster ranking, tier look-up tables and the weighted multi-tier collision count.
+//
+// The six cumulative tier bitsets of a subspace collapse into one 256-entry table of 4-bit weights
+// (number of tiers a cluster belongs to): 32 words = one word per shared-memory bank, so a warp's 32
+// look-ups into the table of one subspace never conflict.  Codes are streamed with 128-bit loads.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace pk {
+namespace {
+
+struct Tiers {
+  long long t[8];
+  int n;
+};
+
+// ---- table builders -----------------------------------------------------------------------------
+
+// From a given cluster order (the collision_fused op): one block per (batch, head, subspace).
+template <typename IdT>
+__global__ void __launch_bounds__(256) lut_from_sorted_kernel(const IdT* __restrict__ ids,
+                                                              const int32_t* __restrict__ counts, int NC,
+                                                              Tiers tiers, uint32_t* __restrict__ lut) {
+  __shared__ long long warp_tot[8];
+  __shared__ unsigned mask[256];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t blk = blockIdx.x;
+  mask[tid] = 0;
+  long long id = -1;
+  long long cnt = 0;
+  if (tid < NC) {
+    id = (long long)ids[blk * NC + tid];
+    if (id >= 0 && id < NC) cnt = counts[blk * NC + id];
+  }
+  long long incl = cnt;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    long long v = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += v;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  long long base = 0;
+  for (int w = 0; w < warp; w++) base += warp_tot[w];
+  const long long excl = base + incl - cnt;
+  unsigned bits = 0;
+  for (int t = 0; t < tiers.n; t++)
+    if (excl < tiers.t[t]) bits |= 1u << t;
+  if (id >= 0 && id < NC && bits) atomicOr(&mask[id], bits);
+  __syncthreads();
+  if (tid < 32) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) w |= (uint32_t)__popc(mask[tid * 8 + i]) << (4 * i);
+    lut[blk * 32 + tid] = w;
+  }
+}
+
+// From the query (the fused chain) and/or to produce the explicit order (rank_clusters op):
+// one block per (batch, head, subspace), thread c owns cluster c.
+// score_c = bf16(sum_j +-q_j), fp32 sum j ascending; order: score descending, id ascending.
+__global__ void __launch_bounds__(256) rank_kernel(const uint16_t* __restrict__ q_blocks,
+                                                   const int32_t* __restrict__ counts, Tiers tiers,
+                                                   uint32_t* __restrict__ lut, int64_t* __restrict__ sorted_ids) {
+  __shared__ float sc[256];
+  __shared__ int cn[256];
+  __shared__ unsigned nib[256];
+  const int c = threadIdx.x;
+  const int64_t blk = blockIdx.x;  // (b*H + h)*16 + subspace
+  float s = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const float qv = bf2f(q_blocks[blk * 8 + j]);
+    s = __fadd_rn(s, ((c >> j) & 1) ? qv : -qv);
+  }
+  s = bfround(s);
+  sc[c] = s;
+  cn[c] = counts ? counts[blk * 256 + c] : 0;
+  __syncthreads();
+  long long excl = 0;
+  int rank = 0;
+  for (int o = 0; o < 256; o++) {
+    const float so = sc[o];
+    const bool before = (so > s) || (so == s && o < c);
+    rank += before;
+    excl += before ? cn[o] : 0;
+  }
+  if (sorted_ids) sorted_ids[blk * 256 + rank] = c;
+  if (lut) {
+    unsigned wgt = 0;
+    for (int t = 0; t < tiers.n; t++) wgt += (excl < tiers.t[t]);
+    nib[c] = wgt;
+    __syncthreads();
+    if (c < 32) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int i = 0; i < 8; i++) w |= nib[c * 8 + i] << (4 * i);
+      lut[blk * 32 + c] = w;
+    }
+  }
+}
+
+// ---- the streaming count --------------------------------------------------------------------------
+
+struct CollParams {
+  const uint8_t* codes;          // element (b,h,s,k) at codes[b*c_b + h*c_h + s*c_s + k*c_l]
+  int64_t c_b, c_h, c_s, c_l;
+  const uint32_t* lut;           // [bs*H][B][32]
+  int32_t* out_i32;              // [bs*H][N]            (OUT_U8 == false)
+  uint8_t* out_u8;               // [bs*H][u8_stride], indexed by virtual key (OUT_U8 == true)
+  uint32_t* chunk_hist;          // [bs*H][n_chunks][256] (OUT_U8 == true)
+  int64_t u8_stride;
+  int H, B;
+  int64_t N;                     // keys per head
+  int mis;                       // virtual key v = key + mis; loads are 16-byte aligned in v
+  int64_t chunk_keys;            // virtual keys per block (multiple of 512)
+};
+
+__device__ __forceinline__ unsigned lut_get(const uint32_t* tab, unsigned code) {
+  return (tab[code >> 3] >> ((code & 7u) << 2)) & 0xFu;
+}
+
+// LAYOUT 0: plane-major ([.., 16, N], key stride 1): a thread owns 16 consecutive keys.
+// LAYOUT 1: key-major ([.., N, 16], subspace stride 1): a warp owns 512 consecutive keys, lane-strided.
+// LAYOUT 2: any strides, any B <= 32: a thread owns one key at a time.
+template <int LAYOUT, bool OUT_U8>
+__global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
+  extern __shared__ uint32_t smem[];
+  uint32_t* lut = smem;                 // B*32 words
+  unsigned* hist = smem + p.B * 32;     // 256 words (OUT_U8 only)
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  for (int i = tid; i < p.B * 32; i += 256) lut[i] = p.lut[(int64_t)bh * p.B * 32 + i];
+  if (OUT_U8) hist[tid] = 0;
+  __syncthreads();
+  const int64_t Nv = p.N + p.mis;
+  const int64_t v_begin = (int64_t)blockIdx.x * p.chunk_keys;
+  const int64_t v_end = min(Nv, v_begin + p.chunk_keys);
+  const uint8_t* base = p.codes + b * p.c_b + h * p.c_h - p.mis * p.c_l;
+  int32_t* out32 = OUT_U8 ? nullptr : p.out_i32 + (int64_t)bh * p.N;
+  uint8_t* out8 = OUT_U8 ? p.out_u8 + (int64_t)bh * p.u8_stride : nullptr;
+
+  if (LAYOUT == 0) {
+    for (int64_t v0 = v_begin + 16 * (int64_t)tid; v0 < v_end; v0 += 16 * 256) {
+      uint4 r[16];
+#pragma unroll
+      for (int s = 0; s < 16; s++) r[s] = __ldg(reinterpret_cast<const uint4*>(base + s * p.c_s + v0));
+      int cnt[16];
+#pragma unroll
+      for (int k = 0; k < 16; k++) cnt[k] = 0;
+#pragma unroll
+      for (int s = 0; s < 16; s++) {
+        const uint32_t w4[4] = {r[s].x, r[s].y, r[s].z, r[s].w};
+#pragma unroll
+        for (int k = 0; k < 16; k++) cnt[k] += lut_get(lut + s * 32, (w4[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+      }
+      const int64_t key0 = v0 - p.mis;
+      if (OUT_U8) {
+        uint32_t pk4[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+          pk4[k >> 2] |= (uint32_t)cnt[k] << (8 * (k & 3));
+          if (key0 + k >= 0 && key0 + k < p.N) atomicAdd(&hist[cnt[k]], 1u);
+        }
+        *reinterpret_cast<uint4*>(out8 + v0) = make_uint4(pk4[0], pk4[1], pk4[2], pk4[3]);
+      } else {
+        if (key0 >= 0 && key0 + 16 <= p.N && ((reinterpret_cast<uintptr_t>(out32 + key0) & 15) == 0)) {
+#pragma unroll
+          for (int q = 0; q < 4; q++)
+            *reinterpret_cast<int4*>(out32 + key0 + 4 * q) =
+                make_int4(cnt[4 * q], cnt[4 * q + 1], cnt[4 * q + 2], cnt[4 * q + 3]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; k++)
+            if (key0 + k >= 0 && key0 + k < p.N) out32[key0 + k] = cnt[k];
+        }
+      }
+    }
+  } else if (LAYOUT == 1) {
+    for (int64_t w0 = v_begin + 512 * (int64_t)warp; w0 < v_end; w0 += 512 * 8) {
+      uint4 r[16];
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        const int64_t v = w0 + 32 * j + lane;
+        r[j] = (v < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + v * 16)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        const uint32_t w4[4] = {r[j].x, r[j].y, r[j].z, r[j].w};
+        int cnt = 0;
+#pragma unroll
+        for (int s = 0; s < 16; s++) cnt += lut_get(lut + s * 32, (w4[s >> 2] >> (8 * (s & 3))) & 0xFFu);
+        const int64_t v = w0 + 32 * j + lane;
+        if (v < v_end) {
+          if (OUT_U8) {
+            out8[v] = (uint8_t)cnt;
+            atomicAdd(&hist[cnt], 1u);
+          } else {
+            out32[v] = cnt;
+          }
+        }
+      }
+    }
+  } else {
+    for (int64_t v = v_begin + tid; v < v_end; v += 256) {
+      const int64_t key = v - p.mis;
+      if (key < 0) continue;
+      int cnt = 0;
+      for (int s = 0; s < p.B; s++) cnt += lut_get(lut + s * 32, base[s * p.c_s + v * p.c_l]);
+      if (OUT_U8) {
+        out8[v] = (uint8_t)cnt;
+        atomicAdd(&hist[cnt], 1u);
+      } else {
+        out32[key] = cnt;
+      }
+    }
+  }
+  if (OUT_U8) {
+    __syncthreads();
+    p.chunk_hist[((int64_t)bh * gridDim.x + blockIdx.x) * 256 + tid] = hist[tid];
+  }
+}
+
+// Unfused single-tier op: codes are int32 [bs,H,N,B] contiguous; one thread per key.
+__global__ void __launch_bounds__(256) collision_i32_kernel(const int32_t* __restrict__ codes,
+                                                            const uint32_t* __restrict__ lut_g, int B, int NC,
+                                                            int64_t N, int32_t* __restrict__ out) {
+  extern __shared__ uint32_t lut[];
+  const int bh = blockIdx.y;
+  for (int i = threadIdx.x; i < B * 32; i += 256) lut[i] = lut_g[(int64_t)bh * B * 32 + i];
+  __syncthreads();
+  for (int64_t k = (int64_t)blockIdx.x * 256 + threadIdx.x; k < N; k += (int64_t)gridDim.x * 256) {
+    const int32_t* row = codes + ((int64_t)bh * N + k) * B;
+    int cnt = 0;
+    for (int s = 0; s < B; s++) {
+      const int32_t c = row[s];
+      if (c >= 0 && c < NC) cnt += lut_get(lut + s * 32, (unsigned)c);
+    }
+    out[(int64_t)bh * N + k] = cnt;
+  }
+}
+
+// single-tier table from (sorted ids, how many leading clusters are selected)
+__global__ void __launch_bounds__(256) lut_single_kernel(const int32_t* __restrict__ ids,
+                                                         const int32_t* __restrict__ topk_cnt, int NC,
+                                                         uint32_t* __restrict__ lut) {
+  __shared__ unsigned sel[256];
+  const int tid = threadIdx.x;
+  const int64_t blk = blockIdx.x;
+  sel[tid] = 0;
+  __syncthreads();
+  if (tid < NC && tid < topk_cnt[blk]) {
+    const int id = ids[blk * NC + tid];
+    if (id >= 0 && id < NC) sel[id] = 1;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) w |= sel[tid * 8 + i] << (4 * i);
+    lut[blk * 32 + tid] = w;
+  }
+}
+
+Tiers make_tiers(const int64_t* tier_counts, int n) {
+  Tiers t;
+  t.n = n;
+  for (int i = 0; i < 8; i++) t.t[i] = i < n ? (long long)tier_counts[i] : 0;
+  return t;
+}
+
+}  // namespace
+
+int64_t collision_chunk_keys(int64_t bs_h, int64_t Nv) {
+  int64_t n_chunks = (2 * (int64_t)sm_count()) / (bs_h > 0 ? bs_h : 1);
+  if (n_chunks < 1) n_chunks = 1;
+  int64_t chunk = (Nv + n_chunks - 1) / n_chunks;
+  chunk = ((chunk + 511) / 512) * 512;
+  if (chunk < 512) chunk = 512;
+  if (chunk > 32768) chunk = 32768;  // the selection kernel keeps one int per key of a chunk in shared memory
+  return chunk;
+}
+
+int launch_rank(const uint16_t* q_blocks, const int32_t* counts, const int64_t* tier_counts, int n_tiers,
+                int64_t bs_h, uint32_t* lut, int64_t* sorted_ids, cudaStream_t st) {
+  rank_kernel<<<(unsigned)(bs_h * 16), 256, 0, st>>>(q_blocks, counts, make_tiers(tier_counts, n_tiers), lut,
+                                                     sorted_ids);
+  return check_launch("rank_clusters");
+}
+
+// Streams the codes of N keys per (batch, head) and writes counts.  counts_u8 / chunk_hist non-null
+// selects the compact internal output (u8 per virtual key + one 256-bin histogram per block).
+int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* out_i32, uint8_t* counts_u8,
+                     int64_t u8_stride, uint32_t* chunk_hist, int* mis_out, int64_t* chunk_keys_out,
+                     int64_t* n_chunks_out, cudaStream_t st) {
+  const int64_t bs = codebook->shape[0], H = codebook->shape[1], B = codebook->shape[2], N = codebook->shape[3];
+  CollParams p;
+  p.codes = (const uint8_t*)codebook->data;
+  p.c_b = codebook->stride[0], p.c_h = codebook->stride[1], p.c_s = codebook->stride[2], p.c_l = codebook->stride[3];
+  p.lut = lut;
+  p.out_i32 = out_i32;
+  p.out_u8 = counts_u8;
+  p.chunk_hist = chunk_hist;
+  p.u8_stride = u8_stride;
+  p.H = (int)H, p.B = (int)B, p.N = N;
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(p.codes);
+  int layout = 2, mis = 0;
+  if (B == 16 && p.c_l == 1 && p.c_s % 16 == 0 && p.c_h % 16 == 0 && p.c_b % 16 == 0) {
+    layout = 0;
+    mis = (int)(addr & 15);
+  } else if (B == 16 && p.c_s == 1 && p.c_l == 16 && (addr & 15) == 0 && p.c_h % 16 == 0 && p.c_b % 16 == 0) {
+    layout = 1;
+  }
+  p.mis = mis;
+  const int64_t Nv = N + mis;
+  p.chunk_keys = collision_chunk_keys(bs * H, Nv);
+  const int64_t n_chunks = (Nv + p.chunk_keys - 1) / p.chunk_keys;
+  if (mis_out) *mis_out = mis;
+  if (chunk_keys_out) *chunk_keys_out = p.chunk_keys;
+  if (n_chunks_out) *n_chunks_out = n_chunks;
+  dim3 grid((unsigned)n_chunks, (unsigned)(bs * H));
+  const size_t smem = (size_t)(B * 32 + 256) * 4;
+  const bool u8 = counts_u8 != nullptr;
+#define PK_LAUNCH_COLL(L, U) collision_kernel<L, U><<<grid, 256, smem, st>>>(p)
+  if (layout == 0) {
+    if (u8) PK_LAUNCH_COLL(0, true); else PK_LAUNCH_COLL(0, false);
+  } else if (layout == 1) {
+    if (u8) PK_LAUNCH_COLL(1, true); else PK_LAUNCH_COLL(1, false);
+  } else {
+    if (u8) PK_LAUNCH_COLL(2, true); else PK_LAUNCH_COLL(2, false);
+  }
+#undef PK_LAUNCH_COLL
+  return check_launch("collision");
+}
+
+}  // namespace pk
+
+using namespace pk;
+
+extern "C" int64_t pk_collision_workspace_bytes(int64_t bs, int64_t H, int64_t B, int64_t NC) {
+  (void)NC;
+  return bs * H * B * 32 * 4;
+}
+
+extern "C" int pk_rank_clusters(const pk_tensor* q_blocks, const pk_tensor* sorted_ids, void* stream) {
+  PK_CHECK_TENSOR(q_blocks, PK_BF16, 4);
+  PK_CHECK_TENSOR(sorted_ids, PK_I64, 4);
+  const int64_t bs = q_blocks->shape[0], H = q_blocks->shape[1];
+  PK_REQUIRE(is_contig(q_blocks) && q_blocks->shape[2] == 16 && q_blocks->shape[3] == 8,
+             "q_blocks must be contiguous [bs,H,16,8]");
+  PK_REQUIRE(is_contig(sorted_ids) && sorted_ids->shape[0] == bs && sorted_ids->shape[1] == H &&
+                 sorted_ids->shape[2] == 16 && sorted_ids->shape[3] == 256,
+             "sorted_ids must be contiguous [bs,H,16,256]");
+  if (bs * H == 0) return PK_OK;
+  return launch_rank((const uint16_t*)q_blocks->data, nullptr, nullptr, 0, bs * H, nullptr,
+                     (int64_t*)sorted_ids->data, (cudaStream_t)stream);
+}
+
+extern "C" int pk_collision_fused(const pk_tensor* sorted_cluster_ids, const pk_tensor* cluster_key_counts,
+                                  const pk_tensor* codebook, const int64_t* tier_counts, int n_tiers,
+                                  const pk_tensor* cache_cnt, void* workspace, int64_t workspace_bytes,
+                                  void* stream) {
+  PK_REQUIRE(sorted_cluster_ids && sorted_cluster_ids->data, "sorted_cluster_ids is null");
+  PK_REQUIRE(sorted_cluster_ids->dtype == PK_I64 || sorted_cluster_ids->dtype == PK_I32,
+             "sorted_cluster_ids must be int64 or int32");
+  PK_REQUIRE(sorted_cluster_ids->ndim == 4, "sorted_cluster_ids must be 4-D");
+  PK_CHECK_TENSOR(cluster_key_counts, PK_I32, 4);
+  PK_CHECK_TENSOR(codebook, PK_U8, 4);
+  PK_CHECK_TENSOR(cache_cnt, PK_I32, 3);
+  const int64_t bs = codebook->shape[0], H = codebook->shape[1], B = codebook->shape[2], N = codebook->shape[3];
+  const int64_t NC = sorted_cluster_ids->shape[3];
+  PK_REQUIRE(n_tiers >= 1 && n_tiers <= 8 && tier_counts, "n_tiers must be in 1..8");
+  PK_REQUIRE(B >= 1 && B <= 32, "subspaces must be in 1..32, got %lld", (long long)B);
+  PK_REQUIRE(NC >= 1 && NC <= 256, "clusters per subspace must be in 1..256, got %lld", (long long)NC);
+  PK_REQUIRE(B * n_tiers <= 255, "subspaces x tiers must not exceed 255");
+  PK_REQUIRE(is_contig(sorted_cluster_ids) && sorted_cluster_ids->shape[0] == bs && sorted_cluster_ids->shape[1] == H &&
+                 sorted_cluster_ids->shape[2] == B,
+             "sorted_cluster_ids must be contiguous [bs,H,B,NC]");
+  PK_REQUIRE(is_contig(cluster_key_counts) && cluster_key_counts->shape[0] == bs && cluster_key_counts->shape[1] == H &&
+                 cluster_key_counts->shape[2] == B && cluster_key_counts->shape[3] == NC,
+             "cluster_key_counts must be contiguous [bs,H,B,NC]");
+  PK_REQUIRE(is_contig(cache_cnt) && cache_cnt->shape[0] == bs && cache_cnt->shape[1] == H && cache_cnt->shape[2] == N,
+             "cache_cnt must be contiguous [bs,H,N]");
+  if (bs * H * N == 0) return PK_OK;
+  if (!workspace || workspace_bytes < pk_collision_workspace_bytes(bs, H, B, NC))
+    return fail(PK_ERR_WORKSPACE, "collision workspace too small: %lld < %lld", (long long)workspace_bytes,
+                (long long)pk_collision_workspace_bytes(bs, H, B, NC));
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t* lut = (uint32_t*)workspace;
+  Tiers tiers = make_tiers(tier_counts, n_tiers);
+  const unsigned nblk = (unsigned)(bs * H * B);
+  if (sorted_cluster_ids->dtype == PK_I64)
+    lut_from_sorted_kernel<int64_t><<<nblk, 256, 0, st>>>((const int64_t*)sorted_cluster_ids->data,
+                                                          (const int32_t*)cluster_key_counts->data, (int)NC, tiers, lut);
+  else
+    lut_from_sorted_kernel<int32_t><<<nblk, 256, 0, st>>>((const int32_t*)sorted_cluster_ids->data,
+                                                          (const int32_t*)cluster_key_counts->data, (int)NC, tiers, lut);
+  int rc = check_launch("collision table");
+  if (rc) return rc;
+  return launch_collision(codebook, lut, (int32_t*)cache_cnt->data, nullptr, 0, nullptr, nullptr, nullptr, nullptr, st);
+}
+
+extern "C" int pk_collision(const pk_tensor* sorted_cluster_ids, const pk_tensor* topk_cluster_cnt,
+                            const pk_tensor* code_book, const pk_tensor* cache_cnt, void* workspace,
+                            int64_t workspace_bytes, void* stream) {
+  PK_CHECK_TENSOR(sorted_cluster_ids, PK_I32, 4);
+  PK_CHECK_TENSOR(topk_cluster_cnt, PK_I32, 3);
+  PK_CHECK_TENSOR(code_book, PK_I32, 4);
+  PK_CHECK_TENSOR(cache_cnt, PK_I32, 3);
+  const int64_t bs = code_book->shape[0], H = code_book->shape[1], N = code_book->shape[2], B = code_book->shape[3];
+  const int64_t NC = sorted_cluster_ids->shape[3];
+  PK_REQUIRE(B >= 1 && B <= 32 && NC >= 1 && NC <= 256, "need B <= 32 and NC <= 256");
+  PK_REQUIRE(is_contig(sorted_cluster_ids) && is_contig(topk_cluster_cnt) && is_contig(code_book) && is_contig(cache_cnt),
+             "all tensors must be contiguous");
+  PK_REQUIRE(sorted_cluster_ids->shape[0] == bs && sorted_cluster_ids->shape[1] == H && sorted_cluster_ids->shape[2] == B &&
+                 topk_cluster_cnt->shape[0] == bs && topk_cluster_cnt->shape[1] == H && topk_cluster_cnt->shape[2] == B &&
+                 cache_cnt->shape[0] == bs && cache_cnt->shape[1] == H && cache_cnt->shape[2] == N,
+             "shape mismatch: ids [bs,H,B,NC], cnt [bs,H,B], code_book [bs,H,N,B], cache_cnt [bs,H,N]");
+  if (bs * H * N == 0) return PK_OK;
+  if (!workspace || workspace_bytes < pk_collision_workspace_bytes(bs, H, B, NC))
+    return fail(PK_ERR_WORKSPACE, "collision workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t* lut = (uint32_t*)workspace;
+  lut_single_kernel<<<(unsigned)(bs * H * B), 256, 0, st>>>((const int32_t*)sorted_cluster_ids->data,
+                                                            (const int32_t*)topk_cluster_cnt->data, (int)NC, lut);
+  int rc = check_launch("collision table");
+  if (rc) return rc;
+  int64_t gx = (N + 255) / 256;
+  int64_t cap = (int64_t)sm_count() * 8 / (bs * H) + 1;
+  if (gx > cap) gx = cap;
+  collision_i32_kernel<<<dim3((unsigned)gx, (unsigned)(bs * H)), 256, (size_t)B * 32 * 4, st>>>(
+      (const int32_t*)code_book->data, lut, (int)B, (int)NC, N, (int32_t*)cache_cnt->data);
+  return check_launch("collision");
+}

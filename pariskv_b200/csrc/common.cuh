@@ -1,0 +1,85 @@
+// Shared host/device helpers of the pariskv_b200 CUDA library (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pariskv_b200.h"
+
+namespace pk {
+
+// ---- host side: status, argument checks, launch accounting (defined in common.cu) ----
+int fail(int code, const char* fmt, ...);
+int check_launch(const char* what, int n_kernels = 1);
+int sm_count();
+
+#define PK_REQUIRE(cond, ...)                               \
+  do {                                                      \
+    if (!(cond)) return pk::fail(PK_ERR_ARG, __VA_ARGS__);  \
+  } while (0)
+
+inline bool is_contig(const pk_tensor* t) {
+  int64_t s = 1;
+  for (int i = t->ndim - 1; i >= 0; --i) {
+    if (t->shape[i] != 1 && t->stride[i] != s) return false;
+    s *= t->shape[i];
+  }
+  return true;
+}
+inline int64_t numel(const pk_tensor* t) {
+  int64_t n = 1;
+  for (int i = 0; i < t->ndim; ++i) n *= t->shape[i];
+  return n;
+}
+inline int elem_size(int dtype) {
+  switch (dtype) {
+    case PK_U8: return 1;
+    case PK_I32: return 4;
+    case PK_I64: return 8;
+    case PK_F32: return 4;
+    case PK_BF16: return 2;
+  }
+  return 0;
+}
+#define PK_CHECK_TENSOR(t, dt, nd)                                                        \
+  do {                                                                                    \
+    PK_REQUIRE((t) != nullptr && (t)->data != nullptr, #t " is null");                    \
+    PK_REQUIRE((t)->dtype == (dt), #t " has dtype tag %d, expected %d", (t)->dtype, (dt)); \
+    PK_REQUIRE((t)->ndim == (nd), #t " has %d dims, expected %d", (t)->ndim, (nd));       \
+  } while (0)
+
+// ---- device side ----
+#ifdef __CUDACC__
+__device__ __forceinline__ float bf2f(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+__device__ __forceinline__ uint16_t f2bf(float f) {
+  return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ float bfround(float f) { return bf2f(f2bf(f)); }
+
+// Order-preserving map of fp32 / int32 to uint32 (larger value -> larger key).
+__device__ __forceinline__ uint32_t ord_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ uint32_t ord_key(int32_t v) { return (uint32_t)v ^ 0x80000000u; }
+
+// exp for non-positive arguments with a fixed operation sequence (the CPU oracle runs the same
+// sequence, so both sides produce identical bits).
+__device__ __forceinline__ float pinned_expf(float x) {
+  if (x < -87.0f) return 0.0f;
+  float n = rintf(__fmul_rn(x, 1.44269504088896341f));
+  float r = __fmaf_rn(n, -0.693145751953125f, x);
+  r = __fmaf_rn(n, -1.428606765330187045e-06f, r);
+  float p = 1.3888889225e-3f;
+  p = __fmaf_rn(p, r, 8.3333337680e-3f);
+  p = __fmaf_rn(p, r, 4.1666667908e-2f);
+  p = __fmaf_rn(p, r, 1.6666667163e-1f);
+  p = __fmaf_rn(p, r, 0.5f);
+  p = __fmaf_rn(p, r, 1.0f);
+  p = __fmaf_rn(p, r, 1.0f);
+  float sc = __uint_as_float((uint32_t)((int)n + 127) << 23);
+  return __fmul_rn(p, sc);
+}
+#endif
+
+}  // namespace pk

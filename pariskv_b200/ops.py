@@ -1,0 +1,269 @@
+"""Python entry points of the CUDA ops: thin wrappers that validate, allocate outputs and scratch with
+torch, and call the C ABI on torch's current stream.  No op has a CPU or PyTorch fallback.
+
+Storage convention: tensors are passed in the reference's LOGICAL shapes (codebook ``[bs,H,16,N]``,
+block weights ``[bs,H,16,N]``, packed 4-bit ``[bs,H,16,N,4]``) with any strides.  Outputs allocated
+here are key-major in memory (``[bs,H,N,16(,4)]``) and returned as permuted views with those shapes;
+that layout turns a rerank candidate into one 64-byte plus one 32-byte record.
+"""
+import math
+
+import torch
+
+from . import _lib as L
+
+_WS = {}
+
+
+def workspace(device, nbytes, tag="default"):
+    """A cached, growable scratch buffer per (device, tag).  Calls on one stream reuse it safely."""
+    key = (torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device(), tag)
+    buf = _WS.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 1 << 16), dtype=torch.uint8, device=device)
+        _WS[key] = buf
+    return buf
+
+
+def _call(name, *args):
+    L.check(getattr(L.load(), name)(*args))
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("pariskv_b200 ops need CUDA tensors; there is no CPU fallback")
+
+
+# --------------------------------------------------------------------------------------------------
+# key coding
+# --------------------------------------------------------------------------------------------------
+def alloc_key_metadata(bs, H, cap, device):
+    """Key-major metadata storage for `cap` keys per head, returned as reference-shaped views:
+    (codebook u8 [bs,H,16,cap], block_weight bf16 [bs,H,16,cap], packed u8 [bs,H,16,cap,4])."""
+    cb = torch.zeros(bs, H, cap, 16, dtype=torch.uint8, device=device)
+    w = torch.zeros(bs, H, cap, 16, dtype=torch.bfloat16, device=device)
+    pk = torch.zeros(bs, H, cap, 16, 4, dtype=torch.uint8, device=device)
+    return cb.permute(0, 1, 3, 2), w.permute(0, 1, 3, 2), pk.permute(0, 1, 3, 2, 4)
+
+
+def encode_keys(keys, signs, codebook=None, block_weight=None, packed_4bit=None, cluster_counts=None):
+    """keys bf16 [bs,H,L,128] -> (codebook, block_weight, packed_4bit); see pk_encode_keys.
+    When `cluster_counts` (i32 [bs,H,16,256]) is given, the code histogram of these keys is ADDED to it."""
+    _require_cuda(keys, signs)
+    bs, H, Lk, D = keys.shape
+    if codebook is None:
+        codebook, block_weight, packed_4bit = alloc_key_metadata(bs, H, Lk, keys.device)
+    if keys.numel() == 0:
+        return codebook, block_weight, packed_4bit
+    d = [L.desc(t) for t in (keys, signs, codebook, block_weight, packed_4bit, cluster_counts)]
+    _call("pk_encode_keys", *[L.ref(x) for x in d], L.stream_ptr(keys.device))
+    return codebook, block_weight, packed_4bit
+
+
+def count_clusters(codebook, counts=None, accumulate=False):
+    _require_cuda(codebook)
+    bs, H, B, N = codebook.shape
+    if counts is None:
+        counts = torch.empty(bs, H, B, 256, dtype=torch.int32, device=codebook.device)
+        accumulate = False
+    dc, dn = L.desc(codebook), L.desc(counts)
+    _call("pk_count_clusters", L.ref(dc), L.ref(dn), int(bool(accumulate)), L.stream_ptr(codebook.device))
+    return counts
+
+
+def query_prep(queries, kv_heads, signs, want_avg=False):
+    """queries bf16 [bs,1,Hq,128] -> q_blocks [bs,H,16,8], q_norm [bs,H,1] (, query_avg [bs,H,128])."""
+    _require_cuda(queries, signs)
+    bs = queries.shape[0]
+    dev = queries.device
+    qb = torch.empty(bs, kv_heads, 16, 8, dtype=torch.bfloat16, device=dev)
+    qn = torch.empty(bs, kv_heads, 1, dtype=torch.bfloat16, device=dev)
+    qa = torch.empty(bs, kv_heads, 128, dtype=torch.bfloat16, device=dev) if want_avg else None
+    d = [L.desc(t) for t in (queries, signs, qb, qn, qa)]
+    _call("pk_query_prep", *[L.ref(x) for x in d], L.stream_ptr(dev))
+    return (qb, qn, qa) if want_avg else (qb, qn)
+
+
+def rank_clusters(q_blocks):
+    _require_cuda(q_blocks)
+    bs, H = q_blocks.shape[:2]
+    ids = torch.empty(bs, H, 16, 256, dtype=torch.int64, device=q_blocks.device)
+    dq, di = L.desc(q_blocks), L.desc(ids)
+    _call("pk_rank_clusters", L.ref(dq), L.ref(di), L.stream_ptr(q_blocks.device))
+    return ids
+
+
+# --------------------------------------------------------------------------------------------------
+# collision
+# --------------------------------------------------------------------------------------------------
+def collision_fused(sorted_cluster_ids, cluster_key_counts, codebook, tier_counts, cache_cnt=None):
+    _require_cuda(sorted_cluster_ids, cluster_key_counts, codebook)
+    bs, H, B, N = codebook.shape
+    dev = codebook.device
+    if cache_cnt is None:
+        cache_cnt = torch.empty(bs, H, N, dtype=torch.int32, device=dev)
+    lib = L.load()
+    nb = lib.pk_collision_workspace_bytes(bs, H, B, sorted_cluster_ids.shape[-1])
+    ws = workspace(dev, nb, "collision")
+    tiers = L.i64_array(list(tier_counts))
+    d = [L.desc(t) for t in (sorted_cluster_ids, cluster_key_counts, codebook, cache_cnt)]
+    _call("pk_collision_fused", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), tiers, len(tier_counts), L.ref(d[3]),
+          ws.data_ptr(), ws.numel(), L.stream_ptr(dev))
+    return cache_cnt
+
+
+def collision(sorted_cluster_ids, topk_cluster_cnt, code_book, cache_cnt):
+    """Unfused single-tier op; code_book is int32 [bs,H,N,B] (the kernel-side layout)."""
+    _require_cuda(sorted_cluster_ids, topk_cluster_cnt, code_book, cache_cnt)
+    bs, H, N, B = code_book.shape
+    dev = code_book.device
+    nb = L.load().pk_collision_workspace_bytes(bs, H, B, sorted_cluster_ids.shape[-1])
+    ws = workspace(dev, nb, "collision")
+    d = [L.desc(t) for t in (sorted_cluster_ids, topk_cluster_cnt, code_book, cache_cnt)]
+    _call("pk_collision", *[L.ref(x) for x in d], ws.data_ptr(), ws.numel(), L.stream_ptr(dev))
+    return cache_cnt
+
+
+# --------------------------------------------------------------------------------------------------
+# top-k
+# --------------------------------------------------------------------------------------------------
+def topk(x, k, order=0):
+    """Exact top-k indices over the last dim of a 2-D or 3-D int32/float32 tensor -> int64.
+    order 0: ascending index; order 1: value descending.  Ties go to the lower index."""
+    _require_cuda(x)
+    if x.dtype not in (torch.int32, torch.float32):
+        x = x.to(torch.int32) if not x.dtype.is_floating_point else x.to(torch.float32)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    out = torch.empty(x2.shape[0], k, dtype=torch.int64, device=x.device)
+    dx, do = L.desc(x2), L.desc(out)
+    _call("pk_topk", L.ref(dx), int(k), L.ref(do), int(order), L.stream_ptr(x.device))
+    return out.view(*lead, k)
+
+
+def final_topk(scores_f32, cand, K):
+    _require_cuda(scores_f32, cand)
+    bs, H, C = scores_f32.shape
+    out = torch.empty(bs, H, K, dtype=torch.int64, device=scores_f32.device)
+    d = [L.desc(t) for t in (scores_f32, cand, out)]
+    _call("pk_final_topk", L.ref(d[0]), L.ref(d[1]), int(K), L.ref(d[2]), L.stream_ptr(scores_f32.device))
+    return out
+
+
+def adaptive_topk(sl_logits, cand_scores, cand_scale, sl_vnorm, cand_indices, cand_vnorm, threshold, K_out,
+                  value_norm=None, sink_size=0, min_k=0, max_k=0, adaptive_k=None, topk_indices=None):
+    _require_cuda(sl_logits, cand_scores, sl_vnorm, cand_indices)
+    bs, H = sl_logits.shape[:2]
+    dev = sl_logits.device
+    if adaptive_k is None:
+        adaptive_k = torch.empty(bs, H, dtype=torch.int64, device=dev)
+    if topk_indices is None:
+        topk_indices = torch.empty(bs, H, K_out, dtype=torch.int64, device=dev)
+    d = [L.desc(t) for t in (sl_logits, cand_scores, sl_vnorm, cand_indices, cand_vnorm, value_norm, adaptive_k,
+                             topk_indices)]
+    _call("pk_adaptive_topk", L.ref(d[0]), L.ref(d[1]), float(cand_scale), L.ref(d[2]), L.ref(d[3]), L.ref(d[4]),
+          L.ref(d[5]), int(sink_size), float(threshold), int(K_out), int(min_k), int(max_k), L.ref(d[6]),
+          L.ref(d[7]), L.stream_ptr(dev))
+    return adaptive_k, topk_indices
+
+
+# --------------------------------------------------------------------------------------------------
+# rerank
+# --------------------------------------------------------------------------------------------------
+def rerank(coarse_indices, key_4bit, key_block_weight, q_blocks, q_norm, mag_centers, approx_scores=None,
+           scores_f32=None, v4b=None, want_f32=False):
+    _require_cuda(coarse_indices, key_4bit, key_block_weight, q_blocks, q_norm, mag_centers)
+    bs, H, C = coarse_indices.shape
+    dev = coarse_indices.device
+    if approx_scores is None:
+        approx_scores = torch.empty(bs, H, C, dtype=torch.bfloat16, device=dev)
+    if scores_f32 is None and want_f32:
+        scores_f32 = torch.empty(bs, H, C, dtype=torch.float32, device=dev)
+    d = [L.desc(t) for t in (coarse_indices, key_4bit, key_block_weight, q_blocks, q_norm, mag_centers,
+                             approx_scores, scores_f32, v4b)]
+    _call("pk_rerank", *[L.ref(x) for x in d], L.stream_ptr(dev))
+    return approx_scores, scores_f32
+
+
+# --------------------------------------------------------------------------------------------------
+# gather / attention
+# --------------------------------------------------------------------------------------------------
+def h2d_gather_kv(src_k, src_v, selected_indices, dst_k, dst_v):
+    _require_cuda(selected_indices, dst_k, dst_v)
+    d = [L.desc(t) for t in (src_k, src_v, selected_indices, dst_k, dst_v)]
+    _call("pk_h2d_gather_kv", *[L.ref(x) for x in d], L.stream_ptr(dst_k.device))
+
+
+def h2d_gather_kv_packed(src_k, src_v, k_packed, v_packed, indices_packed, cu_seqlens_topk, cu_seqlens_k,
+                         sink_local_end, global_k):
+    _require_cuda(k_packed, v_packed, indices_packed, cu_seqlens_topk, cu_seqlens_k)
+    d = [L.desc(t) for t in (src_k, src_v, k_packed, v_packed, indices_packed, cu_seqlens_topk, cu_seqlens_k)]
+    _call("pk_h2d_gather_kv_packed", *[L.ref(x) for x in d], int(sink_local_end), int(global_k),
+          L.stream_ptr(k_packed.device))
+
+
+def gather_kv_out_cpu(src, index, out, n_threads=0):
+    for t in (src, index, out):
+        if t.is_cuda:
+            raise RuntimeError("gather_kv_out_cpu works on host tensors")
+    d = [L.desc(t) for t in (src, index, out)]
+    _call("pk_gather_kv_out_cpu", *[L.ref(x) for x in d], int(n_threads))
+
+
+def sparse_attention(queries, window_k, window_v, n_window, store_k=None, store_v=None, selected=None, n_sel=None,
+                     index_offset=0, scale=None, out=None):
+    """Decode attention over window rows [0, n_window) plus the selected rows of the K/V store (device or
+    pinned host memory); see pk_sparse_attention."""
+    _require_cuda(queries, window_k, window_v, selected)
+    bs, _, Hq, D = queries.shape
+    dev = queries.device
+    if out is None:
+        out = torch.empty_like(queries)
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    K = selected.shape[2] if selected is not None else 0
+    nb = L.load().pk_attention_workspace_bytes(bs, Hq, n_window + K)
+    ws = workspace(dev, nb, "attention")
+    d = [L.desc(t) for t in (queries, window_k, window_v, store_k, store_v, selected, n_sel, out)]
+    _call("pk_sparse_attention", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(n_window), L.ref(d[3]), L.ref(d[4]),
+          L.ref(d[5]), L.ref(d[6]), int(index_offset), float(scale), L.ref(d[7]), ws.data_ptr(), ws.numel(),
+          L.stream_ptr(dev))
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# the fused retrieval chain
+# --------------------------------------------------------------------------------------------------
+def retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, cluster_key_counts, tier_counts,
+             C, K, final_indices=None, want=()):
+    """queries -> final top-K key indices (ascending) in one call.  `want` may name extra outputs among
+    {"cand", "scores_f32", "q_blocks", "q_norm", "query_avg"}; returns (final_indices, extras dict)."""
+    _require_cuda(queries, codebook, key_block_weight, key_4bit, cluster_key_counts)
+    bs, H, B, N = codebook.shape
+    dev = codebook.device
+    if final_indices is None:
+        final_indices = torch.empty(bs, H, K, dtype=torch.int64, device=dev)
+    extras = {}
+    if "cand" in want:
+        extras["cand"] = torch.empty(bs, H, C, dtype=torch.int64, device=dev)
+    if "scores_f32" in want:
+        extras["scores_f32"] = torch.empty(bs, H, C, dtype=torch.float32, device=dev)
+    if "q_blocks" in want:
+        extras["q_blocks"] = torch.empty(bs, H, 16, 8, dtype=torch.bfloat16, device=dev)
+    if "q_norm" in want:
+        extras["q_norm"] = torch.empty(bs, H, 1, dtype=torch.bfloat16, device=dev)
+    if "query_avg" in want:
+        extras["query_avg"] = torch.empty(bs, H, 128, dtype=torch.bfloat16, device=dev)
+    nb = L.load().pk_retrieve_workspace_bytes(bs, H, N, C)
+    ws = workspace(dev, nb, "retrieve")
+    tiers = L.i64_array(list(tier_counts))
+    d = [L.desc(t) for t in (queries, signs, mag_centers, codebook, key_block_weight, key_4bit, cluster_key_counts,
+                             final_indices, extras.get("cand"), extras.get("scores_f32"), extras.get("q_blocks"),
+                             extras.get("q_norm"), extras.get("query_avg"))]
+    _call("pk_retrieve", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), L.ref(d[3]), L.ref(d[4]), L.ref(d[5]), L.ref(d[6]),
+          tiers, len(tier_counts), int(C), int(K), L.ref(d[7]), L.ref(d[8]), L.ref(d[9]), L.ref(d[10]),
+          L.ref(d[11]), L.ref(d[12]), ws.data_ptr(), ws.numel(), L.stream_ptr(dev))
+    return final_indices, extras

@@ -1,0 +1,361 @@
+"""GPU parity tests: every CUDA op, called through the C ABI, against the CPU oracle on the same
+seeded inputs.  Integer / index results must be bit-exact; rerank scores within 1e-3 relative."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits, bits_of, srht_signs, synth_keys, synth_queries
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from pariskv_b200 import ops as _ops
+    return _ops
+
+
+def _encode_oracle_vs_gpu(ops, oracle, keys, signs, layout):
+    bs, H, L, _ = keys.shape
+    cb_o, w_o, pk_o = oracle.encode(keys, signs)
+    kg, sg = keys.to(DEV), signs.to(DEV)
+    counts = torch.zeros(bs, H, 16, 256, dtype=torch.int32, device=DEV)
+    if layout == "key_major":
+        cb, w, pk = ops.encode_keys(kg, sg, cluster_counts=counts)
+    else:  # the reference's plane-major tensors, written through a view that starts at column 4
+        cbf = torch.zeros(bs, H, 16, L + 8, dtype=torch.uint8, device=DEV)
+        wf = torch.zeros(bs, H, 16, L + 8, dtype=torch.bfloat16, device=DEV)
+        pkf = torch.zeros(bs, H, 16, L + 8, 4, dtype=torch.uint8, device=DEV)
+        cb, w, pk = cbf[..., 4:4 + L], wf[..., 4:4 + L], pkf[..., 4:4 + L, :]
+        ops.encode_keys(kg, sg, cb, w, pk, cluster_counts=counts)
+    assert torch.equal(cb.cpu(), cb_o), "sign codes differ"
+    assert torch.equal(pk.cpu(), pk_o), "4-bit codes differ"
+    assert torch.equal(bits_of(w), bits_of(w_o)), "block weights differ"
+    assert torch.equal(counts.cpu(), oracle.cluster_counts(cb_o))
+    assert torch.equal(ops.count_clusters(cb).cpu(), oracle.cluster_counts(cb_o))
+    return cb, w, pk, counts
+
+
+@pytest.mark.parametrize("layout", ["key_major", "plane_major"])
+@pytest.mark.parametrize("L", [1, 15, 16, 17, 127, 1000])
+def test_encode_bit_exact(ops, oracle, layout, L):
+    g = torch.Generator().manual_seed(L)
+    keys = synth_keys(g, 2, 3, L)
+    if L > 3:
+        keys[0, 0, 0] = 0
+        keys[0, 0, 1] = 0
+        keys[0, 0, 1, 9] = 2.0
+    _encode_oracle_vs_gpu(ops, oracle, keys, srht_signs(), layout)
+
+
+def test_encode_golden(ops, golden):
+    e = golden("encode")
+    keys, signs = bf16_from_bits(e["keys"]), bf16_from_bits(e["signs"])
+    cb, w, pk = ops.encode_keys(keys.to(DEV), signs.to(DEV))
+    assert torch.equal(cb.cpu(), torch.from_numpy(e["codebook"]))
+    assert torch.equal(pk.cpu(), torch.from_numpy(e["packed_4bit"]))
+    assert torch.equal(bits_of(w), bits_of(bf16_from_bits(e["block_weight"])))
+
+
+def test_encode_empty(ops):
+    keys = torch.empty(1, 2, 0, 128, dtype=torch.bfloat16, device=DEV)
+    cb, w, pk = ops.encode_keys(keys, srht_signs().to(DEV))
+    assert cb.shape == (1, 2, 16, 0)
+
+
+@pytest.mark.parametrize("group", [1, 4, 7])
+def test_query_prep_and_rank(ops, oracle, group):
+    g = torch.Generator().manual_seed(3 + group)
+    keys = synth_keys(g, 2, 2, 64)
+    q = synth_queries(g, keys, group)
+    signs = srht_signs()
+    qb_o, qn_o = oracle.query_prep(q, 2, signs)
+    qb, qn, qa = ops.query_prep(q.to(DEV), 2, signs.to(DEV), want_avg=True)
+    assert torch.equal(bits_of(qb), bits_of(qb_o))
+    assert torch.equal(bits_of(qn), bits_of(qn_o))
+    ids = ops.rank_clusters(qb)
+    assert torch.equal(ids.cpu(), oracle.cluster_rank(qb_o))
+
+
+def test_query_prep_golden(ops, golden):
+    q = golden("query_collision")
+    qb, qn = ops.query_prep(bf16_from_bits(q["queries"]).to(DEV), 2, bf16_from_bits(q["signs"]).to(DEV))
+    assert torch.equal(bits_of(qb), bits_of(bf16_from_bits(q["q_blocks"])))
+    assert torch.equal(bits_of(qn), bits_of(bf16_from_bits(q["q_norm"])))
+
+
+def _rand_collision_inputs(gen, bs, H, B, NC, N):
+    ids = torch.stack([torch.stack([torch.stack([torch.randperm(NC, generator=gen) for _ in range(B)])
+                                    for _ in range(H)]) for _ in range(bs)])
+    ckc = torch.randint(1, max(2, N // 4), (bs, H, B, NC), generator=gen, dtype=torch.int32)
+    cb = torch.randint(0, NC, (bs, H, B, N), generator=gen, dtype=torch.int32).to(torch.uint8)
+    return ids, ckc, cb
+
+
+@pytest.mark.parametrize("N", [1, 31, 32, 33, 1023, 1025, 5000])
+@pytest.mark.parametrize("layout", ["plane", "plane_offset4", "plane_offset3", "key_major", "generic"])
+def test_collision_fused_bit_exact(ops, oracle, N, layout):
+    g = torch.Generator().manual_seed(N)
+    bs, H, B, NC = 2, 3, 16, 256
+    ids, ckc, cb = _rand_collision_inputs(g, bs, H, B, NC, N)
+    tiers = oracle.tier_counts(N * 40, 0.2)
+    ref = oracle.collision(ids, ckc, cb, tiers)
+    if layout == "plane":
+        cbg = cb.to(DEV)
+    elif layout.startswith("plane_offset"):
+        off = int(layout[-1])
+        full = torch.zeros(bs, H, B, N + 32, dtype=torch.uint8, device=DEV)
+        full[..., off:off + N] = cb.to(DEV)
+        cbg = full[..., off:off + N]
+    elif layout == "key_major":
+        cbg = cb.to(DEV).permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
+    else:  # odd strides: falls to the byte-wise kernel
+        full = torch.zeros(bs, H, B, N + 5, dtype=torch.uint8, device=DEV)
+        full[..., :N] = cb.to(DEV)
+        cbg = full[..., :N]
+    out = ops.collision_fused(ids.to(DEV), ckc.to(DEV), cbg, tiers)
+    assert torch.equal(out.cpu(), ref)
+    out32 = ops.collision_fused(ids.to(torch.int32).to(DEV), ckc.to(DEV), cbg, tiers[-1:])
+    assert torch.equal(out32.cpu(), oracle.collision(ids, ckc, cb, tiers[-1:]))
+
+
+def test_collision_golden(ops, golden):
+    c = golden("collision")
+    for tag in ("n2048", "n1000"):
+        out = ops.collision_fused(torch.from_numpy(c[tag + "_sorted_ids"].astype(np.int64)).to(DEV),
+                                  torch.from_numpy(c[tag + "_cluster_counts"]).to(DEV),
+                                  torch.from_numpy(c[tag + "_codebook"]).to(DEV), c[tag + "_tier_counts"].tolist())
+        assert torch.equal(out.cpu(), torch.from_numpy(c[tag + "_cache_cnt"]))
+    cb = torch.from_numpy(c["single_codebook"]).to(DEV).transpose(-1, -2).contiguous()
+    out = torch.empty(1, 2, 777, dtype=torch.int32, device=DEV)
+    ops.collision(torch.from_numpy(c["single_sorted_ids"]).to(DEV), torch.from_numpy(c["single_topk_cluster_cnt"]).to(DEV),
+                  cb, out)
+    assert torch.equal(out.cpu(), torch.from_numpy(c["single_cache_cnt"]))
+
+
+@pytest.mark.parametrize("L,k", [(1, 1), (31, 31), (33, 1), (1000, 100), (4097, 4096), (20000, 2000), (300000, 30000)])
+@pytest.mark.parametrize("kind", ["counts", "float_counts", "float", "ties"])
+def test_topk_exact(ops, oracle, L, k, kind):
+    g = torch.Generator().manual_seed(L + k)
+    rows = 3
+    if kind == "counts":
+        x = torch.randint(0, 97, (rows, L), generator=g, dtype=torch.int32)
+    elif kind == "float_counts":
+        x = torch.randint(0, 97, (rows, L), generator=g).to(torch.float32)
+    elif kind == "float":
+        x = torch.randn(rows, L, generator=g) * 50
+    else:
+        x = torch.randint(-2, 3, (rows, L), generator=g, dtype=torch.int32)
+    out = ops.topk(x.to(DEV), k)
+    assert torch.equal(out.cpu(), oracle.topk(x, k))
+    if k <= 4096:
+        out = ops.topk(x.to(DEV), k, order=1)
+        assert torch.equal(out.cpu(), oracle.topk(x, k, sorted_by_value=True))
+
+
+def test_topk_3d_strided_rows(ops, oracle):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randint(0, 97, (2, 4, 3000), generator=g, dtype=torch.int32)
+    out = ops.topk(x.to(DEV)[:, :, :2500], 300)
+    assert torch.equal(out.cpu(), oracle.topk(x[:, :, :2500].contiguous(), 300))
+
+
+def test_topk_rejects_bad_k(ops):
+    x = torch.zeros(2, 10, dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.topk(x, 11)
+    with pytest.raises(RuntimeError):
+        ops.topk(x, 0)
+
+
+def _rerank_inputs(gen, bs, H, N):
+    sign = torch.randint(0, 2, (bs, H, 16, N, 8), generator=gen)
+    mag = torch.randint(0, 8, (bs, H, 16, N, 8), generator=gen)
+    v4 = (sign << 3) | mag
+    k4 = ((v4[..., 1::2] << 4) | v4[..., 0::2]).to(torch.uint8)
+    w = torch.randn(bs, H, 16, N, generator=gen).abs().to(torch.bfloat16)
+    qb = torch.randn(bs, H, 16, 8, generator=gen).to(torch.bfloat16)
+    qn = (torch.randn(bs, H, 1, generator=gen).abs() + 0.1).to(torch.bfloat16)
+    return k4, w, qb, qn
+
+
+@pytest.mark.parametrize("layout", ["key_major", "plane_major"])
+@pytest.mark.parametrize("C", [1, 127, 129, 1500])
+def test_rerank_matches_oracle(ops, oracle, layout, C):
+    g = torch.Generator().manual_seed(C)
+    bs, H, N = 2, 2, 3000
+    k4, w, qb, qn = _rerank_inputs(g, bs, H, N)
+    _, cen = oracle.constants()
+    cand = torch.stack([torch.stack([torch.randperm(N, generator=g)[:C].sort().values for _ in range(H)])
+                        for _ in range(bs)])
+    s32_o, sbf_o = oracle.rerank(cand, k4, w, qb, qn, cen)
+    if layout == "key_major":
+        k4g = k4.to(DEV).permute(0, 1, 3, 2, 4).contiguous().permute(0, 1, 3, 2, 4)
+        wg = w.to(DEV).permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
+    else:
+        k4g, wg = k4.to(DEV), w.to(DEV)
+    v4b = torch.zeros(bs, H, 16, C, 8, dtype=torch.bfloat16, device=DEV)
+    sbf, s32 = ops.rerank(cand.to(DEV), k4g, wg, qb.to(DEV), qn.to(DEV), cen.to(DEV), v4b=v4b, want_f32=True)
+    assert torch.equal(s32.cpu(), s32_o), "fp32 scores must be bit-identical to the oracle's pinned order"
+    assert torch.equal(bits_of(sbf), bits_of(sbf_o))
+    # the optional unpacked-level output equals +-center[level]
+    nib = torch.stack([k4 & 0xF, k4 >> 4], -1).view(bs, H, 16, N, 8).long()
+    lev = torch.where((nib & 8) > 0, cen.float()[nib & 7], -cen.float()[nib & 7])
+    idx = cand.view(bs, H, 1, C, 1).expand(bs, H, 16, C, 8)
+    assert torch.equal(v4b.float().cpu(), torch.gather(lev, 3, idx))
+
+
+def test_rerank_golden_within_tolerance(ops, golden):
+    r = golden("rerank")
+    N = r["key_4bit"].shape[3]
+    cand = torch.arange(N).view(1, 1, N).expand(1, 2, N).contiguous()
+    _, s32 = ops.rerank(cand.to(DEV), torch.from_numpy(r["key_4bit"]).to(DEV), bf16_from_bits(r["key_block_weight"]).to(DEV),
+                        bf16_from_bits(r["q_blocks"]).to(DEV), bf16_from_bits(r["q_norm"]).to(DEV),
+                        bf16_from_bits(r["mag_centers"]).to(DEV), want_f32=True)
+    ref = torch.from_numpy(r["scores_fp32"])
+    rel = ((s32.cpu() - ref).abs() / ref.abs().clamp(min=1e-3 * ref.abs().max())).max().item()
+    assert rel <= 1e-3, rel  # tolerance stated by the task: 1e-3 relative, fp32 accumulate
+    fin = ops.final_topk(s32, cand.to(DEV), int(r["final_topk"]))
+    for h in range(2):
+        assert set(fin[0, h].tolist()) == set(r["final_fp32"][0, h].tolist())
+
+
+def test_final_topk(ops, oracle):
+    g = torch.Generator().manual_seed(11)
+    s = torch.randn(2, 3, 5000, generator=g)
+    s[0, 0, :100] = 1.5  # ties at the top
+    cand = torch.stack([torch.stack([torch.randperm(40000, generator=g)[:5000].sort().values for _ in range(3)])
+                        for _ in range(2)])
+    out = ops.final_topk(s.to(DEV), cand.to(DEV), 256)
+    assert torch.equal(out.cpu(), oracle.final_topk(s, cand, 256))
+
+
+def test_adaptive_topk_golden_configs(ops, oracle, golden):
+    a = golden("adaptive_topk")
+    for i in range(4):
+        cs = bf16_from_bits(a[f"c{i}_cand_scores"])
+        scale = float(a[f"c{i}_attn_scale"])
+        sl = torch.from_numpy(a[f"c{i}_sl_logits"])
+        slv = torch.from_numpy(a[f"c{i}_sl_vnorm"])
+        cv = torch.from_numpy(a[f"c{i}_cand_vnorm"])
+        ci = torch.from_numpy(a[f"c{i}_cand_indices"].astype(np.int64))
+        thr = float(a[f"c{i}_threshold"])
+        K_out = min(int(a[f"c{i}_topk_cap"]), cs.shape[-1])
+        k_ref = torch.from_numpy(a[f"c{i}_adaptive_k"])
+        idx_ref = torch.from_numpy(a[f"c{i}_topk_indices"].astype(np.int64))
+        # v2 form: bf16 scores scaled in the kernel
+        k, idx = ops.adaptive_topk(sl.to(DEV), cs.to(DEV), scale, slv.to(DEV), ci.to(DEV), cv.to(DEV), thr, K_out)
+        assert torch.equal(k.cpu(), k_ref), f"config {i}: adaptive_k differs from the reference"
+        for b in range(k.shape[0]):
+            for h in range(k.shape[1]):
+                kk = int(k_ref[b, h])
+                assert set(idx[b, h, :kk].tolist()) == set(idx_ref[b, h, :kk].tolist())
+        # against the oracle everything is bit-exact, order included
+        cl = torch.from_numpy((cs.float().numpy() * np.float32(scale)).astype(np.float32))
+        k_o, idx_o = oracle.adaptive_topk(sl, slv, cl, cv, ci, thr, K_out)
+        assert torch.equal(k.cpu(), k_o)
+        assert torch.equal(idx.cpu(), idx_o)
+        # v1 form: fp32 logits, scale 1; gathered value norms
+        vn = torch.zeros(ci.shape[0], ci.shape[1], int(ci.max()) + 5)
+        vn.scatter_(2, ci + 4, cv)
+        k1, idx1 = ops.adaptive_topk(sl.to(DEV), cl.to(DEV), 1.0, slv.to(DEV), ci.to(DEV), None, thr, K_out,
+                                     value_norm=vn.to(DEV), sink_size=4)
+        assert torch.equal(k1.cpu(), k_o) and torch.equal(idx1.cpu(), idx_o)
+        kc, _ = ops.adaptive_topk(sl.to(DEV), cs.to(DEV), scale, slv.to(DEV), ci.to(DEV), cv.to(DEV), thr, K_out,
+                                  min_k=300, max_k=500)
+        assert torch.equal(kc.cpu(), k_o.clamp(300, 500))
+
+
+def test_h2d_gather_matches_indexing(ops, oracle):
+    # the reference's own self-check shape: bs 2, 8 heads, N 32768, k 100 (cache_hub/gather_trans/trans_h2d.py:108-147)
+    g = torch.Generator().manual_seed(0)
+    bs, H, N, K = 2, 8, 32768, 100
+    sk = torch.randn(bs, H, N, 128, generator=g).to(torch.bfloat16).pin_memory()
+    sv = torch.randn(bs, H, N, 128, generator=g).to(torch.bfloat16).pin_memory()
+    idx = torch.randint(0, N, (bs, H, K), generator=g)
+    dk = torch.zeros(bs, H, 160, 128, dtype=torch.bfloat16, device=DEV)
+    dv = torch.zeros_like(dk)
+    ops.h2d_gather_kv(sk, sv, idx.to(DEV), dk, dv)
+    assert torch.equal(dk[:, :, :K].cpu(), oracle.gather(sk, idx))
+    assert torch.equal(dv[:, :, :K].cpu(), oracle.gather(sv, idx))
+    assert dk[:, :, K:].abs().sum().item() == 0
+    # host-side gather op
+    out = torch.empty(bs, H, K, 128, dtype=torch.bfloat16)
+    ops.gather_kv_out_cpu(sk, idx, out)
+    assert torch.equal(out, oracle.gather(sk, idx))
+    with pytest.raises(RuntimeError):
+        bad = idx.clone()
+        bad[0, 0, 0] = N
+        ops.gather_kv_out_cpu(sk, bad, out)
+
+
+def test_h2d_gather_packed(ops):
+    g = torch.Generator().manual_seed(1)
+    bs, H, N = 1, 4, 4096
+    sk = torch.randn(bs, H, N, 128, generator=g).to(torch.bfloat16).pin_memory()
+    sv = torch.randn(bs, H, N, 128, generator=g).to(torch.bfloat16).pin_memory()
+    ks = [5, 0, 300, 77]
+    sl_end = 10
+    cu_topk = torch.tensor([0] + list(np.cumsum(ks)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(np.cumsum([k + sl_end for k in ks])), dtype=torch.int32)
+    idx = torch.cat([torch.randperm(N, generator=g)[:k] for k in ks])
+    kp = torch.zeros(int(cu_k[-1]), 128, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    ops.h2d_gather_kv_packed(sk, sv, kp, vp, idx.to(DEV), cu_topk.to(DEV), cu_k.to(DEV), sl_end, max(ks))
+    for vh in range(4):
+        sel = idx[cu_topk[vh]:cu_topk[vh + 1]]
+        o = int(cu_k[vh]) + sl_end
+        assert torch.equal(kp[o:o + ks[vh]].cpu(), sk[0, vh, sel])
+        assert torch.equal(vp[o:o + ks[vh]].cpu(), sv[0, vh, sel])
+        assert kp[int(cu_k[vh]):o].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("store", ["pinned_host", "device"])
+@pytest.mark.parametrize("n_window,K,group", [(0, 64, 4), (68, 0, 4), (196, 256, 4), (70, 1000, 7), (5, 33, 1)])
+def test_sparse_attention(ops, oracle, store, n_window, K, group):
+    g = torch.Generator().manual_seed(n_window + K)
+    bs, H, N = 2, 2, 5000
+    keys = synth_keys(g, bs, H, N)
+    vals = torch.randn(bs, H, N, 128, generator=g).to(torch.bfloat16)
+    q = synth_queries(g, keys, group) * 3
+    wk = torch.randn(bs, H, 256, 128, generator=g).to(torch.bfloat16)
+    wv = torch.randn(bs, H, 256, 128, generator=g).to(torch.bfloat16)
+    sel = torch.stack([torch.stack([torch.randperm(N - 4, generator=g)[:K].sort().values for _ in range(H)])
+                       for _ in range(bs)]) if K else None
+    off = 4
+    ks = keys.pin_memory() if store == "pinned_host" else keys.to(DEV)
+    vs = vals.pin_memory() if store == "pinned_host" else vals.to(DEV)
+    out = ops.sparse_attention(q.to(DEV), wk.to(DEV), wv.to(DEV), n_window, ks if K else None, vs if K else None,
+                               sel.to(DEV) if K else None, index_offset=off)
+    rows_k = [wk[:, :, :n_window]]
+    rows_v = [wv[:, :, :n_window]]
+    if K:
+        rows_k.append(oracle.gather(keys, sel + off))
+        rows_v.append(oracle.gather(vals, sel + off))
+    ref = oracle.attention(q, torch.cat(rows_k, 2), torch.cat(rows_v, 2))
+    err = (out.float().cpu() - ref).abs().max().item()
+    assert err <= 2e-2, err  # tolerance stated by the task: bf16 output, max abs 2e-2
+
+
+def test_sparse_attention_per_head_counts(ops, oracle):
+    g = torch.Generator().manual_seed(9)
+    bs, H, N, K = 1, 4, 2000, 300
+    keys = synth_keys(g, bs, H, N)
+    vals = torch.randn(bs, H, N, 128, generator=g).to(torch.bfloat16)
+    q = synth_queries(g, keys, 4) * 3
+    wk = torch.randn(bs, H, 80, 128, generator=g).to(torch.bfloat16)
+    wv = torch.randn(bs, H, 80, 128, generator=g).to(torch.bfloat16)
+    sel = torch.stack([torch.stack([torch.randperm(N, generator=g)[:K] for _ in range(H)]) for _ in range(bs)])
+    n_sel = torch.tensor([[300, 0, 17, 129]], dtype=torch.int32)
+    out = ops.sparse_attention(q.to(DEV), wk.to(DEV), wv.to(DEV), 80, keys.to(DEV), vals.to(DEV), sel.to(DEV),
+                               n_sel=n_sel.to(DEV))
+    for h in range(H):
+        n = int(n_sel[0, h])
+        kk = torch.cat([wk[:, h:h + 1], oracle.gather(keys[:, h:h + 1], sel[:, h:h + 1, :n])], 2)
+        vv = torch.cat([wv[:, h:h + 1], oracle.gather(vals[:, h:h + 1], sel[:, h:h + 1, :n])], 2)
+        ref = oracle.attention(q[:, :, 4 * h:4 * h + 4], kk, vv)
+        assert (out[:, :, 4 * h:4 * h + 4].float().cpu() - ref).abs().max().item() <= 2e-2
