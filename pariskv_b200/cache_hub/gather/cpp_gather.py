@@ -1,0 +1,8 @@
+"""Host-side K/V row gather with the reference's surface (cache_hub/gather/cpp_gather.py:10-41)."""
+from types import SimpleNamespace
+
+from ... import ops
+
+
+def load_gather_ext(verbose: bool = False):
+    return SimpleNamespace(gather_kv_out_cpu=lambda src, index, out: ops.gather_kv_out_cpu(src, index, out))

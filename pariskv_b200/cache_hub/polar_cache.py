@@ -1,0 +1,292 @@
+"""ParisKV cache on B200: zone layout, key coding at flush, retrieval and sparse decode attention.
+
+Mirror of the reference class ``cache_hub/polar_cache.py:101`` (constructor arguments, the methods
+``prefill_update_kv_cache / decode_update_kv_cache / compute / sync`` and the attribute ``context``), so a
+model runtime written for the reference decodes through it unchanged.  The body is a different design:
+
+* Per layer there is a small GPU *window* ``[sink | local | update buffer]`` and a *zone store* that
+  holds every older token: pinned host memory read through UVA when ``enable_offload`` is set, device
+  memory otherwise.  Both modes run the same kernels.
+* Zone metadata (sign codes, 4-bit codes, rerank weights) is stored key-major and indexed by the
+  zone-relative position, so record 0 is 16-byte aligned and a rerank candidate is two contiguous records.
+  ``codebook_gpu / key_block_weight_gpu / key_4bit_packed_gpu`` expose them in the reference's logical
+  shapes through permuted views.
+* One decode step of one layer is: a row append, ``ops.retrieve`` (five launches), ``ops.sparse_attention``
+  (two launches).  No host synchronisation, no allocation, no concatenation.
+* Every layer keeps its own buffer counter (the reference derives the slot of every layer from layer 0's
+  counter, which makes layers >= 1 lag by one slot); a layer flushes its own buffer when it fills:
+  the oldest ``dynamic_update_interval`` local rows are coded, added to the cluster histogram, copied to the
+  zone store on the same stream, and the window slides.
+"""
+import json
+import math
+import os
+
+import torch
+
+from .. import ops
+from .cache import KV_Cache
+
+USE_RABITQ_RERANK = True
+TIER_RATIOS = (0.05, 0.15, 0.30, 0.50, 0.75, 1.0)  # reference: cache_hub/polar_cache.py:1221
+
+
+def srht_signs(device, seed=42):
+    """The SRHT diagonal drawn exactly as the reference draws it (cache_hub/polar_cache.py:56-68):
+    seed 42 on the device generator, RNG state restored afterwards."""
+    cpu_state = torch.get_rng_state()
+    cuda_state = torch.cuda.get_rng_state(device)
+    torch.manual_seed(seed)
+    signs = torch.randint(0, 2, (128,), device=device, dtype=torch.bfloat16) * 2 - 1
+    torch.set_rng_state(cpu_state)
+    torch.cuda.set_rng_state(cuda_state, device)
+    return signs.contiguous()
+
+
+class polar_cache(KV_Cache):
+
+    def __init__(self, valid_start, layer_num: int, batch_size: int, max_length: int, num_key_value_heads: int,
+                 num_heads: int, head_dim: int, dtype: torch.dtype, layer_mapping: dict, max_new_length: int,
+                 sink_size: int, local_size: int, core: int = 0, nprobe: int = 0, cache_unit_size: int = 0,
+                 cache_cluster_num: int = 0, num_gpus: int = 1, model_size: int = 0,
+                 codebook_path: str = "./turboquant/codebooks/codebook_d128_m8_Kr1_Kw256_rabitq_sign.json",
+                 final_topk: int = 100, dynamic_update_interval: int = 512, full_attention_threshold: int = 2000,
+                 enable_offload: bool = True, srht_sign_vector=None) -> None:
+        super().__init__(layer_num, batch_size, max_length, num_key_value_heads, num_heads, head_dim, dtype,
+                         layer_mapping, num_gpus, model_size)
+        if head_dim != 128:
+            raise ValueError("the CUDA kernels are built for head_dim 128")
+        if dtype != torch.bfloat16:
+            raise ValueError("the CUDA kernels are built for bfloat16 K/V")
+        self.valid_start = valid_start
+        self.sink_size = sink_size
+        self.local_size = local_size
+        self.steady_size = sink_size + local_size
+        self.dynamic_update_interval = dynamic_update_interval if dynamic_update_interval is not None else local_size
+        self.group_size = num_heads // num_key_value_heads
+        self.max_new_length = max_new_length
+        self.input_length = max_length - max_new_length
+        self.FULL_ATTENTION_THRESHOLD = full_attention_threshold
+        self.final_topk = final_topk
+        self.enable_offload = enable_offload
+        self.polar_m, self.polar_K_r, self.polar_K_omega = 8, 1, 256
+        if codebook_path and os.path.exists(codebook_path):
+            with open(codebook_path) as f:
+                cfg = json.load(f)["config"]
+            if (cfg["d"], cfg["m"], cfg["K_r"], cfg["K_omega"]) != (128, 8, 1, 256):
+                raise ValueError(f"unsupported codebook parameters {cfg}: the kernels implement the sign codebook "
+                                 "d=128, m=8, K_r=1, K_omega=256")
+        self.polar_B = head_dim // self.polar_m
+        self.device = torch.device(list(layer_mapping.values())[0] if layer_mapping else "cuda:0")
+        dev = self.device
+        self.srht_diagonal_signs = (srht_sign_vector.to(dev, torch.bfloat16).contiguous()
+                                    if srht_sign_vector is not None else srht_signs(dev))
+        # bf16 roundings of the reference's literals (cache_hub/polar_cache.py:188-193); the thresholds are
+        # compiled into the encode kernel, the centers are an operand of the rerank
+        self._mag_thresholds = torch.tensor([0.0843, 0.1698, 0.2578, 0.3499, 0.4487, 0.5585, 0.6901],
+                                            device=dev, dtype=torch.bfloat16)
+        self._mag_centers = torch.tensor([0.0420, 0.1266, 0.2130, 0.3025, 0.3973, 0.5001, 0.6169, 0.7633],
+                                         device=dev, dtype=torch.bfloat16)
+        I = self.dynamic_update_interval
+        self.window_capacity = self.steady_size + I
+        self.unified_kv_capacity = self.input_length + self.max_new_length
+        # zone capacity: everything that can ever leave the window, rounded up to whole flushes
+        zone_cap = max(0, self.unified_kv_capacity - self.steady_size)
+        self.zone_capacity = (zone_cap + I - 1) // I * I + I
+        bs, H = batch_size, self.kv_head
+        self.unified_keys_gpu = [torch.zeros(bs, H, self.window_capacity, 128, dtype=dtype, device=dev)
+                                 for _ in range(layer_num)]
+        self.unified_values_gpu = [torch.zeros(bs, H, self.window_capacity, 128, dtype=dtype, device=dev)
+                                   for _ in range(layer_num)]
+        if enable_offload:
+            self.unified_keys_cpu = [torch.zeros(bs, H, self.zone_capacity, 128, dtype=dtype, pin_memory=True)
+                                     for _ in range(layer_num)]
+            self.unified_values_cpu = [torch.zeros(bs, H, self.zone_capacity, 128, dtype=dtype, pin_memory=True)
+                                       for _ in range(layer_num)]
+            self._store_k, self._store_v = self.unified_keys_cpu, self.unified_values_cpu
+        else:
+            self.unified_keys_cpu = self.unified_values_cpu = None
+            self._store_k = [torch.zeros(bs, H, self.zone_capacity, 128, dtype=dtype, device=dev)
+                             for _ in range(layer_num)]
+            self._store_v = [torch.zeros(bs, H, self.zone_capacity, 128, dtype=dtype, device=dev)
+                             for _ in range(layer_num)]
+        self.codebook_gpu, self.key_block_weight_gpu, self.key_4bit_packed_gpu = [], [], []
+        for _ in range(layer_num):
+            cb, w, pk = ops.alloc_key_metadata(bs, H, self.zone_capacity, dev)
+            self.codebook_gpu.append(cb)
+            self.key_block_weight_gpu.append(w)
+            self.key_4bit_packed_gpu.append(pk)
+        self.cluster_key_counts_gpu = [torch.zeros(bs, H, self.polar_B, 256, dtype=torch.int32, device=dev)
+                                       for _ in range(layer_num)]
+        self.cpu_valid_end = [0] * layer_num        # searchable keys per layer (zone length N)
+        self.current_seq_len = [0] * layer_num      # tokens seen per layer
+        self._window_len = [0] * layer_num          # valid rows of the window per layer
+        self._slide_tmp_k = torch.empty(bs, H, max(local_size, 1), 128, dtype=dtype, device=dev)
+        self._slide_tmp_v = torch.empty_like(self._slide_tmp_k)
+        self._all_rows = None
+        self.context = 0
+        self.last_topk_indices = None               # [bs,H,K] of the most recent compute (for inspection)
+
+    # ------------------------------------------------------------------------------------------------
+    # prefill
+    # ------------------------------------------------------------------------------------------------
+    def prefill_update_kv_cache(self, query_states, key_states, value_states, layer_idx, batch_idx):
+        """key_states / value_states: [bsz, seq_len, kv_heads, 128].  bsz == 1 fills sample `batch_idx`;
+        bsz == batch_size fills all samples in lockstep (same valid_start).  Returns the K/V to attend in
+        the prefill itself, as the reference does (cache_hub/polar_cache.py:379-387)."""
+        bsz, seq_len = key_states.shape[:2]
+        assert seq_len <= self.input_length, "prompt longer than the cache was sized for"
+        if bsz == 1:
+            vs = self._valid_start(batch_idx)
+            self._prefill_sample(key_states[0], value_states[0], layer_idx, batch_idx, vs)
+            last = batch_idx + 1 == self.batch_size
+        else:
+            vs = self._valid_start(0)
+            if batch_idx != 0:
+                return key_states[:, vs:], value_states[:, vs:]
+            assert bsz == self.batch_size, "lockstep prefill needs the whole batch"
+            for b in range(1, bsz):
+                assert self._valid_start(b) == vs, "lockstep multi-batch prefill requires one valid_start"
+            for b in range(bsz):
+                self._prefill_sample(key_states[b], value_states[b], layer_idx, b, vs)
+            last = True
+        if last:
+            self.current_seq_len[layer_idx] = seq_len - vs
+            if layer_idx == self.layer_num - 1:
+                self.context += seq_len - vs
+        return key_states[:, vs:], value_states[:, vs:]
+
+    def _valid_start(self, b):
+        vs = self.valid_start
+        if isinstance(vs, (list, tuple)) or (torch.is_tensor(vs) and vs.dim() > 0):
+            return int(vs[b])
+        return int(vs)
+
+    def _prefill_sample(self, k, v, layer, b, vs):
+        """k, v: [seq_len, H, 128] of one sample; tokens before `vs` are padding."""
+        k = k[vs:].to(self.dtype)
+        v = v[vs:].to(self.dtype)
+        P = k.shape[0]
+        sink, local = self.sink_size, self.local_size
+        wk, wv = self.unified_keys_gpu[layer], self.unified_values_gpu[layer]
+        N = max(0, P - self.steady_size)
+        if N == 0:  # short prompt: everything stays in the window
+            n = min(P, self.window_capacity)
+            wk[b, :, :n] = k[:n].transpose(0, 1)
+            wv[b, :, :n] = v[:n].transpose(0, 1)
+            self._window_len[layer] = n
+            self.cpu_valid_end[layer] = 0
+            return
+        wk[b, :, :sink] = k[:sink].transpose(0, 1)
+        wv[b, :, :sink] = v[:sink].transpose(0, 1)
+        wk[b, :, sink:sink + local] = k[P - local:].transpose(0, 1)
+        wv[b, :, sink:sink + local] = v[P - local:].transpose(0, 1)
+        self._window_len[layer] = self.steady_size
+        zk = k[sink:sink + N].transpose(0, 1)   # [H, N, 128] strided view, rows 16-byte aligned
+        zv = v[sink:sink + N].transpose(0, 1)
+        self._append_zone(layer, b, zk, zv, 0, N, reset_counts=True)
+        self.cpu_valid_end[layer] = N
+
+    def _append_zone(self, layer, b, zk, zv, start, n, reset_counts=False):
+        """Code n keys ([H, n, 128]) of sample b into zone records [start, start+n) and copy K/V to the store."""
+        sl = slice(start, start + n)
+        counts = self.cluster_key_counts_gpu[layer][b:b + 1]
+        if reset_counts:
+            counts.zero_()
+        ops.encode_keys(zk.unsqueeze(0), self.srht_diagonal_signs,
+                        self.codebook_gpu[layer][b:b + 1, :, :, sl], self.key_block_weight_gpu[layer][b:b + 1, :, :, sl],
+                        self.key_4bit_packed_gpu[layer][b:b + 1, :, :, sl, :], cluster_counts=counts)
+        sk, sv = self._store_k[layer], self._store_v[layer]
+        if zk.stride(1) != 128:  # token-major source (prefill): make per-head rows contiguous first
+            zk, zv = zk.contiguous(), zv.contiguous()
+        for h in range(self.kv_head):  # contiguous per-head blocks: one async copy each, on the current stream
+            sk[b, h, sl].copy_(zk[h], non_blocking=True)
+            sv[b, h, sl].copy_(zv[h], non_blocking=True)
+
+    # ------------------------------------------------------------------------------------------------
+    # decode
+    # ------------------------------------------------------------------------------------------------
+    def decode_update_kv_cache(self, key_states, value_states, layer_idx):
+        """Append the step's K/V row ([bs, 1, H, 128]) to the window; flush the update buffer when full."""
+        pos = self._window_len[layer_idx]
+        self.unified_keys_gpu[layer_idx][:, :, pos] = key_states[:, 0]
+        self.unified_values_gpu[layer_idx][:, :, pos] = value_states[:, 0]
+        self._window_len[layer_idx] = pos + 1
+        self.current_seq_len[layer_idx] += 1
+        if layer_idx == 0:
+            self.context += 1
+        if self._window_len[layer_idx] == self.window_capacity:
+            self._flush(layer_idx)
+        return None, None
+
+    def _flush(self, layer):
+        """Move the oldest `interval` local rows into the zone (reference: _update_polar_index,
+        cache_hub/polar_cache.py:743-821, done here per layer and without blocking the host)."""
+        I, sink, local = self.dynamic_update_interval, self.sink_size, self.local_size
+        wk, wv = self.unified_keys_gpu[layer], self.unified_values_gpu[layer]
+        N = self.cpu_valid_end[layer]
+        assert N + I <= self.zone_capacity, "zone store is full"
+        for b in range(self.batch_size):
+            self._append_zone(layer, b, wk[b, :, sink:sink + I], wv[b, :, sink:sink + I], N, I)
+        # slide [sink+I, sink+local+I) down to [sink, sink+local)
+        if I < local:
+            tk, tv = self._slide_tmp_k[:, :, :local], self._slide_tmp_v[:, :, :local]
+            tk.copy_(wk[:, :, sink + I:sink + I + local])
+            tv.copy_(wv[:, :, sink + I:sink + I + local])
+            wk[:, :, sink:sink + local] = tk
+            wv[:, :, sink:sink + local] = tv
+        else:
+            wk[:, :, sink:sink + local] = wk[:, :, sink + I:sink + I + local]
+            wv[:, :, sink:sink + local] = wv[:, :, sink + I:sink + I + local]
+        self.cpu_valid_end[layer] = N + I
+        self._window_len[layer] = self.steady_size
+
+    # ------------------------------------------------------------------------------------------------
+    # attention
+    # ------------------------------------------------------------------------------------------------
+    def _get_adaptive_ratios(self, retrieval_len):
+        """(candidate_ratio, collision_ratio) by zone length: cache_hub/polar_cache.py:1113-1124."""
+        if retrieval_len < 5000:
+            return 0.5, 0.5
+        if retrieval_len < 10000:
+            return 0.25, 0.3
+        if retrieval_len < 30000:
+            return 0.2, 0.25
+        return 0.1, 0.2
+
+    def retrieval_plan(self, N):
+        """(tier thresholds, candidate count C, final K) for a zone of N keys
+        (cache_hub/polar_cache.py:1221-1222, :1239-1240, :1300)."""
+        cand_ratio, coll_ratio = self._get_adaptive_ratios(N)
+        tiers = [int(math.ceil(N * coll_ratio * r)) for r in TIER_RATIOS]
+        C = max(1, int(math.ceil(N * cand_ratio)))
+        return tiers, C, min(self.final_topk, C)
+
+    def compute(self, queries, layer_idx):
+        """Decode attention of one token: queries [bs, 1, num_heads, 128] -> [bs, 1, num_heads, 128]."""
+        queries = queries.contiguous()
+        N = self.cpu_valid_end[layer_idx]
+        n_win = self._window_len[layer_idx]
+        total = self.current_seq_len[layer_idx]
+        wk, wv = self.unified_keys_gpu[layer_idx], self.unified_values_gpu[layer_idx]
+        sk, sv = self._store_k[layer_idx], self._store_v[layer_idx]
+        full = total < max(self.FULL_ATTENTION_THRESHOLD, self.steady_size + 2 * self.final_topk) or N <= 0
+        if full:  # cache_hub/polar_cache.py:1033-1045: attend everything
+            if N <= 0:
+                return ops.sparse_attention(queries, wk, wv, n_win)
+            if self._all_rows is None or self._all_rows.shape[-1] < N:
+                self._all_rows = torch.arange(self.zone_capacity, device=self.device).expand(
+                    self.batch_size, self.kv_head, -1).contiguous()
+            sel = self._all_rows[:, :, :N].contiguous() if N != self._all_rows.shape[-1] else self._all_rows
+            return ops.sparse_attention(queries, wk, wv, n_win, sk, sv, sel)
+        tiers, C, K = self.retrieval_plan(N)
+        final, _ = ops.retrieve(queries, self.srht_diagonal_signs, self._mag_centers,
+                                self.codebook_gpu[layer_idx][:, :, :, :N], self.key_block_weight_gpu[layer_idx][:, :, :, :N],
+                                self.key_4bit_packed_gpu[layer_idx][:, :, :, :N, :], self.cluster_key_counts_gpu[layer_idx],
+                                tiers, C, K)
+        self.last_topk_indices = final
+        return ops.sparse_attention(queries, wk, wv, n_win, sk, sv, final)
+
+    def sync(self, layer_idx, batch_idx):
+        """No-op: copies to the zone store are ordered on the compute stream."""
+        return None

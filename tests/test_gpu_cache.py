@@ -1,0 +1,119 @@
+"""The cache class (prefill, append, flush, retrieval, attention) against a plain state machine built from
+the oracle: the searchable zone is token positions [sink, P - local + f*I), the window is the sink rows plus
+everything newer (reference invariants: cache_hub/polar_cache.py:645-699, :743-881, :1002-1107)."""
+import pytest
+import torch
+
+from conftest import synth_keys
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _make_cache(P, max_new, bs, H, Hq, sink, local, I, topk, offload, layers=2, thr=2000):
+    from pariskv_b200.cache_hub.polar_cache import polar_cache
+    return polar_cache(valid_start=[0] * bs, layer_num=layers, batch_size=bs, max_length=P + max_new,
+                       num_key_value_heads=H, num_heads=Hq, head_dim=128, dtype=torch.bfloat16,
+                       layer_mapping={str(i): DEV for i in range(layers)}, max_new_length=max_new, sink_size=sink,
+                       local_size=local, core=0, nprobe=0, cache_unit_size=0, cache_cluster_num=0, num_gpus=1,
+                       model_size=8, final_topk=topk, dynamic_update_interval=I, full_attention_threshold=thr,
+                       enable_offload=offload)
+
+
+def _oracle_step(oracle, cache, q, K_all, V_all, zone_end, layer):
+    """K_all / V_all: every token so far [bs,H,T,128] (CPU).  Returns (attention fp32, final indices or None)."""
+    sink = cache.sink_size
+    T = K_all.shape[2]
+    N = max(0, zone_end - sink)
+    signs = cache.srht_diagonal_signs.cpu()
+    win_idx = list(range(min(sink, T))) + list(range(max(zone_end, sink), T)) if N > 0 else list(range(T))
+    wk, wv = K_all[:, :, win_idx], V_all[:, :, win_idx]
+    full = T < max(cache.FULL_ATTENTION_THRESHOLD, cache.steady_size + 2 * cache.final_topk) or N <= 0
+    if full:
+        if N > 0:
+            wk = torch.cat([wk, K_all[:, :, sink:zone_end]], 2)
+            wv = torch.cat([wv, V_all[:, :, sink:zone_end]], 2)
+        return oracle.attention(q, wk, wv), None
+    zk, zv = K_all[:, :, sink:zone_end].contiguous(), V_all[:, :, sink:zone_end].contiguous()
+    cb, w, pk = oracle.encode(zk, signs)
+    tiers, C, K = cache.retrieval_plan(N)
+    _, coll = cache._get_adaptive_ratios(N)
+    assert tiers == oracle.tier_counts(N, coll)
+    r = oracle.retrieve(q, signs, cb, w, pk, oracle.cluster_counts(cb), cache._mag_centers.cpu(), coll, C, K)
+    att = oracle.attention(q, torch.cat([wk, oracle.gather(zk, r["final"])], 2),
+                           torch.cat([wv, oracle.gather(zv, r["final"])], 2))
+    return att, r["final"]
+
+
+@pytest.mark.parametrize("offload", [True, False])
+def test_cache_decode_matches_state_machine(oracle, offload):
+    g = torch.Generator().manual_seed(7)
+    bs, H, Hq, sink, local, I, topk, P, steps, layers = 2, 2, 8, 4, 16, 8, 32, 2100, 19, 2
+    cache = _make_cache(P, 64, bs, H, Hq, sink, local, I, topk, offload, layers)
+    Ks = [synth_keys(g, bs, H, P) for _ in range(layers)]
+    Vs = [torch.randn(bs, H, P, 128, generator=g).to(torch.bfloat16) for _ in range(layers)]
+    for l in range(layers):  # lockstep prefill: [bs, seq, H, 128]
+        k_in, v_in = Ks[l].transpose(1, 2).contiguous().to(DEV), Vs[l].transpose(1, 2).contiguous().to(DEV)
+        rk, rv = cache.prefill_update_kv_cache(None, k_in, v_in, l, 0)
+        assert rk.shape == k_in.shape
+    assert cache.context == P and cache.cpu_valid_end == [P - sink - local] * layers
+    flushed = 0
+    for t in range(steps):
+        for l in range(layers):
+            nk = synth_keys(g, bs, H, 1)
+            nv = torch.randn(bs, H, 1, 128, generator=g).to(torch.bfloat16)
+            Ks[l] = torch.cat([Ks[l], nk], 2)
+            Vs[l] = torch.cat([Vs[l], nv], 2)
+            cache.decode_update_kv_cache(nk.transpose(1, 2).contiguous().to(DEV), nv.transpose(1, 2).contiguous().to(DEV), l)
+            q = (torch.randn(bs, 1, Hq, 128, generator=g) * 0.5).to(torch.bfloat16)
+            out = cache.compute(q.to(DEV), l)
+            f = (t + 1) // I
+            zone_end = P - local + f * I
+            ref, fin = _oracle_step(oracle, cache, q, Ks[l], Vs[l], zone_end, l)
+            assert cache.cpu_valid_end[l] == zone_end - sink
+            assert torch.equal(cache.last_topk_indices.cpu(), fin), f"step {t} layer {l}: retrieved set differs"
+            err = (out.float().cpu() - ref).abs().max().item()
+            assert err <= 2e-2, (t, l, err)
+        flushed = (t + 1) // I
+    assert flushed == 2 and cache.context == P + steps
+    # metadata of the flushed keys equals a fresh encode of the same token positions
+    zone = Ks[0][:, :, sink:P - local + 2 * I].contiguous()
+    cb, w, pk = oracle.encode(zone, cache.srht_diagonal_signs.cpu())
+    N = zone.shape[2]
+    assert torch.equal(cache.codebook_gpu[0][:, :, :, :N].cpu(), cb)
+    assert torch.equal(cache.key_4bit_packed_gpu[0][:, :, :, :N].cpu(), pk)
+    assert torch.equal(cache.cluster_key_counts_gpu[0].cpu(), oracle.cluster_counts(cb))
+
+
+def test_cache_short_prompt_dense_path(oracle):
+    g = torch.Generator().manual_seed(3)
+    bs, H, Hq, sink, local, I, topk = 1, 2, 8, 4, 8, 4, 16
+    cache = _make_cache(10, 40, bs, H, Hq, sink, local, I, topk, True, layers=1)
+    K = synth_keys(g, bs, H, 10)
+    V = torch.randn(bs, H, 10, 128, generator=g).to(torch.bfloat16)
+    cache.prefill_update_kv_cache(None, K.transpose(1, 2).contiguous().to(DEV), V.transpose(1, 2).contiguous().to(DEV), 0, 0)
+    for t in range(14):  # crosses steady (12) and two flushes of 4
+        nk, nv = synth_keys(g, bs, H, 1), torch.randn(bs, H, 1, 128, generator=g).to(torch.bfloat16)
+        K, V = torch.cat([K, nk], 2), torch.cat([V, nv], 2)
+        cache.decode_update_kv_cache(nk.transpose(1, 2).contiguous().to(DEV), nv.transpose(1, 2).contiguous().to(DEV), 0)
+        q = torch.randn(bs, 1, Hq, 128, generator=g).to(torch.bfloat16)
+        out = cache.compute(q.to(DEV), 0)
+        ref = oracle.attention(q, K, V)  # short context: dense attention over every token
+        assert (out.float().cpu() - ref).abs().max().item() <= 2e-2, t
+    assert cache.cpu_valid_end[0] == 12 and cache._window_len[0] == 12
+
+
+def test_dropin_names_resolve():
+    import pariskv_b200.dropin as dropin
+    dropin.install(force=True)
+    from attn_hub import polar_decode_attn, polar_prefill_attn  # noqa: F401
+    from cache_hub.polar_cache import polar_cache
+    assert polar_cache.__module__ == "pariskv_b200.cache_hub.polar_cache"
+    from cache_hub.topk import load_radix_topk_ext
+    x = torch.randint(0, 97, (1, 2, 500), dtype=torch.int32, device=DEV)
+    idx = load_radix_topk_ext().radix_topk_3d(x, 50)
+    assert idx.shape == (1, 2, 50) and idx.dtype == torch.int64
+    q = torch.randn(1, 5, 8, 128, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(1, 5, 2, 128, device=DEV, dtype=torch.bfloat16)
+    out = polar_prefill_attn(q, k, k, causal=True)
+    assert out.shape == q.shape
