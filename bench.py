@@ -1,0 +1,446 @@
+#!/usr/bin/env python
+"""Decode benchmark of the ParisKV retrieval path on B200.
+
+Workload (the 128K-context configuration): Qwen3-8B architecture (36 layers, hidden 4096, 32 query /
+8 KV heads, head_dim 128, SwiGLU 12288, RMSNorm, per-head q/k norm, RoPE), random-init bf16 weights,
+batch 1, 131072 prefilled tokens with synthetic keys (N(0,1), four channels x8, lognormal norms), sink 4,
+local 64, update buffer 128, top-k 2048, full K/V in pinned host memory read through UVA.  One step is one
+decode token through all layers: dense projections by torch/cuBLAS (harness), K/V append, retrieval chain and
+sparse attention by this repository's CUDA library through its cache class.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  `value` is decode tokens/s with the token fed back on the device; `e2e` is
+the same loop driven from the host: every step copies the token id from pinned host memory and reads the next
+token back.  `--impl reference` times the CPU restatement of the reference's retrieval path (oracle/) on the
+host cores instead; see the `sample` field for what one step covers.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG = dict(layers=36, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=12288, vocab=151936,
+           rope_theta=1.0e6, context=131072, sink=4, local=64, interval=128, topk=2048)
+OUTLIERS = (7, 37, 71, 101)
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------------------------------------
+# the model harness (dense part: library GEMMs; not the product)
+# --------------------------------------------------------------------------------------------------------
+class DecoderHarness:
+    def __init__(self, cfg, device, seed):
+        g = torch.Generator(device=device).manual_seed(seed)
+        L, Hd, Hq, Hk, D, Ff, V = (cfg[k] for k in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab"))
+        self.cfg, self.device = cfg, device
+
+        def w(*shape, std=0.02):
+            return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
+
+        self.embed = w(V, Hd)
+        self.lm_head = w(V, Hd)
+        self.wqkv = [w((Hq + 2 * Hk) * D, Hd) for _ in range(L)]
+        self.wo = [w(Hd, Hq * D) for _ in range(L)]
+        self.wgu = [w(2 * Ff, Hd) for _ in range(L)]
+        self.wd = [w(Hd, Ff) for _ in range(L)]
+        ones = lambda n: torch.ones(n, device=device, dtype=torch.bfloat16)
+        self.ln1 = [ones(Hd) for _ in range(L)]
+        self.ln2 = [ones(Hd) for _ in range(L)]
+        self.qn = [ones(D) for _ in range(L)]
+        self.kn = [ones(D) for _ in range(L)]
+        self.lnf = ones(Hd)
+        self._inv_freq = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, D, 2, device=device, dtype=torch.float32) / D))
+
+    @staticmethod
+    def rope(x, cos, sin):
+        """x [1, heads, 128]; rotate-half RoPE with the step's cos / sin [64]."""
+        x1, x2 = x[..., :64].float(), x[..., 64:].float()
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).to(torch.bfloat16)
+
+    def step(self, cache, token):
+        """One decode token through all layers; token: int64 [1] on the device.  Returns next token [1]."""
+        c = self.cfg
+        Hq, Hk, D = c["q_heads"], c["kv_heads"], c["head_dim"]
+        ang = cache.context * self._inv_freq
+        cos, sin = torch.cos(ang), torch.sin(ang)
+        h = self.embed[token]                                   # [1, hidden]
+        for l in range(c["layers"]):
+            x = F.rms_norm(h, (c["hidden"],), self.ln1[l], 1e-6)
+            qkv = F.linear(x, self.wqkv[l])
+            q = qkv[:, :Hq * D].view(1, Hq, D)
+            k = qkv[:, Hq * D:(Hq + Hk) * D].view(1, Hk, D)
+            v = qkv[:, (Hq + Hk) * D:].view(1, 1, Hk, D)
+            q = self.rope(F.rms_norm(q, (D,), self.qn[l], 1e-6), cos, sin)
+            k = self.rope(F.rms_norm(k, (D,), self.kn[l], 1e-6), cos, sin)
+            cache.decode_update_kv_cache(k.view(1, 1, Hk, D), v, l)
+            attn = cache.compute(q.view(1, 1, Hq, D), l)
+            h = h + F.linear(attn.view(1, Hq * D), self.wo[l])
+            x = F.rms_norm(h, (c["hidden"],), self.ln2[l], 1e-6)
+            gu = F.linear(x, self.wgu[l])
+            h = h + F.linear(F.silu(gu[:, :c["ffn"]]) * gu[:, c["ffn"]:], self.wd[l])
+        logits = F.linear(F.rms_norm(h, (c["hidden"],), self.lnf, 1e-6), self.lm_head)
+        return logits.argmax(-1)
+
+
+def synth_kv(gen, P, H, device):
+    """Synthetic prefilled keys / values [1, P, H, 128] in bf16 with the benchmark's key distribution."""
+    z = torch.randn(1, P, H, 128, generator=gen, device=device, dtype=torch.float32)
+    z[..., list(OUTLIERS)] *= 8.0
+    z *= torch.exp(0.5 * torch.randn(1, P, H, 1, generator=gen, device=device, dtype=torch.float32))
+    v = torch.randn(1, P, H, 128, generator=gen, device=device, dtype=torch.float32)
+    return z.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
+def build_cache(cfg, device, max_new, seed):
+    from pariskv_b200.cache_hub.polar_cache import polar_cache
+    P = cfg["context"]
+    cache = polar_cache(valid_start=[0], layer_num=cfg["layers"], batch_size=1, max_length=P + max_new,
+                        num_key_value_heads=cfg["kv_heads"], num_heads=cfg["q_heads"], head_dim=cfg["head_dim"],
+                        dtype=torch.bfloat16, layer_mapping={str(i): str(device) for i in range(cfg["layers"])},
+                        max_new_length=max_new, sink_size=cfg["sink"], local_size=cfg["local"], core=0, nprobe=0,
+                        cache_unit_size=0, cache_cluster_num=0, num_gpus=1, model_size=8, final_topk=cfg["topk"],
+                        dynamic_update_interval=cfg["interval"], enable_offload=True)
+    g = torch.Generator(device=device).manual_seed(seed)
+    for l in range(cfg["layers"]):
+        k, v = synth_kv(g, P, cfg["kv_heads"], device)
+        cache.prefill_update_kv_cache(None, k, v, l, 0)
+        del k, v
+    torch.cuda.synchronize(device)
+    return cache
+
+
+# --------------------------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 6 or not f[0].isdigit():
+                continue
+            mhz.append(int(f[0]))
+            mx = int(f[1])
+            for n, val in zip(names, f[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# --------------------------------------------------------------------------------------------------------
+# CPU baseline: the oracle's restatement of the reference path, one layer-step at a time
+# --------------------------------------------------------------------------------------------------------
+def cpu_layer_state(cfg, n_layers, seed):
+    """Zone metadata and K/V of n_layers layers at the benchmark's sizes, built on the CPU by the oracle."""
+    from oracle import oracle as O
+    P, H = cfg["context"], cfg["kv_heads"]
+    N = P - cfg["sink"] - cfg["local"]
+    g = torch.Generator().manual_seed(seed)
+    signs = torch.randint(0, 2, (128,), generator=g).to(torch.bfloat16) * 2 - 1
+    layers = []
+    for _ in range(n_layers):
+        z = torch.randn(1, H, N, 128, generator=g)
+        z[..., list(OUTLIERS)] *= 8.0
+        z *= torch.exp(0.5 * torch.randn(1, H, N, 1, generator=g))
+        keys = z.to(torch.bfloat16)
+        vals = torch.randn(1, H, N, 128, generator=g).to(torch.bfloat16)
+        cb, w, pk = O.encode(keys, signs)
+        layers.append(dict(keys=keys, vals=vals, cb=cb, w=w, pk=pk, counts=O.cluster_counts(cb)))
+    win = cfg["sink"] + cfg["local"] + cfg["interval"] // 2
+    wk = torch.randn(1, H, win, 128, generator=g).to(torch.bfloat16)
+    wv = torch.randn(1, H, win, 128, generator=g).to(torch.bfloat16)
+    return signs, layers, wk, wv, g
+
+
+def cpu_layer_step(cfg, signs, st, wk, wv, q):
+    """Retrieval chain + gather + attention of one layer and one token on the CPU (oracle)."""
+    from oracle import oracle as O
+    N = st["cb"].shape[3]
+    cand_ratio, coll_ratio = O.adaptive_ratios(N)
+    C = O.candidate_len(N, cand_ratio)
+    _, cen = O.constants()
+    r = O.retrieve(q, signs, st["cb"], st["w"], st["pk"], st["counts"], cen, coll_ratio, C, cfg["topk"])
+    k = torch.cat([wk, O.gather(st["keys"], r["final"])], 2)
+    v = torch.cat([wv, O.gather(st["vals"], r["final"])], 2)
+    return O.attention(q, k, v)
+
+
+def run_cpu_baseline(cfg, budget_s, seed=0, n_layers=2):
+    signs, layers, wk, wv, g = cpu_layer_state(cfg, n_layers, seed)
+    q = torch.randn(1, 1, cfg["q_heads"], 128, generator=g).to(torch.bfloat16)
+    cpu_layer_step(cfg, signs, layers[0], wk, wv, q)  # warm
+    t0, n = time.perf_counter(), 0
+    while True:
+        cpu_layer_step(cfg, signs, layers[n % n_layers], wk, wv, q)
+        n += 1
+        if time.perf_counter() - t0 > budget_s or n >= 200:
+            break
+    per_layer = (time.perf_counter() - t0) / n
+    return per_layer, n
+
+
+def reference_arm(args, rank):
+    """Times the CPU restatement of the reference's retrieval path (oracle/, OpenMP on all host cores)."""
+    if rank != 0:
+        return
+    cfg = CFG
+    torch.set_num_threads(os.cpu_count() or 1)
+    signs, layers, wk, wv, g = cpu_layer_state(cfg, 2, 0)
+    q = torch.randn(1, 1, cfg["q_heads"], 128, generator=g).to(torch.bfloat16)
+    sample_layers = 4  # one timed "step" = 4 layer-steps; a token is 36 of them
+    for _ in range(max(args.warmup, 1)):
+        cpu_layer_step(cfg, signs, layers[0], wk, wv, q)
+    steps = min(args.steps, 24)
+    t0 = time.perf_counter()
+    for s in range(steps):
+        for i in range(sample_layers):
+            cpu_layer_step(cfg, signs, layers[(s + i) % 2], wk, wv, q)
+    el = time.perf_counter() - t0
+    per_layer = el / (steps * sample_layers)
+    tok_s = 1.0 / (per_layer * cfg["layers"])
+    cores = os.cpu_count() or 1
+    sample = (f"{steps} steps x {sample_layers} layer-steps of the retrieval chain + row gather + attention at N="
+              f"{cfg['context'] - cfg['sink'] - cfg['local']} keys/head (oracle C port, OpenMP); tokens/s = 1 / (36 x "
+              "mean layer-step); the dense projections of the model are NOT included, which favours this arm")
+    line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": per_layer * cfg["layers"] * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "decode step, Qwen3-8B architecture, batch 1, 131072-token context, sink 4 / local 64 / "
+                        "update buffer 128, top-k 2048 per KV head, K/V in pinned host memory (UVA), random-init bf16",
+            "layers": CFG["layers"], "context": CFG["context"], "topk": CFG["topk"],
+            "sharding": "one independent sequence per GPU (replicas)" if n_gpus > 1 else "single GPU",
+            "l2": "inputs larger than L2: 16.4 GB of weights and 36 x 16.8 MB of codes are streamed every step"}
+
+
+# --------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
+    ap.add_argument("--stage-steps", type=int, default=16, help="extra steps with per-kernel event timing")
+    ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the line invalid)")
+    ap.add_argument("--context", type=int, default=None, help="debug only: shorter context (marks the line invalid)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the CUDA library has no CPU fallback")
+    args.warmup = max(args.warmup, 3)
+    cfg = dict(CFG)
+    debug = False
+    if args.layers:
+        cfg["layers"], debug = args.layers, True
+    if args.context:
+        cfg["context"], debug = args.context, True
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    from pariskv_b200 import _lib
+    from pariskv_b200.build import build
+    build()
+    _lib.load()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    K, W, S = args.steps, args.warmup, args.stage_steps
+    max_new = W + 2 * K + S + 2 * cfg["interval"] + 8
+    t_setup = time.time()
+    model = DecoderHarness(cfg, device, seed=1234)
+    cache = build_cache(cfg, device, max_new, seed=100 + rank)
+    setup_s = time.time() - t_setup
+    token = torch.tensor([11], device=device)
+
+    # ---- warm-up ----
+    for _ in range(W):
+        token = model.step(cache, token)
+    barrier()
+
+    # ---- timed region 1: device-resident loop ----
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = _lib.launch_count()
+    barrier()
+    e0.record()
+    for _ in range(K):
+        token = model.step(cache, token)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop()
+
+    # ---- timed region 2: host-driven loop (token id in from pinned host memory, next token out) ----
+    tok_in = torch.empty(1, dtype=torch.int64).pin_memory()
+    tok_out = torch.empty(1, dtype=torch.int64).pin_memory()
+    tok_in[0] = int(token.item())
+    dev_tok = torch.empty(1, dtype=torch.int64, device=device)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(K):
+        dev_tok.copy_(tok_in, non_blocking=True)
+        nxt = model.step(cache, dev_tok)
+        tok_out.copy_(nxt, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        tok_in[0] = tok_out[0]
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+
+    # ---- per-kernel event timing on extra steps (not part of either headline number) ----
+    stage = {}
+    if S > 0:
+        _lib.timing_enable(True)
+        for _ in range(S):
+            token = model.step(cache, token)
+        torch.cuda.synchronize(device)
+        stage = _lib.timing_read()
+        _lib.timing_enable(False)
+
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = load_peaks()
+    H, Lyr = cfg["kv_heads"], cfg["layers"]
+    N = cache.cpu_valid_end[0]
+    tiers, C, Kf = cache.retrieval_plan(N)
+    n_rows = cfg["sink"] + cfg["local"] + cfg["interval"] // 2 + Kf
+    alg = {  # algorithmic bytes per launch (one layer, all KV heads): codes + counts; candidates; rows
+        "collision": 20 * N * H,
+        "select_rerank": (4 * N + 8 * C + 106 * C) * H,
+        "final_topk": (10 * C + 8 * Kf) * H,
+        "attention": n_rows * 512 * H,
+    }
+    stages_out = {}
+    for name, (tot_ms, cnt) in stage.items():
+        us = tot_ms * 1e3 / cnt
+        ent = {"avg_us": round(us, 3), "launches": cnt}
+        if name in alg:
+            ent["algorithmic_bytes"] = alg[name]
+            ent["achieved_gbs"] = round(alg[name] / (us * 1e-6) / 1e9, 1)
+        stages_out[name] = ent
+    retrieval_us = sum(stages_out.get(s, {}).get("avg_us", 0.0) for s in
+                       ("query_prep", "rank_table", "collision", "select_rerank", "final_topk"))
+    coll = stages_out.get("collision", {})
+    roofline = {"kernel": "collision_kernel (weighted multi-tier collision count)", "bound": "hbm",
+                "achieved": coll.get("achieved_gbs"), "peak": peak, "unit": "GB/s",
+                "frac": round(coll["achieved_gbs"] / peak, 4) if coll else None, "peak_kind": f"of {peak_kind}",
+                "traffic": None, "algorithmic_bytes_per_launch": alg["collision"]}
+    att = stages_out.get("attention", {})
+    host_link = {"kernel": "sparse_attention_kernel (UVA fetch of the selected K/V rows fused with attention)",
+                 "bytes_per_launch_over_host_link": Kf * 512 * H,
+                 "achieved_gbs": round(Kf * 512 * H / (att["avg_us"] * 1e-6) / 1e9, 2) if att else None,
+                 "reference_peak_gbs": 55.6, "reference_peak_kind": "pinned cudaMemcpyAsync H2D measured on this pool"}
+
+    cpu = None
+    if world == 1 or True:
+        try:
+            per_layer, n = run_cpu_baseline(CFG if not debug else cfg, args.cpu_baseline_seconds)
+            cpu = {"value": 1.0 / (per_layer * Lyr), "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+                   "sample": f"{n} layer-steps (retrieval chain + row gather + attention, N={N} keys/head) by the "
+                             "oracle's C port with OpenMP; tokens/s = 1 / (layers x mean layer-step); dense "
+                             "projections excluded"}
+        except Exception as e:  # the baseline is reporting only: never fail the bench on it
+            cpu = {"value": None, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+                   "sample": f"failed: {type(e).__name__}: {e}"}
+
+    line = {
+        "metric": "decode_tokens_per_s", "value": world * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+        "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "clocks": clocks,
+        "e2e": {"value": world * K / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8,
+                "ms_per_step": ms_e2e / K},
+        "gpu_launches": int(launches),
+        "roofline": roofline, "host_link": host_link, "stages": stages_out,
+        "retrieval_us_per_step_per_layer": round(retrieval_us, 2),
+        "cpu_baseline": cpu,
+        "published_reference": {"decode_tok_s_128k_bs1": 41.10, "note": "hardware and model unstated by the reference"},
+        "setup_s": round(setup_s, 1), "zone_keys_per_head": N, "candidates": C, "final_topk": Kf,
+    }
+    if debug:
+        line["invalid"] = "debug run with reduced layers/context"
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

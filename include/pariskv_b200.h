@@ -51,6 +51,14 @@ const char* pk_last_error(void);
 /* Number of kernels launched by this library in this process (all threads). */
 int64_t pk_launch_count(void);
 
+/* Optional instrumentation, no counterpart in the reference: when enabled, every kernel launch of the
+ * decode path is bracketed by CUDA events on its own stream.  pk_timing_read waits for the recorded
+ * events, sums elapsed milliseconds and launch counts per stage (stage ids: 0 query prep, 1 cluster
+ * ranking/table, 2 collision, 3 select+rerank, 4 final top-k, 5 attention tiles, 6 attention merge,
+ * 7 encode, 8 stand-alone top-k, 9 stand-alone rerank, 10 UVA gather) and clears the record. */
+int pk_timing_enable(int on);
+int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages);
+
 /* ---- (a) key coding ---------------------------------------------------------------------- */
 
 /* SRHT normalise-rotate + 8-bit sign code + 4-bit (sign | 3-bit level) code + fused rerank weight

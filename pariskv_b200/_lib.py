@@ -32,6 +32,8 @@ SIGNATURES = {
     "pk_version": (_INT, []),
     "pk_last_error": (ctypes.c_char_p, []),
     "pk_launch_count": (_I64, []),
+    "pk_timing_enable": (_INT, [_INT]),
+    "pk_timing_read": (_INT, [ctypes.POINTER(ctypes.c_double), _I64P, _INT]),
     "pk_encode_keys": (_INT, [TP, TP, TP, TP, TP, TP, _VP]),
     "pk_count_clusters": (_INT, [TP, TP, _INT, _VP]),
     "pk_query_prep": (_INT, [TP, TP, TP, TP, TP, _VP]),
@@ -112,3 +114,20 @@ def i64_array(values):
 
 def launch_count() -> int:
     return int(load().pk_launch_count())
+
+
+STAGES = ["query_prep", "rank_table", "collision", "select_rerank", "final_topk", "attention", "attention_merge",
+          "encode", "topk", "rerank", "uva_gather", "count_clusters"]
+
+
+def timing_enable(on: bool):
+    check(load().pk_timing_enable(int(bool(on))))
+
+
+def timing_read():
+    """-> {stage: (total_ms, launches)} for every stage recorded since the last read."""
+    n = len(STAGES)
+    ms = (ctypes.c_double * n)()
+    cnt = (ctypes.c_int64 * n)()
+    check(load().pk_timing_read(ms, cnt, n))
+    return {STAGES[i]: (float(ms[i]), int(cnt[i])) for i in range(n) if cnt[i]}

@@ -279,9 +279,14 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
   p.ws = (float*)workspace;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((unsigned)n_tiles, (unsigned)(H * p.n_qgroups), (unsigned)bs);
-  sparse_attention_kernel<<<grid, ATT_THREADS, 2 * ATT_TILE * 256, st>>>(p);
-  int rc = check_launch("sparse_attention");
+  int rc;
+  {
+    StageTimer tm(ST_ATTENTION, st);
+    sparse_attention_kernel<<<grid, ATT_THREADS, 2 * ATT_TILE * 256, st>>>(p);
+    rc = check_launch("sparse_attention");
+  }
   if (rc) return rc;
+  StageTimer tm(ST_ATTENTION_MERGE, st);
   attention_merge_kernel<<<(unsigned)(bs * Hq), 128, 0, st>>>(p.ws, n_tiles, (uint16_t*)out->data);
   return check_launch("attention_merge");
 }

@@ -283,6 +283,7 @@ int64_t collision_chunk_keys(int64_t bs_h, int64_t Nv) {
 
 int launch_rank(const uint16_t* q_blocks, const int32_t* counts, const int64_t* tier_counts, int n_tiers,
                 int64_t bs_h, uint32_t* lut, int64_t* sorted_ids, cudaStream_t st) {
+  StageTimer tm(ST_RANK, st);
   rank_kernel<<<(unsigned)(bs_h * 16), 256, 0, st>>>(q_blocks, counts, make_tiers(tier_counts, n_tiers), lut,
                                                      sorted_ids);
   return check_launch("rank_clusters");
@@ -321,6 +322,7 @@ int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* ou
   dim3 grid((unsigned)n_chunks, (unsigned)(bs * H));
   const size_t smem = (size_t)(B * 32 + 256) * 4;
   const bool u8 = counts_u8 != nullptr;
+  StageTimer tm(ST_COLLISION, st);
 #define PK_LAUNCH_COLL(L, U) collision_kernel<L, U><<<grid, 256, smem, st>>>(p)
   if (layout == 0) {
     if (u8) PK_LAUNCH_COLL(0, true); else PK_LAUNCH_COLL(0, false);
@@ -389,13 +391,17 @@ extern "C" int pk_collision_fused(const pk_tensor* sorted_cluster_ids, const pk_
   uint32_t* lut = (uint32_t*)workspace;
   Tiers tiers = make_tiers(tier_counts, n_tiers);
   const unsigned nblk = (unsigned)(bs * H * B);
-  if (sorted_cluster_ids->dtype == PK_I64)
-    lut_from_sorted_kernel<int64_t><<<nblk, 256, 0, st>>>((const int64_t*)sorted_cluster_ids->data,
-                                                          (const int32_t*)cluster_key_counts->data, (int)NC, tiers, lut);
-  else
-    lut_from_sorted_kernel<int32_t><<<nblk, 256, 0, st>>>((const int32_t*)sorted_cluster_ids->data,
-                                                          (const int32_t*)cluster_key_counts->data, (int)NC, tiers, lut);
-  int rc = check_launch("collision table");
+  int rc;
+  {
+    StageTimer tm(ST_RANK, st);
+    if (sorted_cluster_ids->dtype == PK_I64)
+      lut_from_sorted_kernel<int64_t><<<nblk, 256, 0, st>>>((const int64_t*)sorted_cluster_ids->data,
+                                                            (const int32_t*)cluster_key_counts->data, (int)NC, tiers, lut);
+    else
+      lut_from_sorted_kernel<int32_t><<<nblk, 256, 0, st>>>((const int32_t*)sorted_cluster_ids->data,
+                                                            (const int32_t*)cluster_key_counts->data, (int)NC, tiers, lut);
+    rc = check_launch("collision table");
+  }
   if (rc) return rc;
   return launch_collision(codebook, lut, (int32_t*)cache_cnt->data, nullptr, 0, nullptr, nullptr, nullptr, nullptr, st);
 }

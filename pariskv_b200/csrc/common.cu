@@ -2,6 +2,8 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -24,6 +26,36 @@ int check_launch(const char* what, int n_kernels) {
   return PK_OK;
 }
 
+// ---- optional per-stage timing with CUDA events (off by default) ----
+namespace {
+struct Span { int stage; cudaEvent_t a, b; };
+constexpr int kMaxSpans = 1 << 16;
+std::mutex g_tmu;
+bool g_timing = false;
+std::vector<Span> g_spans;       // recorded since the last read
+std::vector<cudaEvent_t> g_pool; // reusable events
+cudaEvent_t take_event() {
+  if (!g_pool.empty()) { cudaEvent_t e = g_pool.back(); g_pool.pop_back(); return e; }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+}  // namespace
+
+StageTimer::StageTimer(int stage, cudaStream_t st) : stage_(stage), st_(st), a_(nullptr), on_(false) {
+  if (!g_timing) return;
+  std::lock_guard<std::mutex> lk(g_tmu);
+  if ((int)g_spans.size() >= kMaxSpans) return;
+  a_ = take_event();
+  if (a_ && cudaEventRecord(a_, st_) == cudaSuccess) on_ = true;
+}
+StageTimer::~StageTimer() {
+  if (!on_) return;
+  std::lock_guard<std::mutex> lk(g_tmu);
+  cudaEvent_t b = take_event();
+  if (b && cudaEventRecord(b, st_) == cudaSuccess) g_spans.push_back({stage_, a_, b});
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -41,4 +73,27 @@ extern "C" {
 int pk_version(void) { return 1; }
 const char* pk_last_error(void) { return pk::g_err; }
 int64_t pk_launch_count(void) { return pk::g_launches.load(std::memory_order_relaxed); }
+
+int pk_timing_enable(int on) {
+  std::lock_guard<std::mutex> lk(pk::g_tmu);
+  pk::g_timing = on != 0;
+  return PK_OK;
+}
+
+int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages) {
+  std::lock_guard<std::mutex> lk(pk::g_tmu);
+  for (int i = 0; i < n_stages; i++) ms_per_stage[i] = 0.0, spans_per_stage[i] = 0;
+  for (auto& s : pk::g_spans) {
+    float ms = 0.0f;
+    if (cudaEventSynchronize(s.b) == cudaSuccess && cudaEventElapsedTime(&ms, s.a, s.b) == cudaSuccess &&
+        s.stage >= 0 && s.stage < n_stages) {
+      ms_per_stage[s.stage] += ms;
+      spans_per_stage[s.stage] += 1;
+    }
+    pk::g_pool.push_back(s.a);
+    pk::g_pool.push_back(s.b);
+  }
+  pk::g_spans.clear();
+  return PK_OK;
+}
 }

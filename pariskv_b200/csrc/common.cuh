@@ -13,6 +13,22 @@ int fail(int code, const char* fmt, ...);
 int check_launch(const char* what, int n_kernels = 1);
 int sm_count();
 
+// Stages of the decode path, for the optional event timing (pk_timing_enable / pk_timing_read).
+enum Stage { ST_QUERY_PREP = 0, ST_RANK = 1, ST_COLLISION = 2, ST_SELECT_RERANK = 3, ST_FINAL_TOPK = 4,
+             ST_ATTENTION = 5, ST_ATTENTION_MERGE = 6, ST_ENCODE = 7, ST_TOPK = 8, ST_RERANK = 9, ST_GATHER = 10,
+             ST_COUNT = 11 };
+// Records one event before and one after the launches issued during its lifetime, on the launch stream.
+class StageTimer {
+ public:
+  StageTimer(int stage, cudaStream_t st);
+  ~StageTimer();
+ private:
+  int stage_;
+  cudaStream_t st_;
+  cudaEvent_t a_;
+  bool on_;
+};
+
 #define PK_REQUIRE(cond, ...)                               \
   do {                                                      \
     if (!(cond)) return pk::fail(PK_ERR_ARG, __VA_ARGS__);  \

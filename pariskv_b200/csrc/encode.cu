@@ -214,6 +214,7 @@ __global__ void __launch_bounds__(32) query_prep_kernel(const uint16_t* queries,
 int launch_query_prep(const uint16_t* queries, int bs, int Hq, int H, const uint16_t* signs,
                       uint16_t* q_blocks, uint16_t* q_norm, uint16_t* query_avg, cudaStream_t st) {
   const int G = Hq / H;
+  StageTimer tm(ST_QUERY_PREP, st);
   query_prep_kernel<<<bs * H, 32, 0, st>>>(queries, Hq, H, G, 1.0f / (float)G, signs, q_blocks, q_norm,
                                            query_avg);
   return check_launch("query_prep");
@@ -278,6 +279,7 @@ extern "C" int pk_encode_keys(const pk_tensor* keys, const pk_tensor* signs, con
   if (chunk > 2048) chunk = 2048;
   p.chunk = chunk;
   dim3 grid((unsigned)((L + chunk - 1) / chunk), (unsigned)(bs * H));
+  StageTimer tm(ST_ENCODE, (cudaStream_t)stream);
   encode_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(p);
   return check_launch("encode_keys");
 }
@@ -302,6 +304,7 @@ extern "C" int pk_count_clusters(const pk_tensor* codebook, const pk_tensor* cou
   if (chunk < 256) chunk = 256;
   if (chunk > 8192) chunk = 8192;
   dim3 grid((unsigned)((N + chunk - 1) / chunk), (unsigned)(bs * H));
+  StageTimer tm(ST_COUNT, st);
   count_kernel<<<grid, 256, (size_t)B * 256 * 4, st>>>((const uint8_t*)codebook->data, codebook->stride[0],
                                                        codebook->stride[1], codebook->stride[2],
                                                        codebook->stride[3], (int)H, (int)B, N, chunk,

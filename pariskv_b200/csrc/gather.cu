@@ -87,6 +87,7 @@ extern "C" int pk_h2d_gather_kv(const pk_tensor* src_k, const pk_tensor* src_v, 
   int64_t blocks = (rows + 7) / 8;
   const int64_t cap = (int64_t)sm_count() * 8;
   if (blocks > cap) blocks = cap;
+  StageTimer tm(ST_GATHER, (cudaStream_t)stream);
   h2d_gather_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
       (const uint4*)src_k->data, (const uint4*)src_v->data, (const int64_t*)selected_indices->data, (uint4*)dst_k->data,
       (uint4*)dst_v->data, bs * H, N, dst_k->shape[2], K);

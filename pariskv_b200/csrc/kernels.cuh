@@ -21,7 +21,7 @@ int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* ou
 
 // topk.cu: exact top-k of rows of 32-bit values; out[row][i] = map ? map[row*map_stride + pos] : pos
 int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride, int64_t L, int64_t k,
-                int64_t* out, const int64_t* map, int64_t map_stride, int order, cudaStream_t st);
+                int64_t* out, const int64_t* map, int64_t map_stride, int order, cudaStream_t st, int stage);
 
 // rerank.cu
 struct RerankArgs {

@@ -266,6 +266,7 @@ int launch_rerank(const RerankArgs& a, int64_t bs_h, uint16_t* scores_bf16, floa
                   cudaStream_t st) {
   int64_t gx = (a.C + RR_THREADS - 1) / RR_THREADS;
   dim3 grid((unsigned)gx, (unsigned)bs_h);
+  StageTimer tm(ST_RERANK, st);
   if (rerank_fast_layout(a))
     rerank_kernel<true><<<grid, RR_THREADS, 0, st>>>(a, scores_bf16, scores_f32, v4b);
   else
@@ -288,6 +289,7 @@ int launch_select_rerank(const RerankArgs& a, int64_t bs_h, const uint8_t* count
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return check_launch("select_rerank smem");
   }
+  StageTimer tm(ST_SELECT_RERANK, st);
   kern<<<grid, SEL_THREADS, smem, st>>>(a, p);
   return check_launch("select_rerank");
 }

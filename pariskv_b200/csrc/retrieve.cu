@@ -127,5 +127,5 @@ extern "C" int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, con
   ra.C = C;
   if ((rc = launch_select_rerank(ra, bh, counts, lay.u8_stride, hist, n_chunks, chunk_keys, mis, N, cd, sc, st)))
     return rc;
-  return launch_topk(sc, true, bh, C, C, K, (int64_t*)final_indices->data, cd, C, 0, st);
+  return launch_topk(sc, true, bh, C, C, K, (int64_t*)final_indices->data, cd, C, 0, st, ST_FINAL_TOPK);
 }

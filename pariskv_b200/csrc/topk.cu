@@ -221,7 +221,8 @@ __global__ void __launch_bounds__(1024) sort_by_value_kernel(const uint32_t* in,
 }  // namespace
 
 int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride, int64_t L, int64_t k,
-                int64_t* out, const int64_t* map, int64_t map_stride, int order, cudaStream_t st) {
+                int64_t* out, const int64_t* map, int64_t map_stride, int order, cudaStream_t st, int stage) {
+  StageTimer tm(stage, st);
   TopkParams p;
   p.in = (const uint32_t*)in;
   p.is_float = is_float ? 1 : 0;
@@ -278,7 +279,7 @@ extern "C" int pk_topk(const pk_tensor* input, int64_t k, const pk_tensor* out, 
   PK_REQUIRE(order == 0 || (order == 1 && k <= 4096), "order 1 (sorted by value) needs k <= 4096");
   if (rows == 0) return PK_OK;
   return launch_topk(input->data, input->dtype == PK_F32, rows, input->stride[0], L, k, (int64_t*)out->data, nullptr,
-                     0, order, (cudaStream_t)stream);
+                     0, order, (cudaStream_t)stream, ST_TOPK);
 }
 
 extern "C" int pk_final_topk(const pk_tensor* scores, const pk_tensor* cand, int64_t K, const pk_tensor* out,
@@ -293,5 +294,5 @@ extern "C" int pk_final_topk(const pk_tensor* scores, const pk_tensor* cand, int
   PK_REQUIRE(out->shape[0] == bs && out->shape[1] == H && out->shape[2] == K, "out must be [bs,H,K]");
   if (bs * H == 0) return PK_OK;
   return launch_topk(scores->data, true, bs * H, C, C, K, (int64_t*)out->data, (const int64_t*)cand->data, C, 0,
-                     (cudaStream_t)stream);
+                     (cudaStream_t)stream, ST_FINAL_TOPK);
 }
