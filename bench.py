@@ -269,6 +269,43 @@ def workload_config(n_gpus):
             "l2": "inputs larger than L2: 16.4 GB of weights and 36 x 16.8 MB of codes are streamed every step"}
 
 
+def kernels_mode(args, cfg, device):
+    """Cache path only: per step and layer one K/V append and one compute() on a random query."""
+    from pariskv_b200 import _lib
+    K, W = args.steps, max(args.warmup, 1)
+    cache = build_cache(cfg, device, W + K + 2 * cfg["interval"] + 8, seed=100)
+    g = torch.Generator(device=device).manual_seed(5)
+    Hq, Hk = cfg["q_heads"], cfg["kv_heads"]
+    qs = torch.randn(K + W, cfg["layers"], 1, 1, Hq, 128, generator=g, device=device).to(torch.bfloat16)
+    kv = torch.randn(2, 1, 1, Hk, 128, generator=g, device=device).to(torch.bfloat16)
+
+    def step(i):
+        for l in range(cfg["layers"]):
+            cache.decode_update_kv_cache(kv[0], kv[1], l)
+            cache.compute(qs[i, l], l)
+
+    for i in range(W):
+        step(i)
+    torch.cuda.synchronize(device)
+    torch.cuda.nvtx.range_push("timed")
+    _lib.timing_enable(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        step(W + i)
+    e1.record()
+    torch.cuda.synchronize(device)
+    torch.cuda.nvtx.range_pop()
+    stage = _lib.timing_read()
+    _lib.timing_enable(False)
+    ms = e0.elapsed_time(e1)
+    out = {"mode": "kernels", "invalid": "profiling target: cache path only, not the benchmark",
+           "layers": cfg["layers"], "steps": K, "us_per_layer_step": ms * 1e3 / (K * cfg["layers"]),
+           "zone_keys_per_head": cache.cpu_valid_end[0],
+           "stages": {k: {"avg_us": round(v[0] * 1e3 / v[1], 3), "launches": v[1]} for k, v in stage.items()}}
+    print(json.dumps(out), flush=True)
+
+
 # --------------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -278,6 +315,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
     ap.add_argument("--stage-steps", type=int, default=16, help="extra steps with per-kernel event timing")
+    ap.add_argument("--mode", default="decode", choices=["decode", "kernels"],
+                    help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
+                         "a small profiling target, its line is marked as such")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the line invalid)")
     ap.add_argument("--context", type=int, default=None, help="debug only: shorter context (marks the line invalid)")
     args = ap.parse_args()
@@ -312,6 +352,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    if args.mode == "kernels":
+        kernels_mode(args, cfg, device)
+        return
     K, W, S = args.steps, args.warmup, args.stage_steps
     max_new = W + 2 * K + S + 2 * cfg["interval"] + 8
     t_setup = time.time()
@@ -321,9 +364,11 @@ def main():
     token = torch.tensor([11], device=device)
 
     # ---- warm-up ----
+    torch.cuda.nvtx.range_push("warmup")
     for _ in range(W):
         token = model.step(cache, token)
     barrier()
+    torch.cuda.nvtx.range_pop()
 
     # ---- timed region 1: device-resident loop ----
     sampler = ClockSampler(local_rank)
@@ -331,11 +376,13 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = _lib.launch_count()
     barrier()
+    torch.cuda.nvtx.range_push("timed")
     e0.record()
     for _ in range(K):
         token = model.step(cache, token)
     e1.record()
     barrier()
+    torch.cuda.nvtx.range_pop()
     ms = e0.elapsed_time(e1)
     launches = _lib.launch_count() - launches0
     clocks = sampler.stop()

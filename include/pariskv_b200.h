@@ -197,7 +197,10 @@ int pk_gather_kv_out_cpu(const pk_tensor* src, const pk_tensor* index, const pk_
  *   selected  i64 [bs,H,K] (device) or NULL with K = 0;  row = selected + index_offset
  *   n_sel     i32 [bs,H] per-head count of valid entries of selected, or NULL (all K)
  *   out       bf16 [bs,1,Hq,128]
- *   workspace >= pk_attention_workspace_bytes(bs,Hq,n_window+K) bytes, device */
+ *   workspace >= pk_attention_workspace_bytes(bs,Hq,n_window+K) bytes, device, 16-byte aligned.  Its first
+ *             256-byte-rounded header (arrival counters and a status word) must be ZERO before the first
+ *             call; every call leaves it zero again.  The status word (int at index bs*Hq) becomes 1 if a
+ *             block gave up waiting for its copies (the output of that head is then not written). */
 int64_t pk_attention_workspace_bytes(int64_t bs, int64_t Hq, int64_t max_rows);
 int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* window_k, const pk_tensor* window_v,
                         int64_t n_window, const pk_tensor* store_k, const pk_tensor* store_v,

@@ -2,12 +2,13 @@
 //
 // Per (batch, KV head) the attended rows are the first n_window rows of the GPU window
 // ([sink | local | update buffer]) followed by the K selected rows of the big K/V store, which may
-// live in pinned host memory.  The rows are cut into tiles of 64; one block per (tile, KV head,
-// batch, group of <= 4 query heads) stages its tile of K and V rows into shared memory with
-// asynchronous 16-byte copies (all 64 x 512 bytes of a tile in flight at once, so a grid keeps
-// megabytes outstanding on the host link), then 16 groups of 8 lanes run an online softmax over the
-// rows for up to four query heads sharing the KV head.  Partial (m, l, o) triples go to a workspace and
-// a second small kernel merges the tiles.  Scores are kept in the log2 domain.
+// live in pinned host memory.  The rows are cut into tiles of 64; one block per (tile, KV head, batch)
+// stages its tile with TMA bulk copies (cp.async.bulk, one 256-byte copy per K row and per V row,
+// completion counted on an mbarrier), so a whole grid keeps megabytes outstanding on the host link.
+// 16 groups of 8 lanes then run an online softmax over the staged rows for the query heads that share
+// the KV head (four at a time), and write partial (m, l, o) records.  The block that finishes last for a
+// (batch, KV head) merges the tiles and writes the output: one launch, no second kernel, no waiting on
+// other blocks.  Scores are kept in the log2 domain.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -16,8 +17,9 @@ namespace {
 
 constexpr int ATT_THREADS = 128;
 constexpr int ATT_TILE = 64;
-constexpr int ATT_GQ = 4;       // query heads per block
+constexpr int ATT_GQ = 4;       // query heads per pass
 constexpr int ATT_REC = 132;    // floats per partial: o[128], m, l, pad, pad
+constexpr int ATT_WAIT_LIMIT = 4000000;  // polls of the copy barrier before giving up
 
 struct AttParams {
   const uint16_t* q;  // [bs][Hq][128]
@@ -34,13 +36,11 @@ struct AttParams {
   int H, Hq, G, n_qgroups;
   int64_t n_tiles;
   float scale_log2;
+  unsigned* counters;     // [bs*H] arrival counters, zero between calls
+  int* status;            // set to 1 if a copy barrier was never completed
   float* ws;              // [bs*Hq][n_tiles][ATT_REC]
+  uint16_t* out;          // [bs][Hq][128]
 };
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-  const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
-}
 
 __device__ __forceinline__ void unpack8f(uint4 v, float* out) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -51,31 +51,45 @@ __device__ __forceinline__ void unpack8f(uint4 v, float* out) {
   }
 }
 
+__device__ __forceinline__ bool mbar_wait(unsigned mb, unsigned parity, int limit) {
+  unsigned done = 0;
+  for (int it = 0; it < limit && !done; it++)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(mb), "r"(parity)
+        : "memory");
+  return done != 0;
+}
+
 __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams p) {
-  extern __shared__ __align__(16) unsigned char dyn[];
-  uint16_t* Ks = reinterpret_cast<uint16_t*>(dyn);                       // [64][128]
-  uint16_t* Vs = reinterpret_cast<uint16_t*>(dyn + ATT_TILE * 256);      // [64][128]
-  float* obuf = reinterpret_cast<float*>(dyn);                           // reused: [16][4][128]
+  extern __shared__ __align__(128) unsigned char dyn[];
+  uint16_t* Ks = reinterpret_cast<uint16_t*>(dyn);                           // [64][128]
+  uint16_t* Vs = reinterpret_cast<uint16_t*>(dyn + ATT_TILE * 256);          // [64][128]
+  float* obuf = reinterpret_cast<float*>(dyn + 2 * ATT_TILE * 256);          // [16][4][128]
+  __shared__ __align__(8) unsigned long long mbar;
   __shared__ float s_m[16][ATT_GQ], s_l[16][ATT_GQ];
   __shared__ unsigned char s_valid[ATT_TILE];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int tile = blockIdx.x;
-  const int h = blockIdx.y / p.n_qgroups, qg = blockIdx.y % p.n_qgroups;
-  const int b = blockIdx.z;
+  __shared__ int s_last;
+  const int tid = threadIdx.x;
+  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int64_t bh = (int64_t)b * p.H + h;
   const int64_t n_sel = p.n_sel ? min((int64_t)p.n_sel[bh], p.K) : p.K;
   const int64_t n_rows = p.n_window + n_sel;
   const int64_t r0 = (int64_t)tile * ATT_TILE;
   const int n_tile = (int)max((int64_t)0, min((int64_t)ATT_TILE, n_rows - r0));
+  const unsigned mb = (unsigned)__cvta_generic_to_shared(&mbar);
 
-  // ---- stage the tile: warp w copies rows w, w+4, ...; lanes 0-15 the K row, 16-31 the V row ----
+  // ---- stage the tile: thread t copies row t/2, K for even t and V for odd t ----
   {
-    const int l = lane & 15;
-    const bool is_v = lane >= 16;
-    for (int i = warp; i < n_tile; i += ATT_THREADS / 32) {
+    const int i = tid >> 1;
+    const bool is_v = tid & 1;
+    const uint16_t* src = nullptr;
+    bool ok = i < n_tile;
+    if (ok) {
       const int64_t r = r0 + i;
-      const uint16_t* src;
-      bool ok = true;
       if (r < p.n_window) {
         src = (is_v ? p.wv : p.wk) + b * p.w_b + h * p.w_h + r * p.w_l;
       } else {
@@ -83,116 +97,144 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
         ok = row >= 0 && row < p.cap_s;
         src = (is_v ? p.sv : p.sk) + (bh * p.cap_s + (ok ? row : 0)) * 128;
       }
-      if (ok) cp_async16((is_v ? Vs : Ks) + i * 128 + l * 8, src + l * 8);
-      if (lane == 0) s_valid[i] = ok;
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (tid == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mb) : "memory");
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (!is_v && i < ATT_TILE) s_valid[i] = ok;
+    const int n_copies = __syncthreads_count(ok);
+    if (tid == 0)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mb), "r"(n_copies * 256) : "memory");
+    __syncthreads();
+    if (ok) {
+      const unsigned dst = (unsigned)__cvta_generic_to_shared((is_v ? Vs : Ks) + i * 128);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 256, [%2];" ::"r"(dst),
+                   "l"(src), "r"(mb)
+                   : "memory");
+    }
   }
-  // ---- queries of this block's heads: lane s holds dims [16s, 16s+16) ----
   const int s = tid & 7, grp = tid >> 3;
-  const int n_heads = min(ATT_GQ, p.G - qg * ATT_GQ);
-  float qf[ATT_GQ][16];
-#pragma unroll
-  for (int g = 0; g < ATT_GQ; g++) {
-    if (g < n_heads) {
-      const uint4* qp = reinterpret_cast<const uint4*>(p.q + ((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * 128 + 16 * s);
-      unpack8f(__ldg(qp), qf[g]);
-      unpack8f(__ldg(qp + 1), qf[g] + 8);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 16; i++) qf[g][i] = 0.0f;
-    }
+  if (!__syncthreads_and(mbar_wait(mb, 0, ATT_WAIT_LIMIT))) {
+    // the copies never completed: report, give them one more bounded chance to land, and leave
+    if (tid == 0) atomicExch(p.status, 1);
+    mbar_wait(mb, 0, ATT_WAIT_LIMIT);
+    return;
   }
-  float m[ATT_GQ], lsum[ATT_GQ], o[ATT_GQ][16];
-#pragma unroll
-  for (int g = 0; g < ATT_GQ; g++) {
-    m[g] = -INFINITY;
-    lsum[g] = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 16; i++) o[g][i] = 0.0f;
-  }
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-  __syncthreads();
 
-  for (int i = grp; i < ATT_TILE; i += 16) {  // uniform trip count per warp: shuffles need all lanes
-    const bool live = i < n_tile && s_valid[i];
-    float kf[16], vf[16];
-    if (live) {
-      const uint4* kp = reinterpret_cast<const uint4*>(Ks + i * 128 + 16 * s);
-      const uint4* vp = reinterpret_cast<const uint4*>(Vs + i * 128 + 16 * s);
-      unpack8f(kp[0], kf);
-      unpack8f(kp[1], kf + 8);
-      unpack8f(vp[0], vf);
-      unpack8f(vp[1], vf + 8);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 16; j++) kf[j] = 0.0f, vf[j] = 0.0f;
-    }
+  for (int qg = 0; qg < p.n_qgroups; qg++) {
+    const int n_heads = min(ATT_GQ, p.G - qg * ATT_GQ);
+    float qf[ATT_GQ][16];
 #pragma unroll
     for (int g = 0; g < ATT_GQ; g++) {
-      float d = 0.0f;
+      if (g < n_heads) {
+        const uint4* qp =
+            reinterpret_cast<const uint4*>(p.q + ((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * 128 + 16 * s);
+        unpack8f(__ldg(qp), qf[g]);
+        unpack8f(__ldg(qp + 1), qf[g] + 8);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 16; j++) d = fmaf(kf[j], qf[g][j], d);
-      d += __shfl_xor_sync(0xffffffffu, d, 1);
-      d += __shfl_xor_sync(0xffffffffu, d, 2);
-      d += __shfl_xor_sync(0xffffffffu, d, 4);
+        for (int i = 0; i < 16; i++) qf[g][i] = 0.0f;
+      }
+    }
+    float m[ATT_GQ], lsum[ATT_GQ], o[ATT_GQ][16];
+#pragma unroll
+    for (int g = 0; g < ATT_GQ; g++) {
+      m[g] = -INFINITY;
+      lsum[g] = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 16; i++) o[g][i] = 0.0f;
+    }
+    for (int i = grp; i < ATT_TILE; i += 16) {  // uniform trip count per warp: shuffles need all lanes
+      const bool live = i < n_tile && s_valid[i];
+      float kf[16], vf[16];
       if (live) {
-        const float sc = d * p.scale_log2;
-        const float mn = fmaxf(m[g], sc);
-        const float corr = exp2f(m[g] - mn);  // m = -inf on the first row gives 0
-        const float pr = exp2f(sc - mn);
-        lsum[g] = lsum[g] * corr + pr;
+        const uint4* kp = reinterpret_cast<const uint4*>(Ks + i * 128 + 16 * s);
+        const uint4* vp = reinterpret_cast<const uint4*>(Vs + i * 128 + 16 * s);
+        unpack8f(kp[0], kf);
+        unpack8f(kp[1], kf + 8);
+        unpack8f(vp[0], vf);
+        unpack8f(vp[1], vf + 8);
+      } else {
 #pragma unroll
-        for (int j = 0; j < 16; j++) o[g][j] = o[g][j] * corr + pr * vf[j];
-        m[g] = mn;
+        for (int j = 0; j < 16; j++) kf[j] = 0.0f, vf[j] = 0.0f;
+      }
+#pragma unroll
+      for (int g = 0; g < ATT_GQ; g++) {
+        float d = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; j++) d = fmaf(kf[j], qf[g][j], d);
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        if (live) {
+          const float sc = d * p.scale_log2;
+          const float mn = fmaxf(m[g], sc);
+          const float corr = exp2f(m[g] - mn);  // m = -inf on the first row gives 0
+          const float pr = exp2f(sc - mn);
+          lsum[g] = lsum[g] * corr + pr;
+#pragma unroll
+          for (int j = 0; j < 16; j++) o[g][j] = o[g][j] * corr + pr * vf[j];
+          m[g] = mn;
+        }
+      }
+    }
+    __syncthreads();  // obuf / s_m / s_l of the previous pass have been consumed
+#pragma unroll
+    for (int g = 0; g < ATT_GQ; g++) {
+#pragma unroll
+      for (int j = 0; j < 16; j++) obuf[(grp * ATT_GQ + g) * 128 + 16 * s + j] = o[g][j];
+      if (s == 0) {
+        s_m[grp][g] = m[g];
+        s_l[grp][g] = lsum[g];
+      }
+    }
+    __syncthreads();
+    for (int g = 0; g < n_heads; g++) {
+      float M = -INFINITY;
+#pragma unroll
+      for (int t = 0; t < 16; t++) M = fmaxf(M, s_m[t][g]);
+      float L = 0.0f, O = 0.0f;
+#pragma unroll
+      for (int t = 0; t < 16; t++) {
+        const float f = (s_m[t][g] == -INFINITY) ? 0.0f : exp2f(s_m[t][g] - M);
+        L += s_l[t][g] * f;
+        O += obuf[(t * ATT_GQ + g) * 128 + tid] * f;
+      }
+      float* rec = p.ws + (((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * p.n_tiles + tile) * ATT_REC;
+      __stcg(rec + tid, O);
+      if (tid == 0) {
+        __stcg(rec + 128, M);
+        __stcg(rec + 129, L);
       }
     }
   }
-  __syncthreads();  // tile no longer needed: its shared memory becomes the merge buffer
-#pragma unroll
-  for (int g = 0; g < ATT_GQ; g++) {
-#pragma unroll
-    for (int j = 0; j < 16; j++) obuf[(grp * ATT_GQ + g) * 128 + 16 * s + j] = o[g][j];
-    if (s == 0) {
-      s_m[grp][g] = m[g];
-      s_l[grp][g] = lsum[g];
-    }
+
+  // ---- the block that arrives last for this (batch, KV head) merges all tiles ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(p.counters + bh, 1u);
+    s_last = prev + 1 == (unsigned)p.n_tiles;
+    if (s_last) p.counters[bh] = 0;  // ready for the next call on this stream
   }
   __syncthreads();
-  for (int g = 0; g < n_heads; g++) {
+  if (!s_last) return;
+  __threadfence();
+  for (int g = 0; g < p.G; g++) {
+    const int64_t bq = (int64_t)b * p.Hq + h * p.G + g;
+    const float* rec = p.ws + bq * p.n_tiles * ATT_REC;
     float M = -INFINITY;
-#pragma unroll
-    for (int t = 0; t < 16; t++) M = fmaxf(M, s_m[t][g]);
+    for (int64_t t = 0; t < p.n_tiles; t++) M = fmaxf(M, __ldcg(rec + t * ATT_REC + 128));
     float L = 0.0f, O = 0.0f;
-#pragma unroll
-    for (int t = 0; t < 16; t++) {
-      const float f = (s_m[t][g] == -INFINITY) ? 0.0f : exp2f(s_m[t][g] - M);
-      L += s_l[t][g] * f;
-      O += obuf[(t * ATT_GQ + g) * 128 + tid] * f;
+    for (int64_t t = 0; t < p.n_tiles; t++) {
+      const float mt = __ldcg(rec + t * ATT_REC + 128);
+      const float f = (mt == -INFINITY) ? 0.0f : exp2f(mt - M);
+      L += __ldcg(rec + t * ATT_REC + 129) * f;
+      O += __ldcg(rec + t * ATT_REC + tid) * f;
     }
-    float* rec = p.ws + (((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * p.n_tiles + tile) * ATT_REC;
-    rec[tid] = O;
-    if (tid == 0) {
-      rec[128] = M;
-      rec[129] = L;
-    }
+    p.out[bq * 128 + tid] = f2bf(L > 0.0f ? O / L : 0.0f);
   }
-}
-
-__global__ void __launch_bounds__(128) attention_merge_kernel(const float* __restrict__ ws, int64_t n_tiles,
-                                                              uint16_t* __restrict__ out) {
-  const int64_t bq = blockIdx.x;
-  const float* rec = ws + bq * n_tiles * ATT_REC;
-  float M = -INFINITY;
-  for (int64_t t = 0; t < n_tiles; t++) M = fmaxf(M, rec[t * ATT_REC + 128]);
-  float L = 0.0f, O = 0.0f;
-  for (int64_t t = 0; t < n_tiles; t++) {
-    const float mt = rec[t * ATT_REC + 128];
-    const float f = (mt == -INFINITY) ? 0.0f : exp2f(mt - M);
-    L += rec[t * ATT_REC + 129] * f;
-    O += rec[t * ATT_REC + threadIdx.x] * f;
-  }
-  out[bq * 128 + threadIdx.x] = f2bf(L > 0.0f ? O / L : 0.0f);
 }
 
 }  // namespace
@@ -200,9 +242,14 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const float* __res
 
 using namespace pk;
 
+namespace {
+inline int64_t att_header_bytes(int64_t bs, int64_t H) { return (bs * H * 4 + 4 + 255) / 256 * 256; }
+}  // namespace
+
 extern "C" int64_t pk_attention_workspace_bytes(int64_t bs, int64_t Hq, int64_t max_rows) {
+  // header (arrival counters + status word, sized for one KV head per query head) followed by the partials
   const int64_t tiles = (max_rows + ATT_TILE - 1) / ATT_TILE;
-  return bs * Hq * (tiles > 0 ? tiles : 1) * ATT_REC * 4;
+  return att_header_bytes(bs, Hq) + bs * Hq * (tiles > 0 ? tiles : 1) * ATT_REC * 4;
 }
 
 extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* window_k, const pk_tensor* window_v,
@@ -276,17 +323,21 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
   p.n_qgroups = (p.G + ATT_GQ - 1) / ATT_GQ;
   p.n_tiles = n_tiles;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.ws = (float*)workspace;
+  PK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "workspace must be 16-byte aligned");
+  p.counters = (unsigned*)workspace;
+  p.status = (int*)workspace + bs * Hq;
+  p.ws = (float*)((char*)workspace + att_header_bytes(bs, Hq));
+  p.out = (uint16_t*)out->data;
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid((unsigned)n_tiles, (unsigned)(H * p.n_qgroups), (unsigned)bs);
-  int rc;
-  {
-    StageTimer tm(ST_ATTENTION, st);
-    sparse_attention_kernel<<<grid, ATT_THREADS, 2 * ATT_TILE * 256, st>>>(p);
-    rc = check_launch("sparse_attention");
+  static bool attr_done = false;
+  constexpr int kSmem = 2 * ATT_TILE * 256 + 16 * ATT_GQ * 128 * 4;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(sparse_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
+      return check_launch("sparse_attention smem");
+    attr_done = true;
   }
-  if (rc) return rc;
-  StageTimer tm(ST_ATTENTION_MERGE, st);
-  attention_merge_kernel<<<(unsigned)(bs * Hq), 128, 0, st>>>(p.ws, n_tiles, (uint16_t*)out->data);
-  return check_launch("attention_merge");
+  dim3 grid((unsigned)n_tiles, (unsigned)H, (unsigned)bs);
+  StageTimer tm(ST_ATTENTION, st);
+  sparse_attention_kernel<<<grid, ATT_THREADS, kSmem, st>>>(p);
+  return check_launch("sparse_attention");
 }

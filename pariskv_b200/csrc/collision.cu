@@ -1,8 +1,9 @@
 // Cluster ranking, tier look-up tables and the weighted multi-tier collision count.
 //
-// The six cumulative tier bitsets of a subspace collapse into one 256-entry table of 4-bit weights
-// (number of tiers a cluster belongs to): 32 words = one word per shared-memory bank, so a warp's 32
-// look-ups into the table of one subspace never conflict.  Codes are streamed with 128-bit loads.
+// The six cumulative tier bitsets of a subspace collapse into one 256-entry byte table (number of tiers a
+// cluster belongs to), 4 KB per (batch, head) in shared memory at a link-time address, so one look-up is a
+// byte extract, a byte load with an immediate offset and an add.  Codes are streamed with 128-bit loads,
+// every thread keeps 256 bytes in flight before it starts counting.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -48,11 +49,11 @@ __global__ void __launch_bounds__(256) lut_from_sorted_kernel(const IdT* __restr
     if (excl < tiers.t[t]) bits |= 1u << t;
   if (id >= 0 && id < NC && bits) atomicOr(&mask[id], bits);
   __syncthreads();
-  if (tid < 32) {
+  if (tid < 64) {
     uint32_t w = 0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) w |= (uint32_t)__popc(mask[tid * 8 + i]) << (4 * i);
-    lut[blk * 32 + tid] = w;
+    for (int i = 0; i < 4; i++) w |= (uint32_t)__popc(mask[tid * 4 + i]) << (8 * i);
+    lut[blk * 64 + tid] = w;
   }
 }
 
@@ -91,11 +92,11 @@ __global__ void __launch_bounds__(256) rank_kernel(const uint16_t* __restrict__ 
     for (int t = 0; t < tiers.n; t++) wgt += (excl < tiers.t[t]);
     nib[c] = wgt;
     __syncthreads();
-    if (c < 32) {
+    if (c < 64) {
       uint32_t w = 0;
 #pragma unroll
-      for (int i = 0; i < 8; i++) w |= nib[c * 8 + i] << (4 * i);
-      lut[blk * 32 + c] = w;
+      for (int i = 0; i < 4; i++) w |= nib[c * 4 + i] << (8 * i);
+      lut[blk * 64 + c] = w;
     }
   }
 }
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(256) rank_kernel(const uint16_t* __restrict__ 
 struct CollParams {
   const uint8_t* codes;          // element (b,h,s,k) at codes[b*c_b + h*c_h + s*c_s + k*c_l]
   int64_t c_b, c_h, c_s, c_l;
-  const uint32_t* lut;           // [bs*H][B][32]
+  const uint32_t* lut;           // [bs*H][B][64] words = 256 byte entries per subspace
   int32_t* out_i32;              // [bs*H][N]            (OUT_U8 == false)
   uint8_t* out_u8;               // [bs*H][u8_stride], indexed by virtual key (OUT_U8 == true)
   uint32_t* chunk_hist;          // [bs*H][n_chunks][256] (OUT_U8 == true)
@@ -113,26 +114,21 @@ struct CollParams {
   int H, B;
   int64_t N;                     // keys per head
   int mis;                       // virtual key v = key + mis; loads are 16-byte aligned in v
-  int64_t chunk_keys;            // virtual keys per block (multiple of 512)
+  int64_t chunk_keys;            // virtual keys per block (multiple of 4096)
 };
 
-__device__ __forceinline__ unsigned lut_get(const uint32_t* tab, unsigned code) {
-  return (tab[code >> 3] >> ((code & 7u) << 2)) & 0xFu;
-}
+// byte k (0..3) of w, zero-extended: one PRMT
+__device__ __forceinline__ unsigned byte_of(uint32_t w, int k) { return __byte_perm(w, 0, 0x4440 | k); }
 
 // LAYOUT 0: plane-major ([.., 16, N], key stride 1): a thread owns 16 consecutive keys.
 // LAYOUT 1: key-major ([.., N, 16], subspace stride 1): a warp owns 512 consecutive keys, lane-strided.
 // LAYOUT 2: any strides, any B <= 32: a thread owns one key at a time.
 template <int LAYOUT, bool OUT_U8>
 __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
-  extern __shared__ uint32_t smem[];
-  uint32_t* lut = smem;                 // B*32 words
-  unsigned* hist = smem + p.B * 32;     // 256 words (OUT_U8 only)
+  __shared__ __align__(16) uint8_t s_lut[32 * 256];
+  __shared__ unsigned hist[256];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-  for (int i = tid; i < p.B * 32; i += 256) lut[i] = p.lut[(int64_t)bh * p.B * 32 + i];
-  if (OUT_U8) hist[tid] = 0;
-  __syncthreads();
   const int64_t Nv = p.N + p.mis;
   const int64_t v_begin = (int64_t)blockIdx.x * p.chunk_keys;
   const int64_t v_end = min(Nv, v_begin + p.chunk_keys);
@@ -140,11 +136,31 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
   int32_t* out32 = OUT_U8 ? nullptr : p.out_i32 + (int64_t)bh * p.N;
   uint8_t* out8 = OUT_U8 ? p.out_u8 + (int64_t)bh * p.u8_stride : nullptr;
 
+  // the first batch of code loads is issued before the table is staged, so both latencies overlap
+  uint4 r[16];
+  if (LAYOUT == 1) {
+    const int64_t w0 = v_begin + 512 * (int64_t)warp;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int64_t v = w0 + 32 * j + lane;
+      r[j] = (v < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + v * 16)) : make_uint4(0, 0, 0, 0);
+    }
+  } else if (LAYOUT == 0) {
+    const int64_t v0 = v_begin + 16 * (int64_t)tid;
+#pragma unroll
+    for (int s = 0; s < 16; s++)
+      r[s] = (v0 < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + s * p.c_s + v0)) : make_uint4(0, 0, 0, 0);
+  }
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(p.lut + (int64_t)bh * p.B * 64);
+    uint4* dst = reinterpret_cast<uint4*>(s_lut);
+    for (int i = tid; i < p.B * 16; i += 256) dst[i] = __ldg(src + i);
+  }
+  if (OUT_U8) hist[tid] = 0;
+  __syncthreads();
+
   if (LAYOUT == 0) {
     for (int64_t v0 = v_begin + 16 * (int64_t)tid; v0 < v_end; v0 += 16 * 256) {
-      uint4 r[16];
-#pragma unroll
-      for (int s = 0; s < 16; s++) r[s] = __ldg(reinterpret_cast<const uint4*>(base + s * p.c_s + v0));
       int cnt[16];
 #pragma unroll
       for (int k = 0; k < 16; k++) cnt[k] = 0;
@@ -152,7 +168,12 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
       for (int s = 0; s < 16; s++) {
         const uint32_t w4[4] = {r[s].x, r[s].y, r[s].z, r[s].w};
 #pragma unroll
-        for (int k = 0; k < 16; k++) cnt[k] += lut_get(lut + s * 32, (w4[k >> 2] >> (8 * (k & 3))) & 0xFFu);
+        for (int k = 0; k < 16; k++) cnt[k] += s_lut[s * 256 + byte_of(w4[k >> 2], k & 3)];
+      }
+      const int64_t vn = v0 + 16 * 256;
+      if (vn < v_end) {
+#pragma unroll
+        for (int s = 0; s < 16; s++) r[s] = __ldg(reinterpret_cast<const uint4*>(base + s * p.c_s + vn));
       }
       const int64_t key0 = v0 - p.mis;
       if (OUT_U8) {
@@ -178,25 +199,32 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
     }
   } else if (LAYOUT == 1) {
     for (int64_t w0 = v_begin + 512 * (int64_t)warp; w0 < v_end; w0 += 512 * 8) {
-      uint4 r[16];
-#pragma unroll
-      for (int j = 0; j < 16; j++) {
-        const int64_t v = w0 + 32 * j + lane;
-        r[j] = (v < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + v * 16)) : make_uint4(0, 0, 0, 0);
-      }
+      int cnt[16];
 #pragma unroll
       for (int j = 0; j < 16; j++) {
         const uint32_t w4[4] = {r[j].x, r[j].y, r[j].z, r[j].w};
-        int cnt = 0;
+        int c = 0;
 #pragma unroll
-        for (int s = 0; s < 16; s++) cnt += lut_get(lut + s * 32, (w4[s >> 2] >> (8 * (s & 3))) & 0xFFu);
+        for (int s = 0; s < 16; s++) c += s_lut[s * 256 + byte_of(w4[s >> 2], s & 3)];
+        cnt[j] = c;
+      }
+      const int64_t wn = w0 + 512 * 8;
+      if (wn < v_end) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          const int64_t v = wn + 32 * j + lane;
+          r[j] = (v < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + v * 16)) : make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
         const int64_t v = w0 + 32 * j + lane;
         if (v < v_end) {
           if (OUT_U8) {
-            out8[v] = (uint8_t)cnt;
-            atomicAdd(&hist[cnt], 1u);
+            out8[v] = (uint8_t)cnt[j];
+            atomicAdd(&hist[cnt[j]], 1u);
           } else {
-            out32[v] = cnt;
+            out32[v] = cnt[j];
           }
         }
       }
@@ -206,7 +234,7 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
       const int64_t key = v - p.mis;
       if (key < 0) continue;
       int cnt = 0;
-      for (int s = 0; s < p.B; s++) cnt += lut_get(lut + s * 32, base[s * p.c_s + v * p.c_l]);
+      for (int s = 0; s < p.B; s++) cnt += s_lut[s * 256 + base[s * p.c_s + v * p.c_l]];
       if (OUT_U8) {
         out8[v] = (uint8_t)cnt;
         atomicAdd(&hist[cnt], 1u);
@@ -225,16 +253,17 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
 __global__ void __launch_bounds__(256) collision_i32_kernel(const int32_t* __restrict__ codes,
                                                             const uint32_t* __restrict__ lut_g, int B, int NC,
                                                             int64_t N, int32_t* __restrict__ out) {
-  extern __shared__ uint32_t lut[];
+  extern __shared__ uint32_t lut_w[];
+  const uint8_t* lut = reinterpret_cast<const uint8_t*>(lut_w);
   const int bh = blockIdx.y;
-  for (int i = threadIdx.x; i < B * 32; i += 256) lut[i] = lut_g[(int64_t)bh * B * 32 + i];
+  for (int i = threadIdx.x; i < B * 64; i += 256) lut_w[i] = lut_g[(int64_t)bh * B * 64 + i];
   __syncthreads();
   for (int64_t k = (int64_t)blockIdx.x * 256 + threadIdx.x; k < N; k += (int64_t)gridDim.x * 256) {
     const int32_t* row = codes + ((int64_t)bh * N + k) * B;
     int cnt = 0;
     for (int s = 0; s < B; s++) {
       const int32_t c = row[s];
-      if (c >= 0 && c < NC) cnt += lut_get(lut + s * 32, (unsigned)c);
+      if (c >= 0 && c < NC) cnt += lut[s * 256 + c];
     }
     out[(int64_t)bh * N + k] = cnt;
   }
@@ -254,11 +283,11 @@ __global__ void __launch_bounds__(256) lut_single_kernel(const int32_t* __restri
     if (id >= 0 && id < NC) sel[id] = 1;
   }
   __syncthreads();
-  if (tid < 32) {
+  if (tid < 64) {
     uint32_t w = 0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) w |= sel[tid * 8 + i] << (4 * i);
-    lut[blk * 32 + tid] = w;
+    for (int i = 0; i < 4; i++) w |= sel[tid * 4 + i] << (8 * i);
+    lut[blk * 64 + tid] = w;
   }
 }
 
@@ -272,11 +301,11 @@ Tiers make_tiers(const int64_t* tier_counts, int n) {
 }  // namespace
 
 int64_t collision_chunk_keys(int64_t bs_h, int64_t Nv) {
+  // one block = 8 warps x 512 keys per pass; about two blocks per SM over the whole grid
   int64_t n_chunks = (2 * (int64_t)sm_count()) / (bs_h > 0 ? bs_h : 1);
   if (n_chunks < 1) n_chunks = 1;
   int64_t chunk = (Nv + n_chunks - 1) / n_chunks;
-  chunk = ((chunk + 511) / 512) * 512;
-  if (chunk < 512) chunk = 512;
+  chunk = ((chunk + 4095) / 4096) * 4096;
   if (chunk > 32768) chunk = 32768;  // the selection kernel keeps one int per key of a chunk in shared memory
   return chunk;
 }
@@ -320,7 +349,7 @@ int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* ou
   if (chunk_keys_out) *chunk_keys_out = p.chunk_keys;
   if (n_chunks_out) *n_chunks_out = n_chunks;
   dim3 grid((unsigned)n_chunks, (unsigned)(bs * H));
-  const size_t smem = (size_t)(B * 32 + 256) * 4;
+  const size_t smem = 0;
   const bool u8 = counts_u8 != nullptr;
   StageTimer tm(ST_COLLISION, st);
 #define PK_LAUNCH_COLL(L, U) collision_kernel<L, U><<<grid, 256, smem, st>>>(p)
@@ -341,7 +370,7 @@ using namespace pk;
 
 extern "C" int64_t pk_collision_workspace_bytes(int64_t bs, int64_t H, int64_t B, int64_t NC) {
   (void)NC;
-  return bs * H * B * 32 * 4;
+  return bs * H * B * 64 * 4;
 }
 
 extern "C" int pk_rank_clusters(const pk_tensor* q_blocks, const pk_tensor* sorted_ids, void* stream) {
@@ -434,7 +463,7 @@ extern "C" int pk_collision(const pk_tensor* sorted_cluster_ids, const pk_tensor
   int64_t gx = (N + 255) / 256;
   int64_t cap = (int64_t)sm_count() * 8 / (bs * H) + 1;
   if (gx > cap) gx = cap;
-  collision_i32_kernel<<<dim3((unsigned)gx, (unsigned)(bs * H)), 256, (size_t)B * 32 * 4, st>>>(
+  collision_i32_kernel<<<dim3((unsigned)gx, (unsigned)(bs * H)), 256, (size_t)B * 64 * 4, st>>>(
       (const int32_t*)code_book->data, lut, (int)B, (int)NC, N, (int32_t*)cache_cnt->data);
   return check_launch("collision");
 }

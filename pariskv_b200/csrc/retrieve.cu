@@ -23,7 +23,7 @@ RetrieveLayout make_layout(int64_t bs, int64_t H, int64_t N, int64_t C) {
   int64_t off = 0;
   l.q_blocks = off, off += align256(bh * 128 * 2);
   l.q_norm = off, off += align256(bh * 2);
-  l.lut = off, off += align256(bh * 16 * 32 * 4);
+  l.lut = off, off += align256(bh * 16 * 64 * 4);
   l.counts = off, off += align256(bh * l.u8_stride);
   l.hist = off, off += align256(bh * l.n_chunks_max * 256 * 4);
   l.scores = off, off += align256(bh * C * 4);

@@ -3,8 +3,10 @@
 // One thread-block cluster per row: the row is cut into contiguous slices, one per CTA; digit
 // histograms live in each CTA's shared memory and are summed across the cluster through distributed
 // shared memory, so the whole selection (varying-bit probe, up to four 8-bit radix passes, tie quota,
-// ordered emission) is ONE launch with no global scratch.  Digits on which all elements of the row
-// agree are skipped, so collision counts (0..96) need a single histogram pass.
+// ordered emission) is ONE launch with no global scratch.  Digits are cut from the highest bit on which
+// the elements of the row differ, so collision counts (0..96) need a single histogram pass and fp32 scores
+// spread over the first histogram instead of piling into two exponent bins.  Rows of up to 16384
+// elements take a single-block variant that keeps the keys in registers.
 // Selected set: first k of (value descending, index ascending); emitted in ascending index.
 #include <cooperative_groups.h>
 
@@ -108,21 +110,18 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
   }
   const unsigned varying = A ^ O;
 
-  // ---- radix passes, most significant digit first ----
-  unsigned prefix = 0, pmask = 0, rem = (unsigned)p.k;
-  for (int d = 3; d >= 0; d--) {
-    const int shift = 8 * d;
-    const unsigned dm = 0xFFu << shift;
-    if ((varying & dm) == 0) {
-      prefix |= A & dm;
-      pmask |= dm;
-      continue;
-    }
+  // ---- radix passes from the highest varying bit down, 8 bits at a time ----
+  unsigned prefix = A, pmask = ~varying, rem = (unsigned)p.k;  // bits that never vary are already decided
+  for (int hi = 31 - __clz(varying | 0u); varying != 0 && hi >= 0; hi -= 8) {
+    const int lo = max(hi - 7, 0);
+    const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));  // bits lo..hi
+    const unsigned above = hi == 31 ? 0u : ~((1u << (hi + 1)) - 1u);        // bits above hi
+    const unsigned fixed = pmask | above;
     if (tid < 256) hist[tid] = 0;
     __syncthreads();
     for (int64_t i = my_begin; i < my_end; i++) {
       const uint32_t k = load_key(row, i, p.is_float);
-      if ((k & pmask) == prefix) atomicAdd(&hist[(k >> shift) & 0xFFu], 1u);
+      if (((k ^ prefix) & fixed) == 0) atomicAdd(&hist[(k & dm) >> lo], 1u);
     }
     cluster.sync();
     if (tid < 256) {
@@ -132,7 +131,7 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
     }
     __syncthreads();
     suffix_select(tot, rem, s_tmp, s_res, tid);
-    prefix |= s_res[0] << shift;
+    prefix = (prefix & ~dm) | (s_res[0] << lo);
     pmask |= dm;
     rem -= s_res[1];
     cluster.sync();  // every CTA has read the remote histograms before they are cleared again
@@ -185,6 +184,98 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
   cluster.sync();  // shared memory must outlive the remote reads above
 }
 
+// Single-block variant for rows of at most 1024 * SPAN elements: every thread keeps SPAN consecutive keys
+// in registers, so the row is read once.
+template <int SPAN>
+__global__ void __launch_bounds__(1024) topk_block_kernel(TopkParams p) {
+  __shared__ unsigned hist[256];
+  __shared__ unsigned red[2];
+  __shared__ unsigned s_tmp[16];
+  __shared__ unsigned s_res[2];
+  __shared__ unsigned long long s_scan[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row_id = blockIdx.x;
+  const uint32_t* row = p.in + row_id * p.row_stride;
+  const int64_t my_begin = (int64_t)tid * SPAN;
+  const int nv = (int)max((int64_t)0, min((int64_t)SPAN, p.L - my_begin));
+  uint32_t key[SPAN];
+#pragma unroll
+  for (int j = 0; j < SPAN; j++) key[j] = j < nv ? load_key(row, my_begin + j, p.is_float) : 0u;
+  if (tid == 0) {
+    red[0] = 0xffffffffu;
+    red[1] = 0u;
+  }
+  __syncthreads();
+  {
+    unsigned a = 0xffffffffu, o = 0u;
+#pragma unroll
+    for (int j = 0; j < SPAN; j++)
+      if (j < nv) {
+        a &= key[j];
+        o |= key[j];
+      }
+    a = __reduce_and_sync(0xffffffffu, a);
+    o = __reduce_or_sync(0xffffffffu, o);
+    if (lane == 0) {
+      atomicAnd(&red[0], a);
+      atomicOr(&red[1], o);
+    }
+  }
+  __syncthreads();
+  const unsigned A = red[0], varying = red[0] ^ red[1];
+  unsigned prefix = A, pmask = ~varying, rem = (unsigned)p.k;
+  for (int hi = 31 - __clz(varying | 0u); varying != 0 && hi >= 0; hi -= 8) {
+    const int lo = max(hi - 7, 0);
+    const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));
+    const unsigned above = hi == 31 ? 0u : ~((1u << (hi + 1)) - 1u);
+    const unsigned fixed = pmask | above;
+    if (tid < 256) hist[tid] = 0;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < SPAN; j++)
+      if (j < nv && ((key[j] ^ prefix) & fixed) == 0) atomicAdd(&hist[(key[j] & dm) >> lo], 1u);
+    __syncthreads();
+    suffix_select(hist, rem, s_tmp, s_res, tid);
+    prefix = (prefix & ~dm) | (s_res[0] << lo);
+    pmask |= dm;
+    rem -= s_res[1];
+    __syncthreads();
+  }
+  const unsigned T = prefix;
+  unsigned n_gt = 0, n_eq = 0;
+#pragma unroll
+  for (int j = 0; j < SPAN; j++)
+    if (j < nv) {
+      n_gt += key[j] > T;
+      n_eq += key[j] == T;
+    }
+  unsigned long long mine = ((unsigned long long)n_gt << 32) | n_eq, incl = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    unsigned long long o = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += o;
+  }
+  if (lane == 31) s_scan[warp] = incl;
+  __syncthreads();
+  unsigned long long base = 0;
+  for (int w = 0; w < warp; w++) base += s_scan[w];
+  unsigned gt_run = (unsigned)((base + incl - mine) >> 32), eq_run = (unsigned)(base + incl - mine);
+  int64_t* out = p.out + row_id * p.k;
+  const int64_t* map = p.map ? p.map + row_id * p.map_stride : nullptr;
+#pragma unroll
+  for (int j = 0; j < SPAN; j++)
+    if (j < nv) {
+      const int64_t i = my_begin + j;
+      if (key[j] > T) {
+        out[gt_run + min(eq_run, rem)] = map ? map[i] : i;
+        gt_run++;
+      } else if (key[j] == T) {
+        if (eq_run < rem) out[gt_run + eq_run] = map ? map[i] : i;
+        eq_run++;
+      }
+    }
+}
+
 // Reorders an emitted top-k list by (value descending, index ascending): one block per row, k <= 4096.
 __global__ void __launch_bounds__(1024) sort_by_value_kernel(const uint32_t* in, int is_float, int64_t row_stride,
                                                              int64_t k, int kp, int64_t* out) {
@@ -228,6 +319,20 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
   p.is_float = is_float ? 1 : 0;
   p.row_stride = row_stride, p.L = L, p.k = k;
   p.out = out, p.map = map, p.map_stride = map_stride;
+  if (L <= 16384) {
+    if (L <= 4096)
+      topk_block_kernel<4><<<(unsigned)rows, 1024, 0, st>>>(p);
+    else if (L <= 8192)
+      topk_block_kernel<8><<<(unsigned)rows, 1024, 0, st>>>(p);
+    else
+      topk_block_kernel<16><<<(unsigned)rows, 1024, 0, st>>>(p);
+    int rc0 = check_launch("topk");
+    if (rc0 || order == 0) return rc0;
+    int kp0 = 1;
+    while (kp0 < k) kp0 <<= 1;
+    sort_by_value_kernel<<<(unsigned)rows, 1024, (size_t)kp0 * 8, st>>>(p.in, p.is_float, row_stride, k, kp0, out);
+    return check_launch("topk sort");
+  }
   unsigned ncta = 1;
   while (ncta < 8 && (int64_t)ncta * 4096 < L) ncta <<= 1;
   if (L > (1 << 18)) ncta = 16;

@@ -20,7 +20,8 @@ def workspace(device, nbytes, tag="default"):
     key = (torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device(), tag)
     buf = _WS.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(int(nbytes), 1 << 16), dtype=torch.uint8, device=device)
+        # zero-filled: the attention kernel keeps arrival counters in its workspace header
+        buf = torch.zeros(max(int(nbytes), 1 << 16), dtype=torch.uint8, device=device)
         _WS[key] = buf
     return buf
 

@@ -146,8 +146,8 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, n), f"{n} is declared in the header but not exported"
     assert sorted(_lib.SIGNATURES) == names, "ctypes signatures and header declarations differ"
     assert lib.pk_version() == 1
-    assert lib.pk_collision_workspace_bytes(1, 8, 16, 256) == 8 * 16 * 128
-    assert lib.pk_attention_workspace_bytes(1, 32, 2244) == 32 * 36 * 132 * 4
+    assert lib.pk_collision_workspace_bytes(1, 8, 16, 256) == 8 * 16 * 256
+    assert lib.pk_attention_workspace_bytes(1, 32, 2244) == 256 + 32 * 36 * 132 * 4
     assert lib.pk_retrieve_workspace_bytes(1, 8, 131004, 13101) > 0
 
 
