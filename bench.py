@@ -76,11 +76,12 @@ class DecoderHarness:
         x1, x2 = x[..., :64].float(), x[..., 64:].float()
         return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).to(torch.bfloat16)
 
-    def step(self, cache, token):
-        """One decode token through all layers; token: int64 [1] on the device.  Returns next token [1]."""
+    def step(self, cache, token, pos_dev=None):
+        """One decode token through all layers; token: int64 [1] on the device.  Returns next token [1].
+        pos_dev (float32 [1] on the device) replaces the host-side position when the step is captured."""
         c = self.cfg
         Hq, Hk, D = c["q_heads"], c["kv_heads"], c["head_dim"]
-        ang = cache.context * self._inv_freq
+        ang = (pos_dev if pos_dev is not None else cache.context) * self._inv_freq
         cos, sin = torch.cos(ang), torch.sin(ang)
         h = self.embed[token]                                   # [1, hidden]
         for l in range(c["layers"]):
@@ -99,6 +100,74 @@ class DecoderHarness:
             h = h + F.linear(F.silu(gu[:, :c["ffn"]]) * gu[:, c["ffn"]:], self.wd[l])
         logits = F.linear(F.rms_norm(h, (c["hidden"],), self.lnf, 1e-6), self.lm_head)
         return logits.argmax(-1)
+
+
+class GraphedDecoder:
+    """Replays the decode step as a CUDA graph.  Between two flushes of the update buffer every launch
+    argument of the step is constant except the window position and the RoPE position, which the kernels
+    read from device words; the step that flushes runs eagerly and the graph is captured again after it."""
+
+    def __init__(self, model, cache):
+        self.model, self.cache = model, cache
+        dev = model.device
+        self.tok = torch.zeros(1, dtype=torch.int64, device=dev)   # static input, fed back by the graph
+        self.nxt = torch.zeros(1, dtype=torch.int64, device=dev)   # static output
+        self.pos = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.graph = None
+        self.stale = True
+        self.captures = 0
+        self.kernel_launches = 0      # launches of this repository's kernels executed through step()
+        self.launches_per_replay = 0
+        self.pool = torch.cuda.graph_pool_handle()
+        self.side = torch.cuda.Stream(device=dev)
+
+    def _capture(self):
+        cache = self.cache
+        cache.device_positions = True
+        cache.sync_device_state()
+        self.pos.fill_(float(cache.context))
+        saved = cache.host_state()
+        # plain capture_begin / capture_end on a side stream: the torch.cuda.graph context also runs the garbage
+        # collector and empties the allocator cache, which costs far more than the capture when it is repeated
+        # after every flush
+        from pariskv_b200 import _lib
+        before = _lib.launch_count()
+        main = torch.cuda.current_stream()
+        g = torch.cuda.CUDAGraph()    # the previous graph stays alive until this one holds the shared pool
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
+            g.capture_begin(pool=self.pool)
+            out = self.model.step(cache, self.tok, self.pos)
+            self.nxt.copy_(out)
+            self.tok.copy_(out)
+            self.pos += 1
+            cache.advance_device_step()
+            g.capture_end()
+        main.wait_stream(self.side)
+        cache.set_host_state(saved)   # capture ran the host bookkeeping of one step without executing it
+        self.launches_per_replay = _lib.launch_count() - before
+        self.graph = g
+        self.stale = False
+        self.captures += 1
+
+    def step(self):
+        """Advance one token; input in self.tok, result in self.nxt (and fed back into self.tok)."""
+        cache = self.cache
+        if cache.next_step_flushes():
+            from pariskv_b200 import _lib
+            before = _lib.launch_count()
+            cache.device_positions = False
+            out = self.model.step(cache, self.tok)      # eager: appends, flushes, re-indexes
+            self.kernel_launches += _lib.launch_count() - before
+            self.nxt.copy_(out)
+            self.tok.copy_(out)
+            self.stale = True                            # the zone grew: launch arguments changed
+            return
+        if self.graph is None or self.stale:
+            self._capture()
+        self.graph.replay()
+        self.kernel_launches += self.launches_per_replay
+        cache.note_replayed_step()
 
 
 def synth_kv(gen, P, H, device):
@@ -315,6 +384,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
     ap.add_argument("--stage-steps", type=int, default=16, help="extra steps with per-kernel event timing")
+    ap.add_argument("--no-graph", action="store_true", help="run every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--mode", default="decode", choices=["decode", "kernels"],
                     help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
                          "a small profiling target, its line is marked as such")
@@ -362,11 +432,23 @@ def main():
     cache = build_cache(cfg, device, max_new, seed=100 + rank)
     setup_s = time.time() - t_setup
     token = torch.tensor([11], device=device)
+    use_graph = not args.no_graph
+    runner = GraphedDecoder(model, cache)
+
+    def advance():
+        nonlocal token
+        if use_graph:
+            runner.step()
+        else:
+            token = model.step(cache, token)
 
     # ---- warm-up ----
     torch.cuda.nvtx.range_push("warmup")
-    for _ in range(W):
+    for _ in range(2):                       # eager first: library handles, workspaces
         token = model.step(cache, token)
+    runner.tok.copy_(token)
+    for _ in range(max(W - 2, 1)):
+        advance()
     barrier()
     torch.cuda.nvtx.range_pop()
 
@@ -374,31 +456,34 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = _lib.launch_count()
+    launches0 = _lib.launch_count() if not use_graph else runner.kernel_launches
     barrier()
     torch.cuda.nvtx.range_push("timed")
     e0.record()
     for _ in range(K):
-        token = model.step(cache, token)
+        advance()
     e1.record()
     barrier()
     torch.cuda.nvtx.range_pop()
     ms = e0.elapsed_time(e1)
-    launches = _lib.launch_count() - launches0
+    launches = (_lib.launch_count() if not use_graph else runner.kernel_launches) - launches0
     clocks = sampler.stop()
 
     # ---- timed region 2: host-driven loop (token id in from pinned host memory, next token out) ----
     tok_in = torch.empty(1, dtype=torch.int64).pin_memory()
     tok_out = torch.empty(1, dtype=torch.int64).pin_memory()
-    tok_in[0] = int(token.item())
-    dev_tok = torch.empty(1, dtype=torch.int64, device=device)
+    tok_in[0] = int((runner.tok if use_graph else token).item())
+    dev_tok = runner.tok if use_graph else torch.empty(1, dtype=torch.int64, device=device)
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     for _ in range(K):
         dev_tok.copy_(tok_in, non_blocking=True)
-        nxt = model.step(cache, dev_tok)
-        tok_out.copy_(nxt, non_blocking=True)
+        if use_graph:
+            runner.step()
+            tok_out.copy_(runner.nxt, non_blocking=True)
+        else:
+            tok_out.copy_(model.step(cache, dev_tok), non_blocking=True)
         torch.cuda.current_stream().synchronize()
         tok_in[0] = tok_out[0]
     f1.record()
@@ -409,6 +494,8 @@ def main():
     stage = {}
     if S > 0:
         _lib.timing_enable(True)
+        cache.device_positions = False
+        token = (runner.tok if use_graph else token).clone()
         for _ in range(S):
             token = model.step(cache, token)
         torch.cuda.synchronize(device)
@@ -480,6 +567,7 @@ def main():
         "retrieval_us_per_step_per_layer": round(retrieval_us, 2),
         "cpu_baseline": cpu,
         "published_reference": {"decode_tok_s_128k_bs1": 41.10, "note": "hardware and model unstated by the reference"},
+        "cuda_graph": {"used": use_graph, "captures": runner.captures},
         "setup_s": round(setup_s, 1), "zone_keys_per_head": N, "candidates": C, "final_topk": Kf,
     }
     if debug:

@@ -55,7 +55,7 @@ int64_t pk_launch_count(void);
  * decode path is bracketed by CUDA events on its own stream.  pk_timing_read waits for the recorded
  * events, sums elapsed milliseconds and launch counts per stage (stage ids: 0 query prep, 1 cluster
  * ranking/table, 2 collision, 3 select+rerank, 4 final top-k, 5 attention tiles, 6 attention merge,
- * 7 encode, 8 stand-alone top-k, 9 stand-alone rerank, 10 UVA gather) and clears the record. */
+ * 7 encode, 8 stand-alone top-k, 9 stand-alone rerank, 10 UVA gather, 11 cluster histogram, 12 row append) and clears the record. */
 int pk_timing_enable(int on);
 int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages);
 
@@ -195,6 +195,9 @@ int pk_gather_kv_out_cpu(const pk_tensor* src, const pk_tensor* index, const pk_
  *   window_k/window_v bf16 [bs,H,cap_w,128] device, last stride 1, row stride 128
  *   store_k/store_v   bf16 [bs,H,cap_s,128] contiguous; pinned HOST (UVA) or device
  *   selected  i64 [bs,H,K] (device) or NULL with K = 0;  row = selected + index_offset
+ *   n_window_dev i32 [1] device, or NULL.  When given, the number of window rows is read on the device as
+ *             min(n_window, n_window_dev[0] + n_window_add) and n_window only sizes the grid, so a captured
+ *             CUDA graph can be replayed while the window fills.
  *   n_sel     i32 [bs,H] per-head count of valid entries of selected, or NULL (all K)
  *   out       bf16 [bs,1,Hq,128]
  *   workspace >= pk_attention_workspace_bytes(bs,Hq,n_window+K) bytes, device, 16-byte aligned.  Its first
@@ -203,10 +206,19 @@ int pk_gather_kv_out_cpu(const pk_tensor* src, const pk_tensor* index, const pk_
  *             block gave up waiting for its copies (the output of that head is then not written). */
 int64_t pk_attention_workspace_bytes(int64_t bs, int64_t Hq, int64_t max_rows);
 int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* window_k, const pk_tensor* window_v,
-                        int64_t n_window, const pk_tensor* store_k, const pk_tensor* store_v,
+                        int64_t n_window, const pk_tensor* n_window_dev, int64_t n_window_add,
+                        const pk_tensor* store_k, const pk_tensor* store_v,
                         const pk_tensor* selected, const pk_tensor* n_sel, int64_t index_offset,
                         float scale, const pk_tensor* out, void* workspace, int64_t workspace_bytes,
                         void* stream);
+
+/* Append one decode step's K/V row to the GPU window: the row writes of polar_cache.decode_update_kv_cache
+ * (cache_hub/polar_cache.py:849-850) as one launch.
+ *   k_row/v_row bf16 [bs,1,H,128]; window_k/window_v bf16 [bs,H,cap,128] (same strides)
+ *   the row index is pos, or pos_dev[0] + pos_add when pos_dev (i32 [1], device) is given; a row index
+ *   outside [0, cap) read from the device is ignored. */
+int pk_append_kv(const pk_tensor* k_row, const pk_tensor* v_row, const pk_tensor* window_k,
+                 const pk_tensor* window_v, int64_t pos, const pk_tensor* pos_dev, int64_t pos_add, void* stream);
 
 /* ---- the whole retrieval chain in one call ------------------------------------------------------- */
 

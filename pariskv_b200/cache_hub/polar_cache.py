@@ -13,6 +13,9 @@ model runtime written for the reference decodes through it unchanged.  The body 
   shapes through permuted views.
 * One decode step of one layer is: a row append, ``ops.retrieve`` (five launches), ``ops.sparse_attention``
   (two launches).  No host synchronisation, no allocation, no concatenation.
+* The window position can be read on the device (``device_positions``): the row append and the attention
+  then take the window length from a device word instead of a launch argument, so a whole decode step can
+  be captured in a CUDA graph and replayed until the next flush.
 * Every layer keeps its own buffer counter (the reference derives the slot of every layer from layer 0's
   counter, which makes layers >= 1 lag by one slot); a layer flushes its own buffer when it fills:
   the oldest ``dynamic_update_interval`` local rows are coded, added to the cluster histogram, copied to the
@@ -124,6 +127,9 @@ class polar_cache(KV_Cache):
         self._slide_tmp_k = torch.empty(bs, H, max(local_size, 1), 128, dtype=dtype, device=dev)
         self._slide_tmp_v = torch.empty_like(self._slide_tmp_k)
         self._all_rows = None
+        # device copy of the window length at the start of the current step (all layers agree between steps)
+        self._dev_state = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.device_positions = False
         self.context = 0
         self.last_topk_indices = None               # [bs,H,K] of the most recent compute (for inspection)
 
@@ -209,8 +215,8 @@ class polar_cache(KV_Cache):
     def decode_update_kv_cache(self, key_states, value_states, layer_idx):
         """Append the step's K/V row ([bs, 1, H, 128]) to the window; flush the update buffer when full."""
         pos = self._window_len[layer_idx]
-        self.unified_keys_gpu[layer_idx][:, :, pos] = key_states[:, 0]
-        self.unified_values_gpu[layer_idx][:, :, pos] = value_states[:, 0]
+        ops.append_kv(key_states, value_states, self.unified_keys_gpu[layer_idx], self.unified_values_gpu[layer_idx],
+                      pos, self._dev_state[0:1] if self.device_positions else None, 0)
         self._window_len[layer_idx] = pos + 1
         self.current_seq_len[layer_idx] += 1
         if layer_idx == 0:
@@ -285,7 +291,38 @@ class polar_cache(KV_Cache):
                                 self.key_4bit_packed_gpu[layer_idx][:, :, :, :N, :], self.cluster_key_counts_gpu[layer_idx],
                                 tiers, C, K)
         self.last_topk_indices = final
+        if self.device_positions:  # rows = (window length at step start) + this step's row, read on the device
+            return ops.sparse_attention(queries, wk, wv, self.window_capacity, sk, sv, final,
+                                        n_window_dev=self._dev_state[0:1], n_window_add=1)
         return ops.sparse_attention(queries, wk, wv, n_win, sk, sv, final)
+
+    # ------------------------------------------------------------------------------------------------
+    # support for replaying a captured decode step
+    # ------------------------------------------------------------------------------------------------
+    def next_step_flushes(self) -> bool:
+        """True when the next appended token fills the update buffer (that step must run eagerly)."""
+        return self._window_len[0] + 1 >= self.window_capacity
+
+    def sync_device_state(self):
+        """Copy the host-side window length to the device word read when device_positions is set."""
+        self._dev_state[0] = self._window_len[0]
+
+    def advance_device_step(self):
+        """Device-side end of a step: one more row in the window (a launch, so it is captured with the step)."""
+        self._dev_state[0:1] += 1
+
+    def host_state(self):
+        return (list(self._window_len), list(self.current_seq_len), self.context, list(self.cpu_valid_end))
+
+    def set_host_state(self, st):
+        self._window_len, self.current_seq_len, self.context, self.cpu_valid_end = list(st[0]), list(st[1]), st[2], list(st[3])
+
+    def note_replayed_step(self):
+        """Host-side bookkeeping of one decode step that ran as a graph replay."""
+        for l in range(self.layer_num):
+            self._window_len[l] += 1
+            self.current_seq_len[l] += 1
+        self.context += 1
 
     def sync(self, layer_idx, batch_idx):
         """No-op: copies to the zone store are ordered on the compute stream."""

@@ -26,7 +26,9 @@ struct AttParams {
   const uint16_t* wk;
   const uint16_t* wv;
   int64_t w_b, w_h, w_l;  // window strides (elements)
-  int64_t n_window;
+  int64_t n_window;       // host value; an upper bound when n_window_dev is set
+  const int32_t* n_window_dev;  // optional: actual window rows = n_window_dev[0] + n_window_add (device memory)
+  int64_t n_window_add;
   const uint16_t* sk;
   const uint16_t* sv;
   int64_t cap_s;          // rows per (b,h) of the store
@@ -77,7 +79,9 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
   const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int64_t bh = (int64_t)b * p.H + h;
   const int64_t n_sel = p.n_sel ? min((int64_t)p.n_sel[bh], p.K) : p.K;
-  const int64_t n_rows = p.n_window + n_sel;
+  const int64_t n_window =
+      p.n_window_dev ? min(p.n_window, max((int64_t)0, (int64_t)p.n_window_dev[0] + p.n_window_add)) : p.n_window;
+  const int64_t n_rows = n_window + n_sel;
   const int64_t r0 = (int64_t)tile * ATT_TILE;
   const int n_tile = (int)max((int64_t)0, min((int64_t)ATT_TILE, n_rows - r0));
   const unsigned mb = (unsigned)__cvta_generic_to_shared(&mbar);
@@ -90,10 +94,10 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
     bool ok = i < n_tile;
     if (ok) {
       const int64_t r = r0 + i;
-      if (r < p.n_window) {
+      if (r < n_window) {
         src = (is_v ? p.wv : p.wk) + b * p.w_b + h * p.w_h + r * p.w_l;
       } else {
-        const int64_t row = p.sel[bh * p.K + (r - p.n_window)] + p.index_offset;
+        const int64_t row = p.sel[bh * p.K + (r - n_window)] + p.index_offset;
         ok = row >= 0 && row < p.cap_s;
         src = (is_v ? p.sv : p.sk) + (bh * p.cap_s + (ok ? row : 0)) * 128;
       }
@@ -221,19 +225,50 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // tile maxima / scale factors are computed one tile per thread, then every thread sums its output
+  // dimension over the tiles with independent loads (no serial chain of L2 round trips)
+  float* s_f = obuf;            // scale factor per tile (reuses the merge buffer)
+  float* s_lt = obuf + 1024;    // l per tile
+  __shared__ float s_red[4];
   for (int g = 0; g < p.G; g++) {
     const int64_t bq = (int64_t)b * p.Hq + h * p.G + g;
     const float* rec = p.ws + bq * p.n_tiles * ATT_REC;
-    float M = -INFINITY;
-    for (int64_t t = 0; t < p.n_tiles; t++) M = fmaxf(M, __ldcg(rec + t * ATT_REC + 128));
-    float L = 0.0f, O = 0.0f;
-    for (int64_t t = 0; t < p.n_tiles; t++) {
+    float mloc = -INFINITY;
+    for (int64_t t = tid; t < p.n_tiles; t += ATT_THREADS) {
       const float mt = __ldcg(rec + t * ATT_REC + 128);
-      const float f = (mt == -INFINITY) ? 0.0f : exp2f(mt - M);
-      L += __ldcg(rec + t * ATT_REC + 129) * f;
-      O += __ldcg(rec + t * ATT_REC + tid) * f;
+      s_f[t & 1023] = mt;
+      s_lt[t & 1023] = __ldcg(rec + t * ATT_REC + 129);
+      mloc = fmaxf(mloc, mt);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
+    __syncthreads();
+    if ((tid & 31) == 0) s_red[tid >> 5] = mloc;
+    __syncthreads();
+    const float M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    for (int64_t t = tid; t < p.n_tiles; t += ATT_THREADS) {
+      const float mt = s_f[t & 1023];
+      s_f[t & 1023] = (mt == -INFINITY) ? 0.0f : exp2f(mt - M);
+    }
+    __syncthreads();
+    float L = 0.0f, O = 0.0f;
+    int64_t t = 0;
+    for (; t + 8 <= p.n_tiles; t += 8) {
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = __ldcg(rec + (t + i) * ATT_REC + tid);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        O += v[i] * s_f[(t + i) & 1023];
+        L += s_lt[(t + i) & 1023] * s_f[(t + i) & 1023];
+      }
+    }
+    for (; t < p.n_tiles; t++) {
+      O += __ldcg(rec + t * ATT_REC + tid) * s_f[t & 1023];
+      L += s_lt[t & 1023] * s_f[t & 1023];
     }
     p.out[bq * 128 + tid] = f2bf(L > 0.0f ? O / L : 0.0f);
+    __syncthreads();
   }
 }
 
@@ -253,7 +288,8 @@ extern "C" int64_t pk_attention_workspace_bytes(int64_t bs, int64_t Hq, int64_t 
 }
 
 extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* window_k, const pk_tensor* window_v,
-                                   int64_t n_window, const pk_tensor* store_k, const pk_tensor* store_v,
+                                   int64_t n_window, const pk_tensor* n_window_dev, int64_t n_window_add,
+                                   const pk_tensor* store_k, const pk_tensor* store_v,
                                    const pk_tensor* selected, const pk_tensor* n_sel, int64_t index_offset,
                                    float scale, const pk_tensor* out, void* workspace, int64_t workspace_bytes,
                                    void* stream) {
@@ -275,7 +311,8 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
                    window_k->shape[2] >= n_window,
                "window_k must be [bs,H,cap>=n_window,128] with last stride 1");
     for (int i = 0; i < 4; i++)
-      PK_REQUIRE(window_k->shape[i] == window_v->shape[i] && window_k->stride[i] == window_v->stride[i],
+      PK_REQUIRE(window_k->shape[i] == window_v->shape[i] &&
+                     (window_k->shape[i] == 1 || window_k->stride[i] == window_v->stride[i]),
                  "window_k and window_v must have the same shape and strides");
     PK_REQUIRE((reinterpret_cast<uintptr_t>(window_k->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(window_v->data) & 15) == 0 &&
                    window_k->stride[0] % 8 == 0 && window_k->stride[1] % 8 == 0 && window_k->stride[2] % 8 == 0,
@@ -313,11 +350,18 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
   if (bs == 0) return PK_OK;
   const int64_t max_rows = n_window + K;
   const int64_t n_tiles = max_rows > 0 ? (max_rows + ATT_TILE - 1) / ATT_TILE : 1;
+  PK_REQUIRE(n_tiles <= 1024, "too many rows for one call: %lld (limit 65536)", (long long)max_rows);
   if (!workspace || workspace_bytes < pk_attention_workspace_bytes(bs, Hq, max_rows))
     return fail(PK_ERR_WORKSPACE, "attention workspace too small: %lld < %lld", (long long)workspace_bytes,
                 (long long)pk_attention_workspace_bytes(bs, Hq, max_rows));
   p.q = (const uint16_t*)queries->data;
   p.n_window = n_window;
+  if (n_window_dev) {
+    PK_CHECK_TENSOR(n_window_dev, PK_I32, 1);
+    PK_REQUIRE(n_window_dev->shape[0] >= 1, "n_window_dev must hold one int32");
+    p.n_window_dev = (const int32_t*)n_window_dev->data;
+    p.n_window_add = n_window_add;
+  }
   p.K = K, p.index_offset = index_offset;
   p.H = (int)H, p.Hq = (int)Hq, p.G = (int)(Hq / H);
   p.n_qgroups = (p.G + ATT_GQ - 1) / ATT_GQ;

@@ -6,6 +6,7 @@
 // every thread keeps 256 bytes in flight before it starts counting.
 #include "common.cuh"
 #include "kernels.cuh"
+#include "rotate.cuh"
 
 namespace pk {
 namespace {
@@ -60,43 +61,94 @@ __global__ void __launch_bounds__(256) lut_from_sorted_kernel(const IdT* __restr
 // From the query (the fused chain) and/or to produce the explicit order (rank_clusters op):
 // one block per (batch, head, subspace), thread c owns cluster c.
 // score_c = bf16(sum_j +-q_j), fp32 sum j ascending; order: score descending, id ascending.
-__global__ void __launch_bounds__(256) rank_kernel(const uint16_t* __restrict__ q_blocks,
-                                                   const int32_t* __restrict__ counts, Tiers tiers,
-                                                   uint32_t* __restrict__ lut, int64_t* __restrict__ sorted_ids) {
+// With `queries` set, warp 0 first does the query preparation itself (group mean, normalise, rotate),
+// so the fused chain needs no separate query kernel; the block of subspace 0 publishes q_blocks / q_norm
+// / query_avg for the later stages.
+struct RankParams {
+  const uint16_t* queries;   // [bs][Hq][128] or null
+  const uint16_t* signs;
+  int Hq, H, G;
+  float inv_g;
+  uint16_t* q_blocks;        // [bs*H][128]: input when queries == null, output otherwise
+  uint16_t* q_norm;          // [bs*H] output (queries != null)
+  uint16_t* query_avg;       // [bs*H][128] optional output
+  const int32_t* counts;     // [bs*H][16][256] or null
+  Tiers tiers;
+  uint32_t* lut;             // [bs*H][16][64] or null
+  int64_t* sorted_ids;       // [bs*H][16][256] or null
+};
+
+__global__ void __launch_bounds__(256) rank_kernel(RankParams p) {
   __shared__ float sc[256];
   __shared__ int cn[256];
   __shared__ unsigned nib[256];
+  __shared__ float s_q[8];
   const int c = threadIdx.x;
   const int64_t blk = blockIdx.x;  // (b*H + h)*16 + subspace
+  const int64_t bh = blk >> 4;
+  const int sub = (int)(blk & 15);
+  if (p.queries) {
+    if (c < 32) {
+      const int s = c & 7;
+      const int b = (int)(bh / p.H), h = (int)(bh % p.H);
+      const uint16_t* q = p.queries + ((int64_t)b * p.Hq + (int64_t)h * p.G) * 128 + 16 * s;
+      float x[16], sg[16];
+#pragma unroll
+      for (int i = 0; i < 16; i++) {
+        float acc = 0.0f;
+        for (int g = 0; g < p.G; g++) acc = __fadd_rn(acc, bf2f(q[g * 128 + i]));
+        x[i] = bfround(__fmul_rn(acc, p.inv_g));
+        sg[i] = bf2f(p.signs[16 * s + i]);
+      }
+      if (sub == 0 && p.query_avg && c < 8)
+#pragma unroll
+        for (int i = 0; i < 16; i++) p.query_avg[bh * 128 + 16 * s + i] = f2bf(x[i]);
+      const float n = rotate16(x, sg, s);
+      if (c < 8) {
+        if (sub == 0) {
+#pragma unroll
+          for (int i = 0; i < 16; i++) p.q_blocks[bh * 128 + 16 * s + i] = f2bf(x[i]);
+          if (c == 0) p.q_norm[bh] = f2bf(n);
+        }
+        if (s == (sub >> 1))
+#pragma unroll
+          for (int j = 0; j < 8; j++) s_q[j] = x[8 * (sub & 1) + j];
+      }
+    }
+  } else if (c < 8) {
+    s_q[c] = bf2f(p.q_blocks[blk * 8 + c]);
+  }
+  cn[c] = p.counts ? p.counts[blk * 256 + c] : 0;
+  __syncthreads();
   float s = 0.0f;
 #pragma unroll
   for (int j = 0; j < 8; j++) {
-    const float qv = bf2f(q_blocks[blk * 8 + j]);
+    const float qv = s_q[j];
     s = __fadd_rn(s, ((c >> j) & 1) ? qv : -qv);
   }
   s = bfround(s);
   sc[c] = s;
-  cn[c] = counts ? counts[blk * 256 + c] : 0;
   __syncthreads();
   long long excl = 0;
   int rank = 0;
+#pragma unroll 8
   for (int o = 0; o < 256; o++) {
     const float so = sc[o];
     const bool before = (so > s) || (so == s && o < c);
     rank += before;
     excl += before ? cn[o] : 0;
   }
-  if (sorted_ids) sorted_ids[blk * 256 + rank] = c;
-  if (lut) {
+  if (p.sorted_ids) p.sorted_ids[blk * 256 + rank] = c;
+  if (p.lut) {
     unsigned wgt = 0;
-    for (int t = 0; t < tiers.n; t++) wgt += (excl < tiers.t[t]);
+    for (int t = 0; t < p.tiers.n; t++) wgt += (excl < p.tiers.t[t]);
     nib[c] = wgt;
     __syncthreads();
     if (c < 64) {
       uint32_t w = 0;
 #pragma unroll
       for (int i = 0; i < 4; i++) w |= nib[c * 4 + i] << (8 * i);
-      lut[blk * 64 + c] = w;
+      p.lut[blk * 64 + c] = w;
     }
   }
 }
@@ -126,9 +178,10 @@ __device__ __forceinline__ unsigned byte_of(uint32_t w, int k) { return __byte_p
 template <int LAYOUT, bool OUT_U8>
 __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
   __shared__ __align__(16) uint8_t s_lut[32 * 256];
-  __shared__ unsigned hist[256];
+  __shared__ unsigned hist[8 * 256];  // eight replicas (lane & 7) cut same-bin collisions inside a warp
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  unsigned* my_hist = hist + ((lane & 7) << 8);
   const int64_t Nv = p.N + p.mis;
   const int64_t v_begin = (int64_t)blockIdx.x * p.chunk_keys;
   const int64_t v_end = min(Nv, v_begin + p.chunk_keys);
@@ -156,11 +209,14 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
     uint4* dst = reinterpret_cast<uint4*>(s_lut);
     for (int i = tid; i < p.B * 16; i += 256) dst[i] = __ldg(src + i);
   }
-  if (OUT_U8) hist[tid] = 0;
+  if (OUT_U8)
+    for (int i = tid; i < 8 * 256; i += 256) hist[i] = 0;
   __syncthreads();
 
   if (LAYOUT == 0) {
-    for (int64_t v0 = v_begin + 16 * (int64_t)tid; v0 < v_end; v0 += 16 * 256) {
+    for (int64_t t0 = v_begin; t0 < v_end; t0 += 16 * 256) {  // block-uniform trip count (the warp votes below)
+      const int64_t v0 = t0 + 16 * (int64_t)tid;
+      const bool live = v0 < v_end;
       int cnt[16];
 #pragma unroll
       for (int k = 0; k < 16; k++) cnt[k] = 0;
@@ -181,10 +237,10 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
 #pragma unroll
         for (int k = 0; k < 16; k++) {
           pk4[k >> 2] |= (uint32_t)cnt[k] << (8 * (k & 3));
-          if (key0 + k >= 0 && key0 + k < p.N) atomicAdd(&hist[cnt[k]], 1u);
+          if (live && key0 + k >= 0 && key0 + k < p.N) atomicAdd(&my_hist[cnt[k]], 1u);
         }
-        *reinterpret_cast<uint4*>(out8 + v0) = make_uint4(pk4[0], pk4[1], pk4[2], pk4[3]);
-      } else {
+        if (live) *reinterpret_cast<uint4*>(out8 + v0) = make_uint4(pk4[0], pk4[1], pk4[2], pk4[3]);
+      } else if (live) {
         if (key0 >= 0 && key0 + 16 <= p.N && ((reinterpret_cast<uintptr_t>(out32 + key0) & 15) == 0)) {
 #pragma unroll
           for (int q = 0; q < 4; q++)
@@ -222,7 +278,7 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
         if (v < v_end) {
           if (OUT_U8) {
             out8[v] = (uint8_t)cnt[j];
-            atomicAdd(&hist[cnt[j]], 1u);
+            atomicAdd(&my_hist[cnt[j]], 1u);
           } else {
             out32[v] = cnt[j];
           }
@@ -237,7 +293,7 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
       for (int s = 0; s < p.B; s++) cnt += s_lut[s * 256 + base[s * p.c_s + v * p.c_l]];
       if (OUT_U8) {
         out8[v] = (uint8_t)cnt;
-        atomicAdd(&hist[cnt], 1u);
+        atomicAdd(&my_hist[cnt], 1u);
       } else {
         out32[key] = cnt;
       }
@@ -245,7 +301,10 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
   }
   if (OUT_U8) {
     __syncthreads();
-    p.chunk_hist[((int64_t)bh * gridDim.x + blockIdx.x) * 256 + tid] = hist[tid];
+    unsigned t = 0;
+#pragma unroll
+    for (int r = 0; r < 8; r++) t += hist[r * 256 + tid];
+    p.chunk_hist[((int64_t)bh * gridDim.x + blockIdx.x) * 256 + tid] = t;
   }
 }
 
@@ -310,11 +369,17 @@ int64_t collision_chunk_keys(int64_t bs_h, int64_t Nv) {
   return chunk;
 }
 
-int launch_rank(const uint16_t* q_blocks, const int32_t* counts, const int64_t* tier_counts, int n_tiers,
-                int64_t bs_h, uint32_t* lut, int64_t* sorted_ids, cudaStream_t st) {
+int launch_rank(const uint16_t* queries, const uint16_t* signs, int Hq, int H, uint16_t* q_blocks, uint16_t* q_norm,
+                uint16_t* query_avg, const int32_t* counts, const int64_t* tier_counts, int n_tiers, int64_t bs_h,
+                uint32_t* lut, int64_t* sorted_ids, cudaStream_t st) {
+  RankParams p;
+  p.queries = queries, p.signs = signs, p.Hq = Hq, p.H = H, p.G = H > 0 ? Hq / H : 1;
+  p.inv_g = 1.0f / (float)p.G;
+  p.q_blocks = q_blocks, p.q_norm = q_norm, p.query_avg = query_avg, p.counts = counts;
+  p.tiers = make_tiers(tier_counts, n_tiers);
+  p.lut = lut, p.sorted_ids = sorted_ids;
   StageTimer tm(ST_RANK, st);
-  rank_kernel<<<(unsigned)(bs_h * 16), 256, 0, st>>>(q_blocks, counts, make_tiers(tier_counts, n_tiers), lut,
-                                                     sorted_ids);
+  rank_kernel<<<(unsigned)(bs_h * 16), 256, 0, st>>>(p);
   return check_launch("rank_clusters");
 }
 
@@ -383,8 +448,8 @@ extern "C" int pk_rank_clusters(const pk_tensor* q_blocks, const pk_tensor* sort
                  sorted_ids->shape[2] == 16 && sorted_ids->shape[3] == 256,
              "sorted_ids must be contiguous [bs,H,16,256]");
   if (bs * H == 0) return PK_OK;
-  return launch_rank((const uint16_t*)q_blocks->data, nullptr, nullptr, 0, bs * H, nullptr,
-                     (int64_t*)sorted_ids->data, (cudaStream_t)stream);
+  return launch_rank(nullptr, nullptr, 0, (int)H, (uint16_t*)q_blocks->data, nullptr, nullptr, nullptr, nullptr, 0, bs * H,
+                     nullptr, (int64_t*)sorted_ids->data, (cudaStream_t)stream);
 }
 
 extern "C" int pk_collision_fused(const pk_tensor* sorted_cluster_ids, const pk_tensor* cluster_key_counts,

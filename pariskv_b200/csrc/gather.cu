@@ -55,6 +55,22 @@ __global__ void __launch_bounds__(256) h2d_gather_packed_kernel(
   }
 }
 
+// One block per (batch, head): lanes 0-15 copy the K row, lanes 16-31 the V row, to window row pos.
+__global__ void __launch_bounds__(32) append_kv_kernel(const uint4* __restrict__ k_row, const uint4* __restrict__ v_row,
+                                                       int64_t k_b, int64_t k_h, int64_t v_b, int64_t v_h,
+                                                       uint4* __restrict__ wk,
+                                                       uint4* __restrict__ wv, int64_t w_b, int64_t w_h, int64_t w_l,
+                                                       int H, int64_t cap, int64_t pos, const int32_t* __restrict__ pos_dev,
+                                                       int64_t pos_add) {
+  const int lane = threadIdx.x, l = lane & 15;
+  const int b = blockIdx.x / H, h = blockIdx.x % H;
+  const int64_t row = pos_dev ? (int64_t)pos_dev[0] + pos_add : pos;
+  if (row < 0 || row >= cap) return;
+  const uint4* src = lane < 16 ? k_row + b * k_b + h * k_h : v_row + b * v_b + h * v_h;
+  uint4* dst = (lane < 16 ? wk : wv) + b * w_b + h * w_h + row * w_l;
+  dst[l] = __ldg(src + l);
+}
+
 }  // namespace
 }  // namespace pk
 
@@ -124,4 +140,45 @@ extern "C" int pk_h2d_gather_kv_packed(const pk_tensor* src_k, const pk_tensor* 
       (const int64_t*)indices_packed->data, (const int32_t*)cu_seqlens_topk->data, (const int32_t*)cu_seqlens_k->data,
       src_k->shape[2], sink_local_end, global_k);
   return check_launch("h2d_gather_kv_packed");
+}
+
+extern "C" int pk_append_kv(const pk_tensor* k_row, const pk_tensor* v_row, const pk_tensor* window_k,
+                            const pk_tensor* window_v, int64_t pos, const pk_tensor* pos_dev, int64_t pos_add,
+                            void* stream) {
+  PK_CHECK_TENSOR(k_row, PK_BF16, 4);
+  PK_CHECK_TENSOR(v_row, PK_BF16, 4);
+  PK_CHECK_TENSOR(window_k, PK_BF16, 4);
+  PK_CHECK_TENSOR(window_v, PK_BF16, 4);
+  const int64_t bs = window_k->shape[0], H = window_k->shape[1], cap = window_k->shape[2];
+  PK_REQUIRE(k_row->shape[0] == bs && k_row->shape[1] == 1 && k_row->shape[2] == H && k_row->shape[3] == 128 &&
+                 k_row->stride[3] == 1,
+             "k_row must be [bs,1,H,128] with last stride 1");
+  for (int i = 0; i < 4; i++) {
+    PK_REQUIRE(k_row->shape[i] == v_row->shape[i], "k_row and v_row must have the same shape");
+    PK_REQUIRE(window_k->shape[i] == window_v->shape[i] &&
+                   (window_k->shape[i] == 1 || window_k->stride[i] == window_v->stride[i]),
+               "window_k and window_v must have the same shape and strides");
+  }
+  PK_REQUIRE(v_row->stride[3] == 1, "v_row must have last stride 1");
+  PK_REQUIRE(window_k->shape[3] == 128 && window_k->stride[3] == 1, "window must be [bs,H,cap,128] with last stride 1");
+  const pk_tensor* ts[4] = {k_row, v_row, window_k, window_v};
+  for (const pk_tensor* t : ts) {
+    PK_REQUIRE((reinterpret_cast<uintptr_t>(t->data) & 15) == 0, "rows must be 16-byte aligned");
+    for (int i = 0; i < 3; i++) PK_REQUIRE(t->stride[i] % 8 == 0, "rows must be 16-byte aligned");
+  }
+  const int32_t* pd = nullptr;
+  if (pos_dev) {
+    PK_CHECK_TENSOR(pos_dev, PK_I32, 1);
+    pd = (const int32_t*)pos_dev->data;
+  } else {
+    PK_REQUIRE(pos >= 0 && pos < cap, "append position %lld outside the window (capacity %lld)", (long long)pos,
+               (long long)cap);
+  }
+  if (bs * H == 0) return PK_OK;
+  StageTimer tm(ST_APPEND, (cudaStream_t)stream);
+  append_kv_kernel<<<(unsigned)(bs * H), 32, 0, (cudaStream_t)stream>>>(
+      (const uint4*)k_row->data, (const uint4*)v_row->data, k_row->stride[0] / 8, k_row->stride[2] / 8,
+      v_row->stride[0] / 8, v_row->stride[2] / 8, (uint4*)window_k->data, (uint4*)window_v->data, window_k->stride[0] / 8, window_k->stride[1] / 8,
+      window_k->stride[2] / 8, (int)H, cap, pos, pd, pos_add);
+  return check_launch("append_kv");
 }

@@ -13,8 +13,10 @@ int launch_query_prep(const uint16_t* queries, int bs, int Hq, int H, const uint
 
 // collision.cu
 int64_t collision_chunk_keys(int64_t bs_h, int64_t Nv);
-int launch_rank(const uint16_t* q_blocks, const int32_t* counts, const int64_t* tier_counts, int n_tiers,
-                int64_t bs_h, uint32_t* lut, int64_t* sorted_ids, cudaStream_t st);
+// queries != null: query preparation is done inside (q_blocks / q_norm / query_avg become outputs)
+int launch_rank(const uint16_t* queries, const uint16_t* signs, int Hq, int H, uint16_t* q_blocks, uint16_t* q_norm,
+                uint16_t* query_avg, const int32_t* counts, const int64_t* tier_counts, int n_tiers, int64_t bs_h,
+                uint32_t* lut, int64_t* sorted_ids, cudaStream_t st);
 int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* out_i32, uint8_t* counts_u8,
                      int64_t u8_stride, uint32_t* chunk_hist, int* mis_out, int64_t* chunk_keys_out,
                      int64_t* n_chunks_out, cudaStream_t st);

@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(RR_THREADS) rerank_kernel(RerankArgs a, uint16
 // One block per (chunk of keys, batch*head).  The per-chunk histograms written by the collision kernel
 // give every block the global threshold bin, the tie quota and its own output offset, so the candidate
 // list comes out in ascending key order with no atomics and no second pass.
-constexpr int SEL_THREADS = 256;
+constexpr int SEL_THREADS = 512;  // the first 256 threads own the 256 count bins
 
 struct SelParams {
   const uint8_t* counts;  // [bs*H][u8_stride], virtual keys
@@ -133,11 +133,22 @@ __global__ void __launch_bounds__(SEL_THREADS) select_rerank_kernel(RerankArgs a
   const int64_t bh = blockIdx.y, chunk = blockIdx.x;
   const int b = (int)(bh / a.H), h = (int)(bh % a.H);
   rerank_setup(sm, a, bh, tid, SEL_THREADS);
-  {
+  if (tid < 256) {
     const uint32_t* hp = p.chunk_hist + bh * p.n_chunks * 256 + tid;
     unsigned t = 0, pr = 0;
-    for (int64_t c = 0; c < p.n_chunks; c++) {
-      const unsigned v = hp[c * 256];
+    int64_t c = 0;
+    for (; c + 8 <= p.n_chunks; c += 8) {  // eight independent loads in flight
+      unsigned v[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = __ldg(hp + (c + i) * 256);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        t += v[i];
+        if (c + i < chunk) pr += v[i];
+      }
+    }
+    for (; c < p.n_chunks; c++) {
+      const unsigned v = __ldg(hp + c * 256);
       t += v;
       if (c < chunk) pr += v;
     }
@@ -147,15 +158,15 @@ __global__ void __launch_bounds__(SEL_THREADS) select_rerank_kernel(RerankArgs a
   if (tid < 4) s_misc[tid] = 0;
   __syncthreads();
   // threshold bin: suffix sums over 256 bins (8 warps x 32 bins)
-  unsigned v = tot[tid], incl = v;
+  unsigned v = tid < 256 ? tot[tid] : 0u, incl = v;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
     unsigned o = __shfl_down_sync(0xffffffffu, incl, off);
     if (lane + off < 32) incl += o;
   }
-  if (lane == 0) s_warp[warp] = incl;
+  if (lane == 0 && warp < 8) s_warp[warp] = incl;
   __syncthreads();
-  {
+  if (tid < 256) {
     unsigned higher = 0;
     for (int w = warp + 1; w < 8; w++) higher += s_warp[w];
     const unsigned suf = incl + higher, above = suf - v;
@@ -166,7 +177,7 @@ __global__ void __launch_bounds__(SEL_THREADS) select_rerank_kernel(RerankArgs a
   }
   __syncthreads();
   const unsigned T = s_misc[0], quota = s_misc[1];
-  if ((unsigned)tid > T && pre[tid]) atomicAdd(&s_misc[2], pre[tid]);
+  if (tid < 256 && (unsigned)tid > T && pre[tid]) atomicAdd(&s_misc[2], pre[tid]);
   if ((unsigned)tid == T) s_misc[3] = pre[tid];
   __syncthreads();
   const unsigned gt_base = s_misc[2], eq_base = s_misc[3];

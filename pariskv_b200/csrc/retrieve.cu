@@ -1,5 +1,5 @@
-// The whole retrieval chain of one decode step as one host call and five launches:
-// query prep -> cluster ranking + tier table -> collision count (u8 + per-block histograms) ->
+// The whole retrieval chain of one decode step as one host call and four launches:
+// query prep + cluster ranking + tier table (one kernel) -> collision count (u8 + per-block histograms) ->
 // candidate selection fused with the 4-bit rerank -> final top-K.  All scratch comes from the caller.
 #include "common.cuh"
 #include "kernels.cuh"
@@ -109,11 +109,9 @@ extern "C" int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, con
     cd = (int64_t*)cand->data;
   }
   cudaStream_t st = (cudaStream_t)stream;
-  if ((rc = launch_query_prep((const uint16_t*)queries->data, (int)bs, (int)Hq, (int)H, (const uint16_t*)signs->data,
-                              qb, qn, qa, st)))
-    return rc;
   uint32_t* lut = (uint32_t*)(ws + lay.lut);
-  if ((rc = launch_rank(qb, (const int32_t*)cluster_key_counts->data, tier_counts, n_tiers, bh, lut, nullptr, st)))
+  if ((rc = launch_rank((const uint16_t*)queries->data, (const uint16_t*)signs->data, (int)Hq, (int)H, qb, qn, qa,
+                        (const int32_t*)cluster_key_counts->data, tier_counts, n_tiers, bh, lut, nullptr, st)))
     return rc;
   int mis = 0;
   int64_t chunk_keys = 0, n_chunks = 0;

@@ -134,7 +134,12 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
     prefix = (prefix & ~dm) | (s_res[0] << lo);
     pmask |= dm;
     rem -= s_res[1];
+    const bool whole_bin = tot[s_res[0]] == rem;  // every element of the threshold bin is selected
     cluster.sync();  // every CTA has read the remote histograms before they are cleared again
+    if (whole_bin) {
+      prefix &= pmask;  // undecided bits zero: the rest of the bin compares >= this key
+      break;
+    }
   }
   const unsigned T = prefix;  // key of the k-th element; take `rem` of the elements equal to it
 
@@ -184,14 +189,17 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
   cluster.sync();  // shared memory must outlive the remote reads above
 }
 
-// Single-block variant for rows of at most 1024 * SPAN elements: every thread keeps SPAN consecutive keys
-// in registers, so the row is read once.
+// Single-block variant for rows of at most 1024 * SPAN elements: every thread keeps SPAN consecutive
+// elements in registers, so the row is read once.  Stage A buckets the VALUES linearly between the row's
+// minimum and maximum into 2048 bins (a monotone map, so bins above the threshold bin are selected outright
+// and the histogram is spread even when fp32 bit patterns share their high bits); stage B runs the exact radix
+// select only over the few elements of the threshold bin.
 template <int SPAN>
 __global__ void __launch_bounds__(1024) topk_block_kernel(TopkParams p) {
-  __shared__ unsigned hist[256];
-  __shared__ unsigned red[2];
-  __shared__ unsigned s_tmp[16];
-  __shared__ unsigned s_res[2];
+  __shared__ unsigned hist[2048];
+  __shared__ float s_mn[32], s_mx[32];
+  __shared__ unsigned s_tmp[32];
+  __shared__ unsigned s_res[3];
   __shared__ unsigned long long s_scan[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t row_id = blockIdx.x;
@@ -199,55 +207,99 @@ __global__ void __launch_bounds__(1024) topk_block_kernel(TopkParams p) {
   const int64_t my_begin = (int64_t)tid * SPAN;
   const int nv = (int)max((int64_t)0, min((int64_t)SPAN, p.L - my_begin));
   uint32_t key[SPAN];
+  float val[SPAN];
+  float mn = INFINITY, mx = -INFINITY;
 #pragma unroll
-  for (int j = 0; j < SPAN; j++) key[j] = j < nv ? load_key(row, my_begin + j, p.is_float) : 0u;
-  if (tid == 0) {
-    red[0] = 0xffffffffu;
-    red[1] = 0u;
-  }
-  __syncthreads();
-  {
-    unsigned a = 0xffffffffu, o = 0u;
-#pragma unroll
-    for (int j = 0; j < SPAN; j++)
-      if (j < nv) {
-        a &= key[j];
-        o |= key[j];
-      }
-    a = __reduce_and_sync(0xffffffffu, a);
-    o = __reduce_or_sync(0xffffffffu, o);
-    if (lane == 0) {
-      atomicAnd(&red[0], a);
-      atomicOr(&red[1], o);
+  for (int j = 0; j < SPAN; j++) {
+    const uint32_t u = j < nv ? __ldg(row + my_begin + j) : 0u;
+    val[j] = p.is_float ? __uint_as_float(u) : (float)(int32_t)u;
+    key[j] = p.is_float ? ord_key(__uint_as_float(u)) : ord_key((int32_t)u);
+    if (j < nv) {
+      mn = fminf(mn, val[j]);
+      mx = fmaxf(mx, val[j]);
     }
   }
-  __syncthreads();
-  const unsigned A = red[0], varying = red[0] ^ red[1];
-  unsigned prefix = A, pmask = ~varying, rem = (unsigned)p.k;
-  for (int hi = 31 - __clz(varying | 0u); varying != 0 && hi >= 0; hi -= 8) {
-    const int lo = max(hi - 7, 0);
-    const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));
-    const unsigned above = hi == 31 ? 0u : ~((1u << (hi + 1)) - 1u);
-    const unsigned fixed = pmask | above;
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
 #pragma unroll
-    for (int j = 0; j < SPAN; j++)
-      if (j < nv && ((key[j] ^ prefix) & fixed) == 0) atomicAdd(&hist[(key[j] & dm) >> lo], 1u);
-    __syncthreads();
-    suffix_select(hist, rem, s_tmp, s_res, tid);
-    prefix = (prefix & ~dm) | (s_res[0] << lo);
-    pmask |= dm;
-    rem -= s_res[1];
-    __syncthreads();
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
   }
-  const unsigned T = prefix;
+  if (lane == 0) s_mn[warp] = mn, s_mx[warp] = mx;
+  hist[tid] = 0;
+  hist[tid + 1024] = 0;
+  __syncthreads();
+  mn = s_mn[lane], mx = s_mx[lane];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  float scale = 2047.0f / (mx - mn);
+  if (!(scale > 0.0f) || !(scale < INFINITY)) scale = 0.0f;  // flat or non-finite range: one bin, stage B decides
+  unsigned bin[SPAN];
+#pragma unroll
+  for (int j = 0; j < SPAN; j++) {
+    bin[j] = min(2047u, (unsigned)((val[j] - mn) * scale));
+    if (j < nv) atomicAdd(&hist[bin[j]], 1u);
+  }
+  __syncthreads();
+  // threshold bin over 2048 bins: thread t owns bins 2t, 2t+1
+  unsigned rem = (unsigned)p.k;
+  auto select_bin = [&]() {
+    const unsigned v0 = hist[2 * tid], v1 = hist[2 * tid + 1];
+    unsigned incl = v0 + v1;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      unsigned o = __shfl_down_sync(0xffffffffu, incl, off);
+      if (lane + off < 32) incl += o;
+    }
+    if (lane == 0) s_tmp[warp] = incl;
+    __syncthreads();
+    unsigned higher = 0;
+    for (int w = warp + 1; w < 32; w++) higher += s_tmp[w];
+    const unsigned suf0 = incl + higher, suf1 = suf0 - v0, ab1 = suf1 - v1;
+    if (suf1 >= rem && ab1 < rem) {
+      s_res[0] = 2 * tid + 1, s_res[1] = ab1, s_res[2] = v1;
+    } else if (suf0 >= rem && suf1 < rem) {
+      s_res[0] = 2 * tid, s_res[1] = suf1, s_res[2] = v0;
+    }
+    __syncthreads();
+  };
+  select_bin();
+  const unsigned tbin = s_res[0];
+  rem -= s_res[1];
+  const bool whole = s_res[2] == rem;  // every element of the threshold bin is selected
+  __syncthreads();
+  unsigned prefix = 0, pmask = 0;
+  if (!whole) {
+    // stage B: exact radix select of the rem-th largest key among the elements of the threshold bin
+    for (int hi = 31; hi >= 0; hi -= 11) {
+      const int lo = max(hi - 10, 0);
+      const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));
+      hist[tid] = 0;
+      hist[tid + 1024] = 0;
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < SPAN; j++)
+        if (j < nv && bin[j] == tbin && ((key[j] ^ prefix) & pmask) == 0) atomicAdd(&hist[(key[j] & dm) >> lo], 1u);
+      __syncthreads();
+      select_bin();
+      prefix = (prefix & ~dm) | (s_res[0] << lo);
+      pmask |= dm;
+      rem -= s_res[1];
+      const bool all = s_res[2] == rem;
+      __syncthreads();
+      if (all) break;  // undecided bits of prefix are zero: the rest of the bin compares >= prefix
+    }
+  }
+  const unsigned T = prefix;  // with `whole`, T = 0: every key of the threshold bin is >= T
   unsigned n_gt = 0, n_eq = 0;
 #pragma unroll
   for (int j = 0; j < SPAN; j++)
     if (j < nv) {
-      n_gt += key[j] > T;
-      n_eq += key[j] == T;
+      const bool in = bin[j] == tbin;
+      n_gt += bin[j] > tbin || (in && key[j] > T);
+      n_eq += in && key[j] == T;
     }
   unsigned long long mine = ((unsigned long long)n_gt << 32) | n_eq, incl = mine;
 #pragma unroll
@@ -266,10 +318,11 @@ __global__ void __launch_bounds__(1024) topk_block_kernel(TopkParams p) {
   for (int j = 0; j < SPAN; j++)
     if (j < nv) {
       const int64_t i = my_begin + j;
-      if (key[j] > T) {
+      const bool in = bin[j] == tbin;
+      if (bin[j] > tbin || (in && key[j] > T)) {
         out[gt_run + min(eq_run, rem)] = map ? map[i] : i;
         gt_run++;
-      } else if (key[j] == T) {
+      } else if (in && key[j] == T) {
         if (eq_run < rem) out[gt_run + eq_run] = map ? map[i] : i;
         eq_run++;
       }

@@ -117,3 +117,54 @@ def test_dropin_names_resolve():
     k = torch.randn(1, 5, 2, 128, device=DEV, dtype=torch.bfloat16)
     out = polar_prefill_attn(q, k, k, causal=True)
     assert out.shape == q.shape
+
+
+def test_cache_step_replayed_as_cuda_graph_matches_eager(oracle):
+    """The append + retrieval + attention of a layer captured once and replayed: the window position is read
+    on the device, so every replay must give the bits of the eager run."""
+    g = torch.Generator().manual_seed(21)
+    bs, H, Hq, sink, local, I, topk, P, layers = 1, 2, 8, 4, 16, 16, 32, 2300, 1
+    K0 = synth_keys(g, bs, H, P)
+    V0 = torch.randn(bs, H, P, 128, generator=g).to(torch.bfloat16)
+    caches = [_make_cache(P, 64, bs, H, Hq, sink, local, I, topk, True, layers) for _ in range(2)]
+    for c in caches:
+        c.prefill_update_kv_cache(None, K0.transpose(1, 2).contiguous().to(DEV), V0.transpose(1, 2).contiguous().to(DEV), 0, 0)
+    eager, graphed = caches
+    k_s = torch.zeros(bs, 1, H, 128, dtype=torch.bfloat16, device=DEV)
+    v_s = torch.zeros_like(k_s)
+    q_s = torch.zeros(bs, 1, Hq, 128, dtype=torch.bfloat16, device=DEV)
+    out_s = torch.zeros_like(q_s)
+    # one eager step on both first (creates workspaces outside the capture)
+    steps = []
+    for t in range(10):
+        steps.append((synth_keys(g, bs, H, 1).transpose(1, 2).contiguous(),
+                      torch.randn(bs, 1, H, 128, generator=g).to(torch.bfloat16),
+                      (torch.randn(bs, 1, Hq, 128, generator=g) * 0.5).to(torch.bfloat16)))
+    refs = []
+    for k, v, q in steps:
+        eager.decode_update_kv_cache(k.to(DEV), v.to(DEV), 0)
+        refs.append(eager.compute(q.to(DEV), 0).clone())
+    k, v, q = steps[0]
+    graphed.decode_update_kv_cache(k.to(DEV), v.to(DEV), 0)
+    assert torch.equal(graphed.compute(q.to(DEV), 0), refs[0])
+    graphed.device_positions = True
+    graphed.sync_device_state()
+    saved = graphed.host_state()
+    torch.cuda.synchronize()
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        graphed.decode_update_kv_cache(k_s, v_s, 0)
+        out_s.copy_(graphed.compute(q_s, 0))
+        graphed.advance_device_step()
+    graphed.set_host_state(saved)
+    for t in range(1, 10):
+        assert not graphed.next_step_flushes()
+        k, v, q = steps[t]
+        k_s.copy_(k)
+        v_s.copy_(v)
+        q_s.copy_(q)
+        gr.replay()
+        graphed.note_replayed_step()
+        torch.cuda.synchronize()
+        assert torch.equal(out_s, refs[t]), f"replay {t} differs from the eager step"
+    assert graphed.host_state() == eager.host_state()
