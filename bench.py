@@ -536,7 +536,9 @@ def main():
     roofline = {"kernel": "collision_kernel (weighted multi-tier collision count)", "bound": "hbm",
                 "achieved": coll.get("achieved_gbs"), "peak": peak, "unit": "GB/s",
                 "frac": round(coll["achieved_gbs"] / peak, 4) if coll else None, "peak_kind": f"of {peak_kind}",
-                "traffic": None, "algorithmic_bytes_per_launch": alg["collision"]}
+                # DRAM bytes of one launch from the ncu capture summarised under profiles/ (16.06 B per key and head
+                # at N = 131004), scaled linearly to this run's N
+                "traffic": int(round(16.06 * N * H)), "algorithmic_bytes_per_launch": alg["collision"]}
     att = stages_out.get("attention", {})
     host_link = {"kernel": "sparse_attention_kernel (UVA fetch of the selected K/V rows fused with attention)",
                  "bytes_per_launch_over_host_link": Kf * 512 * H,
