@@ -110,6 +110,23 @@ int pk_collision_fused(const pk_tensor* sorted_cluster_ids, const pk_tensor* clu
                        const pk_tensor* cache_cnt, void* workspace, int64_t workspace_bytes,
                        void* stream);
 
+/* The same count for callers that cannot allocate device memory and have no scratch buffer to pass: code
+ * running inside a serving runtime that owns the whole HBM pool, a latency-critical thread that must stay off
+ * the device allocator, a caller that only holds input and output pointers.  It has no counterpart in the
+ * reference.  The tier table lives in a 256 KB array inside the library image (held on every GPU that loads
+ * the library, until exit), so the problem is limited to pk_collision_fused_static_max_triples() = 1024
+ * (batch x head x subspace) triples, e.g. batch 8 x 8 heads x 16 subspaces; larger calls are rejected with
+ * PK_ERR_WORKSPACE.  No cudaMalloc / cudaFree or allocating library call is made.  The first call on a device
+ * looks up the array's device address (cudaGetSymbolAddress with that device current); make that first call
+ * before any stream capture begins.  All calls share the one array and it keeps the last call's table:
+ * nothing needs clearing (each call rewrites every word it reads), but two calls whose kernels may overlap on
+ * the GPU (different streams, or different host threads on different streams) race on it - serialise them.
+ * Arguments and results are those of pk_collision_fused. */
+int64_t pk_collision_fused_static_max_triples(void);
+int pk_collision_fused_static(const pk_tensor* sorted_cluster_ids, const pk_tensor* cluster_key_counts,
+                              const pk_tensor* codebook, const int64_t* tier_counts, int n_tiers,
+                              const pk_tensor* cache_cnt, void* stream);
+
 /* Single-tier unfused collision count: module update_cache_cnt.update_cache_cnt of
  * cache_hub/collision/collision.cu:161-281 (Python: collision.py:87-98).
  *   sorted_cluster_ids i32 [bs,H,B,NC]; topk_cluster_cnt i32 [bs,H,B];

@@ -41,6 +41,8 @@ SIGNATURES = {
     "pk_collision_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
     "pk_collision_fused": (_INT, [TP, TP, TP, _I64P, _INT, TP, _VP, _I64, _VP]),
     "pk_collision": (_INT, [TP, TP, TP, TP, _VP, _I64, _VP]),
+    "pk_collision_fused_static_max_triples": (_I64, []),
+    "pk_collision_fused_static": (_INT, [TP, TP, TP, _I64P, _INT, TP, _VP]),
     "pk_topk": (_INT, [TP, _I64, TP, _INT, _VP]),
     "pk_final_topk": (_INT, [TP, TP, _I64, TP, _VP]),
     "pk_adaptive_topk": (_INT, [TP, TP, _F32, TP, TP, TP, TP, _I64, _F32, _I64, _I64, _I64, TP, TP, _VP]),

@@ -4,6 +4,8 @@
 // cluster belongs to), 4 KB per (batch, head) in shared memory at a link-time address, so one look-up is a
 // byte extract, a byte load with an immediate offset and an add.  Codes are streamed with 128-bit loads,
 // every thread keeps 256 bytes in flight before it starts counting.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.cuh"
 #include "rotate.cuh"
@@ -531,4 +533,63 @@ extern "C" int pk_collision(const pk_tensor* sorted_cluster_ids, const pk_tensor
   collision_i32_kernel<<<dim3((unsigned)gx, (unsigned)(bs * H)), 256, (size_t)B * 64 * 4, st>>>(
       (const int32_t*)code_book->data, lut, (int)B, (int)NC, N, (int32_t*)cache_cnt->data);
   return check_launch("collision");
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Collision count for callers that may not allocate.
+//
+// pk_collision_fused needs a scratch table from its caller.  Some callers have nowhere to get one: a plugin
+// loaded into a serving process whose runtime has already claimed nearly all of HBM for its own pool (a
+// cudaMalloc from the plugin then fails or fragments the pool), a real-time decode thread that is forbidden to
+// touch the device allocator because an allocation can stall the whole device, or code that was handed raw
+// input / output pointers and nothing else.  For them the table lives in the array below, which is part of
+// the library image: every GPU that loads the library holds these 256 KB until the process exits.
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+constexpr int64_t kStaticTableBytes = 256 * 1024;  // tables for up to 1024 (batch x head x subspace) triples
+static __device__ __align__(256) unsigned char g_static_tier_table[kStaticTableBytes];
+
+// Device address of the array, looked up once per device.  The array's name is only a host-side handle here;
+// a kernel must be given the address that cudaGetSymbolAddress returns for the device that is current.
+static std::mutex g_static_mu;
+static void* g_static_ptr[64] = {nullptr};
+
+int static_table_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return fail(PK_ERR_CUDA, "cannot identify the current device");
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_tier_table);
+    if (e != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return fail(PK_ERR_CUDA, "cudaGetSymbolAddress(static tier table): %s", cudaGetErrorString(e));
+    }
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return PK_OK;
+}
+}  // namespace
+
+extern "C" int64_t pk_collision_fused_static_max_triples(void) { return kStaticTableBytes / 256; }
+
+extern "C" int pk_collision_fused_static(const pk_tensor* sorted_cluster_ids, const pk_tensor* cluster_key_counts,
+                                         const pk_tensor* codebook, const int64_t* tier_counts, int n_tiers,
+                                         const pk_tensor* cache_cnt, void* stream) {
+  PK_REQUIRE(codebook != nullptr && codebook->ndim == 4, "codebook must be a 4-D tensor");
+  const int64_t triples = codebook->shape[0] * codebook->shape[1] * codebook->shape[2];
+  if (triples * 256 > kStaticTableBytes)
+    return fail(PK_ERR_WORKSPACE,
+                "pk_collision_fused_static handles at most %lld (batch x head x subspace) triples, got %lld; use "
+                "pk_collision_fused with caller-provided scratch for larger problems",
+                (long long)(kStaticTableBytes / 256), (long long)triples);
+  void* table = nullptr;
+  const int rc = static_table_address(&table);
+  if (rc) return rc;
+  // The table kernel rewrites every word that the counting kernel reads (64 words per triple), so nothing left
+  // over from an earlier call can leak into this one and nothing has to be cleared.
+  return pk_collision_fused(sorted_cluster_ids, cluster_key_counts, codebook, tier_counts, n_tiers, cache_cnt, table,
+                            kStaticTableBytes, stream);
 }

@@ -114,6 +114,19 @@ def collision_fused(sorted_cluster_ids, cluster_key_counts, codebook, tier_count
     return cache_cnt
 
 
+def collision_fused_static(sorted_cluster_ids, cluster_key_counts, codebook, tier_counts, cache_cnt):
+    """collision_fused for callers that must not allocate: the caller passes the output tensor, the tier table
+    lives in a fixed 256 KB array inside the library (at most 1024 batch x head x subspace triples).  Calls
+    share that array, so do not let two of them overlap on the GPU; make the first call on a device before any
+    stream capture."""
+    _require_cuda(sorted_cluster_ids, cluster_key_counts, codebook, cache_cnt)
+    tiers = L.i64_array(list(tier_counts))
+    d = [L.desc(t) for t in (sorted_cluster_ids, cluster_key_counts, codebook, cache_cnt)]
+    _call("pk_collision_fused_static", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), tiers, len(tier_counts), L.ref(d[3]),
+          L.stream_ptr(codebook.device))
+    return cache_cnt
+
+
 def collision(sorted_cluster_ids, topk_cluster_cnt, code_book, cache_cnt):
     """Unfused single-tier op; code_book is int32 [bs,H,N,B] (the kernel-side layout)."""
     _require_cuda(sorted_cluster_ids, topk_cluster_cnt, code_book, cache_cnt)
