@@ -65,35 +65,30 @@ class DecoderHarness:
         ones = lambda n: torch.ones(n, device=device, dtype=torch.bfloat16)
         self.ln1 = [ones(Hd) for _ in range(L)]
         self.ln2 = [ones(Hd) for _ in range(L)]
-        self.qn = [ones(D) for _ in range(L)]
-        self.kn = [ones(D) for _ in range(L)]
+        # per-head-dim norm weights of q and k (Qwen3), stacked so both are applied in one multiply
+        self.qkn = [torch.cat([ones(D).expand(Hq, D), ones(D).expand(Hk, D)]).contiguous() for _ in range(L)]
         self.lnf = ones(Hd)
         self._inv_freq = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, D, 2, device=device, dtype=torch.float32) / D))
 
-    @staticmethod
-    def rope(x, cos, sin):
-        """x [1, heads, 128]; rotate-half RoPE with the step's cos / sin [64]."""
-        x1, x2 = x[..., :64].float(), x[..., 64:].float()
-        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1).to(torch.bfloat16)
-
     def step(self, cache, token, pos_dev=None):
         """One decode token through all layers; token: int64 [1] on the device.  Returns next token [1].
-        pos_dev (float32 [1] on the device) replaces the host-side position when the step is captured."""
+        pos_dev (float32 [1] on the device) replaces the host-side position when the step is captured.
+        q and k share one RMS-norm and one rotate-half RoPE call per layer (stacked per-head weights)."""
         c = self.cfg
         Hq, Hk, D = c["q_heads"], c["kv_heads"], c["head_dim"]
         ang = (pos_dev if pos_dev is not None else cache.context) * self._inv_freq
-        cos, sin = torch.cos(ang), torch.sin(ang)
-        h = self.embed[token]                                   # [1, hidden]
+        cos = torch.cos(ang).repeat(2).to(torch.bfloat16)          # [128]
+        sin = torch.sin(ang)
+        sin = torch.cat([-sin, sin]).to(torch.bfloat16)            # sign of rotate-half folded in
+        h = self.embed[token]                                      # [1, hidden]
         for l in range(c["layers"]):
             x = F.rms_norm(h, (c["hidden"],), self.ln1[l], 1e-6)
             qkv = F.linear(x, self.wqkv[l])
-            q = qkv[:, :Hq * D].view(1, Hq, D)
-            k = qkv[:, Hq * D:(Hq + Hk) * D].view(1, Hk, D)
+            qk = F.rms_norm(qkv[:, :(Hq + Hk) * D].view(1, Hq + Hk, D), (D,), None, 1e-6) * self.qkn[l]
+            qk = qk * cos + torch.roll(qk, 64, -1) * sin            # rotate-half RoPE
             v = qkv[:, (Hq + Hk) * D:].view(1, 1, Hk, D)
-            q = self.rope(F.rms_norm(q, (D,), self.qn[l], 1e-6), cos, sin)
-            k = self.rope(F.rms_norm(k, (D,), self.kn[l], 1e-6), cos, sin)
-            cache.decode_update_kv_cache(k.view(1, 1, Hk, D), v, l)
-            attn = cache.compute(q.view(1, 1, Hq, D), l)
+            cache.decode_update_kv_cache(qk[:, Hq:].view(1, 1, Hk, D), v, l)
+            attn = cache.compute(qk[:, :Hq].view(1, 1, Hq, D), l)
             h = h + F.linear(attn.view(1, Hq * D), self.wo[l])
             x = F.rms_norm(h, (c["hidden"],), self.ln2[l], 1e-6)
             gu = F.linear(x, self.wgu[l])

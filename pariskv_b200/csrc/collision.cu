@@ -81,27 +81,34 @@ struct RankParams {
 };
 
 __global__ void __launch_bounds__(256) rank_kernel(RankParams p) {
-  __shared__ float sc[256];
-  __shared__ int cn[256];
+  // entry o: x = sortable key ((ordered bf16 score) << 8 | (255 - o)), y = keys in cluster o
+  __shared__ __align__(16) uint2 ent[256];
   __shared__ unsigned nib[256];
   __shared__ float s_q[8];
   const int c = threadIdx.x;
   const int64_t blk = blockIdx.x;  // (b*H + h)*16 + subspace
   const int64_t bh = blk >> 4;
   const int sub = (int)(blk & 15);
+  const unsigned my_cnt = p.counts ? (unsigned)__ldg(p.counts + blk * 256 + c) : 0u;
   if (p.queries) {
     if (c < 32) {
       const int s = c & 7;
       const int b = (int)(bh / p.H), h = (int)(bh % p.H);
       const uint16_t* q = p.queries + ((int64_t)b * p.Hq + (int64_t)h * p.G) * 128 + 16 * s;
-      float x[16], sg[16];
+      float x[16], sg[16], acc[16];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.signs + 16 * s)), sg);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.signs + 16 * s) + 1), sg + 8);
 #pragma unroll
-      for (int i = 0; i < 16; i++) {
-        float acc = 0.0f;
-        for (int g = 0; g < p.G; g++) acc = __fadd_rn(acc, bf2f(q[g * 128 + i]));
-        x[i] = bfround(__fmul_rn(acc, p.inv_g));
-        sg[i] = bf2f(p.signs[16 * s + i]);
+      for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+      for (int g = 0; g < p.G; g++) {  // fp32 sum over the group, g ascending
+        float v[16];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(q + g * 128)), v);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(q + g * 128) + 1), v + 8);
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc[i] = __fadd_rn(acc[i], v[i]);
       }
+#pragma unroll
+      for (int i = 0; i < 16; i++) x[i] = bfround(__fmul_rn(acc[i], p.inv_g));
       if (sub == 0 && p.query_avg && c < 8)
 #pragma unroll
         for (int i = 0; i < 16; i++) p.query_avg[bh * 128 + 16 * s + i] = f2bf(x[i]);
@@ -120,7 +127,6 @@ __global__ void __launch_bounds__(256) rank_kernel(RankParams p) {
   } else if (c < 8) {
     s_q[c] = bf2f(p.q_blocks[blk * 8 + c]);
   }
-  cn[c] = p.counts ? p.counts[blk * 256 + c] : 0;
   __syncthreads();
   float s = 0.0f;
 #pragma unroll
@@ -128,22 +134,26 @@ __global__ void __launch_bounds__(256) rank_kernel(RankParams p) {
     const float qv = s_q[j];
     s = __fadd_rn(s, ((c >> j) & 1) ? qv : -qv);
   }
-  s = bfround(s);
-  sc[c] = s;
+  // order of (score descending, id ascending) as one unsigned compare; -0 counts as +0 like a float compare
+  unsigned bits = f2bf(s);
+  if (bits == 0x8000u) bits = 0u;
+  const unsigned ord = (bits & 0x8000u) ? (~bits & 0xFFFFu) : (bits | 0x8000u);
+  const unsigned my_key = (ord << 8) | (unsigned)(255 - c);
+  ent[c] = make_uint2(my_key, my_cnt);
   __syncthreads();
-  long long excl = 0;
-  int rank = 0;
-#pragma unroll 8
-  for (int o = 0; o < 256; o++) {
-    const float so = sc[o];
-    const bool before = (so > s) || (so == s && o < c);
-    rank += before;
-    excl += before ? cn[o] : 0;
+  unsigned excl = 0, rank = 0;
+  const uint4* e4 = reinterpret_cast<const uint4*>(ent);
+#pragma unroll 16
+  for (int o = 0; o < 128; o++) {
+    const uint4 e = e4[o];  // two entries per 128-bit read (a broadcast: every thread reads the same word)
+    const bool b0 = e.x > my_key, b1 = e.z > my_key;
+    rank += (unsigned)b0 + (unsigned)b1;
+    excl += (b0 ? e.y : 0u) + (b1 ? e.w : 0u);
   }
   if (p.sorted_ids) p.sorted_ids[blk * 256 + rank] = c;
   if (p.lut) {
     unsigned wgt = 0;
-    for (int t = 0; t < p.tiers.n; t++) wgt += (excl < p.tiers.t[t]);
+    for (int t = 0; t < p.tiers.n; t++) wgt += ((long long)excl < p.tiers.t[t]);
     nib[c] = wgt;
     __syncthreads();
     if (c < 64) {

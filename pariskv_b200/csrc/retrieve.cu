@@ -57,6 +57,8 @@ extern "C" int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, con
              "queries must be contiguous [bs,1,Hq,128] with Hq a multiple of H");
   PK_REQUIRE(signs->shape[0] == 128 && signs->stride[0] == 1 && mag_centers->shape[0] == 8 && mag_centers->stride[0] == 1,
              "signs must be [128], mag_centers [8]");
+  PK_REQUIRE((reinterpret_cast<uintptr_t>(queries->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(signs->data) & 15) == 0,
+             "queries and signs must be 16-byte aligned");
   PK_REQUIRE(is_contig(cluster_key_counts) && cluster_key_counts->shape[0] == bs && cluster_key_counts->shape[1] == H &&
                  cluster_key_counts->shape[2] == 16 && cluster_key_counts->shape[3] == 256,
              "cluster_key_counts must be contiguous [bs,H,16,256]");

@@ -1,14 +1,16 @@
 // Exact, deterministic top-k of rows of 32-bit values (int32 counts or fp32 scores).
 //
-// One thread-block cluster per row: the row is cut into contiguous slices, one per CTA; digit
-// histograms live in each CTA's shared memory and are summed across the cluster through distributed
-// shared memory, so the whole selection (varying-bit probe, up to four 8-bit radix passes, tie quota,
-// ordered emission) is ONE launch with no global scratch.  Digits are cut from the highest bit on which
-// the elements of the row differ, so collision counts (0..96) need a single histogram pass and fp32 scores
-// spread over the first histogram instead of piling into two exponent bins.  Rows of up to 16384
-// elements take a single-block variant that keeps the keys in registers.
+// One thread-block cluster per row: the row is cut into contiguous slices, one per CTA, and all exchange
+// between the CTAs goes through distributed shared memory, so the whole selection is ONE launch with no
+// global scratch.  Stage A buckets the VALUES linearly between the row's minimum and maximum into 2048 bins
+// (a monotone map: bins above the threshold bin are selected outright, and the histogram is spread even when
+// fp32 bit patterns share their high bits); stage B runs an exact 11-bit radix select over the few elements
+// of the threshold bin.  Histograms are reduced by segments: CTA r sums bins [r*2048/n, (r+1)*2048/n) over the
+// cluster, the CTA whose segment holds the threshold finds it and publishes it.
 // Selected set: first k of (value descending, index ascending); emitted in ascending index.
 #include <cooperative_groups.h>
+
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.cuh"
@@ -18,7 +20,8 @@ namespace cg = cooperative_groups;
 namespace pk {
 namespace {
 
-constexpr int TK_THREADS = 512;
+constexpr int TK_THREADS = 256;
+constexpr int TK_BINS = 2048;
 
 struct TopkParams {
   const uint32_t* in;
@@ -29,126 +32,214 @@ struct TopkParams {
   int64_t map_stride;
 };
 
+constexpr int TK_CACHE = 4096;  // elements of a CTA's slice kept in shared memory (the rest is re-read from L2)
+
 __device__ __forceinline__ uint32_t load_key(const uint32_t* row, int64_t i, int is_float) {
   const uint32_t u = __ldg(row + i);
   return is_float ? ord_key(__uint_as_float(u)) : ord_key((int32_t)u);
 }
+__device__ __forceinline__ uint32_t key_of(uint32_t u, int is_float) {
+  return is_float ? ord_key(__uint_as_float(u)) : ord_key((int32_t)u);
+}
+__device__ __forceinline__ float val_of(uint32_t u, int is_float) {
+  return is_float ? __uint_as_float(u) : (float)(int32_t)u;
+}
 
-// Among 256 bins (tot[b] valid for tid < 256, in shared memory), find the bin where the suffix sum
-// first reaches `rem`: returns bin and the number of elements in higher bins.
-__device__ void suffix_select(const unsigned* tot, unsigned rem, unsigned* s_tmp, unsigned* s_res, int tid) {
-  // s_tmp[0..7]: per-warp totals; warps 0..7 cover bins 32w..32w+31
+// Threshold bin of a[0..n) (shared memory, n a multiple of 256 or n < 256 a power of two): the bin where the
+// suffix sum first reaches rem.  Result (bin, elements in higher bins, elements in the bin) in res[0..2].
+__device__ void block_select(const unsigned* a, int n, unsigned rem, unsigned* s_warp, unsigned* res, int tid) {
   const int lane = tid & 31, warp = tid >> 5;
-  unsigned v = 0, incl = 0;
-  if (warp < 8) {
-    v = tot[tid];
-    incl = v;  // inclusive suffix within the warp: sum of lanes >= lane
+  const int per = max(1, n / TK_THREADS);
+  const int b0 = tid * per;
+  unsigned mine = 0;
+  if (b0 < n)
+    for (int i = 0; i < per; i++) mine += a[b0 + i];
+  unsigned incl = mine;  // inclusive suffix over threads
 #pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      unsigned o = __shfl_down_sync(0xffffffffu, incl, off);
-      if (lane + off < 32) incl += o;
-    }
-    if (lane == 0) s_tmp[warp] = incl;
+  for (int off = 1; off < 32; off <<= 1) {
+    unsigned o = __shfl_down_sync(0xffffffffu, incl, off);
+    if (lane + off < 32) incl += o;
   }
+  if (lane == 0) s_warp[warp] = incl;
   __syncthreads();
-  if (warp < 8) {
-    unsigned higher = 0;
-    for (int w = warp + 1; w < 8; w++) higher += s_tmp[w];
-    const unsigned suf = incl + higher;        // elements in bins >= tid
-    const unsigned above = suf - v;            // elements in bins > tid
-    if (suf >= rem && above < rem) {
-      s_res[0] = (unsigned)tid;
-      s_res[1] = above;
+  unsigned higher = 0;
+  for (int w = warp + 1; w < TK_THREADS / 32; w++) higher += s_warp[w];
+  const unsigned suf = incl + higher;  // elements in bins >= b0
+  unsigned above = suf - mine;         // elements in bins >= b0 + per
+  if (b0 < n && suf >= rem && above < rem) {
+    for (int i = per - 1; i >= 0; i--) {  // walk my bins from the top
+      const unsigned v = a[b0 + i];
+      if (above + v >= rem) {
+        res[0] = (unsigned)(b0 + i), res[1] = above, res[2] = v;
+        break;
+      }
+      above += v;
     }
   }
   __syncthreads();
 }
 
+// NCTA (cluster size) is a template parameter so that every loop over the ranks is unrolled and its remote
+// shared-memory loads are issued together instead of one round trip after the other.
+template <int NCTA>
 __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) {
   cg::cluster_group cluster = cg::this_cluster();
-  __shared__ unsigned hist[256];
-  __shared__ unsigned tot[256];
-  __shared__ unsigned red[4];     // and, or, n_gt, n_eq of this CTA
-  __shared__ unsigned s_tmp[16];
-  __shared__ unsigned s_res[2];
+  __shared__ unsigned hist[TK_BINS];
+  __shared__ unsigned seg[TK_BINS];        // my segment of the cluster-wide histogram (seg_bins entries used)
+  __shared__ float cl_mm[2];               // min, max of my slice
+  __shared__ unsigned cl_segtot;           // elements in my segment
+  __shared__ unsigned cl_res[3];           // published by the CTA that owns the threshold bin
+  __shared__ unsigned cl_cnt[2];           // n_gt, n_eq of my slice
+  __shared__ unsigned s_warp[TK_THREADS / 32];
+  __shared__ float s_f[2 * TK_THREADS / 32];
   __shared__ unsigned long long s_scan[TK_THREADS / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const unsigned rank = cluster.block_rank(), ncta = cluster.num_blocks();
+  const unsigned rank = cluster.block_rank();
+  constexpr unsigned ncta = NCTA;
   const int64_t row_id = blockIdx.y;
   const uint32_t* row = p.in + row_id * p.row_stride;
-  const int64_t per = (p.L + ncta - 1) / ncta;
-  const int64_t begin = min(p.L, (int64_t)rank * per), end = min(p.L, begin + per);
-  const int64_t span = (per + TK_THREADS - 1) / TK_THREADS;
+  const int64_t per_cta = (p.L + ncta - 1) / ncta;
+  const int64_t begin = min(p.L, (int64_t)rank * per_cta), end = min(p.L, begin + per_cta);
+  const int64_t span = (per_cta + TK_THREADS - 1) / TK_THREADS;
   const int64_t my_begin = min(end, begin + tid * span), my_end = min(end, my_begin + span);
+  constexpr int seg_bins = TK_BINS / NCTA;
 
-  // ---- which bits vary over the row ----
-  if (tid == 0) {
-    red[0] = 0xffffffffu;
-    red[1] = 0u;
-  }
+  // ---- the slice is read once, coalesced, into shared memory; every pass below works from there ----
+  __shared__ uint32_t cache[TK_CACHE];
+  const int cache_n = (int)min((int64_t)TK_CACHE, end - begin);
+#pragma unroll 4
+  for (int j = tid; j < cache_n; j += TK_THREADS) cache[j] = __ldg(row + begin + j);
   __syncthreads();
-  {
-    unsigned a = 0xffffffffu, o = 0u;
-    for (int64_t i = my_begin; i < my_end; i++) {
-      const uint32_t k = load_key(row, i, p.is_float);
-      a &= k;
-      o |= k;
+  auto raw = [&](int64_t i) -> uint32_t { return i - begin < cache_n ? cache[i - begin] : __ldg(row + i); };
+
+  // ---- range of the row ----
+  float mn = INFINITY, mx = -INFINITY;
+  for (int64_t i = my_begin; i < my_end; i++) {
+    const float v = val_of(raw(i), p.is_float);
+    mn = fminf(mn, v);
+    mx = fmaxf(mx, v);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  if (lane == 0) s_f[warp] = mn, s_f[TK_THREADS / 32 + warp] = mx;
+  for (int i = tid; i < TK_BINS; i += TK_THREADS) hist[i] = 0;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < TK_THREADS / 32; w++) {
+      mn = fminf(mn, s_f[w]);
+      mx = fmaxf(mx, s_f[TK_THREADS / 32 + w]);
     }
-    a = __reduce_and_sync(0xffffffffu, a);
-    o = __reduce_or_sync(0xffffffffu, o);
-    if (lane == 0) {
-      atomicAnd(&red[0], a);
-      atomicOr(&red[1], o);
-    }
+    cl_mm[0] = mn, cl_mm[1] = mx;
   }
   cluster.sync();
-  unsigned A = 0xffffffffu, O = 0u;
-  for (unsigned r = 0; r < ncta; r++) {
-    const unsigned* rr = cluster.map_shared_rank(red, r);
-    A &= rr[0];
-    O |= rr[1];
+  {
+    float a[NCTA], b[NCTA];
+#pragma unroll
+    for (int r = 0; r < NCTA; r++) {
+      const float* mm = cluster.map_shared_rank(cl_mm, r);
+      a[r] = mm[0], b[r] = mm[1];
+    }
+    mn = a[0], mx = b[0];
+#pragma unroll
+    for (int r = 1; r < NCTA; r++) mn = fminf(mn, a[r]), mx = fmaxf(mx, b[r]);
   }
-  const unsigned varying = A ^ O;
+  float scale = (float)(TK_BINS - 1) / (mx - mn);
+  if (!(scale > 0.0f) || !(scale < INFINITY)) scale = 0.0f;  // flat or non-finite range: one bin, stage B decides
+  auto bin_of = [&](float v) -> unsigned { return min((unsigned)(TK_BINS - 1), (unsigned)((v - mn) * scale)); };
 
-  // ---- radix passes from the highest varying bit down, 8 bits at a time ----
-  unsigned prefix = A, pmask = ~varying, rem = (unsigned)p.k;  // bits that never vary are already decided
-  for (int hi = 31 - __clz(varying | 0u); varying != 0 && hi >= 0; hi -= 8) {
-    const int lo = max(hi - 7, 0);
-    const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));  // bits lo..hi
-    const unsigned above = hi == 31 ? 0u : ~((1u << (hi + 1)) - 1u);        // bits above hi
-    const unsigned fixed = pmask | above;
-    if (tid < 256) hist[tid] = 0;
+  // Cluster-wide threshold bin of the local histograms `hist`: every CTA returns the same (bin, above, count).
+  auto cluster_select = [&](unsigned rem, unsigned& bin, unsigned& above, unsigned& count) {
+    cluster.sync();  // all local histograms are complete
+    unsigned part = 0;
+    for (int i = tid; i < seg_bins; i += TK_THREADS) {
+      unsigned v[NCTA];
+#pragma unroll
+      for (int r = 0; r < NCTA; r++) v[r] = cluster.map_shared_rank(hist, r)[rank * seg_bins + i];
+      unsigned t = 0;
+#pragma unroll
+      for (int r = 0; r < NCTA; r++) t += v[r];
+      seg[i] = t;
+      part += t;
+    }
+    part = __reduce_add_sync(0xffffffffu, part);
+    if (lane == 0) s_warp[warp] = part;
     __syncthreads();
-    for (int64_t i = my_begin; i < my_end; i++) {
-      const uint32_t k = load_key(row, i, p.is_float);
-      if (((k ^ prefix) & fixed) == 0) atomicAdd(&hist[(k & dm) >> lo], 1u);
+    if (tid == 0) {
+      unsigned t = 0;
+      for (int w = 0; w < TK_THREADS / 32; w++) t += s_warp[w];
+      cl_segtot = t;
+    }
+    cluster.sync();  // segment totals are published; nobody reads remote histograms any more
+    unsigned st[NCTA];
+#pragma unroll
+    for (int r = 0; r < NCTA; r++) st[r] = *cluster.map_shared_rank(&cl_segtot, r);
+    unsigned higher = 0;
+    int owner = 0;
+    bool found = false;
+#pragma unroll
+    for (int r = NCTA - 1; r >= 0; r--) {
+      if (!found) {
+        if (higher + st[r] >= rem) {
+          owner = r;
+          found = true;
+        } else {
+          higher += st[r];
+        }
+      }
+    }
+    if ((int)rank == owner) {
+      block_select(seg, seg_bins, rem - higher, s_warp, cl_res, tid);
+      if (tid == 0) {
+        cl_res[0] += owner * seg_bins;
+        cl_res[1] += higher;
+      }
     }
     cluster.sync();
-    if (tid < 256) {
-      unsigned t = 0;
-      for (unsigned r = 0; r < ncta; r++) t += cluster.map_shared_rank(hist, r)[tid];
-      tot[tid] = t;
-    }
-    __syncthreads();
-    suffix_select(tot, rem, s_tmp, s_res, tid);
-    prefix = (prefix & ~dm) | (s_res[0] << lo);
-    pmask |= dm;
-    rem -= s_res[1];
-    const bool whole_bin = tot[s_res[0]] == rem;  // every element of the threshold bin is selected
-    cluster.sync();  // every CTA has read the remote histograms before they are cleared again
-    if (whole_bin) {
-      prefix &= pmask;  // undecided bits zero: the rest of the bin compares >= this key
-      break;
+    const unsigned* res = cluster.map_shared_rank(cl_res, owner);
+    bin = res[0], above = res[1], count = res[2];
+  };
+
+  // ---- stage A: value buckets ----
+  for (int64_t i = my_begin; i < my_end; i++) atomicAdd(&hist[bin_of(val_of(raw(i), p.is_float))], 1u);
+  unsigned rem = (unsigned)p.k, tbin, ab, cb;
+  cluster_select(rem, tbin, ab, cb);
+  rem -= ab;
+  unsigned prefix = 0, pmask = 0;
+  if (cb != rem) {
+    // ---- stage B: exact radix select of the rem-th largest key among the elements of the threshold bin ----
+    for (int hi = 31; hi >= 0; hi -= 11) {
+      const int lo = max(hi - 10, 0);
+      const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));
+      // remote reads of `hist` ended before the second barrier of the previous cluster_select
+      for (int i = tid; i < TK_BINS; i += TK_THREADS) hist[i] = 0;
+      __syncthreads();
+      for (int64_t i = my_begin; i < my_end; i++) {
+        const uint32_t u = raw(i);
+        if (bin_of(val_of(u, p.is_float)) != tbin) continue;
+        const uint32_t k = key_of(u, p.is_float);
+        if (((k ^ prefix) & pmask) == 0) atomicAdd(&hist[(k & dm) >> lo], 1u);
+      }
+      unsigned dbin;
+      cluster_select(rem, dbin, ab, cb);
+      prefix = (prefix & ~dm) | (dbin << lo);
+      pmask |= dm;
+      rem -= ab;
+      if (cb == rem) break;  // the whole digit bin is taken; undecided bits of prefix stay zero
     }
   }
-  const unsigned T = prefix;  // key of the k-th element; take `rem` of the elements equal to it
+  const unsigned T = prefix;  // with the whole threshold bin taken T = 0 and every key of the bin is >= T
 
   // ---- count, scan, emit in index order ----
   unsigned n_gt = 0, n_eq = 0;
   for (int64_t i = my_begin; i < my_end; i++) {
-    const uint32_t k = load_key(row, i, p.is_float);
-    n_gt += (k > T);
-    n_eq += (k == T);
+    const uint32_t u = raw(i);
+    const unsigned b = bin_of(val_of(u, p.is_float));
+    const uint32_t k = key_of(u, p.is_float);
+    n_gt += b > tbin || (b == tbin && k > T);
+    n_eq += b == tbin && k == T;
   }
   unsigned long long mine = ((unsigned long long)n_gt << 32) | n_eq, incl = mine;
 #pragma unroll
@@ -164,169 +255,37 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
     total += s_scan[w];
   }
   if (tid == 0) {
-    red[2] = (unsigned)(total >> 32);
-    red[3] = (unsigned)total;
+    cl_cnt[0] = (unsigned)(total >> 32);
+    cl_cnt[1] = (unsigned)total;
   }
   cluster.sync();
   unsigned gt_run = (unsigned)((base + incl - mine) >> 32), eq_run = (unsigned)(base + incl - mine);
-  for (unsigned r = 0; r < rank; r++) {
-    const unsigned* rr = cluster.map_shared_rank(red, r);
-    gt_run += rr[2];
-    eq_run += rr[3];
+  {
+    unsigned g[NCTA], e[NCTA];
+#pragma unroll
+    for (int r = 0; r < NCTA; r++) {
+      const unsigned* c2 = cluster.map_shared_rank(cl_cnt, r);
+      g[r] = c2[0], e[r] = c2[1];
+    }
+#pragma unroll
+    for (int r = 0; r < NCTA; r++)
+      if ((unsigned)r < rank) gt_run += g[r], eq_run += e[r];
   }
   int64_t* out = p.out + row_id * p.k;
   const int64_t* map = p.map ? p.map + row_id * p.map_stride : nullptr;
   for (int64_t i = my_begin; i < my_end; i++) {
-    const uint32_t k = load_key(row, i, p.is_float);
-    if (k > T) {
+    const uint32_t u = raw(i);
+    const unsigned b = bin_of(val_of(u, p.is_float));
+    const uint32_t k = key_of(u, p.is_float);
+    if (b > tbin || (b == tbin && k > T)) {
       out[gt_run + min(eq_run, rem)] = map ? map[i] : i;
       gt_run++;
-    } else if (k == T) {
+    } else if (b == tbin && k == T) {
       if (eq_run < rem) out[gt_run + eq_run] = map ? map[i] : i;
       eq_run++;
     }
   }
   cluster.sync();  // shared memory must outlive the remote reads above
-}
-
-// Single-block variant for rows of at most 1024 * SPAN elements: every thread keeps SPAN consecutive
-// elements in registers, so the row is read once.  Stage A buckets the VALUES linearly between the row's
-// minimum and maximum into 2048 bins (a monotone map, so bins above the threshold bin are selected outright
-// and the histogram is spread even when fp32 bit patterns share their high bits); stage B runs the exact radix
-// select only over the few elements of the threshold bin.
-template <int SPAN>
-__global__ void __launch_bounds__(1024) topk_block_kernel(TopkParams p) {
-  __shared__ unsigned hist[2048];
-  __shared__ float s_mn[32], s_mx[32];
-  __shared__ unsigned s_tmp[32];
-  __shared__ unsigned s_res[3];
-  __shared__ unsigned long long s_scan[32];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t row_id = blockIdx.x;
-  const uint32_t* row = p.in + row_id * p.row_stride;
-  const int64_t my_begin = (int64_t)tid * SPAN;
-  const int nv = (int)max((int64_t)0, min((int64_t)SPAN, p.L - my_begin));
-  uint32_t key[SPAN];
-  float val[SPAN];
-  float mn = INFINITY, mx = -INFINITY;
-#pragma unroll
-  for (int j = 0; j < SPAN; j++) {
-    const uint32_t u = j < nv ? __ldg(row + my_begin + j) : 0u;
-    val[j] = p.is_float ? __uint_as_float(u) : (float)(int32_t)u;
-    key[j] = p.is_float ? ord_key(__uint_as_float(u)) : ord_key((int32_t)u);
-    if (j < nv) {
-      mn = fminf(mn, val[j]);
-      mx = fmaxf(mx, val[j]);
-    }
-  }
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  }
-  if (lane == 0) s_mn[warp] = mn, s_mx[warp] = mx;
-  hist[tid] = 0;
-  hist[tid + 1024] = 0;
-  __syncthreads();
-  mn = s_mn[lane], mx = s_mx[lane];
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-  }
-  float scale = 2047.0f / (mx - mn);
-  if (!(scale > 0.0f) || !(scale < INFINITY)) scale = 0.0f;  // flat or non-finite range: one bin, stage B decides
-  unsigned bin[SPAN];
-#pragma unroll
-  for (int j = 0; j < SPAN; j++) {
-    bin[j] = min(2047u, (unsigned)((val[j] - mn) * scale));
-    if (j < nv) atomicAdd(&hist[bin[j]], 1u);
-  }
-  __syncthreads();
-  // threshold bin over 2048 bins: thread t owns bins 2t, 2t+1
-  unsigned rem = (unsigned)p.k;
-  auto select_bin = [&]() {
-    const unsigned v0 = hist[2 * tid], v1 = hist[2 * tid + 1];
-    unsigned incl = v0 + v1;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      unsigned o = __shfl_down_sync(0xffffffffu, incl, off);
-      if (lane + off < 32) incl += o;
-    }
-    if (lane == 0) s_tmp[warp] = incl;
-    __syncthreads();
-    unsigned higher = 0;
-    for (int w = warp + 1; w < 32; w++) higher += s_tmp[w];
-    const unsigned suf0 = incl + higher, suf1 = suf0 - v0, ab1 = suf1 - v1;
-    if (suf1 >= rem && ab1 < rem) {
-      s_res[0] = 2 * tid + 1, s_res[1] = ab1, s_res[2] = v1;
-    } else if (suf0 >= rem && suf1 < rem) {
-      s_res[0] = 2 * tid, s_res[1] = suf1, s_res[2] = v0;
-    }
-    __syncthreads();
-  };
-  select_bin();
-  const unsigned tbin = s_res[0];
-  rem -= s_res[1];
-  const bool whole = s_res[2] == rem;  // every element of the threshold bin is selected
-  __syncthreads();
-  unsigned prefix = 0, pmask = 0;
-  if (!whole) {
-    // stage B: exact radix select of the rem-th largest key among the elements of the threshold bin
-    for (int hi = 31; hi >= 0; hi -= 11) {
-      const int lo = max(hi - 10, 0);
-      const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));
-      hist[tid] = 0;
-      hist[tid + 1024] = 0;
-      __syncthreads();
-#pragma unroll
-      for (int j = 0; j < SPAN; j++)
-        if (j < nv && bin[j] == tbin && ((key[j] ^ prefix) & pmask) == 0) atomicAdd(&hist[(key[j] & dm) >> lo], 1u);
-      __syncthreads();
-      select_bin();
-      prefix = (prefix & ~dm) | (s_res[0] << lo);
-      pmask |= dm;
-      rem -= s_res[1];
-      const bool all = s_res[2] == rem;
-      __syncthreads();
-      if (all) break;  // undecided bits of prefix are zero: the rest of the bin compares >= prefix
-    }
-  }
-  const unsigned T = prefix;  // with `whole`, T = 0: every key of the threshold bin is >= T
-  unsigned n_gt = 0, n_eq = 0;
-#pragma unroll
-  for (int j = 0; j < SPAN; j++)
-    if (j < nv) {
-      const bool in = bin[j] == tbin;
-      n_gt += bin[j] > tbin || (in && key[j] > T);
-      n_eq += in && key[j] == T;
-    }
-  unsigned long long mine = ((unsigned long long)n_gt << 32) | n_eq, incl = mine;
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    unsigned long long o = __shfl_up_sync(0xffffffffu, incl, off);
-    if (lane >= off) incl += o;
-  }
-  if (lane == 31) s_scan[warp] = incl;
-  __syncthreads();
-  unsigned long long base = 0;
-  for (int w = 0; w < warp; w++) base += s_scan[w];
-  unsigned gt_run = (unsigned)((base + incl - mine) >> 32), eq_run = (unsigned)(base + incl - mine);
-  int64_t* out = p.out + row_id * p.k;
-  const int64_t* map = p.map ? p.map + row_id * p.map_stride : nullptr;
-#pragma unroll
-  for (int j = 0; j < SPAN; j++)
-    if (j < nv) {
-      const int64_t i = my_begin + j;
-      const bool in = bin[j] == tbin;
-      if (bin[j] > tbin || (in && key[j] > T)) {
-        out[gt_run + min(eq_run, rem)] = map ? map[i] : i;
-        gt_run++;
-      } else if (in && key[j] == T) {
-        if (eq_run < rem) out[gt_run + eq_run] = map ? map[i] : i;
-        eq_run++;
-      }
-    }
 }
 
 // Reorders an emitted top-k list by (value descending, index ascending): one block per row, k <= 4096.
@@ -372,30 +331,25 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
   p.is_float = is_float ? 1 : 0;
   p.row_stride = row_stride, p.L = L, p.k = k;
   p.out = out, p.map = map, p.map_stride = map_stride;
-  if (L <= 16384) {
-    if (L <= 4096)
-      topk_block_kernel<4><<<(unsigned)rows, 1024, 0, st>>>(p);
-    else if (L <= 8192)
-      topk_block_kernel<8><<<(unsigned)rows, 1024, 0, st>>>(p);
-    else
-      topk_block_kernel<16><<<(unsigned)rows, 1024, 0, st>>>(p);
-    int rc0 = check_launch("topk");
-    if (rc0 || order == 0) return rc0;
-    int kp0 = 1;
-    while (kp0 < k) kp0 <<= 1;
-    sort_by_value_kernel<<<(unsigned)rows, 1024, (size_t)kp0 * 8, st>>>(p.in, p.is_float, row_stride, k, kp0, out);
-    return check_launch("topk sort");
-  }
+  // about 1024 elements per CTA, at most 16 CTAs per row (clusters above 8 need the non-portable opt-in)
   unsigned ncta = 1;
-  while (ncta < 8 && (int64_t)ncta * 4096 < L) ncta <<= 1;
-  if (L > (1 << 18)) ncta = 16;
-  static bool attr_set = false;
-  if (ncta > 8 && !attr_set) {
-    if (cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+  static int max_cta = 0;
+  if (max_cta == 0) {
+    const char* e = getenv("PK_TOPK_MAX_CTA");
+    max_cta = e ? atoi(e) : 8;  // measured on B200: 8 CTAs per row is the fastest for rows of ~13 K
+    if (max_cta < 1) max_cta = 1;
+  }
+  while (ncta < 16 && ncta < (unsigned)max_cta && (int64_t)ncta * 1024 < L) ncta <<= 1;
+  static int nonportable = -1;  // -1 unknown, 0 refused, 1 allowed
+  if (ncta > 8) {
+    if (nonportable < 0)
+      nonportable = cudaFuncSetAttribute(topk_cluster_kernel<16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
+                            cudaSuccess
+                        ? 1
+                        : 0;
+    if (nonportable == 0) {
       cudaGetLastError();
       ncta = 8;
-    } else {
-      attr_set = true;
     }
   }
   cudaLaunchConfig_t cfg = {};
@@ -410,7 +364,14 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel, p);
+  cudaError_t e;
+  switch (ncta) {
+    case 1: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<1>, p); break;
+    case 2: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<2>, p); break;
+    case 4: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<4>, p); break;
+    case 8: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<8>, p); break;
+    default: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<16>, p); break;
+  }
   if (e != cudaSuccess) return fail(PK_ERR_CUDA, "topk launch: %s", cudaGetErrorString(e));
   int rc = check_launch("topk");
   if (rc || order == 0) return rc;
