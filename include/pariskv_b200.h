@@ -243,7 +243,8 @@ int pk_append_kv(const pk_tensor* k_row, const pk_tensor* v_row, const pk_tensor
  * polar_cache.collision_based_topk_batch (cache_hub/polar_cache.py:1126-1162, :1207-1304).
  *   codebook / key_block_weight / key_4bit: views of the N searchable keys (as pk_collision_fused /
  *   pk_rerank); cluster_key_counts i32 [bs,H,16,256]; tier_counts host array (6);
- *   C candidates, K final; final_indices i64 [bs,H,K] ascending key index.
+ *   C candidates, K final; final_indices i64 [bs,H,K] ascending key index.  K = 0 stops after the rerank
+ *   (final_indices may be NULL): the adaptive-k variants rank the C candidates themselves.
  *   Optional outputs (NULL to skip): cand i64 [bs,H,C], scores_f32 f32 [bs,H,C],
  *   q_blocks bf16 [bs,H,16,8], q_norm bf16 [bs,H,1], query_avg bf16 [bs,H,128]. */
 int64_t pk_retrieve_workspace_bytes(int64_t bs, int64_t H, int64_t N, int64_t C);

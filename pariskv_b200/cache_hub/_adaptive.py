@@ -1,0 +1,105 @@
+"""Shared body of the two adaptive-k cache variants: value-norm bookkeeping and the adaptive selection step.
+
+Both variants keep all C rerank candidates, weight them by exp(logit - max) * ||v|| together with the window
+rows, and attend the shortest benefit-ordered prefix that reaches a share `threshold` of the total benefit
+(reference: cache_hub/polar_cache_atten_value_indices_adaptive_k.py:1510-1589,
+cache_hub/polar_cache_adaptivek_varlen.py:1684-1812).  Here the selection is one kernel
+(ops.adaptive_topk), the value norms of the candidates are gathered inside it, and the attention kernel takes
+per-head row counts, so there is no host synchronisation, no index packing and no staging copy.
+"""
+import math
+
+import torch
+
+from .. import ops
+from .polar_cache import polar_cache as _base_cache
+
+
+class AdaptiveKCache(_base_cache):
+    # (candidate_ratio, collision_ratio) by zone length, adaptive variants
+    # (cache_hub/polar_cache_adaptivek_varlen.py:2115-2126)
+    def _get_adaptive_ratios(self, retrieval_len):
+        if retrieval_len < 5000:
+            return 0.5, 0.5
+        if retrieval_len < 10000:
+            return 0.25, 0.3
+        if retrieval_len < 30000:
+            return 0.2, 0.25
+        return 0.05, 0.2
+
+    def _init_adaptive(self, threshold, min_k, max_k, per_head):
+        self.adaptive_topk_threshold = float(threshold)
+        self._min_k, self._max_k, self._per_head = int(min_k), int(max_k), bool(per_head)
+        if self._max_k > 4096:
+            raise ValueError("adaptive top-k supports at most 4096 rows per head")
+        dev, bs, H = self.device, self.batch_size, self.kv_head
+        self._attn_scale = 1.0 / math.sqrt(self.head_dim)
+        # ||v|| of the window rows and of the zone rows (zone-relative index), fp32
+        self._sl_vnorm_cache = [torch.zeros(bs, H, self.window_capacity, dtype=torch.float32, device=dev)
+                                for _ in range(self.layer_num)]
+        self.value_norm_gpu = [torch.zeros(bs, H, self.zone_capacity, dtype=torch.float32, device=dev)
+                               for _ in range(self.layer_num)]
+        self.last_adaptive = None   # (adaptive_k, topk_indices, n_sel, sl_logits, cand, cand_scores) of the last compute
+
+    # ---- value norms follow every K/V write -------------------------------------------------------------
+    def _prefill_sample(self, k, v, layer, b, vs):
+        super()._prefill_sample(k, v, layer, b, vs)
+        vn = torch.linalg.vector_norm(v[vs:].to(self.dtype).float(), dim=-1).transpose(0, 1)  # [H, P]
+        P = vn.shape[1]
+        N = self.cpu_valid_end[layer]
+        sink, local = self.sink_size, self.local_size
+        if N == 0:
+            n = self._window_len[layer]
+            self._sl_vnorm_cache[layer][b, :, :n] = vn[:, :n]
+            return
+        self._sl_vnorm_cache[layer][b, :, :sink] = vn[:, :sink]
+        self._sl_vnorm_cache[layer][b, :, sink:sink + local] = vn[:, P - local:]
+        self.value_norm_gpu[layer][b, :, :N] = vn[:, sink:sink + N]
+
+    def decode_update_kv_cache(self, key_states, value_states, layer_idx):
+        if self.device_positions:
+            raise RuntimeError("the adaptive-k variants track value norms on the host side of the step: run them eagerly")
+        pos = self._window_len[layer_idx]
+        self._sl_vnorm_cache[layer_idx][:, :, pos] = torch.linalg.vector_norm(value_states[:, 0].float(), dim=-1)
+        return super().decode_update_kv_cache(key_states, value_states, layer_idx)
+
+    def _flush(self, layer):
+        I, sink, local = self.dynamic_update_interval, self.sink_size, self.local_size
+        N = self.cpu_valid_end[layer]
+        vn = self._sl_vnorm_cache[layer]
+        self.value_norm_gpu[layer][:, :, N:N + I] = vn[:, :, sink:sink + I]
+        vn[:, :, sink:sink + local] = vn[:, :, sink + I:sink + I + local].clone()
+        super()._flush(layer)
+
+    # ---- decode attention ---------------------------------------------------------------------------------
+    def compute(self, queries, layer_idx):
+        queries = queries.contiguous()
+        N = self.cpu_valid_end[layer_idx]
+        n_win = self._window_len[layer_idx]
+        total = self.current_seq_len[layer_idx]
+        if total < max(self.FULL_ATTENTION_THRESHOLD, self.steady_size + 2 * self.final_topk) or N <= 0:
+            return super().compute(queries, layer_idx)
+        wk, wv = self.unified_keys_gpu[layer_idx], self.unified_values_gpu[layer_idx]
+        tiers, C, _ = self.retrieval_plan(N)
+        _, ex = ops.retrieve(queries, self.srht_diagonal_signs, self._mag_centers,
+                             self.codebook_gpu[layer_idx][:, :, :, :N], self.key_block_weight_gpu[layer_idx][:, :, :, :N],
+                             self.key_4bit_packed_gpu[layer_idx][:, :, :, :N, :], self.cluster_key_counts_gpu[layer_idx],
+                             tiers, C, 0, want=("cand", "scores_f32", "query_avg"))
+        cand, cand_scores = ex["cand"], ex["scores_f32"].to(torch.bfloat16)   # the reference ranks bf16 scores
+        # window logits: a small dense product, left to the library as the reference does
+        sl_logits = torch.einsum("bhd,bhkd->bhk", ex["query_avg"], wk[:, :, :n_win]).to(torch.float32) * self._attn_scale
+        K_out = min(self._max_k, C)
+        min_k = min(self._min_k, K_out)
+        adaptive_k, topk = ops.adaptive_topk(sl_logits.contiguous(), cand_scores, self._attn_scale,
+                                             self._sl_vnorm_cache[layer_idx][:, :, :n_win], cand, None,
+                                             self.adaptive_topk_threshold, K_out,
+                                             value_norm=self.value_norm_gpu[layer_idx], sink_size=0,
+                                             min_k=max(1, min_k), max_k=max(1, K_out))
+        if self._per_head:
+            n_sel = adaptive_k.to(torch.int32)
+        else:  # dense variant: every head attends the first max-over-heads rows of its own ranking
+            n_sel = adaptive_k.max().to(torch.int32).expand_as(adaptive_k).contiguous()
+        self.last_adaptive = (adaptive_k, topk, n_sel, sl_logits, cand, cand_scores)
+        self.last_topk_indices = topk
+        return ops.sparse_attention(queries, wk, wv, n_win, self._store_k[layer_idx], self._store_v[layer_idx], topk,
+                                    n_sel=n_sel)

@@ -48,7 +48,7 @@ extern "C" int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, con
   PK_CHECK_TENSOR(mag_centers, PK_BF16, 1);
   PK_CHECK_TENSOR(codebook, PK_U8, 4);
   PK_CHECK_TENSOR(cluster_key_counts, PK_I32, 4);
-  PK_CHECK_TENSOR(final_indices, PK_I64, 3);
+  if (K > 0) PK_CHECK_TENSOR(final_indices, PK_I64, 3);
   const int64_t bs = codebook->shape[0], H = codebook->shape[1], N = codebook->shape[3], Hq = queries->shape[2];
   const int64_t bh = bs * H;
   PK_REQUIRE(codebook->shape[2] == 16, "the fused chain supports 16 subspaces of 8 dims");
@@ -64,11 +64,12 @@ extern "C" int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, con
              "cluster_key_counts must be contiguous [bs,H,16,256]");
   PK_REQUIRE(n_tiers >= 1 && n_tiers <= 8 && tier_counts, "n_tiers must be in 1..8");
   PK_REQUIRE(N >= 1 && N < (1ll << 31), "N out of range");
-  PK_REQUIRE(C >= 1 && C <= N && K >= 1 && K <= C, "need 1 <= K <= C <= N (K=%lld C=%lld N=%lld)", (long long)K,
+  PK_REQUIRE(C >= 1 && C <= N && K >= 0 && K <= C, "need 0 <= K <= C <= N (K=%lld C=%lld N=%lld)", (long long)K,
              (long long)C, (long long)N);
-  PK_REQUIRE(is_contig(final_indices) && final_indices->shape[0] == bs && final_indices->shape[1] == H &&
-                 final_indices->shape[2] == K,
-             "final_indices must be contiguous [bs,H,K]");
+  if (K > 0)
+    PK_REQUIRE(is_contig(final_indices) && final_indices->shape[0] == bs && final_indices->shape[1] == H &&
+                   final_indices->shape[2] == K,
+               "final_indices must be contiguous [bs,H,K]");
   RerankArgs ra;
   int rc = fill_rerank_args(&ra, key_4bit, key_block_weight);
   if (rc) return rc;
@@ -127,5 +128,6 @@ extern "C" int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, con
   ra.C = C;
   if ((rc = launch_select_rerank(ra, bh, counts, lay.u8_stride, hist, n_chunks, chunk_keys, mis, N, cd, sc, st)))
     return rc;
+  if (K == 0) return PK_OK;  // the caller ranks the candidates itself (adaptive-k)
   return launch_topk(sc, true, bh, C, C, K, (int64_t*)final_indices->data, cd, C, 0, st, ST_FINAL_TOPK);
 }

@@ -9,7 +9,8 @@ import importlib
 import sys
 
 _SUBMODULES = [
-    "cache_hub", "cache_hub.cache", "cache_hub.polar_cache", "cache_hub.collision", "cache_hub.collision.collision",
+    "cache_hub", "cache_hub.cache", "cache_hub.polar_cache", "cache_hub.polar_cache_adaptivek_varlen",
+    "cache_hub.polar_cache_atten_value_indices_adaptive_k", "cache_hub.collision", "cache_hub.collision.collision",
     "cache_hub.collision_fused", "cache_hub.collision_fused.collison_interface", "cache_hub.topk", "cache_hub.rerank",
     "cache_hub.rerank.rerank", "cache_hub.adaptive_k_fused", "cache_hub.adaptive_k_fused.adaptive_topk",
     "cache_hub.gather", "cache_hub.gather.cpp_gather", "cache_hub.gather_trans", "cache_hub.gather_trans.trans_h2d",

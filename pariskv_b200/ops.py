@@ -266,7 +266,7 @@ def retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, 
     _require_cuda(queries, codebook, key_block_weight, key_4bit, cluster_key_counts)
     bs, H, B, N = codebook.shape
     dev = codebook.device
-    if final_indices is None:
+    if final_indices is None and K > 0:
         final_indices = torch.empty(bs, H, K, dtype=torch.int64, device=dev)
     extras = {}
     if "cand" in want:

@@ -1,0 +1,84 @@
+"""The two adaptive-k cache variants against the oracle: the selection (adaptive_k, benefit-ordered indices)
+must be bit-exact given the same logits and candidate scores; the attention output within bf16 tolerance."""
+import pytest
+import torch
+
+from conftest import synth_keys
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _make(kind, P, bs, H, Hq, sink, local, I, **extra):
+    if kind == "dense":
+        from pariskv_b200.cache_hub.polar_cache_atten_value_indices_adaptive_k import polar_cache
+    else:
+        from pariskv_b200.cache_hub.polar_cache_adaptivek_varlen import polar_cache
+    return polar_cache(valid_start=[0] * bs, layer_num=1, batch_size=bs, max_length=P + 64, num_key_value_heads=H,
+                       num_heads=Hq, head_dim=128, dtype=torch.bfloat16, layer_mapping={"0": DEV}, max_new_length=64,
+                       sink_size=sink, local_size=local, core=0, nprobe=0, cache_unit_size=0, cache_cluster_num=0,
+                       num_gpus=1, model_size=8, final_topk=64, dynamic_update_interval=I, enable_offload=True, **extra)
+
+
+@pytest.mark.parametrize("kind,extra", [("dense", dict(adaptive_topk_threshold=0.9, adaptive_topk_max_k=256)),
+                                        ("varlen", dict(adaptive_topk_threshold=0.85, adaptive_topk_min_k=20,
+                                                        adaptive_topk_max_k=200))])
+def test_adaptive_cache_matches_oracle(oracle, kind, extra):
+    g = torch.Generator().manual_seed(5)
+    bs, H, Hq, sink, local, I, P, steps = 1, 2, 8, 4, 16, 8, 2400, 11
+    cache = _make(kind, P, bs, H, Hq, sink, local, I, **extra)
+    K = synth_keys(g, bs, H, P)
+    V = (torch.randn(bs, H, P, 128, generator=g) * torch.exp(0.5 * torch.randn(bs, H, P, 1, generator=g))).to(torch.bfloat16)
+    cache.prefill_update_kv_cache(None, K.transpose(1, 2).contiguous().to(DEV), V.transpose(1, 2).contiguous().to(DEV), 0, 0)
+    for t in range(steps):
+        nk = synth_keys(g, bs, H, 1)
+        nv = torch.randn(bs, H, 1, 128, generator=g).to(torch.bfloat16)
+        K, V = torch.cat([K, nk], 2), torch.cat([V, nv], 2)
+        cache.decode_update_kv_cache(nk.transpose(1, 2).contiguous().to(DEV), nv.transpose(1, 2).contiguous().to(DEV), 0)
+        # queries aligned with a few cached keys so the benefit mass is concentrated
+        pick = torch.randint(sink, P - local, (bs, H), generator=g)
+        qk = torch.stack([torch.stack([K[b, h, pick[b, h]].float() for h in range(H)]) for b in range(bs)])
+        q = (qk / qk.norm(dim=-1, keepdim=True) * 6.0).unsqueeze(2).expand(bs, H, Hq // H, 128)
+        q = (q + 0.3 * torch.randn(bs, H, Hq // H, 128, generator=g)).reshape(bs, 1, Hq, 128).to(torch.bfloat16)
+        out = cache.compute(q.to(DEV), 0)
+        ak, topk, n_sel, sl_logits, cand, cand_scores = cache.last_adaptive
+        f = (t + 1) // I
+        zone_end = P - local + f * I
+        N = zone_end - sink
+        assert cache.cpu_valid_end[0] == N
+        # value norms tracked by the cache equal the norms of the tokens in the zone / window
+        vn = torch.linalg.vector_norm(V.float(), dim=-1)
+        assert torch.allclose(cache.value_norm_gpu[0][:, :, :N].cpu(), vn[:, :, sink:zone_end], rtol=1e-6)
+        win_idx = list(range(sink)) + list(range(zone_end, K.shape[2]))
+        n_win = len(win_idx)
+        assert torch.allclose(cache._sl_vnorm_cache[0][:, :, :n_win].cpu(), vn[:, :, win_idx], rtol=1e-6)
+        # the candidate stage equals the oracle's
+        zk, zv = K[:, :, sink:zone_end].contiguous(), V[:, :, sink:zone_end].contiguous()
+        signs = cache.srht_diagonal_signs.cpu()
+        cb, w, pk = oracle.encode(zk, signs)
+        tiers, C, _ = cache.retrieval_plan(N)
+        _, coll = cache._get_adaptive_ratios(N)
+        r = oracle.retrieve(q, signs, cb, w, pk, oracle.cluster_counts(cb), cache._mag_centers.cpu(), coll, C, 1)
+        assert torch.equal(cand.cpu(), r["cand"])
+        assert torch.equal(cand_scores.cpu().view(torch.int16), r["score_bf16"].view(torch.int16))
+        # adaptive selection: same inputs into the oracle -> same k and same order
+        K_out = min(cache._max_k, C)
+        scale = cache._attn_scale
+        cl = (cand_scores.float().cpu().numpy() * torch.tensor(scale, dtype=torch.float32).numpy())
+        cvn = torch.gather(vn[:, :, sink:zone_end], 2, r["cand"])
+        k_o, idx_o = oracle.adaptive_topk(sl_logits.cpu(), vn[:, :, win_idx].float(), torch.from_numpy(cl), cvn,
+                                          r["cand"], cache.adaptive_topk_threshold, K_out)
+        k_o = k_o.clamp(max(1, min(cache._min_k, K_out)), K_out)
+        assert torch.equal(ak.cpu(), k_o), (t, ak.cpu().tolist(), k_o.tolist())
+        assert torch.equal(topk.cpu(), idx_o)
+        want_n = k_o if kind == "varlen" else k_o.max().expand_as(k_o)
+        assert torch.equal(n_sel.cpu().long(), want_n)
+        # attention over window + the per-head prefixes
+        for h in range(H):
+            n = int(want_n[0, h])
+            kk = torch.cat([K[:, h:h + 1][:, :, win_idx], oracle.gather(zk[:, h:h + 1], idx_o[:, h:h + 1, :n])], 2)
+            vv = torch.cat([V[:, h:h + 1][:, :, win_idx], oracle.gather(zv[:, h:h + 1], idx_o[:, h:h + 1, :n])], 2)
+            g0, g1 = h * (Hq // H), (h + 1) * (Hq // H)
+            ref = oracle.attention(q[:, :, g0:g1], kk, vv)
+            assert (out[:, :, g0:g1].float().cpu() - ref).abs().max().item() <= 2e-2, (t, h)
+    assert cache.cpu_valid_end[0] == P - sink - local + I
