@@ -217,6 +217,9 @@ int pk_gather_kv_out_cpu(const pk_tensor* src, const pk_tensor* index, const pk_
  *             CUDA graph can be replayed while the window fills.
  *   n_sel     i32 [bs,H] per-head count of valid entries of selected, or NULL (all K)
  *   out       bf16 [bs,1,Hq,128]
+ *   lse       f32 [bs,Hq] or NULL: log2 of the softmax denominator of every query head (scores scaled and in
+ *             the log2 domain, -inf for an empty row set); lets partial results over disjoint row sets be
+ *             merged exactly: out = sum_r out_r * 2^(lse_r - LSE), LSE = log2 sum_r 2^lse_r
  *   workspace >= pk_attention_workspace_bytes(bs,Hq,n_window+K) bytes, device, 16-byte aligned.  Its first
  *             256-byte-rounded header (arrival counters and a status word) must be ZERO before the first
  *             call; every call leaves it zero again.  The status word (int at index bs*Hq) becomes 1 if a
@@ -226,8 +229,8 @@ int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* window_k, con
                         int64_t n_window, const pk_tensor* n_window_dev, int64_t n_window_add,
                         const pk_tensor* store_k, const pk_tensor* store_v,
                         const pk_tensor* selected, const pk_tensor* n_sel, int64_t index_offset,
-                        float scale, const pk_tensor* out, void* workspace, int64_t workspace_bytes,
-                        void* stream);
+                        float scale, const pk_tensor* out, const pk_tensor* lse, void* workspace,
+                        int64_t workspace_bytes, void* stream);
 
 /* Append one decode step's K/V row to the GPU window: the row writes of polar_cache.decode_update_kv_cache
  * (cache_hub/polar_cache.py:849-850) as one launch.

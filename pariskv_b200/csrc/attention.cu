@@ -42,6 +42,7 @@ struct AttParams {
   int* status;            // set to 1 if a copy barrier was never completed
   float* ws;              // [bs*Hq][n_tiles][ATT_REC]
   uint16_t* out;          // [bs][Hq][128]
+  float* lse;             // optional [bs][Hq]: log2 of the softmax denominator (scaled scores, log2 domain)
 };
 
 __device__ __forceinline__ void unpack8f(uint4 v, float* out) {
@@ -268,6 +269,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
       L += s_lt[t & 1023] * s_f[t & 1023];
     }
     p.out[bq * 128 + tid] = f2bf(L > 0.0f ? O / L : 0.0f);
+    if (p.lse && tid == 0) p.lse[bq] = L > 0.0f ? M + log2f(L) : -INFINITY;
     __syncthreads();
   }
 }
@@ -291,8 +293,8 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
                                    int64_t n_window, const pk_tensor* n_window_dev, int64_t n_window_add,
                                    const pk_tensor* store_k, const pk_tensor* store_v,
                                    const pk_tensor* selected, const pk_tensor* n_sel, int64_t index_offset,
-                                   float scale, const pk_tensor* out, void* workspace, int64_t workspace_bytes,
-                                   void* stream) {
+                                   float scale, const pk_tensor* out, const pk_tensor* lse, void* workspace,
+                                   int64_t workspace_bytes, void* stream) {
   PK_CHECK_TENSOR(queries, PK_BF16, 4);
   PK_CHECK_TENSOR(out, PK_BF16, 4);
   const int64_t bs = queries->shape[0], Hq = queries->shape[2];
@@ -372,6 +374,11 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
   p.status = (int*)workspace + bs * Hq;
   p.ws = (float*)((char*)workspace + att_header_bytes(bs, Hq));
   p.out = (uint16_t*)out->data;
+  if (lse) {
+    PK_CHECK_TENSOR(lse, PK_F32, 2);
+    PK_REQUIRE(is_contig(lse) && lse->shape[0] == bs && lse->shape[1] == Hq, "lse must be contiguous [bs,Hq]");
+    p.lse = (float*)lse->data;
+  }
   cudaStream_t st = (cudaStream_t)stream;
   static bool attr_done = false;
   constexpr int kSmem = 2 * ATT_TILE * 256 + 16 * ATT_GQ * 128 * 4;

@@ -236,7 +236,7 @@ def append_kv(k_row, v_row, window_k, window_v, pos, pos_dev=None, pos_add=0):
 
 
 def sparse_attention(queries, window_k, window_v, n_window, store_k=None, store_v=None, selected=None, n_sel=None,
-                     index_offset=0, scale=None, out=None, n_window_dev=None, n_window_add=0):
+                     index_offset=0, scale=None, out=None, n_window_dev=None, n_window_add=0, lse=None):
     """Decode attention over window rows [0, n_window) plus the selected rows of the K/V store (device or
     pinned host memory); see pk_sparse_attention."""
     _require_cuda(queries, window_k, window_v, selected)
@@ -249,9 +249,9 @@ def sparse_attention(queries, window_k, window_v, n_window, store_k=None, store_
     K = selected.shape[2] if selected is not None else 0
     nb = L.load().pk_attention_workspace_bytes(bs, Hq, n_window + K)
     ws = workspace(dev, nb, "attention")
-    d = [L.desc(t) for t in (queries, window_k, window_v, store_k, store_v, selected, n_sel, out, n_window_dev)]
+    d = [L.desc(t) for t in (queries, window_k, window_v, store_k, store_v, selected, n_sel, out, n_window_dev, lse)]
     _call("pk_sparse_attention", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(n_window), L.ref(d[8]), int(n_window_add),
-          L.ref(d[3]), L.ref(d[4]), L.ref(d[5]), L.ref(d[6]), int(index_offset), float(scale), L.ref(d[7]),
+          L.ref(d[3]), L.ref(d[4]), L.ref(d[5]), L.ref(d[6]), int(index_offset), float(scale), L.ref(d[7]), L.ref(d[9]),
           ws.data_ptr(), ws.numel(), L.stream_ptr(dev))
     return out
 
