@@ -422,6 +422,21 @@ def main():
         return
     K, W, S = args.steps, args.warmup, args.stage_steps
     max_new = W + 2 * K + S + 2 * cfg["interval"] + 8
+    # pinned host memory for the K/V store: refuse early rather than drive the box out of memory
+    need_gb = world * 2 * cfg["layers"] * cfg["kv_heads"] * (cfg["context"] + max_new + cfg["interval"]) * 256 / 1e9
+    try:
+        import psutil
+        avail_gb = psutil.virtual_memory().available / 1e9
+    except Exception:
+        avail_gb = None
+    if avail_gb is not None and avail_gb < need_gb * 1.2 + 8 * world:
+        if rank == 0:
+            print(json.dumps({"metric": "decode_tokens_per_s", "value": None, "unit": "tok/s", "n_gpus": world,
+                              "error": f"needs {need_gb:.0f} GB of pinned host memory for {world} independent sequences, "
+                                       f"{avail_gb:.0f} GB available"}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     t_setup = time.time()
     model = DecoderHarness(cfg, device, seed=1234)
     cache = build_cache(cfg, device, max_new, seed=100 + rank)
