@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
   const int64_t r0 = (int64_t)tile * ATT_TILE;
   const int n_tile = (int)max((int64_t)0, min((int64_t)ATT_TILE, n_rows - r0));
   const unsigned mb = (unsigned)__cvta_generic_to_shared(&mbar);
+  pdl_wait();  // the selected indices come from the top-k kernel
 
   // ---- stage the tile: thread t copies row t/2, K for even t and V for odd t ----
   {
@@ -389,6 +390,6 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
   }
   dim3 grid((unsigned)n_tiles, (unsigned)H, (unsigned)bs);
   StageTimer tm(ST_ATTENTION, st);
-  sparse_attention_kernel<<<grid, ATT_THREADS, kSmem, st>>>(p);
+  launch_chain(sparse_attention_kernel, grid, dim3(ATT_THREADS), (size_t)kSmem, st, p);
   return check_launch("sparse_attention");
 }

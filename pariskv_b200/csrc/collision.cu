@@ -89,6 +89,8 @@ __global__ void __launch_bounds__(256) rank_kernel(RankParams p) {
   const int64_t blk = blockIdx.x;  // (b*H + h)*16 + subspace
   const int64_t bh = blk >> 4;
   const int sub = (int)(blk & 15);
+  pdl_wait();     // first kernel of the chain: its inputs come from kernels outside the chain
+  pdl_trigger();
   const unsigned my_cnt = p.counts ? (unsigned)__ldg(p.counts + blk * 256 + c) : 0u;
   if (p.queries) {
     if (c < 32) {
@@ -216,13 +218,15 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
     for (int s = 0; s < 16; s++)
       r[s] = (v0 < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + s * p.c_s + v0)) : make_uint4(0, 0, 0, 0);
   }
+  if (OUT_U8)
+    for (int i = tid; i < 8 * 256; i += 256) hist[i] = 0;
+  pdl_wait();     // the code loads above do not depend on the ranking kernel; the table below does
+  pdl_trigger();
   {
     const uint4* src = reinterpret_cast<const uint4*>(p.lut + (int64_t)bh * p.B * 64);
     uint4* dst = reinterpret_cast<uint4*>(s_lut);
     for (int i = tid; i < p.B * 16; i += 256) dst[i] = __ldg(src + i);
   }
-  if (OUT_U8)
-    for (int i = tid; i < 8 * 256; i += 256) hist[i] = 0;
   __syncthreads();
 
   if (LAYOUT == 0) {
@@ -391,7 +395,8 @@ int launch_rank(const uint16_t* queries, const uint16_t* signs, int Hq, int H, u
   p.tiers = make_tiers(tier_counts, n_tiers);
   p.lut = lut, p.sorted_ids = sorted_ids;
   StageTimer tm(ST_RANK, st);
-  rank_kernel<<<(unsigned)(bs_h * 16), 256, 0, st>>>(p);
+  if (launch_chain(rank_kernel, dim3((unsigned)(bs_h * 16)), dim3(256), 0, st, p) != cudaSuccess)
+    return check_launch("rank_clusters");
   return check_launch("rank_clusters");
 }
 
@@ -429,7 +434,7 @@ int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* ou
   const size_t smem = 0;
   const bool u8 = counts_u8 != nullptr;
   StageTimer tm(ST_COLLISION, st);
-#define PK_LAUNCH_COLL(L, U) collision_kernel<L, U><<<grid, 256, smem, st>>>(p)
+#define PK_LAUNCH_COLL(L, U) launch_chain(collision_kernel<L, U>, grid, dim3(256), smem, st, p)
   if (layout == 0) {
     if (u8) PK_LAUNCH_COLL(0, true); else PK_LAUNCH_COLL(0, false);
   } else if (layout == 1) {

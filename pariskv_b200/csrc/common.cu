@@ -2,6 +2,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -54,6 +55,15 @@ StageTimer::~StageTimer() {
   std::lock_guard<std::mutex> lk(g_tmu);
   cudaEvent_t b = take_event();
   if (b && cudaEventRecord(b, st_) == cudaSuccess) g_spans.push_back({stage_, a_, b});
+}
+
+bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("PK_PDL");
+    on = (e && e[0] == '1') ? 1 : 0;  // off unless asked for: measured neutral when the step is replayed as a graph
+  }
+  return on == 1;
 }
 
 int sm_count() {

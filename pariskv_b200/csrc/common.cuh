@@ -64,8 +64,38 @@ inline int elem_size(int dtype) {
     PK_REQUIRE((t)->ndim == (nd), #t " has %d dims, expected %d", (t)->ndim, (nd));       \
   } while (0)
 
+// ---- programmatic dependent launch --------------------------------------------------------------------
+// The kernels of the decode chain are launched with the programmatic-stream-serialization attribute: a kernel
+// may be scheduled while its predecessor is still running, does the part of its prologue that does not read the
+// predecessor's output, and then blocks in pdl_wait() until the predecessor has completed and flushed.  Every
+// kernel signals pdl_trigger() only AFTER its own pdl_wait(), so completion is transitive along the chain.
+// Without the launch attribute both instructions do nothing.  The attribute is set only when PK_PDL=1 is in the
+// environment: with the decode step replayed as a CUDA graph it measured neutral on B200.
+bool pdl_enabled();
+
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+#endif
+
 // ---- device side ----
 #ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float bf2f(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
 __device__ __forceinline__ uint16_t f2bf(float f) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(f));

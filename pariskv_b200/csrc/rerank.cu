@@ -132,7 +132,9 @@ __global__ void __launch_bounds__(SEL_THREADS) select_rerank_kernel(RerankArgs a
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t bh = blockIdx.y, chunk = blockIdx.x;
   const int b = (int)(bh / a.H), h = (int)(bh % a.H);
-  rerank_setup(sm, a, bh, tid, SEL_THREADS);
+  rerank_setup(sm, a, bh, tid, SEL_THREADS);  // query blocks: written two kernels back, complete by now
+  pdl_wait();                                   // counts and block histograms come from the collision kernel
+  pdl_trigger();
   if (tid < 256) {
     const uint32_t* hp = p.chunk_hist + bh * p.n_chunks * 256 + tid;
     unsigned t = 0, pr = 0;
@@ -301,7 +303,7 @@ int launch_select_rerank(const RerankArgs& a, int64_t bs_h, const uint8_t* count
       return check_launch("select_rerank smem");
   }
   StageTimer tm(ST_SELECT_RERANK, st);
-  kern<<<grid, SEL_THREADS, smem, st>>>(a, p);
+  launch_chain(kern, grid, dim3(SEL_THREADS), smem, st, a, p);
   return check_launch("select_rerank");
 }
 

@@ -107,6 +107,8 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
   // ---- the slice is read once, coalesced, into shared memory; every pass below works from there ----
   __shared__ uint32_t cache[TK_CACHE];
   const int cache_n = (int)min((int64_t)TK_CACHE, end - begin);
+  pdl_wait();
+  pdl_trigger();
 #pragma unroll 4
   for (int j = tid; j < cache_n; j += TK_THREADS) cache[j] = __ldg(row + begin + j);
   __syncthreads();
@@ -357,13 +359,15 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
   cfg.blockDim = dim3(TK_THREADS);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = ncta;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e;
   switch (ncta) {
     case 1: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<1>, p); break;
