@@ -333,6 +333,99 @@ def workload_config(n_gpus):
             "l2": "inputs larger than L2: 16.4 GB of weights and 36 x 16.8 MB of codes are streamed every step"}
 
 
+def ops_mode(args, cfg, device):
+    """Stand-alone ops at the 128K-context shapes, event-timed back to back over rotating inputs larger than
+    L2: prefill key coding, the reference-layout (plane-major, int32 counts) collision / top-k / rerank ops, the
+    adaptive-k kernel and the bare UVA gather.  A profiling target, not the benchmark."""
+    from pariskv_b200 import _lib, ops
+    H, N = cfg["kv_heads"], cfg["context"] - cfg["sink"] - cfg["local"]
+    g = torch.Generator(device=device).manual_seed(9)
+    R = max(2, args.layers or 8)                       # rotating input sets
+    signs = (torch.randint(0, 2, (128,), generator=g, device=device).to(torch.bfloat16) * 2 - 1)
+    cen = torch.tensor([0.0420, 0.1266, 0.2130, 0.3025, 0.3973, 0.5001, 0.6169, 0.7633], dtype=torch.bfloat16, device=device)
+    keys = [synth_kv(g, N, H, device)[0].transpose(1, 2).contiguous() for _ in range(R)]     # [1,H,N,128]
+    meta, counts = [], []
+    for r in range(R):
+        c = torch.zeros(1, H, 16, 256, dtype=torch.int32, device=device)
+        meta.append(ops.encode_keys(keys[r], signs, cluster_counts=c))
+        counts.append(c)
+    # the reference's plane-major storage of the same metadata
+    # (capacity a multiple of 16, searchable keys starting at column `sink` = 4, as the reference's cache slices them)
+    cap = (N + 4 + 15) // 16 * 16
+    plane = []
+    for cb, w, pk in meta:
+        a = torch.zeros(1, H, 16, cap, dtype=torch.uint8, device=device)
+        b = torch.zeros(1, H, 16, cap, dtype=torch.bfloat16, device=device)
+        c = torch.zeros(1, H, 16, cap, 4, dtype=torch.uint8, device=device)
+        a[..., 4:4 + N], b[..., 4:4 + N], c[..., 4:4 + N, :] = cb, w, pk
+        plane.append((a[..., 4:4 + N], b[..., 4:4 + N], c[..., 4:4 + N, :]))
+    q = torch.randn(R, 1, 1, cfg["q_heads"], 128, generator=g, device=device).to(torch.bfloat16)
+    C, K = max(1, math.ceil(N * 0.1)), cfg["topk"]
+    tiers = [int(math.ceil(N * 0.2 * r)) for r in (0.05, 0.15, 0.30, 0.50, 0.75, 1.0)]
+    qb, ids, cnt, cand, s32, sbf = [], [], [], [], [], []
+    for r in range(R):
+        a, b = ops.query_prep(q[r], H, signs)
+        qb.append((a, b))
+        ids.append(ops.rank_clusters(a))
+        cnt.append(ops.collision_fused(ids[r], counts[r], plane[r][0], tiers))
+        cand.append(ops.topk(cnt[r], C))
+        x, y = ops.rerank(cand[r], plane[r][2], plane[r][1], a, b, cen, want_f32=True)
+        sbf.append(x)
+        s32.append(y)
+    sk = [keys[r].cpu().pin_memory() for r in range(min(R, 4))]
+    dst = torch.empty(1, H, K, 128, dtype=torch.bfloat16, device=device)
+    fin = [ops.final_topk(s32[r], cand[r], K) for r in range(R)]
+    S = 196
+    sl_logits = torch.randn(1, H, S, generator=g, device=device)
+    vn = torch.rand(1, H, S, generator=g, device=device) + 0.5
+    cvn = torch.rand(1, H, C, generator=g, device=device) + 0.5
+    tests = {
+        "encode_keys (prefill, key-major out)": (lambda r: ops.encode_keys(keys[r], signs, *meta[r]), 368 * N * H),
+        "encode_keys (prefill, plane-major out)": (lambda r: ops.encode_keys(keys[r], signs, *plane[r]), 368 * N * H),
+        "collision_fused op (plane-major codes, int32 counts)": (lambda r: ops.collision_fused(ids[r], counts[r], plane[r][0], tiers, cnt[r]), 20 * N * H),
+        "collision_fused op (key-major codes, int32 counts)": (lambda r: ops.collision_fused(ids[r], counts[r], meta[r][0], tiers, cnt[r]), 20 * N * H),
+        "topk op (int32 counts, C of N)": (lambda r: ops.topk(cnt[r], C), (4 * N + 8 * C) * H),
+        "rerank op (key-major records)": (lambda r: ops.rerank(cand[r], meta[r][2], meta[r][1], qb[r][0], qb[r][1], cen, sbf[r], s32[r]), 106 * C * H),
+        "rerank op (plane-major records)": (lambda r: ops.rerank(cand[r], plane[r][2], plane[r][1], qb[r][0], qb[r][1], cen, sbf[r], s32[r]), 106 * C * H),
+        "final_topk op (fp32 scores, K of C)": (lambda r: ops.final_topk(s32[r], cand[r], K), (10 * C + 8 * K) * H),
+        "adaptive_topk op (C candidates, cap 2048)": (lambda r: ops.adaptive_topk(sl_logits, sbf[r], 0.0884, vn, cand[r], cvn, 0.9, min(2048, C)), 14 * C * H),
+        "h2d_gather_kv op (pinned host rows)": (lambda r: ops.h2d_gather_kv(sk[r % len(sk)], sk[(r + 1) % len(sk)], fin[r], dst, dst), K * 512 * H),
+    }
+    peak, kind = load_peaks()
+    out = {}
+    reps = max(args.steps, 4) if args.steps != 256 else 20
+    torch.cuda.nvtx.range_push("timed")
+    side = torch.cuda.Stream(device=device)
+    for name, (fn, nbytes) in tests.items():
+        for r in range(R):
+            fn(r)
+        torch.cuda.synchronize(device)
+        # replay the calls as one CUDA graph so the figure is device time, not Python call overhead
+        gr = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            gr.capture_begin()
+            for i in range(reps):
+                fn(i % R)
+            gr.capture_end()
+        torch.cuda.current_stream().wait_stream(side)
+        gr.replay()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        gr.replay()
+        e1.record()
+        torch.cuda.synchronize(device)
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        out[name] = {"avg_us": round(us, 2), "algorithmic_bytes": nbytes, "achieved_gbs": round(nbytes / us / 1e3, 1),
+                     "frac_of_hbm_peak": round(nbytes / us / 1e3 / peak, 4)}
+        del gr
+    torch.cuda.nvtx.range_pop()
+    print(json.dumps({"mode": "ops", "invalid": "profiling target: stand-alone ops, not the benchmark",
+                      "keys_per_head": N, "heads": H, "candidates": C, "topk": K, "peak_gbs": peak,
+                      "peak_kind": kind, "rotating_sets": R, "ops": out}), flush=True)
+
+
 def kernels_mode(args, cfg, device):
     """Cache path only: per step and layer one K/V append and one compute() on a random query."""
     from pariskv_b200 import _lib
@@ -380,7 +473,7 @@ def main():
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
     ap.add_argument("--stage-steps", type=int, default=16, help="extra steps with per-kernel event timing")
     ap.add_argument("--no-graph", action="store_true", help="run every step eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--mode", default="decode", choices=["decode", "kernels"],
+    ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops"],
                     help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
                          "a small profiling target, its line is marked as such")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the line invalid)")
@@ -419,6 +512,9 @@ def main():
 
     if args.mode == "kernels":
         kernels_mode(args, cfg, device)
+        return
+    if args.mode == "ops":
+        ops_mode(args, cfg, device)
         return
     K, W, S = args.steps, args.warmup, args.stage_steps
     max_new = W + 2 * K + S + 2 * cfg["interval"] + 8

@@ -29,6 +29,7 @@ struct AkParams {
   int H;
   int64_t S, C, K_out, min_k, max_k;
   int K_pad;
+  int cache_c;   // benefits kept in shared memory (C when they fit, else 0: recomputed per pass)
   float threshold;
   int64_t* ak_out;
   int64_t* topk_out;
@@ -63,10 +64,12 @@ __global__ void __launch_bounds__(AK_THREADS) adaptive_topk_kernel(AkParams p) {
   extern __shared__ __align__(16) unsigned char dyn[];
   unsigned long long* sk = reinterpret_cast<unsigned long long*>(dyn);      // K_pad composite keys
   float* locs = reinterpret_cast<float*>(dyn + (size_t)p.K_pad * 8);        // K_pad in-chunk prefix sums
+  float* bcache = reinterpret_cast<float*>(dyn + (size_t)p.K_pad * 12);     // cache_c benefits
   __shared__ float s_red[32];
-  __shared__ unsigned hist[256];
-  __shared__ unsigned s_warp[8];
-  __shared__ unsigned s_res[2];
+  __shared__ unsigned hist[2048];
+  __shared__ unsigned s_warp[32];
+  __shared__ unsigned s_res[3];
+  __shared__ unsigned s_ao[2];
   __shared__ unsigned s_scan[32];
   __shared__ unsigned s_counter;
   __shared__ int s_fk;
@@ -89,7 +92,11 @@ __global__ void __launch_bounds__(AK_THREADS) adaptive_topk_kernel(AkParams p) {
   for (int64_t s = tid; s < p.S; s += AK_THREADS) m = fmaxf(m, sll[s]);
   for (int64_t c = tid; c < p.C; c += AK_THREADS) m = fmaxf(m, logit(c));
   const float gmax = block_max_1024(m, s_red, tid);
-  auto benefit = [&](int64_t c) -> float { return __fmul_rn(pinned_expf(__fsub_rn(logit(c), gmax)), vnorm(c)); };
+  auto compute_benefit = [&](int64_t c) -> float {
+    return __fmul_rn(pinned_expf(__fsub_rn(logit(c), gmax)), vnorm(c));
+  };
+  const bool cached = p.cache_c > 0;
+  auto benefit = [&](int64_t c) -> float { return cached ? bcache[c] : compute_benefit(c); };
 
   // 2./3. benefit sums: strided sequential partials, then the pairwise tree
   float part = 0.0f;
@@ -97,46 +104,63 @@ __global__ void __launch_bounds__(AK_THREADS) adaptive_topk_kernel(AkParams p) {
     part = __fadd_rn(part, __fmul_rn(pinned_expf(__fsub_rn(sll[s], gmax)), slv[s]));
   const float sl_ben = tree_sum_1024(part, s_red, tid);
   part = 0.0f;
-  for (int64_t c = tid; c < p.C; c += AK_THREADS) part = __fadd_rn(part, benefit(c));
+  unsigned a_bits = 0xffffffffu, o_bits = 0u;
+  for (int64_t c = tid; c < p.C; c += AK_THREADS) {
+    const float bn = compute_benefit(c);
+    if (cached) bcache[c] = bn;
+    part = __fadd_rn(part, bn);
+    a_bits &= __float_as_uint(bn), o_bits |= __float_as_uint(bn);
+  }
   const float total = __fadd_rn(sl_ben, tree_sum_1024(part, s_red, tid));
+  if (tid == 0) s_ao[0] = 0xffffffffu, s_ao[1] = 0u;
+  __syncthreads();
+  a_bits = __reduce_and_sync(0xffffffffu, a_bits);
+  o_bits = __reduce_or_sync(0xffffffffu, o_bits);
+  if (lane == 0) {
+    atomicAnd(&s_ao[0], a_bits);
+    atomicOr(&s_ao[1], o_bits);
+  }
+  __syncthreads();
 
-  // 4. exact radix select of the K_out-th largest benefit (bit patterns of non-negative floats are ordered)
-  unsigned prefix = 0, pmask = 0, rem = (unsigned)p.K_out;
-  for (int d = 3; d >= 0; d--) {
-    const int shift = 8 * d;
-    if (tid < 256) hist[tid] = 0;
+  // 4. exact radix select of the K_out-th largest benefit (bit patterns of non-negative floats are ordered):
+  //    11-bit digits from the highest bit on which the benefits differ; stops when a whole digit bin is taken
+  const unsigned varying = s_ao[0] ^ s_ao[1];
+  unsigned prefix = s_ao[0] & ~varying, pmask = ~varying, rem = (unsigned)p.K_out;
+  for (int hi = varying ? 31 - __clz(varying) : -1; hi >= 0; hi -= 11) {
+    const int lo = max(hi - 10, 0);
+    const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));
+    hist[tid] = 0;
+    hist[tid + 1024] = 0;
     __syncthreads();
     for (int64_t c = tid; c < p.C; c += AK_THREADS) {
       const unsigned u = __float_as_uint(benefit(c));
-      if ((u & pmask) == prefix) atomicAdd(&hist[(u >> shift) & 0xFFu], 1u);
+      if (((u ^ prefix) & pmask) == 0) atomicAdd(&hist[(u & dm) >> lo], 1u);
     }
     __syncthreads();
-    unsigned v = 0, incl = 0;
-    if (warp < 8) {
-      v = hist[tid];
-      incl = v;
+    const unsigned v0 = hist[2 * tid], v1 = hist[2 * tid + 1];  // thread t owns bins 2t, 2t+1
+    unsigned incl = v0 + v1;
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        unsigned o = __shfl_down_sync(0xffffffffu, incl, off);
-        if (lane + off < 32) incl += o;
-      }
-      if (lane == 0) s_warp[warp] = incl;
+    for (int off = 1; off < 32; off <<= 1) {
+      unsigned o = __shfl_down_sync(0xffffffffu, incl, off);
+      if (lane + off < 32) incl += o;
+    }
+    if (lane == 0) s_warp[warp] = incl;
+    __syncthreads();
+    unsigned higher = 0;
+    for (int w = warp + 1; w < 32; w++) higher += s_warp[w];
+    const unsigned suf0 = incl + higher, suf1 = suf0 - v0, ab1 = suf1 - v1;
+    if (suf1 >= rem && ab1 < rem) {
+      s_res[0] = 2 * tid + 1, s_res[1] = ab1, s_res[2] = v1;
+    } else if (suf0 >= rem && suf1 < rem) {
+      s_res[0] = 2 * tid, s_res[1] = suf1, s_res[2] = v0;
     }
     __syncthreads();
-    if (warp < 8) {
-      unsigned higher = 0;
-      for (int w = warp + 1; w < 8; w++) higher += s_warp[w];
-      const unsigned suf = incl + higher, above = suf - v;
-      if (suf >= rem && above < rem) {
-        s_res[0] = (unsigned)tid;
-        s_res[1] = above;
-      }
-    }
-    __syncthreads();
-    prefix |= s_res[0] << shift;
-    pmask |= 0xFFu << shift;
+    prefix = (prefix & ~dm) | (s_res[0] << lo);
+    pmask |= dm;
     rem -= s_res[1];
+    const bool all = s_res[2] == rem;
     __syncthreads();
+    if (all) break;  // undecided bits of prefix stay zero: the rest of the bin compares >= prefix
   }
   const unsigned T = prefix;  // take all benefits > T and the first `rem` (by position) equal to T
 
@@ -297,8 +321,9 @@ extern "C" int pk_adaptive_topk(const pk_tensor* sl_logits, const pk_tensor* can
   p.threshold = threshold;
   p.ak_out = (int64_t*)adaptive_k->data;
   p.topk_out = (int64_t*)topk_indices->data;
-  const size_t smem = (size_t)kp * 12;
-  if (smem > 40 * 1024) {
+  p.cache_c = C <= 36 * 1024 ? (int)C : 0;   // up to 144 KB of benefits in shared memory
+  const size_t smem = (size_t)kp * 12 + (size_t)p.cache_c * 4;
+  if (smem > 30 * 1024) {
     if (cudaFuncSetAttribute(adaptive_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return check_launch("adaptive_topk smem");
   }

@@ -32,7 +32,7 @@ struct TopkParams {
   int64_t map_stride;
 };
 
-constexpr int TK_CACHE = 4096;  // elements of a CTA's slice kept in shared memory (the rest is re-read from L2)
+constexpr int TK_CACHE = 16384;  // elements of a CTA's slice kept in (dynamic) shared memory; the rest is re-read from L2
 
 __device__ __forceinline__ uint32_t load_key(const uint32_t* row, int64_t i, int is_float) {
   const uint32_t u = __ldg(row + i);
@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
   __shared__ unsigned cl_segtot;           // elements in my segment
   __shared__ unsigned cl_res[3];           // published by the CTA that owns the threshold bin
   __shared__ unsigned cl_cnt[2];           // n_gt, n_eq of my slice
+  __shared__ unsigned cl_ao[2];            // AND, OR of the keys of the threshold bin in my slice
   __shared__ unsigned s_warp[TK_THREADS / 32];
   __shared__ float s_f[2 * TK_THREADS / 32];
   __shared__ unsigned long long s_scan[TK_THREADS / 32];
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
   constexpr int seg_bins = TK_BINS / NCTA;
 
   // ---- the slice is read once, coalesced, into shared memory; every pass below works from there ----
-  __shared__ uint32_t cache[TK_CACHE];
+  extern __shared__ uint32_t cache[];  // min(slice, TK_CACHE) words, sized by the launcher
   const int cache_n = (int)min((int64_t)TK_CACHE, end - begin);
   pdl_wait();
   pdl_trigger();
@@ -211,8 +212,40 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
   rem -= ab;
   unsigned prefix = 0, pmask = 0;
   if (cb != rem) {
+    // Do the keys of the threshold bin differ at all?  (Integer counts never do: distinct counts fall into
+    // distinct bins.)  AND / OR over the bin, reduced through the cluster.
+    unsigned a = 0xffffffffu, o = 0u;
+    for (int64_t i = my_begin; i < my_end; i++) {
+      const uint32_t u = raw(i);
+      if (bin_of(val_of(u, p.is_float)) != tbin) continue;
+      const uint32_t k = key_of(u, p.is_float);
+      a &= k, o |= k;
+    }
+    a = __reduce_and_sync(0xffffffffu, a);
+    o = __reduce_or_sync(0xffffffffu, o);
+    if (tid == 0) cl_ao[0] = 0xffffffffu, cl_ao[1] = 0u;
+    __syncthreads();
+    if (lane == 0) {
+      atomicAnd(&cl_ao[0], a);
+      atomicOr(&cl_ao[1], o);
+    }
+    cluster.sync();
+    {
+      unsigned aa[NCTA], oo[NCTA];
+#pragma unroll
+      for (int r = 0; r < NCTA; r++) {
+        const unsigned* q = cluster.map_shared_rank(cl_ao, r);
+        aa[r] = q[0], oo[r] = q[1];
+      }
+      a = aa[0], o = oo[0];
+#pragma unroll
+      for (int r = 1; r < NCTA; r++) a &= aa[r], o |= oo[r];
+    }
+    const unsigned varying = a ^ o;
+    prefix = a & ~varying;
+    pmask = ~varying;
     // ---- stage B: exact radix select of the rem-th largest key among the elements of the threshold bin ----
-    for (int hi = 31; hi >= 0; hi -= 11) {
+    for (int hi = varying ? 31 - __clz(varying) : -1; hi >= 0; hi -= 11) {
       const int lo = max(hi - 10, 0);
       const unsigned dm = ((hi == 31 ? 0u : (1u << (hi + 1))) - (1u << lo));
       // remote reads of `hist` ended before the second barrier of the previous cluster_select
@@ -357,7 +390,17 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(ncta, (unsigned)rows);
   cfg.blockDim = dim3(TK_THREADS);
-  cfg.dynamicSmemBytes = 0;
+  const int64_t slice = (L + ncta - 1) / ncta;
+  cfg.dynamicSmemBytes = (size_t)(slice < TK_CACHE ? slice : TK_CACHE) * 4;
+  static bool smem_attr = false;
+  if (!smem_attr) {
+    cudaFuncSetAttribute(topk_cluster_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
+    cudaFuncSetAttribute(topk_cluster_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
+    cudaFuncSetAttribute(topk_cluster_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
+    cudaFuncSetAttribute(topk_cluster_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
+    cudaFuncSetAttribute(topk_cluster_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
+    smem_attr = true;
+  }
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
