@@ -464,21 +464,173 @@ def kernels_mode(args, cfg, device):
 
 
 # --------------------------------------------------------------------------------------------------------
+# --------------------------------------------------------------------------------------------------------
+# the million-token workload: one sequence, its zone sharded over the ranks (strong scaling)
+# --------------------------------------------------------------------------------------------------------
+CFG_1M = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256,
+              rope_theta=2.8e8, context=1048576, sink=4, local=64, interval=128, topk=2048)
+SHARD_BLOCK = 65536     # keys are drawn in fixed global blocks so the sequence is the same for every world size
+
+
+def synth_block(layer, block, n, H, device, seed):
+    g = torch.Generator(device=device).manual_seed(seed + 1000003 * layer + block)
+    z = torch.randn(1, H, n, 128, generator=g, device=device, dtype=torch.float32)
+    z[..., list(OUTLIERS)] *= 8.0
+    z *= torch.exp(0.5 * torch.randn(1, H, n, 1, generator=g, device=device, dtype=torch.float32))
+    v = torch.randn(1, H, n, 128, generator=g, device=device, dtype=torch.float32)
+    return z.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
+def seqshard_mode(args, device, rank, world, local_rank):
+    """One decode sequence whose zone is split into `world` contiguous chunks: per-rank retrieval over the local
+    chunk, all-gather of the local top lists, attention over the owned rows, merge through the softmax
+    denominators.  The dense part of the model is replicated on every rank."""
+    from pariskv_b200 import _lib
+    from pariskv_b200.dist import SequenceShardedCache, sequence_shard
+    cfg = dict(CFG_1M)
+    debug = False
+    if args.layers:
+        cfg["layers"], debug = args.layers, True
+    if args.context:
+        cfg["context"], debug = args.context, True
+    K, W = args.steps, max(args.warmup, 3)
+    if K + W + 2 > cfg["interval"]:
+        raise SystemExit(f"--mode seqshard holds at most {cfg['interval'] - 2} steps (steps + warmup): the "
+                         "sequence-sharded form does not flush the update buffer yet")
+    H, Lyr = cfg["kv_heads"], cfg["layers"]
+    n_total = cfg["context"] - cfg["sink"] - cfg["local"]
+    start, end = sequence_shard(n_total, rank, world)
+    need_gb = 2 * Lyr * H * n_total * 256 / 1e9          # all ranks together: they share the host
+    try:
+        import psutil
+        avail_gb = psutil.virtual_memory().available / 1e9
+    except Exception:
+        avail_gb = None
+    if avail_gb is not None and avail_gb < need_gb * 1.1 + 8 * world:
+        if rank == 0:
+            print(json.dumps({"metric": "decode_tokens_per_s", "value": None, "unit": "tok/s", "n_gpus": world,
+                              "error": f"needs {need_gb:.0f} GB of pinned host memory, {avail_gb:.0f} GB available"}),
+                  flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    t_setup = time.time()
+    model = DecoderHarness(cfg, device, seed=1234)
+    cache = SequenceShardedCache(Lyr, H, cfg["q_heads"], n_total, cfg["sink"], cfg["local"], cfg["interval"],
+                                 cfg["topk"], device, rank, world)
+    for l in range(Lyr):
+        ks, vs = [], []
+        for b in range(start // SHARD_BLOCK, (max(end, start + 1) - 1) // SHARD_BLOCK + 1):
+            b0 = b * SHARD_BLOCK
+            n = min(SHARD_BLOCK, n_total - b0)
+            k, v = synth_block(l, b, n, H, device, seed=77)
+            lo, hi = max(start, b0) - b0, min(end, b0 + n) - b0
+            ks.append(k[:, :, lo:hi])
+            vs.append(v[:, :, lo:hi])
+        wk, wv = synth_block(l, 1 << 20, cfg["sink"] + cfg["local"], H, device, seed=77)
+        cache.load_layer(l, torch.cat(ks, 2), torch.cat(vs, 2), wk, wv)
+        torch.cuda.synchronize(device)
+        del ks, vs
+    setup_s = time.time() - t_setup
+    use_graph = not args.no_graph
+    runner = GraphedDecoder(model, cache)
+    token = torch.tensor([11], device=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    def advance():
+        nonlocal token
+        if use_graph:
+            runner.step()
+        else:
+            token = model.step(cache, token)
+
+    for _ in range(2):
+        token = model.step(cache, token)
+    runner.tok.copy_(token)
+    for _ in range(W - 2):
+        advance()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = _lib.launch_count() if not use_graph else runner.kernel_launches
+    barrier()
+    e0.record()
+    for _ in range(K):
+        advance()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = (_lib.launch_count() if not use_graph else runner.kernel_launches) - launches0
+    clocks = sampler.stop()
+    last = (runner.tok if use_graph else token).clone()
+    agree = True
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        toks = torch.empty(world, dtype=torch.int64, device=device)
+        dist.all_gather_into_tensor(toks, last)
+        agree = bool((toks == toks[0]).all().item())
+    if rank == 0:
+        from pariskv_b200.dist import local_plan
+        tiers, c_local, k_local = local_plan(n_total, world, 0.2, 0.1, cfg["topk"])
+        line = {
+            "metric": "decode_tokens_per_s", "value": K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"Llama-3-8B-shaped decoder, one sequence of {cfg['context']} tokens, bs 1, top-k "
+                                   f"{cfg['topk']}, zone of {n_total} keys per head split into {world} contiguous "
+                                   "chunk(s); dense layers replicated; K/V rows in pinned host memory",
+                       "layers": Lyr, "kv_heads": H, "q_heads": cfg["q_heads"], "parallelism": f"sp{world}",
+                       "l2": "per-step working set (codes of all layers) exceeds L2"},
+            "clocks": clocks, "gpu_launches": int(launches), "ranks_agree": agree,
+            "cuda_graph": {"used": use_graph, "captures": runner.captures},
+            "setup_s": round(setup_s, 1), "zone_keys_per_head": n_total, "shard_keys_per_head": end - start,
+            "candidates_per_shard": c_local, "local_topk": k_local,
+        }
+        if debug:
+            line["invalid"] = "debug run with reduced layers/context"
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        # graphs that hold captured collectives must be gone before the communicator is torn down (tearing it down
+        # first waits for ever); a timer ends the process if the teardown still does not return
+        import gc
+        import threading
+        runner.graph = None
+        gc.collect()
+        barrier()
+        sys.stdout.flush()
+        guard = threading.Timer(30.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
+        dist.destroy_process_group()
+        guard.cancel()
+        os._exit(0)      # nothing left to finalise; skips destructors that could wait on the communicator
+
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=None, help="default 256 (64 for --mode seqshard)")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
     ap.add_argument("--stage-steps", type=int, default=16, help="extra steps with per-kernel event timing")
     ap.add_argument("--no-graph", action="store_true", help="run every step eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops"],
+    ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops", "seqshard"],
                     help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
                          "a small profiling target, its line is marked as such")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the line invalid)")
     ap.add_argument("--context", type=int, default=None, help="debug only: shorter context (marks the line invalid)")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 64 if args.mode == "seqshard" else 256
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -498,6 +650,8 @@ def main():
     torch.cuda.set_device(device)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if args.mode == "seqshard":      # small all-gathers only: plain peer transfers, no NVLink multicast objects
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
 
     from pariskv_b200 import _lib
@@ -510,6 +664,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    if args.mode == "seqshard":
+        seqshard_mode(args, device, rank, world, local_rank)
+        return
     if args.mode == "kernels":
         kernels_mode(args, cfg, device)
         return

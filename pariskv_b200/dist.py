@@ -118,7 +118,7 @@ def merge_partial_attention(out: torch.Tensor, lse: torch.Tensor, group=None) ->
 
 def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global, store_k,
                             store_v, n_total, start, end, collision_ratio, candidate_ratio, final_topk,
-                            window_k=None, window_v=None, n_window=0, group=None):
+                            window_k=None, window_v=None, n_window=0, group=None, n_window_dev=None, n_window_add=0):
     """One layer, one decode step of the sequence-sharded form on this rank's shard [start, end) of a zone of
     n_total keys.  codebook / key_block_weight / key_4bit / store_* hold the shard only (local index = global -
     start); counts_global is the all-reduced cluster histogram.  The window rows are attended by the rank that
@@ -126,6 +126,11 @@ def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_wei
     from . import ops
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     tiers, c_local, k_local = local_plan(n_total, world, collision_ratio, candidate_ratio, final_topk)
+    if world == 1:   # the whole zone is local: the plain chain, nothing to exchange
+        final, _ = ops.retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global,
+                                tiers, c_local, k_local)
+        return ops.sparse_attention(queries, window_k, window_v, n_window, store_k, store_v, final,
+                                    n_window_dev=n_window_dev, n_window_add=n_window_add), final
     fin_local, ex = ops.retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global,
                                  tiers, c_local, k_local, want=("cand", "scores_f32"))
     scores = torch.gather(ex["scores_f32"], 2, torch.searchsorted(ex["cand"], fin_local))
@@ -133,5 +138,108 @@ def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_wei
     local, n_owned = owned_rows(final, start, end)
     bs, _, Hq, _ = queries.shape
     lse = torch.empty(bs, Hq, dtype=torch.float32, device=queries.device)
-    out = ops.sparse_attention(queries, window_k, window_v, n_window, store_k, store_v, local, n_sel=n_owned, lse=lse)
+    out = ops.sparse_attention(queries, window_k, window_v, n_window, store_k, store_v, local, n_sel=n_owned, lse=lse,
+                               n_window_dev=n_window_dev, n_window_add=n_window_add)
     return merge_partial_attention(out, lse, group), final
+
+
+class SequenceShardedCache:
+    """Decode-side cache of the sequence-sharded form: this rank holds one contiguous chunk of every layer's
+    zone (codes / 4-bit records / weights in HBM, K/V rows in pinned host memory) plus a full copy of the small
+    GPU window; rank 0 attends the window.  It exposes the calls a decode loop makes on the single-GPU cache
+    (`decode_update_kv_cache`, `compute`, `context`).  The zone is fixed after `load_layer`: the update buffer
+    must not overflow (no flush in this form yet), which holds for runs shorter than the buffer."""
+
+    def __init__(self, layer_num, num_kv_heads, num_heads, n_total, sink_size, local_size, interval, final_topk,
+                 device, rank, world, group=None, collision_ratio=0.2, candidate_ratio=0.1, srht_sign_vector=None):
+        from .cache_hub.polar_cache import srht_signs
+        self.layer_num, self.kv_head, self.num_heads = layer_num, num_kv_heads, num_heads
+        self.n_total, self.sink_size, self.local_size, self.interval = n_total, sink_size, local_size, interval
+        self.final_topk, self.device, self.rank, self.world, self.group = final_topk, device, rank, world, group
+        self.collision_ratio, self.candidate_ratio = collision_ratio, candidate_ratio
+        self.start, self.end = sequence_shard(n_total, rank, world)
+        self.signs = (srht_sign_vector.to(device, torch.bfloat16).contiguous() if srht_sign_vector is not None
+                      else srht_signs(device))
+        self.centers = torch.tensor([0.0420, 0.1266, 0.2130, 0.3025, 0.3973, 0.5001, 0.6169, 0.7633],
+                                    device=device, dtype=torch.bfloat16)
+        cap = sink_size + local_size + interval
+        self.window_capacity = cap
+        self.window_k = [torch.zeros(1, num_kv_heads, cap, 128, dtype=torch.bfloat16, device=device) for _ in range(layer_num)]
+        self.window_v = [torch.zeros(1, num_kv_heads, cap, 128, dtype=torch.bfloat16, device=device) for _ in range(layer_num)]
+        self._window_len = [0] * layer_num
+        self.meta = [None] * layer_num
+        self.counts = [None] * layer_num
+        self.store_k = [None] * layer_num
+        self.store_v = [None] * layer_num
+        self.context = 0
+        self.last_topk_indices = None
+        self.device_positions = False     # window length read from a device word (captured steps)
+        self._dev_state = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def load_layer(self, layer, shard_keys, shard_values, window_keys, window_values):
+        """shard_keys / shard_values: bf16 [1,H,n_local,128] on the device (this rank's chunk of the zone);
+        window_*: bf16 [1,H,sink+local,128] (sink rows then the last `local` rows of the prompt)."""
+        from . import ops
+        counts = torch.zeros(1, self.kv_head, 16, 256, dtype=torch.int32, device=self.device)
+        self.meta[layer] = ops.encode_keys(shard_keys, self.signs, cluster_counts=counts)
+        self.counts[layer] = allreduce_cluster_counts(counts, self.group)
+        n_local = shard_keys.shape[2]
+        sk = torch.empty(1, self.kv_head, max(n_local, 1), 128, dtype=torch.bfloat16, pin_memory=True)
+        sv = torch.empty(1, self.kv_head, max(n_local, 1), 128, dtype=torch.bfloat16, pin_memory=True)
+        sk[:, :, :n_local].copy_(shard_keys, non_blocking=True)
+        sv[:, :, :n_local].copy_(shard_values, non_blocking=True)
+        self.store_k[layer], self.store_v[layer] = sk, sv
+        n = window_keys.shape[2]
+        self.window_k[layer][:, :, :n] = window_keys
+        self.window_v[layer][:, :, :n] = window_values
+        self._window_len[layer] = n
+        if layer == self.layer_num - 1:
+            self.context = self.sink_size + self.n_total + self.local_size
+
+    def decode_update_kv_cache(self, key_states, value_states, layer_idx):
+        from . import ops
+        pos = self._window_len[layer_idx]
+        if pos >= self.window_capacity:
+            raise RuntimeError("update buffer full: the sequence-sharded form has no flush yet")
+        ops.append_kv(key_states, value_states, self.window_k[layer_idx], self.window_v[layer_idx], pos,
+                      self._dev_state[0:1] if self.device_positions else None, 0)
+        self._window_len[layer_idx] = pos + 1
+        if layer_idx == 0:
+            self.context += 1
+        return None, None
+
+    def compute(self, queries, layer_idx):
+        cb, w, pk = self.meta[layer_idx]
+        first = self.rank == 0
+        out, final = sequence_sharded_attend(
+            queries.contiguous(), self.signs, self.centers, cb, w, pk, self.counts[layer_idx], self.store_k[layer_idx],
+            self.store_v[layer_idx], self.n_total, self.start, self.end, self.collision_ratio, self.candidate_ratio,
+            self.final_topk, window_k=self.window_k[layer_idx] if first else None,
+            window_v=self.window_v[layer_idx] if first else None,
+            n_window=(self.window_capacity if self.device_positions else self._window_len[layer_idx]) if first else 0,
+            group=self.group, n_window_dev=self._dev_state[0:1] if (first and self.device_positions) else None,
+            n_window_add=1 if (first and self.device_positions) else 0)
+        self.last_topk_indices = final
+        return out
+
+    # ---- support for replaying a captured decode step (same calls as the single-GPU cache) ----
+    def next_step_flushes(self) -> bool:
+        return False
+
+    def sync_device_state(self):
+        self._dev_state[0] = self._window_len[0]
+
+    def advance_device_step(self):
+        self._dev_state[0:1] += 1
+
+    def host_state(self):
+        return (list(self._window_len), self.context)
+
+    def set_host_state(self, st):
+        self._window_len, self.context = list(st[0]), st[1]
+
+    def note_replayed_step(self):
+        if self._window_len[0] + 1 > self.window_capacity:
+            raise RuntimeError("update buffer full: the sequence-sharded form has no flush yet")
+        self._window_len = [n + 1 for n in self._window_len]
+        self.context += 1
