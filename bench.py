@@ -501,6 +501,8 @@ def seqshard_mode(args, device, rank, world, local_rank):
     n_total = cfg["context"] - cfg["sink"] - cfg["local"]
     start, end = sequence_shard(n_total, rank, world)
     need_gb = 2 * Lyr * H * n_total * 256 / 1e9          # all ranks together: they share the host
+    if args.store == "hbm" or (args.store == "auto" and Lyr * H * (end - start) * 624 + (36 << 30) < 180e9):
+        need_gb = 2 * H * (end - start) * 256 * 2 / 1e9   # staging of one layer only
     try:
         import psutil
         avail_gb = psutil.virtual_memory().available / 1e9
@@ -517,7 +519,7 @@ def seqshard_mode(args, device, rank, world, local_rank):
     t_setup = time.time()
     model = DecoderHarness(cfg, device, seed=1234)
     cache = SequenceShardedCache(Lyr, H, cfg["q_heads"], n_total, cfg["sink"], cfg["local"], cfg["interval"],
-                                 cfg["topk"], device, rank, world)
+                                 cfg["topk"], device, rank, world, store=args.store)
     for l in range(Lyr):
         ks, vs = [], []
         for b in range(start // SHARD_BLOCK, (max(end, start + 1) - 1) // SHARD_BLOCK + 1):
@@ -585,7 +587,7 @@ def seqshard_mode(args, device, rank, world, local_rank):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"Llama-3-8B-shaped decoder, one sequence of {cfg['context']} tokens, bs 1, top-k "
                                    f"{cfg['topk']}, zone of {n_total} keys per head split into {world} contiguous "
-                                   "chunk(s); dense layers replicated; K/V rows in pinned host memory",
+                                   f"chunk(s); dense layers replicated; K/V rows in {'HBM' if cache.store == 'hbm' else 'pinned host memory'}",
                        "layers": Lyr, "kv_heads": H, "q_heads": cfg["q_heads"], "parallelism": f"sp{world}",
                        "l2": "per-step working set (codes of all layers) exceeds L2"},
             "clocks": clocks, "gpu_launches": int(launches), "ranks_agree": agree,
@@ -626,6 +628,8 @@ def main():
     ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops", "seqshard"],
                     help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
                          "a small profiling target, its line is marked as such")
+    ap.add_argument("--store", default="auto", choices=["auto", "host", "hbm"],
+                    help="--mode seqshard: where a shard's K/V rows live (auto: HBM when they fit, else pinned host)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the line invalid)")
     ap.add_argument("--context", type=int, default=None, help="debug only: shorter context (marks the line invalid)")
     args = ap.parse_args()

@@ -258,6 +258,31 @@ int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, const pk_tenso
                 const pk_tensor* scores_f32, const pk_tensor* q_blocks, const pk_tensor* q_norm,
                 const pk_tensor* query_avg, void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ---- sequence-sharded form: the glue on either side of the two all-gathers ------------------------- */
+
+/* The reference has no multi-GPU retrieval; its single-GPU selection (cache_hub/polar_cache.py:1207-1304) and
+ * attention (attn_hub/polar_attn.py:17-113) are what the sharded form must reproduce.  Every rank holds one
+ * contiguous chunk [start, end) of the zone, runs pk_retrieve over it (local indices), and then:
+ *   pk_shard_pack_topk     cand i64 [bs,H,C] ascending, scores f32 [bs,H,C], local_final i64 [bs,H,Kl] (a subset
+ *                          of cand) -> packed i64 [bs,H,Kl,2] = (fp32 score bits, global index = local + start);
+ *                          the host all-gathers `packed` rank-major into [world,bs,H,Kl,2];
+ *   pk_shard_unpack_topk   gathered -> scores f32 / indices i64 [bs,H,world*Kl], rank-major per row (ascending
+ *                          global index, because the chunks are ascending), ready for pk_final_topk;
+ *   pk_shard_owned_rows    final i64 [bs,H,K] ascending global -> local i64 [bs,H,K] (the rows inside
+ *                          [start,end) first, minus start; the rest 0) and n_owned i32 [bs,H] (pk_sparse_attention's
+ *                          selected / n_sel);
+ *   pk_shard_pack_partial  out bf16 [bs,1,Hq,128], lse f32 [bs,Hq] -> packed f32 [bs,Hq,129]; all-gathered into
+ *                          [world,bs,Hq,129];
+ *   pk_shard_merge_partial gathered -> out bf16 [bs,1,Hq,128]: sum_r 2^(lse_r - max) out_r / sum_r 2^(lse_r - max),
+ *                          ranks with lse = -inf (no rows) skipped. */
+int pk_shard_pack_topk(const pk_tensor* cand, const pk_tensor* scores, const pk_tensor* local_final, int64_t start,
+                       const pk_tensor* packed, void* stream);
+int pk_shard_unpack_topk(const pk_tensor* gathered, const pk_tensor* scores, const pk_tensor* indices, void* stream);
+int pk_shard_owned_rows(const pk_tensor* final_indices, int64_t start, int64_t end, const pk_tensor* local,
+                        const pk_tensor* n_owned, void* stream);
+int pk_shard_pack_partial(const pk_tensor* out, const pk_tensor* lse, const pk_tensor* packed, void* stream);
+int pk_shard_merge_partial(const pk_tensor* gathered, const pk_tensor* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

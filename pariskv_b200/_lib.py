@@ -56,6 +56,11 @@ SIGNATURES = {
     "pk_retrieve_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
     "pk_retrieve": (_INT, [TP, TP, TP, TP, TP, TP, TP, _I64P, _INT, _I64, _I64, TP, TP, TP, TP, TP, TP, _VP, _I64,
                            _VP]),
+    "pk_shard_pack_topk": (_INT, [TP, TP, TP, _I64, TP, _VP]),
+    "pk_shard_unpack_topk": (_INT, [TP, TP, TP, _VP]),
+    "pk_shard_owned_rows": (_INT, [TP, _I64, _I64, TP, TP, _VP]),
+    "pk_shard_pack_partial": (_INT, [TP, TP, TP, _VP]),
+    "pk_shard_merge_partial": (_INT, [TP, TP, _VP]),
 }
 
 _lib = None

@@ -1,0 +1,182 @@
+// Exchange glue of the sequence-sharded form: every rank retrieves over its contiguous chunk of the zone, the local
+// top lists are all-gathered, the global top-K is selected from them, each rank attends the rows it owns and the
+// partial results are merged through their softmax denominators.  The collectives themselves are issued by the
+// host (NCCL all-gather of one packed buffer each); these kernels are the packing, unpacking and merging on either
+// side of them, one launch each.
+#include "common.cuh"
+
+namespace pk {
+
+// Position of `key` in the ascending row a[0..n): first element >= key.
+__device__ __forceinline__ int lower_bound_i64(const int64_t* __restrict__ a, int n, int64_t key) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(a + mid) < key) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// packed[row][j] = (score bits of local_final[row][j] as int64, local_final[row][j] + start)
+__global__ void __launch_bounds__(256) shard_pack_kernel(const int64_t* __restrict__ cand, const float* __restrict__ scores,
+                                                         const int64_t* __restrict__ local_final, int64_t* __restrict__ packed,
+                                                         int C, int Kl, int64_t start) {
+  const int row = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= Kl) return;
+  const int64_t idx = local_final[(int64_t)row * Kl + j];
+  const int64_t* c = cand + (int64_t)row * C;
+  int p = lower_bound_i64(c, C, idx);
+  if (p >= C) p = C - 1;
+  const float s = scores[(int64_t)row * C + p];
+  int64_t* o = packed + ((int64_t)row * Kl + j) * 2;
+  o[0] = (int64_t)__float_as_int(s);
+  o[1] = idx + start;
+}
+
+// gathered [world][rows][Kl][2] -> scores [rows][world*Kl], indices [rows][world*Kl] (rank-major within a row)
+__global__ void __launch_bounds__(256) shard_unpack_kernel(const int64_t* __restrict__ gathered, float* __restrict__ scores,
+                                                           int64_t* __restrict__ indices, int world, int rows, int Kl) {
+  const int row = blockIdx.y;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= world * Kl) return;
+  const int w = t / Kl, j = t - w * Kl;
+  const longlong2 v = *reinterpret_cast<const longlong2*>(gathered + (((int64_t)w * rows + row) * Kl + j) * 2);
+  scores[(int64_t)row * world * Kl + t] = __int_as_float((int)v.x);
+  indices[(int64_t)row * world * Kl + t] = v.y;
+}
+
+// final [rows][K] ascending global indices -> local [rows][K] (the rows inside [start,end) first, minus start, the
+// rest 0) and n_owned [rows]
+__global__ void __launch_bounds__(256) shard_owned_kernel(const int64_t* __restrict__ final_idx, int64_t* __restrict__ local,
+                                                          int32_t* __restrict__ n_owned, int K, int64_t start, int64_t end) {
+  const int row = blockIdx.x;
+  const int64_t* f = final_idx + (int64_t)row * K;
+  __shared__ int s_lo, s_n;
+  if (threadIdx.x == 0) {
+    const int lo = lower_bound_i64(f, K, start);
+    const int hi = lower_bound_i64(f, K, end);
+    s_lo = lo;
+    s_n = hi - lo;
+    n_owned[row] = hi - lo;
+  }
+  __syncthreads();
+  const int lo = s_lo, n = s_n;
+  for (int j = threadIdx.x; j < K; j += blockDim.x)
+    local[(int64_t)row * K + j] = j < n ? f[lo + j] - start : 0;
+}
+
+// packed [rows][129] fp32 = (attention output over the local rows, log2 of the local softmax denominator)
+__global__ void __launch_bounds__(128) shard_pack_partial_kernel(const __nv_bfloat16* __restrict__ out, const float* __restrict__ lse,
+                                                                 float* __restrict__ packed) {
+  const int row = blockIdx.x, d = threadIdx.x;
+  packed[(int64_t)row * 129 + d] = __bfloat162float(out[(int64_t)row * 128 + d]);
+  if (d == 0) packed[(int64_t)row * 129 + 128] = lse[row];
+}
+
+// gathered [world][rows][129] -> out [rows][128]: exact softmax over the union of the ranks' row sets
+__global__ void __launch_bounds__(128) shard_merge_partial_kernel(const float* __restrict__ gathered, __nv_bfloat16* __restrict__ out,
+                                                                  int world, int rows) {
+  const int row = blockIdx.x, d = threadIdx.x;
+  float m = -INFINITY;
+  for (int w = 0; w < world; w++) m = fmaxf(m, gathered[((int64_t)w * rows + row) * 129 + 128]);
+  float acc = 0.f, den = 0.f;
+  for (int w = 0; w < world; w++) {
+    const float* g = gathered + ((int64_t)w * rows + row) * 129;
+    const float l = g[128];
+    const float wt = (l == -INFINITY) ? 0.f : exp2f(l - m);   // a rank without rows contributes nothing
+    if (wt != 0.f) acc = fmaf(wt, g[d], acc);
+    den += wt;
+  }
+  out[(int64_t)row * 128 + d] = __float2bfloat16(den > 0.f ? acc / den : 0.f);
+}
+
+}  // namespace pk
+
+using namespace pk;
+
+extern "C" int pk_shard_pack_topk(const pk_tensor* cand, const pk_tensor* scores, const pk_tensor* local_final,
+                                  int64_t start, const pk_tensor* packed, void* stream) {
+  PK_CHECK_TENSOR(cand, PK_I64, 3);
+  PK_CHECK_TENSOR(scores, PK_F32, 3);
+  PK_CHECK_TENSOR(local_final, PK_I64, 3);
+  PK_CHECK_TENSOR(packed, PK_I64, 4);
+  const int64_t bs = cand->shape[0], H = cand->shape[1], C = cand->shape[2], Kl = local_final->shape[2];
+  PK_REQUIRE(is_contig(cand) && is_contig(scores) && is_contig(local_final) && is_contig(packed), "tensors must be contiguous");
+  PK_REQUIRE(scores->shape[0] == bs && scores->shape[1] == H && scores->shape[2] == C, "scores must be [bs,H,C] like cand");
+  PK_REQUIRE(local_final->shape[0] == bs && local_final->shape[1] == H, "local_final must be [bs,H,Kl]");
+  PK_REQUIRE(packed->shape[0] == bs && packed->shape[1] == H && packed->shape[2] == Kl && packed->shape[3] == 2,
+             "packed must be [bs,H,Kl,2]");
+  PK_REQUIRE(C >= 1 && C < (1LL << 31) && Kl < (1LL << 31) && bs * H < 65536, "sizes out of range");
+  PK_REQUIRE((reinterpret_cast<uintptr_t>(packed->data) & 15) == 0, "packed must be 16-byte aligned");
+  if (bs * H * Kl == 0) return PK_OK;
+  shard_pack_kernel<<<dim3((unsigned)((Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
+      (const int64_t*)cand->data, (const float*)scores->data, (const int64_t*)local_final->data, (int64_t*)packed->data,
+      (int)C, (int)Kl, start);
+  return check_launch("shard_pack_topk");
+}
+
+extern "C" int pk_shard_unpack_topk(const pk_tensor* gathered, const pk_tensor* scores, const pk_tensor* indices,
+                                    void* stream) {
+  PK_CHECK_TENSOR(gathered, PK_I64, 5);
+  PK_CHECK_TENSOR(scores, PK_F32, 3);
+  PK_CHECK_TENSOR(indices, PK_I64, 3);
+  const int64_t world = gathered->shape[0], bs = gathered->shape[1], H = gathered->shape[2], Kl = gathered->shape[3];
+  PK_REQUIRE(gathered->shape[4] == 2 && is_contig(gathered) && is_contig(scores) && is_contig(indices),
+             "gathered must be contiguous [world,bs,H,Kl,2], outputs contiguous");
+  PK_REQUIRE(scores->shape[0] == bs && scores->shape[1] == H && scores->shape[2] == world * Kl &&
+                 indices->shape[0] == bs && indices->shape[1] == H && indices->shape[2] == world * Kl,
+             "scores / indices must be [bs,H,world*Kl]");
+  PK_REQUIRE(world * Kl < (1LL << 31) && bs * H < 65536, "sizes out of range");
+  PK_REQUIRE((reinterpret_cast<uintptr_t>(gathered->data) & 15) == 0, "gathered must be 16-byte aligned");
+  if (numel(gathered) == 0) return PK_OK;
+  shard_unpack_kernel<<<dim3((unsigned)((world * Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
+      (const int64_t*)gathered->data, (float*)scores->data, (int64_t*)indices->data, (int)world, (int)(bs * H), (int)Kl);
+  return check_launch("shard_unpack_topk");
+}
+
+extern "C" int pk_shard_owned_rows(const pk_tensor* final_indices, int64_t start, int64_t end, const pk_tensor* local,
+                                   const pk_tensor* n_owned, void* stream) {
+  PK_CHECK_TENSOR(final_indices, PK_I64, 3);
+  PK_CHECK_TENSOR(local, PK_I64, 3);
+  PK_CHECK_TENSOR(n_owned, PK_I32, 2);
+  const int64_t bs = final_indices->shape[0], H = final_indices->shape[1], K = final_indices->shape[2];
+  PK_REQUIRE(is_contig(final_indices) && is_contig(local) && is_contig(n_owned), "tensors must be contiguous");
+  PK_REQUIRE(local->shape[0] == bs && local->shape[1] == H && local->shape[2] == K && n_owned->shape[0] == bs &&
+                 n_owned->shape[1] == H,
+             "local must be [bs,H,K] and n_owned [bs,H]");
+  PK_REQUIRE(start <= end && K < (1LL << 31), "bad shard range");
+  if (bs * H == 0) return PK_OK;
+  shard_owned_kernel<<<(unsigned)(bs * H), 256, 0, (cudaStream_t)stream>>>(
+      (const int64_t*)final_indices->data, (int64_t*)local->data, (int32_t*)n_owned->data, (int)K, start, end);
+  return check_launch("shard_owned_rows");
+}
+
+extern "C" int pk_shard_pack_partial(const pk_tensor* out, const pk_tensor* lse, const pk_tensor* packed, void* stream) {
+  PK_CHECK_TENSOR(out, PK_BF16, 4);
+  PK_CHECK_TENSOR(lse, PK_F32, 2);
+  PK_CHECK_TENSOR(packed, PK_F32, 3);
+  const int64_t bs = out->shape[0], Hq = out->shape[2];
+  PK_REQUIRE(out->shape[1] == 1 && out->shape[3] == 128 && is_contig(out), "out must be contiguous [bs,1,Hq,128]");
+  PK_REQUIRE(lse->shape[0] == bs && lse->shape[1] == Hq && is_contig(lse), "lse must be contiguous [bs,Hq]");
+  PK_REQUIRE(packed->shape[0] == bs && packed->shape[1] == Hq && packed->shape[2] == 129 && is_contig(packed),
+             "packed must be contiguous [bs,Hq,129]");
+  if (bs * Hq == 0) return PK_OK;
+  shard_pack_partial_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)out->data, (const float*)lse->data, (float*)packed->data);
+  return check_launch("shard_pack_partial");
+}
+
+extern "C" int pk_shard_merge_partial(const pk_tensor* gathered, const pk_tensor* out, void* stream) {
+  PK_CHECK_TENSOR(gathered, PK_F32, 4);
+  PK_CHECK_TENSOR(out, PK_BF16, 4);
+  const int64_t world = gathered->shape[0], bs = gathered->shape[1], Hq = gathered->shape[2];
+  PK_REQUIRE(gathered->shape[3] == 129 && is_contig(gathered), "gathered must be contiguous [world,bs,Hq,129]");
+  PK_REQUIRE(out->shape[0] == bs && out->shape[1] == 1 && out->shape[2] == Hq && out->shape[3] == 128 && is_contig(out),
+             "out must be contiguous [bs,1,Hq,128]");
+  PK_REQUIRE(world >= 1 && world <= 1024, "world size out of range");
+  if (bs * Hq == 0) return PK_OK;
+  shard_merge_partial_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
+      (const float*)gathered->data, (__nv_bfloat16*)out->data, (int)world, (int)(bs * Hq));
+  return check_launch("shard_merge_partial");
+}

@@ -107,13 +107,18 @@ def merge_partial_attention(out: torch.Tensor, lse: torch.Tensor, group=None) ->
     packed[..., D] = lse
     flat = torch.empty(world * bs, Hq, D + 1, dtype=torch.float32, device=out.device)
     dist.all_gather_into_tensor(flat, packed, group=group)
-    gathered = flat.view(world, bs, Hq, D + 1)
+    return merge_gathered_partials(flat.view(world, bs, Hq, D + 1)).to(out.dtype)
+
+
+def merge_gathered_partials(gathered: torch.Tensor) -> torch.Tensor:
+    """gathered fp32 [world,bs,Hq,D+1] = (partial output, log2 denominator) of every rank -> fp32 [bs,1,Hq,D]."""
+    D = gathered.shape[-1] - 1
     l = gathered[..., D]                                        # [world,bs,Hq]
     m = l.max(dim=0, keepdim=True).values
     w = torch.where(torch.isinf(l) & (l < 0), torch.zeros_like(l), torch.exp2(l - torch.where(torch.isinf(m), torch.zeros_like(m), m)))
     denom = w.sum(0).clamp_min(1e-38)
     merged = (gathered[..., :D] * w.unsqueeze(-1)).sum(0) / denom.unsqueeze(-1)
-    return merged.unsqueeze(1).to(out.dtype)
+    return merged.unsqueeze(1)
 
 
 def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global, store_k,
@@ -133,14 +138,23 @@ def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_wei
                                     n_window_dev=n_window_dev, n_window_add=n_window_add), final
     fin_local, ex = ops.retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global,
                                  tiers, c_local, k_local, want=("cand", "scores_f32"))
-    scores = torch.gather(ex["scores_f32"], 2, torch.searchsorted(ex["cand"], fin_local))
-    final = merge_local_topk(scores, fin_local + start, min(final_topk, world * k_local), group)
-    local, n_owned = owned_rows(final, start, end)
     bs, _, Hq, _ = queries.shape
-    lse = torch.empty(bs, Hq, dtype=torch.float32, device=queries.device)
+    H, dev = codebook.shape[1], queries.device
+    # exchange 1: (score, global index) of the local top list, one packed buffer, one all-gather
+    packed = ops.shard_pack_topk(ex["cand"], ex["scores_f32"], fin_local, start)
+    flat = torch.empty(world * bs, H, k_local, 2, dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(flat, packed, group=group)          # output = inputs concatenated along dim 0
+    scores, indices = ops.shard_unpack_topk(flat.view(world, bs, H, k_local, 2))
+    final = ops.final_topk(scores, indices, min(final_topk, world * k_local))
+    local, n_owned = ops.shard_owned_rows(final, start, end)
+    lse = torch.empty(bs, Hq, dtype=torch.float32, device=dev)
     out = ops.sparse_attention(queries, window_k, window_v, n_window, store_k, store_v, local, n_sel=n_owned, lse=lse,
                                n_window_dev=n_window_dev, n_window_add=n_window_add)
-    return merge_partial_attention(out, lse, group), final
+    # exchange 2: (partial output, log2 denominator), one packed buffer, one all-gather
+    part = ops.shard_pack_partial(out, lse)
+    flat2 = torch.empty(world * bs, Hq, 129, dtype=torch.float32, device=dev)
+    dist.all_gather_into_tensor(flat2, part, group=group)
+    return ops.shard_merge_partial(flat2.view(world, bs, Hq, 129)), final
 
 
 class SequenceShardedCache:
@@ -151,7 +165,8 @@ class SequenceShardedCache:
     must not overflow (no flush in this form yet), which holds for runs shorter than the buffer."""
 
     def __init__(self, layer_num, num_kv_heads, num_heads, n_total, sink_size, local_size, interval, final_topk,
-                 device, rank, world, group=None, collision_ratio=0.2, candidate_ratio=0.1, srht_sign_vector=None):
+                 device, rank, world, group=None, collision_ratio=0.2, candidate_ratio=0.1, srht_sign_vector=None,
+                 store="host"):
         from .cache_hub.polar_cache import srht_signs
         self.layer_num, self.kv_head, self.num_heads = layer_num, num_kv_heads, num_heads
         self.n_total, self.sink_size, self.local_size, self.interval = n_total, sink_size, local_size, interval
@@ -173,6 +188,14 @@ class SequenceShardedCache:
         self.store_v = [None] * layer_num
         self.context = 0
         self.last_topk_indices = None
+        if store not in ("host", "hbm", "auto"):
+            raise ValueError("store must be 'host', 'hbm' or 'auto'")
+        if store == "auto":   # keep the shard's K/V rows in HBM when they fit beside the codes, else pinned host memory
+            n_local = self.end - self.start
+            need = layer_num * num_kv_heads * n_local * (512 + 112)
+            free, _ = torch.cuda.mem_get_info(device)
+            store = "hbm" if need + (16 << 30) < free else "host"
+        self.store = store
         self.device_positions = False     # window length read from a device word (captured steps)
         self._dev_state = torch.zeros(1, dtype=torch.int32, device=device)
 
@@ -184,10 +207,13 @@ class SequenceShardedCache:
         self.meta[layer] = ops.encode_keys(shard_keys, self.signs, cluster_counts=counts)
         self.counts[layer] = allreduce_cluster_counts(counts, self.group)
         n_local = shard_keys.shape[2]
-        sk = torch.empty(1, self.kv_head, max(n_local, 1), 128, dtype=torch.bfloat16, pin_memory=True)
-        sv = torch.empty(1, self.kv_head, max(n_local, 1), 128, dtype=torch.bfloat16, pin_memory=True)
-        sk[:, :, :n_local].copy_(shard_keys, non_blocking=True)
-        sv[:, :, :n_local].copy_(shard_values, non_blocking=True)
+        if self.store == "hbm" and n_local > 0:
+            sk, sv = shard_keys.contiguous().clone(), shard_values.contiguous().clone()
+        else:
+            sk = torch.empty(1, self.kv_head, max(n_local, 1), 128, dtype=torch.bfloat16, pin_memory=True)
+            sv = torch.empty(1, self.kv_head, max(n_local, 1), 128, dtype=torch.bfloat16, pin_memory=True)
+            sk[:, :, :n_local].copy_(shard_keys, non_blocking=True)
+            sv[:, :, :n_local].copy_(shard_values, non_blocking=True)
         self.store_k[layer], self.store_v[layer] = sk, sv
         n = window_keys.shape[2]
         self.window_k[layer][:, :, :n] = window_keys

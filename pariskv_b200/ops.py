@@ -289,3 +289,60 @@ def retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, 
           tiers, len(tier_counts), int(C), int(K), L.ref(d[7]), L.ref(d[8]), L.ref(d[9]), L.ref(d[10]),
           L.ref(d[11]), L.ref(d[12]), ws.data_ptr(), ws.numel(), L.stream_ptr(dev))
     return final_indices, extras
+
+
+# --------------------------------------------------------------------------------------------------
+# sequence-sharded form: packing / unpacking around the two all-gathers
+# --------------------------------------------------------------------------------------------------
+def shard_pack_topk(cand, scores, local_final, start, packed=None):
+    """(cand, scores, local_final) -> packed i64 [bs,H,Kl,2]; see pk_shard_pack_topk."""
+    _require_cuda(cand, scores, local_final)
+    bs, H, Kl = local_final.shape
+    if packed is None:
+        packed = torch.empty(bs, H, Kl, 2, dtype=torch.int64, device=cand.device)
+    d = [L.desc(t) for t in (cand, scores, local_final, packed)]
+    _call("pk_shard_pack_topk", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(start), L.ref(d[3]), L.stream_ptr(cand.device))
+    return packed
+
+
+def shard_unpack_topk(gathered):
+    """gathered i64 [world,bs,H,Kl,2] -> (scores f32, indices i64) [bs,H,world*Kl]; see pk_shard_unpack_topk."""
+    _require_cuda(gathered)
+    world, bs, H, Kl, _ = gathered.shape
+    scores = torch.empty(bs, H, world * Kl, dtype=torch.float32, device=gathered.device)
+    indices = torch.empty(bs, H, world * Kl, dtype=torch.int64, device=gathered.device)
+    d = [L.desc(t) for t in (gathered, scores, indices)]
+    _call("pk_shard_unpack_topk", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), L.stream_ptr(gathered.device))
+    return scores, indices
+
+
+def shard_owned_rows(final_indices, start, end):
+    """final i64 [bs,H,K] -> (local i64 [bs,H,K], n_owned i32 [bs,H]); see pk_shard_owned_rows."""
+    _require_cuda(final_indices)
+    bs, H, K = final_indices.shape
+    local = torch.empty_like(final_indices)
+    n_owned = torch.empty(bs, H, dtype=torch.int32, device=final_indices.device)
+    d = [L.desc(t) for t in (final_indices, local, n_owned)]
+    _call("pk_shard_owned_rows", L.ref(d[0]), int(start), int(end), L.ref(d[1]), L.ref(d[2]),
+          L.stream_ptr(final_indices.device))
+    return local, n_owned
+
+
+def shard_pack_partial(out, lse):
+    """(out bf16 [bs,1,Hq,128], lse f32 [bs,Hq]) -> packed f32 [bs,Hq,129]; see pk_shard_pack_partial."""
+    _require_cuda(out, lse)
+    bs, _, Hq, _ = out.shape
+    packed = torch.empty(bs, Hq, 129, dtype=torch.float32, device=out.device)
+    d = [L.desc(t) for t in (out, lse, packed)]
+    _call("pk_shard_pack_partial", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), L.stream_ptr(out.device))
+    return packed
+
+
+def shard_merge_partial(gathered):
+    """gathered f32 [world,bs,Hq,129] -> out bf16 [bs,1,Hq,128]; see pk_shard_merge_partial."""
+    _require_cuda(gathered)
+    world, bs, Hq, _ = gathered.shape
+    out = torch.empty(bs, 1, Hq, 128, dtype=torch.bfloat16, device=gathered.device)
+    d = [L.desc(t) for t in (gathered, out)]
+    _call("pk_shard_merge_partial", L.ref(d[0]), L.ref(d[1]), L.stream_ptr(gathered.device))
+    return out

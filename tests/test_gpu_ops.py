@@ -359,3 +359,48 @@ def test_sparse_attention_per_head_counts(ops, oracle):
         vv = torch.cat([wv[:, h:h + 1], oracle.gather(vals[:, h:h + 1], sel[:, h:h + 1, :n])], 2)
         ref = oracle.attention(q[:, :, 4 * h:4 * h + 4], kk, vv)
         assert (out[:, :, 4 * h:4 * h + 4].float().cpu() - ref).abs().max().item() <= 2e-2
+
+
+# ---- glue kernels of the sequence-sharded form (against the torch formulation used by the gloo tests) ----
+def test_shard_pack_unpack_owned_merge(ops):
+    from pariskv_b200 import dist as pkd
+    g = torch.Generator().manual_seed(11)
+    bs, H, C, Kl, world, start = 2, 3, 5000, 257, 3, 70000
+    cand = torch.stack([torch.randperm(40000, generator=g)[:C].sort().values for _ in range(bs * H)]).view(bs, H, C)
+    scores = torch.randn(bs, H, C, generator=g)
+    pos = torch.stack([torch.randperm(C, generator=g)[:Kl].sort().values for _ in range(bs * H)]).view(bs, H, Kl)
+    fin = torch.gather(cand, 2, pos)
+    packed = ops.shard_pack_topk(cand.cuda(), scores.cuda(), fin.cuda(), start).cpu()
+    assert torch.equal(packed[..., 1], fin + start)
+    assert torch.equal(packed[..., 0].to(torch.int32).view(torch.float32), torch.gather(scores, 2, pos))
+
+    gathered = torch.randint(-2 ** 31, 2 ** 31 - 1, (world, bs, H, Kl, 2), generator=g, dtype=torch.int64)
+    sc, idx = ops.shard_unpack_topk(gathered.cuda())
+    want = gathered.permute(1, 2, 0, 3, 4).reshape(bs, H, world * Kl, 2)
+    assert torch.equal(idx.cpu(), want[..., 1])
+    assert torch.equal(sc.cpu().view(torch.int32), want[..., 0].to(torch.int32))
+
+    final = torch.stack([torch.randperm(100000, generator=g)[:Kl].sort().values for _ in range(bs * H)]).view(bs, H, Kl)
+    for (s, e) in ((0, 100000), (30000, 60000), (99999, 100000), (50, 50)):
+        local, n = ops.shard_owned_rows(final.cuda(), s, e)
+        wl, wn = pkd.owned_rows(final, s, e)
+        assert torch.equal(n.cpu(), wn)
+        for b in range(bs):
+            for h in range(H):
+                k = int(wn[b, h])
+                assert torch.equal(local.cpu()[b, h, :k], wl[b, h, :k])
+                assert int(local.cpu()[b, h, k:].abs().sum()) == 0
+
+    Hq = 8
+    parts = torch.randn(world, bs, Hq, 129, generator=g)
+    parts[..., 128] *= 6
+    parts[1, :, 2, 128] = float("-inf")                 # a rank without rows for some heads
+    parts[:, 1, 5, 128] = float("-inf")                 # nobody has rows: result 0
+    parts[..., :128] = parts[..., :128].to(torch.bfloat16).float()
+    got = ops.shard_merge_partial(parts.cuda()).float().cpu()
+    want = pkd.merge_gathered_partials(parts)
+    want[1, 0, 5] = 0
+    assert (got - want).abs().max().item() <= 1e-2
+    out = parts[0, :, :, :128].to(torch.bfloat16).unsqueeze(1).contiguous()
+    pp = ops.shard_pack_partial(out.cuda(), parts[0, :, :, 128].contiguous().cuda()).cpu()
+    assert torch.equal(pp[..., :128], out[:, 0].float()) and torch.equal(pp[..., 128], parts[0, :, :, 128])
