@@ -210,7 +210,9 @@ int pk_gather_kv_out_cpu(const pk_tensor* src, const pk_tensor* index, const pk_
  * window plus K selected rows of the big store:
  *   queries   bf16 [bs,1,Hq,128] contiguous
  *   window_k/window_v bf16 [bs,H,cap_w,128] device, last stride 1, row stride 128
- *   store_k/store_v   bf16 [bs,H,cap_s,128] contiguous; pinned HOST (UVA) or device
+ *   store_k/store_v   bf16 [bs,H,cap_s,128], last stride 1, other strides equal for both and multiples of 8
+ *                     elements (e.g. the two halves of one [bs,H,cap_s,2,128] buffer, which puts the K and V row
+ *                     of a key in the same page); pinned HOST (UVA) or device
  *   selected  i64 [bs,H,K] (device) or NULL with K = 0;  row = selected + index_offset
  *   n_window_dev i32 [1] device, or NULL.  When given, the number of window rows is read on the device as
  *             min(n_window, n_window_dev[0] + n_window_add) and n_window only sizes the grid, so a captured

@@ -32,6 +32,7 @@ struct AttParams {
   const uint16_t* sk;
   const uint16_t* sv;
   int64_t cap_s;          // rows per (b,h) of the store
+  int64_t s_b, s_h, s_l;  // store strides in elements (batch, head, row); K and V share them
   const int64_t* sel;     // [bs*H][K]
   const int32_t* n_sel;   // [bs*H] or null
   int64_t K, index_offset;
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
       } else {
         const int64_t row = p.sel[bh * p.K + (r - n_window)] + p.index_offset;
         ok = row >= 0 && row < p.cap_s;
-        src = (is_v ? p.sv : p.sk) + (bh * p.cap_s + (ok ? row : 0)) * 128;
+        src = (is_v ? p.sv : p.sk) + b * p.s_b + h * p.s_h + (ok ? row : 0) * p.s_l;
       }
     }
     if (tid == 0) {
@@ -331,12 +332,19 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
     K = selected->shape[2];
     PK_REQUIRE(H == 0 || store_k->shape[1] == H, "window and store disagree on the number of KV heads");
     H = store_k->shape[1];
-    PK_REQUIRE(is_contig(store_k) && is_contig(store_v) && store_k->shape[0] == bs && store_k->shape[3] == 128 &&
-                   store_v->shape[0] == bs && store_v->shape[1] == H && store_v->shape[2] == store_k->shape[2] &&
-                   store_v->shape[3] == 128,
-               "store_k / store_v must be contiguous [bs,H,cap,128]");
+    PK_REQUIRE(store_k->shape[0] == bs && store_k->shape[3] == 128 && store_v->shape[0] == bs && store_v->shape[1] == H &&
+                   store_v->shape[2] == store_k->shape[2] && store_v->shape[3] == 128 && store_k->stride[3] == 1 &&
+                   store_v->stride[3] == 1,
+               "store_k / store_v must be [bs,H,cap,128] with last stride 1");
+    for (int i = 0; i < 3; i++) {
+      PK_REQUIRE(store_k->shape[i] == 1 || store_k->stride[i] == store_v->stride[i], "store_k and store_v must have the same strides");
+      PK_REQUIRE(store_k->shape[i] == 1 || store_k->stride[i] % 8 == 0, "store rows must be 16-byte aligned");
+    }
     PK_REQUIRE((reinterpret_cast<uintptr_t>(store_k->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(store_v->data) & 15) == 0,
                "store rows must be 16-byte aligned");
+    p.s_b = store_k->shape[0] == 1 ? 0 : store_k->stride[0];
+    p.s_h = store_k->shape[1] == 1 ? 0 : store_k->stride[1];
+    p.s_l = store_k->shape[2] == 1 ? 128 : store_k->stride[2];
     PK_REQUIRE(is_contig(selected) && selected->shape[0] == bs && selected->shape[1] == H,
                "selected must be contiguous [bs,H,K]");
     p.sk = (const uint16_t*)store_k->data, p.sv = (const uint16_t*)store_v->data;

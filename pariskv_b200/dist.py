@@ -207,13 +207,14 @@ class SequenceShardedCache:
         self.meta[layer] = ops.encode_keys(shard_keys, self.signs, cluster_counts=counts)
         self.counts[layer] = allreduce_cluster_counts(counts, self.group)
         n_local = shard_keys.shape[2]
+        # K and V row of a key next to each other: one host address translation per selected key instead of two
+        kv = torch.stack((shard_keys, shard_values), dim=3)          # [1,H,n,2,128] on the device
         if self.store == "hbm" and n_local > 0:
-            sk, sv = shard_keys.contiguous().clone(), shard_values.contiguous().clone()
+            skv = kv
         else:
-            sk = torch.empty(1, self.kv_head, max(n_local, 1), 128, dtype=torch.bfloat16, pin_memory=True)
-            sv = torch.empty(1, self.kv_head, max(n_local, 1), 128, dtype=torch.bfloat16, pin_memory=True)
-            sk[:, :, :n_local].copy_(shard_keys, non_blocking=True)
-            sv[:, :, :n_local].copy_(shard_values, non_blocking=True)
+            skv = torch.empty(1, self.kv_head, max(n_local, 1), 2, 128, dtype=torch.bfloat16, pin_memory=True)
+            skv[:, :, :n_local].copy_(kv, non_blocking=True)
+        sk, sv = skv[:, :, :, 0], skv[:, :, :, 1]
         self.store_k[layer], self.store_v[layer] = sk, sv
         n = window_keys.shape[2]
         self.window_k[layer][:, :, :n] = window_keys

@@ -361,6 +361,27 @@ def test_sparse_attention_per_head_counts(ops, oracle):
         assert (out[:, :, 4 * h:4 * h + 4].float().cpu() - ref).abs().max().item() <= 2e-2
 
 
+@pytest.mark.parametrize("where", ["pinned_host", "device"])
+def test_sparse_attention_interleaved_store(ops, where):
+    """K and V rows as the two strided halves of one [bs,H,N,2,128] buffer give the same bits as separate stores."""
+    g = torch.Generator().manual_seed(21)
+    bs, H, N, K = 2, 2, 3000, 200
+    keys = synth_keys(g, bs, H, N)
+    vals = torch.randn(bs, H, N, 128, generator=g).to(torch.bfloat16)
+    q = (synth_queries(g, keys, 4) * 3).to(DEV)
+    wk = torch.randn(bs, H, 16, 128, generator=g).to(torch.bfloat16).to(DEV)
+    wv = torch.randn(bs, H, 16, 128, generator=g).to(torch.bfloat16).to(DEV)
+    sel = torch.stack([torch.stack([torch.randperm(N, generator=g)[:K].sort().values for _ in range(H)])
+                       for _ in range(bs)]).to(DEV)
+    kv = torch.stack((keys, vals), dim=3)
+    kv = kv.pin_memory() if where == "pinned_host" else kv.to(DEV)
+    a = ops.sparse_attention(q, wk, wv, 16, kv[:, :, :, 0], kv[:, :, :, 1], sel)
+    b = ops.sparse_attention(q, wk, wv, 16, keys.to(DEV), vals.to(DEV), sel)
+    assert torch.equal(a, b)
+    with pytest.raises(RuntimeError):   # K and V must share strides
+        ops.sparse_attention(q, wk, wv, 16, kv[:, :, :, 0], vals.to(DEV), sel)
+
+
 # ---- glue kernels of the sequence-sharded form (against the torch formulation used by the gloo tests) ----
 def test_shard_pack_unpack_owned_merge(ops):
     from pariskv_b200 import dist as pkd
