@@ -426,6 +426,63 @@ def ops_mode(args, cfg, device):
                       "peak_kind": kind, "rotating_sets": R, "ops": out}), flush=True)
 
 
+def prefill_mode(args, cfg, device):
+    """Cache ingestion at prefill: per layer, key coding of the whole prompt plus the offload of its K/V rows to
+    pinned host memory.  Two figures: the time the COMPUTE stream is busy (what the cache adds to a prefill whose
+    attention runs on that stream) and the time until the last offload has landed."""
+    from pariskv_b200 import _lib
+    from pariskv_b200.cache_hub.polar_cache import polar_cache
+    P, Lyr, H = cfg["context"], cfg["layers"], cfg["kv_heads"]
+    reps = max(1, min(args.steps, 4)) if args.steps != 256 else 2
+    cache = polar_cache(valid_start=[0], layer_num=Lyr, batch_size=1, max_length=P + 256, num_key_value_heads=H,
+                        num_heads=cfg["q_heads"], head_dim=128, dtype=torch.bfloat16,
+                        layer_mapping={str(i): str(device) for i in range(Lyr)}, max_new_length=256,
+                        sink_size=cfg["sink"], local_size=cfg["local"], core=0, nprobe=0, cache_unit_size=0,
+                        cache_cluster_num=0, num_gpus=1, model_size=8, final_topk=cfg["topk"],
+                        dynamic_update_interval=cfg["interval"], enable_offload=True)
+    g = torch.Generator(device=device).manual_seed(3)
+    kv = [synth_kv(g, P, H, device) for _ in range(2)]          # two rotating prompts' worth of K/V
+    # pinned-copy reference rate on this box: one contiguous 1 GiB device -> host transfer
+    src = torch.empty(1 << 30, dtype=torch.uint8, device=device)
+    dst = torch.empty(1 << 30, dtype=torch.uint8, pin_memory=True)
+    dst.copy_(src, non_blocking=True)
+    torch.cuda.synchronize(device)
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    dst.copy_(src, non_blocking=True)
+    c1.record()
+    torch.cuda.synchronize(device)
+    d2h_gbs = (1 << 30) / (c0.elapsed_time(c1) * 1e-3) / 1e9
+    del src, dst
+    res = []
+    for rep in range(reps + 1):
+        torch.cuda.synchronize(device)
+        n0 = _lib.launch_count()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        for l in range(Lyr):
+            k, v = kv[l % 2]
+            cache.prefill_update_kv_cache(None, k, v, l, 0)
+        e1.record()                                   # compute stream done (coding + staging)
+        for l in range(Lyr):
+            cache.sync(l, 0)                          # stream-side wait for every layer's offload
+        e2.record()
+        torch.cuda.synchronize(device)
+        if rep > 0:                                   # the first pass warms the allocator and the pinned pages
+            res.append((e0.elapsed_time(e1), e0.elapsed_time(e2), _lib.launch_count() - n0))
+    comp = sum(r[0] for r in res) / len(res)
+    total = sum(r[1] for r in res) / len(res)
+    N = P - cfg["sink"] - cfg["local"]
+    offload_bytes = Lyr * H * N * 512
+    print(json.dumps({
+        "mode": "prefill", "invalid": "profiling target: cache ingestion only, not the benchmark",
+        "context": P, "layers": Lyr, "kv_heads": H, "passes": len(res),
+        "compute_stream_ms": round(comp, 3), "compute_stream_ms_per_layer": round(comp / Lyr, 3),
+        "until_offloaded_ms": round(total, 3), "tokens_per_s_ingested": round(P / (total * 1e-3), 1),
+        "offload_gbs": round(offload_bytes / (total * 1e-3) / 1e9, 2), "pinned_d2h_copy_gbs": round(d2h_gbs, 2),
+        "offload_bytes": offload_bytes, "gpu_launches_per_pass": res[-1][2]}), flush=True)
+
+
 def kernels_mode(args, cfg, device):
     """Cache path only: per step and layer one K/V append and one compute() on a random query."""
     from pariskv_b200 import _lib
@@ -625,7 +682,7 @@ def main():
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
     ap.add_argument("--stage-steps", type=int, default=16, help="extra steps with per-kernel event timing")
     ap.add_argument("--no-graph", action="store_true", help="run every step eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops", "seqshard"],
+    ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops", "seqshard", "prefill"],
                     help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
                          "a small profiling target, its line is marked as such")
     ap.add_argument("--store", default="auto", choices=["auto", "host", "hbm"],
@@ -676,6 +733,9 @@ def main():
         return
     if args.mode == "ops":
         ops_mode(args, cfg, device)
+        return
+    if args.mode == "prefill":
+        prefill_mode(args, cfg, device)
         return
     K, W, S = args.steps, args.warmup, args.stage_steps
     max_new = W + 2 * K + S + 2 * cfg["interval"] + 8

@@ -74,6 +74,7 @@ class AdaptiveKCache(_base_cache):
     # ---- decode attention ---------------------------------------------------------------------------------
     def compute(self, queries, layer_idx):
         queries = queries.contiguous()
+        self._wait_offload(layer_idx)
         N = self.cpu_valid_end[layer_idx]
         n_win = self._window_len[layer_idx]
         total = self.current_seq_len[layer_idx]

@@ -115,6 +115,12 @@ class polar_cache(KV_Cache):
         self._store_v = [t[:, :, :, 1] for t in self._store_kv]
         self.unified_keys_cpu = self._store_k if enable_offload else None
         self.unified_values_cpu = self._store_v if enable_offload else None
+        # bulk offload (prefill): device -> pinned host copies run on their own stream so that the compute stream is
+        # free for the next layer's prefill; one event per layer, waited for (on the stream, not the host) by the
+        # first consumer of that layer's store (cache_hub/polar_cache.py:202-210, :617-639)
+        self._copy_stream = torch.cuda.Stream(device=dev) if enable_offload else None
+        self._offload_event = [None] * layer_num
+        self.BULK_OFFLOAD_ROWS = 4096
         self.codebook_gpu, self.key_block_weight_gpu, self.key_4bit_packed_gpu = [], [], []
         for _ in range(layer_num):
             cb, w, pk = ops.alloc_key_metadata(bs, H, self.zone_capacity, dev)
@@ -206,8 +212,28 @@ class polar_cache(KV_Cache):
                         self.key_4bit_packed_gpu[layer][b:b + 1, :, :, sl, :], cluster_counts=counts)
         skv = self._store_kv[layer]
         kv = torch.stack((zk, zv), dim=2)  # [H, n, 2, 128] on the device: K and V rows interleaved as the store holds them
+        if self._copy_stream is not None and n >= self.BULK_OFFLOAD_ROWS:
+            cur = torch.cuda.current_stream(kv.device)
+            self._wait_offload(layer)                 # an earlier bulk copy of this layer must stay ordered
+            self._copy_stream.wait_stream(cur)
+            with torch.cuda.stream(self._copy_stream):
+                for h in range(self.kv_head):
+                    skv[b, h, sl].copy_(kv[h], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self._copy_stream)
+            kv.record_stream(self._copy_stream)       # keep the staging tensor alive until the copies have run
+            self._offload_event[layer] = ev
+            return
+        self._wait_offload(layer)
         for h in range(self.kv_head):  # contiguous per-head blocks: one async copy each, on the current stream
             skv[b, h, sl].copy_(kv[h], non_blocking=True)
+
+    def _wait_offload(self, layer):
+        """Order the current stream after the layer's pending bulk offload, if any (no host block)."""
+        ev = self._offload_event[layer]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            self._offload_event[layer] = None
 
     # ------------------------------------------------------------------------------------------------
     # decode
@@ -271,6 +297,7 @@ class polar_cache(KV_Cache):
     def compute(self, queries, layer_idx):
         """Decode attention of one token: queries [bs, 1, num_heads, 128] -> [bs, 1, num_heads, 128]."""
         queries = queries.contiguous()
+        self._wait_offload(layer_idx)
         N = self.cpu_valid_end[layer_idx]
         n_win = self._window_len[layer_idx]
         total = self.current_seq_len[layer_idx]
@@ -325,5 +352,7 @@ class polar_cache(KV_Cache):
         self.context += 1
 
     def sync(self, layer_idx, batch_idx):
-        """No-op: copies to the zone store are ordered on the compute stream."""
+        """Order the current stream after the layer's bulk offload (cache_hub/polar_cache.py:617-639).  The
+        reference blocks the host here; a stream-side wait is enough because every consumer is a kernel."""
+        self._wait_offload(layer_idx)
         return None

@@ -168,3 +168,37 @@ def test_cache_step_replayed_as_cuda_graph_matches_eager(oracle):
         torch.cuda.synchronize()
         assert torch.equal(out_s, refs[t]), f"replay {t} differs from the eager step"
     assert graphed.host_state() == eager.host_state()
+
+
+def test_bulk_offload_on_copy_stream(oracle):
+    """A prompt long enough for the copy-stream offload: the store holds exactly the zone rows (K and V interleaved),
+    and a decode step issued right after the prefill (no host synchronisation) sees them."""
+    g = torch.Generator().manual_seed(17)
+    bs, H, Hq, sink, local, I, topk, P, layers = 1, 2, 8, 4, 16, 8, 32, 6000, 2
+    cache = _make_cache(P, 32, bs, H, Hq, sink, local, I, topk, True, layers)
+    assert cache.BULK_OFFLOAD_ROWS <= P - sink - local
+    Ks = [synth_keys(g, bs, H, P) for _ in range(layers)]
+    Vs = [torch.randn(bs, H, P, 128, generator=g).to(torch.bfloat16) for _ in range(layers)]
+    for l in range(layers):
+        cache.prefill_update_kv_cache(None, Ks[l].transpose(1, 2).contiguous().to(DEV),
+                                      Vs[l].transpose(1, 2).contiguous().to(DEV), l, 0)
+        assert cache._offload_event[l] is not None
+    outs, fins = [], []
+    qs = [torch.randn(bs, 1, Hq, 128, generator=g).to(torch.bfloat16) for _ in range(layers)]
+    nk = torch.randn(bs, 1, H, 128, generator=g).to(torch.bfloat16)
+    nv = torch.randn(bs, 1, H, 128, generator=g).to(torch.bfloat16)
+    for l in range(layers):           # straight after the prefill: ordering comes from the layer's event
+        cache.decode_update_kv_cache(nk.to(DEV), nv.to(DEV), l)
+        outs.append(cache.compute(qs[l].to(DEV), l))
+        fins.append(cache.last_topk_indices)
+        assert cache._offload_event[l] is None
+    torch.cuda.synchronize()
+    N = P - sink - local
+    for l in range(layers):
+        assert torch.equal(cache.unified_keys_cpu[l][:, :, :N], Ks[l][:, :, sink:sink + N])
+        assert torch.equal(cache.unified_values_cpu[l][:, :, :N], Vs[l][:, :, sink:sink + N])
+        K_all = torch.cat([Ks[l], nk.transpose(1, 2)], 2)
+        V_all = torch.cat([Vs[l], nv.transpose(1, 2)], 2)
+        att, fin = _oracle_step(oracle, cache, qs[l], K_all, V_all, P - local, l)
+        assert torch.equal(fins[l].cpu(), fin)
+        assert (outs[l].float().cpu() - att).abs().max().item() <= 2e-2
