@@ -397,6 +397,8 @@ def ops_mode(args, cfg, device):
     torch.cuda.nvtx.range_push("timed")
     side = torch.cuda.Stream(device=device)
     for name, (fn, nbytes) in tests.items():
+        if args.only and args.only not in name:
+            continue
         for r in range(R):
             fn(r)
         torch.cuda.synchronize(device)
@@ -685,6 +687,7 @@ def main():
     ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops", "seqshard", "prefill"],
                     help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
                          "a small profiling target, its line is marked as such")
+    ap.add_argument("--only", default=None, help="--mode ops: run only the ops whose name contains this text")
     ap.add_argument("--store", default="auto", choices=["auto", "host", "hbm"],
                     help="--mode seqshard: where a shard's K/V rows live (auto: HBM when they fit, else pinned host)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the line invalid)")

@@ -285,6 +285,31 @@ int pk_shard_owned_rows(const pk_tensor* final_indices, int64_t start, int64_t e
 int pk_shard_pack_partial(const pk_tensor* out, const pk_tensor* lse, const pk_tensor* packed, void* stream);
 int pk_shard_merge_partial(const pk_tensor* gathered, const pk_tensor* out, void* stream);
 
+/* The same two exchanges over peer memory instead of a collective.  Every rank owns one buffer with the same layout,
+ * mapped into every peer's address space (peer_bases[r] = address of rank r's buffer as seen from THIS process):
+ * at gather_offset the gather area of the exchange ([world][bs*H][Kl][2] i64, or [world][bs*Hq][129] f32), at
+ * flags_offset `world` u32 flag words, zero before the first use.  `control` points to 16 bytes of LOCAL device
+ * memory per exchange (exchange number, arrival counter, status, pad), zero before the first use.
+ *   pk_shard_exchange_*  computes this rank's rows (as pk_shard_pack_*), stores them into slot `rank` of every
+ *                        peer's gather area and then publishes the exchange number in word `rank` of every
+ *                        peer's flags;
+ *   pk_shard_collect_*   (launched after the matching exchange on the same stream) waits until all `world` local
+ *                        flag words carry the current exchange number and then does the work of
+ *                        pk_shard_unpack_topk / pk_shard_merge_partial on the local gather area.
+ * The wait is bounded (about a second); on expiry control[2] is set to 1, the kernel continues on whatever the
+ * buffer holds, and the caller must treat the results as invalid.  Ranks must issue the exchanges in the same
+ * order; the two exchanges of a layer use different areas, flags and control blocks.  At most 16 ranks.
+ * No counterpart in the reference. */
+int pk_shard_exchange_topk(const pk_tensor* cand, const pk_tensor* scores, const pk_tensor* local_final, int64_t start,
+                           const uint64_t* peer_bases, int world, int rank, int64_t gather_offset,
+                           int64_t flags_offset, void* control, void* stream);
+int pk_shard_collect_topk(uint64_t local_base, int64_t gather_offset, int64_t flags_offset, void* control, int world,
+                          int64_t Kl, const pk_tensor* scores, const pk_tensor* indices, void* stream);
+int pk_shard_exchange_partial(const pk_tensor* out, const pk_tensor* lse, const uint64_t* peer_bases, int world,
+                              int rank, int64_t gather_offset, int64_t flags_offset, void* control, void* stream);
+int pk_shard_collect_partial(uint64_t local_base, int64_t gather_offset, int64_t flags_offset, void* control, int world,
+                             const pk_tensor* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -26,6 +26,8 @@ class PkTensor(ctypes.Structure):
 TP = ctypes.POINTER(PkTensor)
 _I64, _INT, _F32, _VP = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 _I64P = ctypes.POINTER(ctypes.c_int64)
+_U64 = ctypes.c_uint64
+_U64P = ctypes.POINTER(ctypes.c_uint64)
 
 # name -> (restype, argtypes); must list every symbol the header declares
 SIGNATURES = {
@@ -61,6 +63,10 @@ SIGNATURES = {
     "pk_shard_owned_rows": (_INT, [TP, _I64, _I64, TP, TP, _VP]),
     "pk_shard_pack_partial": (_INT, [TP, TP, TP, _VP]),
     "pk_shard_merge_partial": (_INT, [TP, TP, _VP]),
+    "pk_shard_exchange_topk": (_INT, [TP, TP, TP, _I64, _U64P, _INT, _INT, _I64, _I64, _VP, _VP]),
+    "pk_shard_collect_topk": (_INT, [_U64, _I64, _I64, _VP, _INT, _I64, TP, TP, _VP]),
+    "pk_shard_exchange_partial": (_INT, [TP, TP, _U64P, _INT, _INT, _I64, _I64, _VP, _VP]),
+    "pk_shard_collect_partial": (_INT, [_U64, _I64, _I64, _VP, _INT, TP, _VP]),
 }
 
 _lib = None
@@ -113,6 +119,10 @@ def check(rc):
     if rc != 0:
         msg = load().pk_last_error().decode("utf-8", "replace")
         raise RuntimeError(f"pariskv_b200 error {rc}: {msg}")
+
+
+def u64_array(values):
+    return (ctypes.c_uint64 * len(values))(*[int(v) for v in values])
 
 
 def i64_array(values):

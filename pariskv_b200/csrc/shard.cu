@@ -91,6 +91,134 @@ __global__ void __launch_bounds__(128) shard_merge_partial_kernel(const float* _
   out[(int64_t)row * 128 + d] = __float2bfloat16(den > 0.f ? acc / den : 0.f);
 }
 
+
+// ---- the same exchanges over peer memory ----------------------------------------------------------------------
+// Every rank owns one symmetric buffer (same layout on every GPU, mapped into every peer's address space):
+//   gather 1  [world][rows][Kl][2] i64, gather 2 [world][rows_q][129] f32, flags 1 u32[world], flags 2 u32[world].
+// The packing kernel stores its rows straight into slot `rank` of EVERY peer's gather area (16-byte stores over
+// NVLink), and after its last block has finished it publishes the exchange number into word `rank` of every peer's
+// flag array (release, system scope).  The consuming kernel on each GPU polls its OWN flag words (acquire, system
+// scope) until all `world` of them carry the current exchange number, then reads its own gather area with L1
+// bypassed.  Exchange numbers come from a word in local memory that the packing kernel advances, so a replayed
+// CUDA graph needs no host-side argument.  One gather area per exchange is enough: a rank can only overwrite a
+// peer's slot after it has passed the other exchange of the same layer, which the peer feeds only after it has
+// consumed this one.  The poll is bounded (about a second): on expiry the kernel raises the status word in the
+// local control block and carries on with whatever is in the buffer; the host checks the word.
+struct PeerSet { char* base[16]; };
+struct PeerCtl { unsigned epoch, arrivals, status, pad; };   // one per exchange, local memory
+
+constexpr long long SHARD_WAIT_POLLS = 1500000;   // x (200 ns back-off + one load): about a second
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Called by every thread of every block after its remote stores; the last block to arrive publishes the flags.
+__device__ __forceinline__ void peer_publish(PeerCtl* ctl, const PeerSet& peers, int64_t flags_off, int rank, int world,
+                                             unsigned total_blocks) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&ctl->arrivals, 1u);
+    if (prev == total_blocks - 1) {
+      __threadfence_system();
+      const unsigned epoch = ctl->epoch + 1;
+      for (int p = 0; p < world; p++)
+        st_release_sys(reinterpret_cast<unsigned*>(peers.base[p] + flags_off) + rank, epoch);
+      ctl->arrivals = 0;
+      ctl->epoch = epoch;     // read by the consuming kernel, which is ordered after this one on the stream
+    }
+  }
+}
+
+// Thread 0 of the block polls the local flag words; returns after a block barrier.
+__device__ __forceinline__ void peer_wait(PeerCtl* ctl, const unsigned* flags, int world) {
+  if (threadIdx.x == 0) {
+    const unsigned want = *reinterpret_cast<volatile unsigned*>(&ctl->epoch);
+    for (int r = 0; r < world; r++) {
+      long long polls = 0;
+      while ((int)(ld_acquire_sys(flags + r) - want) < 0) {
+        if (++polls > SHARD_WAIT_POLLS) {
+          atomicExch(&ctl->status, 1u);
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(256) shard_pack_peer_kernel(const int64_t* __restrict__ cand, const float* __restrict__ scores,
+                                                              const int64_t* __restrict__ local_final, int C, int Kl,
+                                                              int64_t start, PeerSet peers, int64_t gather_off,
+                                                              int64_t flags_off, int rank, int world, int rows, PeerCtl* ctl) {
+  const int row = blockIdx.y;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j < Kl) {
+    const int64_t idx = local_final[(int64_t)row * Kl + j];
+    const int64_t* c = cand + (int64_t)row * C;
+    int p = lower_bound_i64(c, C, idx);
+    if (p >= C) p = C - 1;
+    longlong2 v;
+    v.x = (int64_t)__float_as_int(scores[(int64_t)row * C + p]);
+    v.y = idx + start;
+    const int64_t slot = (((int64_t)rank * rows + row) * Kl + j) * 16;
+    for (int q = 0; q < world; q++) *reinterpret_cast<longlong2*>(peers.base[q] + gather_off + slot) = v;
+  }
+  peer_publish(ctl, peers, flags_off, rank, world, gridDim.x * gridDim.y);
+}
+
+__global__ void __launch_bounds__(256) shard_unpack_peer_kernel(const int64_t* gathered, const unsigned* flags, PeerCtl* ctl,
+                                                                float* __restrict__ scores, int64_t* __restrict__ indices,
+                                                                int world, int rows, int Kl) {
+  peer_wait(ctl, flags, world);
+  const int row = blockIdx.y;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= world * Kl) return;
+  const int w = t / Kl, j = t - w * Kl;
+  const longlong2 v = __ldcg(reinterpret_cast<const longlong2*>(gathered + (((int64_t)w * rows + row) * Kl + j) * 2));
+  scores[(int64_t)row * world * Kl + t] = __int_as_float((int)v.x);
+  indices[(int64_t)row * world * Kl + t] = v.y;
+}
+
+__global__ void __launch_bounds__(128) shard_pack_partial_peer_kernel(const __nv_bfloat16* __restrict__ out, const float* __restrict__ lse,
+                                                                      PeerSet peers, int64_t gather_off, int64_t flags_off,
+                                                                      int rank, int world, int rows, PeerCtl* ctl) {
+  const int row = blockIdx.x, d = threadIdx.x;
+  const float v = __bfloat162float(out[(int64_t)row * 128 + d]);
+  const float l = lse[row];
+  const int64_t slot = ((int64_t)rank * rows + row) * 129;
+  for (int q = 0; q < world; q++) {
+    float* g = reinterpret_cast<float*>(peers.base[q] + gather_off) + slot;
+    g[d] = v;
+    if (d == 0) g[128] = l;
+  }
+  peer_publish(ctl, peers, flags_off, rank, world, gridDim.x);
+}
+
+__global__ void __launch_bounds__(128) shard_merge_partial_peer_kernel(const float* gathered, const unsigned* flags, PeerCtl* ctl,
+                                                                       __nv_bfloat16* __restrict__ out, int world, int rows) {
+  peer_wait(ctl, flags, world);
+  const int row = blockIdx.x, d = threadIdx.x;
+  float m = -INFINITY;
+  for (int w = 0; w < world; w++) m = fmaxf(m, __ldcg(gathered + ((int64_t)w * rows + row) * 129 + 128));
+  float acc = 0.f, den = 0.f;
+  for (int w = 0; w < world; w++) {
+    const float* g = gathered + ((int64_t)w * rows + row) * 129;
+    const float l = __ldcg(g + 128);
+    const float wt = (l == -INFINITY) ? 0.f : exp2f(l - m);
+    if (wt != 0.f) acc = fmaf(wt, __ldcg(g + d), acc);
+    den += wt;
+  }
+  out[(int64_t)row * 128 + d] = __float2bfloat16(den > 0.f ? acc / den : 0.f);
+}
+
 }  // namespace pk
 
 using namespace pk;
@@ -179,4 +307,86 @@ extern "C" int pk_shard_merge_partial(const pk_tensor* gathered, const pk_tensor
   shard_merge_partial_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
       (const float*)gathered->data, (__nv_bfloat16*)out->data, (int)world, (int)(bs * Hq));
   return check_launch("shard_merge_partial");
+}
+
+// ---- peer-memory forms ------------------------------------------------------------------------------------------
+static int fill_peers(PeerSet* ps, const uint64_t* peer_bases, int world, int rank) {
+  PK_REQUIRE(peer_bases != nullptr, "peer_bases is null");
+  PK_REQUIRE(world >= 1 && world <= 16 && rank >= 0 && rank < world, "world must be 1..16 and rank inside it");
+  for (int i = 0; i < 16; i++) ps->base[i] = nullptr;
+  for (int i = 0; i < world; i++) {
+    PK_REQUIRE(peer_bases[i] != 0 && (peer_bases[i] & 15) == 0, "peer buffer %d is null or not 16-byte aligned", i);
+    ps->base[i] = reinterpret_cast<char*>(peer_bases[i]);
+  }
+  return PK_OK;
+}
+
+extern "C" int pk_shard_exchange_topk(const pk_tensor* cand, const pk_tensor* scores, const pk_tensor* local_final,
+                                      int64_t start, const uint64_t* peer_bases, int world, int rank,
+                                      int64_t gather_offset, int64_t flags_offset, void* control, void* stream) {
+  PK_CHECK_TENSOR(cand, PK_I64, 3);
+  PK_CHECK_TENSOR(scores, PK_F32, 3);
+  PK_CHECK_TENSOR(local_final, PK_I64, 3);
+  const int64_t bs = cand->shape[0], H = cand->shape[1], C = cand->shape[2], Kl = local_final->shape[2];
+  PK_REQUIRE(is_contig(cand) && is_contig(scores) && is_contig(local_final), "tensors must be contiguous");
+  PK_REQUIRE(scores->shape[0] == bs && scores->shape[1] == H && scores->shape[2] == C, "scores must be [bs,H,C] like cand");
+  PK_REQUIRE(local_final->shape[0] == bs && local_final->shape[1] == H, "local_final must be [bs,H,Kl]");
+  PK_REQUIRE(C >= 1 && C < (1LL << 31) && Kl >= 1 && Kl < (1LL << 31) && bs * H >= 1 && bs * H < 65536, "sizes out of range");
+  PK_REQUIRE(control != nullptr && gather_offset >= 0 && flags_offset >= 0 && gather_offset % 16 == 0 && flags_offset % 4 == 0,
+             "control block or offsets invalid");
+  PeerSet ps;
+  int rc;
+  if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
+  shard_pack_peer_kernel<<<dim3((unsigned)((Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
+      (const int64_t*)cand->data, (const float*)scores->data, (const int64_t*)local_final->data, (int)C, (int)Kl, start, ps,
+      gather_offset, flags_offset, rank, world, (int)(bs * H), (PeerCtl*)control);
+  return check_launch("shard_exchange_topk");
+}
+
+extern "C" int pk_shard_collect_topk(uint64_t local_base, int64_t gather_offset, int64_t flags_offset, void* control,
+                                     int world, int64_t Kl, const pk_tensor* scores, const pk_tensor* indices, void* stream) {
+  PK_CHECK_TENSOR(scores, PK_F32, 3);
+  PK_CHECK_TENSOR(indices, PK_I64, 3);
+  const int64_t bs = scores->shape[0], H = scores->shape[1];
+  PK_REQUIRE(world >= 1 && world <= 16 && Kl >= 1 && world * Kl < (1LL << 31) && bs * H >= 1 && bs * H < 65536, "sizes out of range");
+  PK_REQUIRE(is_contig(scores) && is_contig(indices) && scores->shape[2] == world * Kl && indices->shape[0] == bs &&
+                 indices->shape[1] == H && indices->shape[2] == world * Kl,
+             "scores / indices must be contiguous [bs,H,world*Kl]");
+  PK_REQUIRE(local_base != 0 && control != nullptr && gather_offset % 16 == 0 && flags_offset % 4 == 0, "buffer or offsets invalid");
+  char* base = reinterpret_cast<char*>(local_base);
+  shard_unpack_peer_kernel<<<dim3((unsigned)((world * Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
+      (const int64_t*)(base + gather_offset), (const unsigned*)(base + flags_offset), (PeerCtl*)control, (float*)scores->data,
+      (int64_t*)indices->data, world, (int)(bs * H), (int)Kl);
+  return check_launch("shard_collect_topk");
+}
+
+extern "C" int pk_shard_exchange_partial(const pk_tensor* out, const pk_tensor* lse, const uint64_t* peer_bases, int world,
+                                         int rank, int64_t gather_offset, int64_t flags_offset, void* control, void* stream) {
+  PK_CHECK_TENSOR(out, PK_BF16, 4);
+  PK_CHECK_TENSOR(lse, PK_F32, 2);
+  const int64_t bs = out->shape[0], Hq = out->shape[2];
+  PK_REQUIRE(out->shape[1] == 1 && out->shape[3] == 128 && is_contig(out), "out must be contiguous [bs,1,Hq,128]");
+  PK_REQUIRE(lse->shape[0] == bs && lse->shape[1] == Hq && is_contig(lse), "lse must be contiguous [bs,Hq]");
+  PK_REQUIRE(bs * Hq >= 1 && control != nullptr && gather_offset % 16 == 0 && flags_offset % 4 == 0, "control block or offsets invalid");
+  PeerSet ps;
+  int rc;
+  if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
+  shard_pack_partial_peer_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)out->data, (const float*)lse->data, ps, gather_offset, flags_offset, rank, world, (int)(bs * Hq),
+      (PeerCtl*)control);
+  return check_launch("shard_exchange_partial");
+}
+
+extern "C" int pk_shard_collect_partial(uint64_t local_base, int64_t gather_offset, int64_t flags_offset, void* control,
+                                        int world, const pk_tensor* out, void* stream) {
+  PK_CHECK_TENSOR(out, PK_BF16, 4);
+  const int64_t bs = out->shape[0], Hq = out->shape[2];
+  PK_REQUIRE(out->shape[1] == 1 && out->shape[3] == 128 && is_contig(out) && bs * Hq >= 1, "out must be contiguous [bs,1,Hq,128]");
+  PK_REQUIRE(world >= 1 && world <= 16 && local_base != 0 && control != nullptr && gather_offset % 16 == 0 && flags_offset % 4 == 0,
+             "buffer or offsets invalid");
+  char* base = reinterpret_cast<char*>(local_base);
+  shard_merge_partial_peer_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
+      (const float*)(base + gather_offset), (const unsigned*)(base + flags_offset), (PeerCtl*)control,
+      (__nv_bfloat16*)out->data, world, (int)(bs * Hq));
+  return check_launch("shard_collect_partial");
 }

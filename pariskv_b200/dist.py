@@ -123,7 +123,8 @@ def merge_gathered_partials(gathered: torch.Tensor) -> torch.Tensor:
 
 def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global, store_k,
                             store_v, n_total, start, end, collision_ratio, candidate_ratio, final_topk,
-                            window_k=None, window_v=None, n_window=0, group=None, n_window_dev=None, n_window_add=0):
+                            window_k=None, window_v=None, n_window=0, group=None, n_window_dev=None, n_window_add=0,
+                            exchange=None):
     """One layer, one decode step of the sequence-sharded form on this rank's shard [start, end) of a zone of
     n_total keys.  codebook / key_block_weight / key_4bit / store_* hold the shard only (local index = global -
     start); counts_global is the all-reduced cluster histogram.  The window rows are attended by the rank that
@@ -140,21 +141,70 @@ def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_wei
                                  tiers, c_local, k_local, want=("cand", "scores_f32"))
     bs, _, Hq, _ = queries.shape
     H, dev = codebook.shape[1], queries.device
-    # exchange 1: (score, global index) of the local top list, one packed buffer, one all-gather
-    packed = ops.shard_pack_topk(ex["cand"], ex["scores_f32"], fin_local, start)
-    flat = torch.empty(world * bs, H, k_local, 2, dtype=torch.int64, device=dev)
-    dist.all_gather_into_tensor(flat, packed, group=group)          # output = inputs concatenated along dim 0
-    scores, indices = ops.shard_unpack_topk(flat.view(world, bs, H, k_local, 2))
+    if exchange is not None:   # both exchanges as stores into peer memory (no collective launch)
+        ops.shard_exchange_topk(ex["cand"], ex["scores_f32"], fin_local, start, exchange)
+        scores, indices = ops.shard_collect_topk(exchange, bs, H, k_local)
+    else:
+        # exchange 1: (score, global index) of the local top list, one packed buffer, one all-gather
+        packed = ops.shard_pack_topk(ex["cand"], ex["scores_f32"], fin_local, start)
+        flat = torch.empty(world * bs, H, k_local, 2, dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(flat, packed, group=group)          # output = inputs concatenated along dim 0
+        scores, indices = ops.shard_unpack_topk(flat.view(world, bs, H, k_local, 2))
     final = ops.final_topk(scores, indices, min(final_topk, world * k_local))
     local, n_owned = ops.shard_owned_rows(final, start, end)
     lse = torch.empty(bs, Hq, dtype=torch.float32, device=dev)
     out = ops.sparse_attention(queries, window_k, window_v, n_window, store_k, store_v, local, n_sel=n_owned, lse=lse,
                                n_window_dev=n_window_dev, n_window_add=n_window_add)
+    if exchange is not None:
+        ops.shard_exchange_partial(out, lse, exchange)
+        return ops.shard_collect_partial(exchange, bs, Hq), final
     # exchange 2: (partial output, log2 denominator), one packed buffer, one all-gather
     part = ops.shard_pack_partial(out, lse)
     flat2 = torch.empty(world * bs, Hq, 129, dtype=torch.float32, device=dev)
     dist.all_gather_into_tensor(flat2, part, group=group)
     return ops.shard_merge_partial(flat2.view(world, bs, Hq, 129)), final
+
+
+class PeerExchange:
+    """Symmetric buffers for the two per-layer exchanges of the sequence-sharded form, so that they run as stores
+    into peer memory plus flag words instead of two collectives (pk_shard_exchange_* / pk_shard_collect_*).
+
+    One buffer per rank from torch's symmetric-memory allocator (same layout everywhere, every peer's copy mapped
+    into this process): [gather 1 | gather 2 | flags 1 | flags 2].  NVLink multicast is not used and is switched
+    off for the allocator (TORCH_SYMM_MEM_DISABLE_MULTICAST=1 must be in the environment before the first
+    allocation; this constructor sets it if absent).  All ranks of `group` must construct it together."""
+
+    def __init__(self, bs, H, Hq, Kl, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if self.world > 16:
+            raise ValueError("at most 16 ranks")
+        self.device, self.bs, self.H, self.Hq, self.Kl = device, bs, H, Hq, Kl
+        al = lambda n: (n + 255) // 256 * 256
+        self.gather1_off = 0
+        self.gather2_off = al(self.world * bs * H * Kl * 16)
+        self.flags1_off = self.gather2_off + al(self.world * bs * Hq * 129 * 4)
+        self.flags2_off = self.flags1_off + 256
+        total = self.flags2_off + 256
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, self.group.group_name)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.local_base = ptrs[self.rank]
+        self.peer_array = _lib.u64_array(ptrs)
+        self.ctl = torch.zeros(8, dtype=torch.int32, device=device)    # two 16-byte control blocks, local
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)                                  # every rank's flags are zero before any store
+
+    def check(self):
+        """Raise if a bounded wait ran out (host synchronisation: call it outside the decode loop)."""
+        st = self.ctl.cpu()
+        if int(st[2]) or int(st[6]):
+            raise RuntimeError("sequence-sharded exchange: a peer's data did not arrive within the wait limit")
 
 
 class SequenceShardedCache:

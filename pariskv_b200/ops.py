@@ -346,3 +346,39 @@ def shard_merge_partial(gathered):
     d = [L.desc(t) for t in (gathered, out)]
     _call("pk_shard_merge_partial", L.ref(d[0]), L.ref(d[1]), L.stream_ptr(gathered.device))
     return out
+
+
+def shard_exchange_topk(cand, scores, local_final, start, px):
+    """Pack this rank's local top list and store it into every peer's gather area; see pk_shard_exchange_topk.
+    px: a dist.PeerExchange."""
+    _require_cuda(cand, scores, local_final)
+    d = [L.desc(t) for t in (cand, scores, local_final)]
+    _call("pk_shard_exchange_topk", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(start), px.peer_array, px.world, px.rank,
+          px.gather1_off, px.flags1_off, px.ctl.data_ptr(), L.stream_ptr(cand.device))
+
+
+def shard_collect_topk(px, bs, H, Kl):
+    """Wait for every rank's local top list, then unpack; see pk_shard_collect_topk."""
+    scores = torch.empty(bs, H, px.world * Kl, dtype=torch.float32, device=px.device)
+    indices = torch.empty(bs, H, px.world * Kl, dtype=torch.int64, device=px.device)
+    d = [L.desc(t) for t in (scores, indices)]
+    _call("pk_shard_collect_topk", px.local_base, px.gather1_off, px.flags1_off, px.ctl.data_ptr(), px.world, int(Kl),
+          L.ref(d[0]), L.ref(d[1]), L.stream_ptr(px.device))
+    return scores, indices
+
+
+def shard_exchange_partial(out, lse, px):
+    """Store this rank's partial attention result into every peer's gather area; see pk_shard_exchange_partial."""
+    _require_cuda(out, lse)
+    d = [L.desc(t) for t in (out, lse)]
+    _call("pk_shard_exchange_partial", L.ref(d[0]), L.ref(d[1]), px.peer_array, px.world, px.rank, px.gather2_off,
+          px.flags2_off, px.ctl.data_ptr() + 16, L.stream_ptr(out.device))
+
+
+def shard_collect_partial(px, bs, Hq):
+    """Wait for every rank's partial result, then merge; see pk_shard_collect_partial."""
+    out = torch.empty(bs, 1, Hq, 128, dtype=torch.bfloat16, device=px.device)
+    d = L.desc(out)
+    _call("pk_shard_collect_partial", px.local_base, px.gather2_off, px.flags2_off, px.ctl.data_ptr() + 16, px.world,
+          L.ref(d), L.stream_ptr(px.device))
+    return out
