@@ -578,7 +578,7 @@ def seqshard_mode(args, device, rank, world, local_rank):
     t_setup = time.time()
     model = DecoderHarness(cfg, device, seed=1234)
     cache = SequenceShardedCache(Lyr, H, cfg["q_heads"], n_total, cfg["sink"], cfg["local"], cfg["interval"],
-                                 cfg["topk"], device, rank, world, store=args.store)
+                                 cfg["topk"], device, rank, world, store=args.store, exchange=args.exchange)
     for l in range(Lyr):
         ks, vs = [], []
         for b in range(start // SHARD_BLOCK, (max(end, start + 1) - 1) // SHARD_BLOCK + 1):
@@ -629,6 +629,8 @@ def seqshard_mode(args, device, rank, world, local_rank):
     launches = (_lib.launch_count() if not use_graph else runner.kernel_launches) - launches0
     clocks = sampler.stop()
     last = (runner.tok if use_graph else token).clone()
+    if cache.px is not None:
+        cache.px.check()
     agree = True
     if world > 1:
         t = torch.tensor([ms], device=device, dtype=torch.float64)
@@ -649,7 +651,7 @@ def seqshard_mode(args, device, rank, world, local_rank):
                                    f"chunk(s); dense layers replicated; K/V rows in {'HBM' if cache.store == 'hbm' else 'pinned host memory'}",
                        "layers": Lyr, "kv_heads": H, "q_heads": cfg["q_heads"], "parallelism": f"sp{world}",
                        "l2": "per-step working set (codes of all layers) exceeds L2"},
-            "clocks": clocks, "gpu_launches": int(launches), "ranks_agree": agree,
+            "clocks": clocks, "gpu_launches": int(launches), "ranks_agree": agree, "exchange": args.exchange,
             "cuda_graph": {"used": use_graph, "captures": runner.captures},
             "setup_s": round(setup_s, 1), "zone_keys_per_head": n_total, "shard_keys_per_head": end - start,
             "candidates_per_shard": c_local, "local_topk": k_local,
@@ -687,6 +689,8 @@ def main():
     ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops", "seqshard", "prefill"],
                     help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
                          "a small profiling target, its line is marked as such")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="--mode seqshard: the two per-layer exchanges as NCCL all-gathers or as stores into peer memory")
     ap.add_argument("--only", default=None, help="--mode ops: run only the ops whose name contains this text")
     ap.add_argument("--store", default="auto", choices=["auto", "host", "hbm"],
                     help="--mode seqshard: where a shard's K/V rows live (auto: HBM when they fit, else pinned host)")
@@ -716,6 +720,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         if args.mode == "seqshard":      # small all-gathers only: plain peer transfers, no NVLink multicast objects
             os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=device)
 
     from pariskv_b200 import _lib

@@ -216,7 +216,7 @@ class SequenceShardedCache:
 
     def __init__(self, layer_num, num_kv_heads, num_heads, n_total, sink_size, local_size, interval, final_topk,
                  device, rank, world, group=None, collision_ratio=0.2, candidate_ratio=0.1, srht_sign_vector=None,
-                 store="host"):
+                 store="host", exchange="nccl"):
         from .cache_hub.polar_cache import srht_signs
         self.layer_num, self.kv_head, self.num_heads = layer_num, num_kv_heads, num_heads
         self.n_total, self.sink_size, self.local_size, self.interval = n_total, sink_size, local_size, interval
@@ -246,6 +246,12 @@ class SequenceShardedCache:
             free, _ = torch.cuda.mem_get_info(device)
             store = "hbm" if need + (16 << 30) < free else "host"
         self.store = store
+        if exchange not in ("nccl", "peer"):
+            raise ValueError("exchange must be 'nccl' or 'peer'")
+        self.px = None
+        if exchange == "peer" and world > 1:   # the two per-layer exchanges as stores into peer memory
+            _, _, k_local = local_plan(n_total, world, collision_ratio, candidate_ratio, final_topk)
+            self.px = PeerExchange(1, num_kv_heads, num_heads, k_local, device, group)
         self.device_positions = False     # window length read from a device word (captured steps)
         self._dev_state = torch.zeros(1, dtype=torch.int32, device=device)
 
@@ -295,7 +301,7 @@ class SequenceShardedCache:
             window_v=self.window_v[layer_idx] if first else None,
             n_window=(self.window_capacity if self.device_positions else self._window_len[layer_idx]) if first else 0,
             group=self.group, n_window_dev=self._dev_state[0:1] if (first and self.device_positions) else None,
-            n_window_add=1 if (first and self.device_positions) else 0)
+            n_window_add=1 if (first and self.device_positions) else 0, exchange=self.px)
         self.last_topk_indices = final
         return out
 

@@ -56,7 +56,7 @@ def _worker(rank, world, port, tmp):
         dist.destroy_process_group()
 
 
-def _cache_check(rank, world, dev):
+def _cache_check(rank, world, dev, exchange="nccl"):
     """SequenceShardedCache: load two layers, append two rows, attend; against the oracle on the whole zone."""
     from oracle import oracle as O
     from pariskv_b200 import dist as pkd
@@ -65,7 +65,7 @@ def _cache_check(rank, world, dev):
     signs = srht_signs()
     _, cen = O.constants()
     cache = pkd.SequenceShardedCache(2, H, 8, N, sink, local, interval, K, dev, rank, world,
-                                     srht_sign_vector=signs)
+                                     srht_sign_vector=signs, exchange=exchange)
     start, end = pkd.sequence_shard(N, rank, world)
     data = []
     for l in range(2):
@@ -84,7 +84,11 @@ def _cache_check(rank, world, dev):
             nv = torch.randn(1, 1, H, 128, generator=g).to(torch.bfloat16)
             q = synth_queries(g, keys, 4) * 4
             cache.decode_update_kv_cache(nk.to(dev), nv.to(dev), l)
-            out = cache.compute(q.to(dev), l)
+            qd = q.to(dev)
+            if world > 1:   # the oracle work between steps skews the ranks by seconds; the peer waits are short
+                torch.cuda.synchronize()
+                dist.barrier()
+            out = cache.compute(qd, l)
             wk = torch.cat([wk, nk.transpose(1, 2)], 2)
             wv = torch.cat([wv, nv.transpose(1, 2)], 2)
             data[l] = (keys, vals, wk, wv)
@@ -96,17 +100,20 @@ def _cache_check(rank, world, dev):
             err = (out.float().cpu() - ref).abs().max().item()
             assert err <= 2e-2, err
     assert cache.context == sink + N + local + 2
+    if cache.px is not None:
+        cache.px.check()
 
 
-def _cache_worker(rank, world, port):
+def _cache_worker(rank, world, port, exchange="nccl"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        _cache_check(rank, world, dev)
+        _cache_check(rank, world, dev, exchange)
     finally:
         dist.destroy_process_group()
 
@@ -118,6 +125,12 @@ def test_sequence_sharded_cache_single_rank():
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_sequence_sharded_cache_on_two_gpus():
     mp.spawn(_cache_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_sharded_cache_peer_exchange_on_two_gpus():
+    """The same check with both exchanges as stores into peer memory (bounded flag waits) instead of NCCL."""
+    mp.spawn(_cache_worker, args=(2, _free_port(), "peer"), nprocs=2, join=True)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
