@@ -174,7 +174,7 @@ def synth_kv(gen, P, H, device):
     return z.to(torch.bfloat16), v.to(torch.bfloat16)
 
 
-def build_cache(cfg, device, max_new, seed):
+def build_cache(cfg, device, max_new, seed, offload=True):
     from pariskv_b200.cache_hub.polar_cache import polar_cache
     P = cfg["context"]
     cache = polar_cache(valid_start=[0], layer_num=cfg["layers"], batch_size=1, max_length=P + max_new,
@@ -182,7 +182,7 @@ def build_cache(cfg, device, max_new, seed):
                         dtype=torch.bfloat16, layer_mapping={str(i): str(device) for i in range(cfg["layers"])},
                         max_new_length=max_new, sink_size=cfg["sink"], local_size=cfg["local"], core=0, nprobe=0,
                         cache_unit_size=0, cache_cluster_num=0, num_gpus=1, model_size=8, final_topk=cfg["topk"],
-                        dynamic_update_interval=cfg["interval"], enable_offload=True)
+                        dynamic_update_interval=cfg["interval"], enable_offload=offload)
     g = torch.Generator(device=device).manual_seed(seed)
     for l in range(cfg["layers"]):
         k, v = synth_kv(g, P, cfg["kv_heads"], device)
@@ -689,6 +689,8 @@ def main():
     ap.add_argument("--mode", default="decode", choices=["decode", "kernels", "ops", "seqshard", "prefill"],
                     help="kernels: only the cache path (append, retrieval chain, attention) per layer, no model; "
                          "a small profiling target, its line is marked as such")
+    ap.add_argument("--no-offload", action="store_true",
+                    help="variant, not the benchmark configuration: keep the K/V rows in HBM instead of pinned host memory")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
                     help="--mode seqshard: the two per-layer exchanges as NCCL all-gathers or as stores into peer memory")
     ap.add_argument("--only", default=None, help="--mode ops: run only the ops whose name contains this text")
@@ -764,7 +766,7 @@ def main():
         return
     t_setup = time.time()
     model = DecoderHarness(cfg, device, seed=1234)
-    cache = build_cache(cfg, device, max_new, seed=100 + rank)
+    cache = build_cache(cfg, device, max_new, seed=100 + rank, offload=not args.no_offload)
     setup_s = time.time() - t_setup
     token = torch.tensor([11], device=device)
     use_graph = not args.no_graph
@@ -909,6 +911,8 @@ def main():
     }
     if debug:
         line["invalid"] = "debug run with reduced layers/context"
+    if args.no_offload:
+        line["invalid"] = "variant: K/V rows resident in HBM; the benchmark configuration keeps them in pinned host memory"
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

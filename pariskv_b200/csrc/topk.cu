@@ -323,6 +323,164 @@ __global__ void __launch_bounds__(TK_THREADS) topk_cluster_kernel(TopkParams p) 
   cluster.sync();  // shared memory must outlive the remote reads above
 }
 
+// ---- rows of up to 16384 elements: one 1024-thread CTA per row, everything in shared memory ----------------------
+// Every element carries a state: 0 = out, 1 = selected, 2 = undecided.  A level histograms a monotone digit of the
+// undecided elements, finds the digit T where the count from above reaches what is still needed, and decides every
+// element whose digit differs from T.  Level 1 uses 4096 equal-width value buckets between the row's minimum and
+// maximum (spread-out bins, so shared-memory atomics rarely collide); if the undecided set is still larger than
+// TS_TIE_CAP — a flat row, or many equal values — radix levels on the key bits (12, 12, 8) follow.  As soon as at
+// most TS_TIE_CAP elements are undecided they are ranked among themselves by (key descending, index ascending); if
+// the last bit is reached with more equal keys than that, the lowest indices win through an ordered count.  The
+// emission is an ordered compaction, so the result comes out in ascending index order like the cluster kernel's.
+constexpr int TS_THREADS = 1024;
+constexpr int TS_MAX = 16384;
+constexpr int TS_TIE_CAP = 1024;
+constexpr int TS_BINS = 4096;
+constexpr size_t TS_SMEM = (size_t)TS_MAX * 4 + TS_BINS * 4 + TS_MAX + (size_t)TS_TIE_CAP * 8;
+
+__global__ void __launch_bounds__(TS_THREADS) topk_small_kernel(TopkParams p) {
+  extern __shared__ __align__(16) unsigned char ts_dyn[];
+  uint32_t* raw = reinterpret_cast<uint32_t*>(ts_dyn);
+  unsigned* hist = reinterpret_cast<unsigned*>(raw + TS_MAX);
+  uint8_t* flag = reinterpret_cast<uint8_t*>(hist + TS_BINS);
+  uint2* tie = reinterpret_cast<uint2*>(flag + TS_MAX);
+  __shared__ unsigned s_wsum[32];
+  __shared__ unsigned long long s_wsum64[32];
+  __shared__ float s_f[64];
+  __shared__ unsigned s_res[3];
+  __shared__ unsigned s_ntie;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row = blockIdx.x;
+  const int L = (int)p.L;
+  const uint32_t* in = p.in + row * p.row_stride;
+  pdl_wait();
+  pdl_trigger();
+  float mn = INFINITY, mx = -INFINITY;
+  for (int i = tid; i < L; i += TS_THREADS) {
+    const uint32_t u = __ldg(in + i);
+    raw[i] = u;
+    flag[i] = 2;
+    const float v = val_of(u, p.is_float);
+    mn = fminf(mn, v), mx = fmaxf(mx, v);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  if (lane == 0) s_f[warp] = mn, s_f[32 + warp] = mx;
+  __syncthreads();
+  mn = s_f[lane], mx = s_f[32 + lane];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  float scale = (float)(TS_BINS - 1) / (mx - mn);
+  if (!(scale > 0.0f) || !(scale < INFINITY)) scale = 0.0f;  // flat or non-finite range: the radix levels decide
+
+  unsigned rem = (unsigned)p.k, undecided = (unsigned)L;
+  // level 0: value buckets; levels 1..3: key bits [31:20], [19:8], [7:0]
+  for (int lv = (scale > 0.0f ? 0 : 1); lv < 4 && undecided > (unsigned)TS_TIE_CAP; lv++) {
+    const int nb = lv == 3 ? 256 : TS_BINS;
+    const int sh = lv == 1 ? 20 : (lv == 2 ? 8 : 0);
+    auto digit = [&](uint32_t u) -> unsigned {
+      if (lv == 0) return min((unsigned)(TS_BINS - 1), (unsigned)((val_of(u, p.is_float) - mn) * scale));
+      return (key_of(u, p.is_float) >> sh) & (unsigned)(nb - 1);
+    };
+    for (int i = tid; i < nb; i += TS_THREADS) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < L; i += TS_THREADS)
+      if (flag[i] == 2) atomicAdd(&hist[digit(raw[i])], 1u);
+    __syncthreads();
+    // threshold digit: highest T with (undecided elements of digit >= T) >= rem
+    const int per = nb >= TS_THREADS ? nb / TS_THREADS : 1;
+    unsigned mine = 0;
+    if (tid * per < nb)
+      for (int j = 0; j < per; j++) mine += hist[tid * per + j];
+    unsigned suf = mine;  // inclusive suffix sum over threads (higher thread = higher digits)
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned o = __shfl_down_sync(0xffffffffu, suf, off);
+      if (lane + off < 32) suf += o;
+    }
+    if (lane == 0) s_wsum[warp] = suf;
+    __syncthreads();
+    unsigned higher_w = 0;
+    for (int w = warp + 1; w < 32; w++) higher_w += s_wsum[w];
+    const unsigned incl = suf + higher_w, higher = incl - mine;
+    if (mine && higher < rem && incl >= rem) {  // the crossing lies inside this thread's digits
+      unsigned acc = higher;
+      for (int j = per - 1; j >= 0; j--) {
+        const unsigned h = hist[tid * per + j];
+        if (acc + h >= rem) {
+          s_res[0] = (unsigned)(tid * per + j), s_res[1] = acc, s_res[2] = h;
+          break;
+        }
+        acc += h;
+      }
+    }
+    __syncthreads();
+    const unsigned T = s_res[0];
+    rem -= s_res[1];
+    undecided = s_res[2];
+    for (int i = tid; i < L; i += TS_THREADS)
+      if (flag[i] == 2) {
+        const unsigned d = digit(raw[i]);
+        if (d != T) flag[i] = d > T ? 1 : 0;
+      }
+    __syncthreads();
+  }
+
+  if (undecided <= (unsigned)TS_TIE_CAP) {  // rank the undecided elements among themselves
+    if (tid == 0) s_ntie = 0;
+    __syncthreads();
+    for (int i = tid; i < L; i += TS_THREADS)
+      if (flag[i] == 2) tie[atomicAdd(&s_ntie, 1u)] = make_uint2(key_of(raw[i], p.is_float), (unsigned)i);
+    __syncthreads();
+    const int n = (int)s_ntie;
+    for (int t = tid; t < n; t += TS_THREADS) {
+      const uint2 me = tie[t];
+      unsigned r = 0;
+      for (int j = 0; j < n; j++) {
+        const uint2 o = tie[j];
+        r += (o.x > me.x || (o.x == me.x && o.y < me.y)) ? 1u : 0u;
+      }
+      flag[me.y] = r < rem ? 1 : 0;
+    }
+    __syncthreads();
+  }
+  // ordered compaction; elements still undecided here have equal keys and are taken in index order up to rem
+  const int per = (L + TS_THREADS - 1) / TS_THREADS;
+  const int i0 = min(L, tid * per), i1 = min(L, i0 + per);
+  unsigned n_sel = 0, n_tie = 0;
+  for (int i = i0; i < i1; i++) {
+    const uint8_t f = flag[i];
+    n_sel += f == 1, n_tie += f == 2;
+  }
+  const unsigned long long mine64 = ((unsigned long long)n_sel << 32) | n_tie;
+  unsigned long long sc = mine64;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const unsigned long long o = __shfl_up_sync(0xffffffffu, sc, off);
+    if (lane >= off) sc += o;
+  }
+  if (lane == 31) s_wsum64[warp] = sc;
+  __syncthreads();
+  unsigned long long base = 0;
+  for (int w = 0; w < warp; w++) base += s_wsum64[w];
+  const unsigned long long excl = base + sc - mine64;
+  unsigned sel_before = (unsigned)(excl >> 32), tie_before = (unsigned)excl;
+  int64_t* out = p.out + row * p.k;
+  const int64_t* map = p.map ? p.map + row * p.map_stride : nullptr;
+  for (int i = i0; i < i1; i++) {
+    const uint8_t f = flag[i];
+    if (f == 1 || (f == 2 && tie_before < rem)) out[sel_before + min(tie_before, rem)] = map ? map[i] : (int64_t)i;
+    sel_before += f == 1;
+    tie_before += f == 2;
+  }
+}
+
 // Reorders an emitted top-k list by (value descending, index ascending): one block per row, k <= 4096.
 __global__ void __launch_bounds__(1024) sort_by_value_kernel(const uint32_t* in, int is_float, int64_t row_stride,
                                                              int64_t k, int kp, int64_t* out) {
@@ -366,6 +524,25 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
   p.is_float = is_float ? 1 : 0;
   p.row_stride = row_stride, p.L = L, p.k = k;
   p.out = out, p.map = map, p.map_stride = map_stride;
+  static int use_small = -1;
+  if (use_small < 0) {
+    const char* e = getenv("PK_TOPK_SMALL");
+    use_small = (e && atoi(e) == 0) ? 0 : 1;
+    if (use_small && cudaFuncSetAttribute(topk_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TS_SMEM) !=
+                         cudaSuccess) {
+      cudaGetLastError();
+      use_small = 0;
+    }
+  }
+  if (use_small && L <= TS_MAX) {  // short rows: one CTA per row, no cluster barriers
+    launch_chain(topk_small_kernel, dim3((unsigned)rows), dim3(TS_THREADS), TS_SMEM, st, p);
+    int rc = check_launch("topk small");
+    if (rc || order == 0) return rc;
+    int kp = 1;
+    while (kp < k) kp <<= 1;
+    sort_by_value_kernel<<<(unsigned)rows, 1024, (size_t)kp * 8, st>>>(p.in, p.is_float, row_stride, k, kp, out);
+    return check_launch("topk sort");
+  }
   // about 1024 elements per CTA, at most 16 CTAs per row (clusters above 8 need the non-portable opt-in)
   unsigned ncta = 1;
   static int max_cta = 0;

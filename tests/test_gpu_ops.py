@@ -157,6 +157,31 @@ def test_topk_exact(ops, oracle, L, k, kind):
         assert torch.equal(out.cpu(), oracle.topk(x, k, sorted_by_value=True))
 
 
+@pytest.mark.parametrize("case", ["all_equal", "two_values", "dense_ties_float", "negatives", "tiny_spread", "signed_zero"])
+@pytest.mark.parametrize("L,k", [(1500, 1), (5000, 2048), (13101, 2048), (16384, 16000), (16384, 16384)])
+def test_topk_short_rows_tie_paths(ops, oracle, L, k, case):
+    """Rows of at most 16384 elements take the one-CTA kernel: exercise its radix levels (values that agree in the top
+    12 / 24 bits), the threshold bin above and below its ranking capacity, and equal keys at the last bit."""
+    g = torch.Generator().manual_seed(L * 7 + k)
+    rows = 2
+    if case == "all_equal":
+        x = torch.full((rows, L), 3.25)
+    elif case == "two_values":
+        x = torch.randint(0, 2, (rows, L), generator=g).to(torch.float32) * 0.5 + 1.0
+    elif case == "dense_ties_float":
+        x = torch.randint(0, 40, (rows, L), generator=g).to(torch.float32) / 7.0
+    elif case == "negatives":
+        x = -torch.rand(rows, L, generator=g) * 1e-3
+    elif case == "tiny_spread":   # all values share the top 24 key bits
+        x = (1.0 + torch.randint(0, 200, (rows, L), generator=g).to(torch.float32) * 2.0 ** -23)
+    else:
+        x = torch.zeros(rows, L)
+        x[:, ::3] = -0.0
+        x[:, 1::5] = 1e-30
+    out = ops.topk(x.to(DEV), k)
+    assert torch.equal(out.cpu(), oracle.topk(x, k))
+
+
 def test_topk_3d_strided_rows(ops, oracle):
     g = torch.Generator().manual_seed(5)
     x = torch.randint(0, 97, (2, 4, 3000), generator=g, dtype=torch.int32)
