@@ -93,13 +93,15 @@ def test_retrieve_headline_shape_config0(ops, oracle):
     assert (out.float().cpu() - refo).abs().max().item() <= 2e-2
 
 
-def test_full_size_properties_128k(ops):
-    """At 131004 keys per head (the 128K-context config) the oracle is not run; check properties that
+@pytest.mark.parametrize("N,C", [(131004, 13101), (1048508, 104851)])
+def test_full_size_properties(ops, N, C):
+    """At 131004 / 1048508 keys per head (the 128K- and 1M-context configs) the oracle is not run; check properties that
     hold at any size: counts bounded by 6 x 16, the candidate list is ascending, has no duplicates and
     dominates every non-candidate, the final list is a subset of the candidates with the K best scores."""
     g = torch.Generator(device=DEV).manual_seed(1)
-    bs, H, N, C, K = 1, 8, 131004, 13101, 2048
-    keys = torch.randn(bs, H, N, 128, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+    bs, H, K = 1, 8, 2048
+    keys = torch.cat([torch.randn(bs, H, n, 128, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
+                      for n in ([N // 4] * 3 + [N - 3 * (N // 4)])], 2)   # in pieces: the fp32 temporary stays small
     q = torch.randn(bs, 1, 4 * H, 128, generator=g, device=DEV, dtype=torch.float32).to(torch.bfloat16)
     signs = srht_signs().to(DEV)
     cen = torch.tensor([0.0420, 0.1266, 0.2130, 0.3025, 0.3973, 0.5001, 0.6169, 0.7633], dtype=torch.bfloat16, device=DEV)
