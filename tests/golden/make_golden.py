@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this folder by RUNNING THE REFERENCE'S OWN PYTHON CODE on CPU.
 
-Run once, in a container that has the reference checkout (default /root/reference):
+Run once, in a container that has a checkout of the reference project:
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py --ref <path of the ParisKV checkout>
 
 The fixtures are committed; nothing else in the repository reads the reference checkout.
 
@@ -69,7 +69,7 @@ def synth_keys(gen, bs, H, N, outliers=(7, 37, 71, 101)):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of the reference (ParisKV) checkout")
     args = ap.parse_args()
     ref = args.ref
     sys.path.insert(0, ref)
