@@ -602,6 +602,8 @@ def seqshard_mode(args, device, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    barrier()       # ranks finish loading at different times; the peer exchange only waits about a second
+
     def advance():
         nonlocal token
         if use_graph:

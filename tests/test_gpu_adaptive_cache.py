@@ -23,9 +23,10 @@ def _make(kind, P, bs, H, Hq, sink, local, I, **extra):
 @pytest.mark.parametrize("kind,extra", [("dense", dict(adaptive_topk_threshold=0.9, adaptive_topk_max_k=256)),
                                         ("varlen", dict(adaptive_topk_threshold=0.85, adaptive_topk_min_k=20,
                                                         adaptive_topk_max_k=200))])
-def test_adaptive_cache_matches_oracle(oracle, kind, extra):
-    g = torch.Generator().manual_seed(5)
-    bs, H, Hq, sink, local, I, P, steps = 1, 2, 8, 4, 16, 8, 2400, 11
+@pytest.mark.parametrize("bs", [1, 3])
+def test_adaptive_cache_matches_oracle(oracle, kind, extra, bs):
+    g = torch.Generator().manual_seed(5 + bs)
+    H, Hq, sink, local, I, P, steps = 2, 8, 4, 16, 8, 2400, 11
     cache = _make(kind, P, bs, H, Hq, sink, local, I, **extra)
     K = synth_keys(g, bs, H, P)
     V = (torch.randn(bs, H, P, 128, generator=g) * torch.exp(0.5 * torch.randn(bs, H, P, 1, generator=g))).to(torch.bfloat16)
@@ -74,11 +75,16 @@ def test_adaptive_cache_matches_oracle(oracle, kind, extra):
         want_n = k_o if kind == "varlen" else k_o.max().expand_as(k_o)
         assert torch.equal(n_sel.cpu().long(), want_n)
         # attention over window + the per-head prefixes
-        for h in range(H):
-            n = int(want_n[0, h])
-            kk = torch.cat([K[:, h:h + 1][:, :, win_idx], oracle.gather(zk[:, h:h + 1], idx_o[:, h:h + 1, :n])], 2)
-            vv = torch.cat([V[:, h:h + 1][:, :, win_idx], oracle.gather(zv[:, h:h + 1], idx_o[:, h:h + 1, :n])], 2)
-            g0, g1 = h * (Hq // H), (h + 1) * (Hq // H)
-            ref = oracle.attention(q[:, :, g0:g1], kk, vv)
-            assert (out[:, :, g0:g1].float().cpu() - ref).abs().max().item() <= 2e-2, (t, h)
+        for b in range(bs):
+            for h in range(H):
+                n = int(want_n[b, h])
+                sb, sh = slice(b, b + 1), slice(h, h + 1)
+                kk = torch.cat([K[sb, sh][:, :, win_idx], oracle.gather(zk[sb, sh], idx_o[sb, sh, :n])], 2)
+                vv = torch.cat([V[sb, sh][:, :, win_idx], oracle.gather(zv[sb, sh], idx_o[sb, sh, :n])], 2)
+                g0, g1 = h * (Hq // H), (h + 1) * (Hq // H)
+                ref = oracle.attention(q[sb, :, g0:g1], kk, vv)
+                # bf16 output: 2e-2 absolute for outputs of order one; the values here carry a lognormal scale, so
+                # allow half a bf16 step (2^-8 relative) of the largest output as well
+                tol = max(2e-2, ref.abs().max().item() * 2.0 ** -8)
+                assert (out[sb, :, g0:g1].float().cpu() - ref).abs().max().item() <= tol, (t, b, h)
     assert cache.cpu_valid_end[0] == P - sink - local + I
