@@ -884,17 +884,18 @@ def main():
                  "achieved_gbs": round(Kf * 512 * H / (att["avg_us"] * 1e-6) / 1e9, 2) if att else None,
                  "reference_peak_gbs": 55.6, "reference_peak_kind": "pinned cudaMemcpyAsync H2D measured on this pool"}
 
-    cpu = None
-    if world == 1 or True:
-        try:
-            per_layer, n = run_cpu_baseline(CFG if not debug else cfg, args.cpu_baseline_seconds)
-            cpu = {"value": 1.0 / (per_layer * Lyr), "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
-                   "sample": f"{n} layer-steps (retrieval chain + row gather + attention, N={N} keys/head) by the "
-                             "oracle's C port with OpenMP; tokens/s = 1 / (layers x mean layer-step); dense "
-                             "projections excluded"}
-        except Exception as e:  # the baseline is reporting only: never fail the bench on it
-            cpu = {"value": None, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
-                   "sample": f"failed: {type(e).__name__}: {e}"}
+    # the CPU baseline: rank 0, single-GPU runs only
+    try:
+        if world > 1:
+            raise RuntimeError("timed at N=1 only")
+        per_layer, n = run_cpu_baseline(CFG if not debug else cfg, args.cpu_baseline_seconds)
+        cpu = {"value": 1.0 / (per_layer * Lyr), "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+               "sample": f"{n} layer-steps (retrieval chain + row gather + attention, N={N} keys/head) by the "
+                         "oracle's C port with OpenMP; tokens/s = 1 / (layers x mean layer-step); dense "
+                         "projections excluded"}
+    except Exception as e:  # the baseline is reporting only: never fail the bench on it
+        cpu = {"value": None, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+               "sample": f"not measured: {type(e).__name__}: {e}"}
 
     line = {
         "metric": "decode_tokens_per_s", "value": world * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
