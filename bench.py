@@ -489,7 +489,7 @@ def kernels_mode(args, cfg, device):
     """Cache path only: per step and layer one K/V append and one compute() on a random query."""
     from pariskv_b200 import _lib
     K, W = args.steps, max(args.warmup, 1)
-    cache = build_cache(cfg, device, W + K + 2 * cfg["interval"] + 8, seed=100)
+    cache = build_cache(cfg, device, W + K + 2 * cfg["interval"] + 8, seed=100, offload=not args.no_offload)
     g = torch.Generator(device=device).manual_seed(5)
     Hq, Hk = cfg["q_heads"], cfg["kv_heads"]
     qs = torch.randn(K + W, cfg["layers"], 1, 1, Hq, 128, generator=g, device=device).to(torch.bfloat16)

@@ -356,12 +356,23 @@ __global__ void __launch_bounds__(TS_THREADS) topk_small_kernel(TopkParams p) {
   pdl_wait();
   pdl_trigger();
   float mn = INFINITY, mx = -INFINITY;
-  for (int i = tid; i < L; i += TS_THREADS) {
-    const uint32_t u = __ldg(in + i);
-    raw[i] = u;
-    flag[i] = 2;
-    const float v = val_of(u, p.is_float);
-    mn = fminf(mn, v), mx = fmaxf(mx, v);
+  for (int base = tid; base < L; base += 8 * TS_THREADS) {  // eight independent loads in flight per thread
+    uint32_t u[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int i = base + j * TS_THREADS;
+      u[j] = i < L ? __ldg(in + i) : 0u;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int i = base + j * TS_THREADS;
+      if (i < L) {
+        raw[i] = u[j];
+        flag[i] = 2;
+        const float v = val_of(u[j], p.is_float);
+        mn = fminf(mn, v), mx = fmaxf(mx, v);
+      }
+    }
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
@@ -473,11 +484,21 @@ __global__ void __launch_bounds__(TS_THREADS) topk_small_kernel(TopkParams p) {
   unsigned sel_before = (unsigned)(excl >> 32), tie_before = (unsigned)excl;
   int64_t* out = p.out + row * p.k;
   const int64_t* map = p.map ? p.map + row * p.map_stride : nullptr;
-  for (int i = i0; i < i1; i++) {
-    const uint8_t f = flag[i];
-    if (f == 1 || (f == 2 && tie_before < rem)) out[sel_before + min(tie_before, rem)] = map ? map[i] : (int64_t)i;
-    sel_before += f == 1;
-    tie_before += f == 2;
+  int64_t mv[TS_MAX / TS_THREADS];  // the chunk's output values, fetched with independent loads (per <= 16)
+#pragma unroll
+  for (int j = 0; j < TS_MAX / TS_THREADS; j++) {
+    const int i = i0 + j;
+    mv[j] = (i < i1) ? (map ? __ldg(map + i) : (int64_t)i) : 0;
+  }
+#pragma unroll
+  for (int j = 0; j < TS_MAX / TS_THREADS; j++) {
+    const int i = i0 + j;
+    if (i < i1) {
+      const uint8_t f = flag[i];
+      if (f == 1 || (f == 2 && tie_before < rem)) out[sel_before + min(tie_before, rem)] = mv[j];
+      sel_before += f == 1;
+      tie_before += f == 2;
+    }
   }
 }
 
