@@ -202,3 +202,42 @@ def test_bulk_offload_on_copy_stream(oracle):
         att, fin = _oracle_step(oracle, cache, qs[l], K_all, V_all, P - local, l)
         assert torch.equal(fins[l].cpu(), fin)
         assert (outs[l].float().cpu() - att).abs().max().item() <= 2e-2
+
+
+def test_long_generation_with_drifting_keys_one_kv_head(oracle):
+    """One KV head per rank (the tensor-parallel split of an 8-KV-head model over 8 GPUs needs no collective on this
+    path), batch 2, a generation that crosses six flushes, appended keys drawn around a mean direction that rotates:
+    every step's retrieved set and attention output against the oracle's state machine, and at the end the coded
+    zone against a fresh encode of the same token positions."""
+    from pariskv_b200 import dist as pkd
+    assert pkd.head_shard(8, 3, 8) == slice(3, 4)
+    g = torch.Generator().manual_seed(23)
+    bs, H, Hq, sink, local, I, topk, P, steps = 2, 1, 8, 4, 16, 8, 32, 2300, 50
+    cache = _make_cache(P, 64, bs, H, Hq, sink, local, I, topk, True, 1)
+    Ks = synth_keys(g, bs, H, P)
+    Vs = torch.randn(bs, H, P, 128, generator=g).to(torch.bfloat16)
+    cache.prefill_update_kv_cache(None, Ks.transpose(1, 2).contiguous().to(DEV), Vs.transpose(1, 2).contiguous().to(DEV), 0, 0)
+    a = torch.randn(128, generator=g)
+    b = torch.randn(128, generator=g)
+    a, b = a / a.norm(), b - (b @ a) * a / (a @ a)
+    b = b / b.norm()
+    for t in range(steps):
+        theta = 0.05 * t                         # the mean direction turns in the (a, b) plane
+        mean = (torch.cos(torch.tensor(theta)) * a + torch.sin(torch.tensor(theta)) * b) * 12.0
+        nk = (mean + torch.randn(bs, H, 1, 128, generator=g)).to(torch.bfloat16)
+        nv = torch.randn(bs, H, 1, 128, generator=g).to(torch.bfloat16)
+        Ks, Vs = torch.cat([Ks, nk], 2), torch.cat([Vs, nv], 2)
+        cache.decode_update_kv_cache(nk.transpose(1, 2).contiguous().to(DEV), nv.transpose(1, 2).contiguous().to(DEV), 0)
+        q = ((mean / 12.0) * 0.5 + torch.randn(bs, 1, Hq, 128, generator=g) * 0.3).to(torch.bfloat16)
+        out = cache.compute(q.to(DEV), 0)
+        zone_end = P - local + ((t + 1) // I) * I
+        ref, fin = _oracle_step(oracle, cache, q, Ks, Vs, zone_end, 0)
+        assert torch.equal(cache.last_topk_indices.cpu(), fin), f"step {t}: retrieved set differs"
+        assert (out.float().cpu() - ref).abs().max().item() <= 2e-2, t
+    assert cache.cpu_valid_end[0] == P - sink - local + 6 * I and cache.context == P + steps
+    zone = Ks[:, :, sink:P - local + 6 * I].contiguous()
+    cb, w, pk = oracle.encode(zone, cache.srht_diagonal_signs.cpu())
+    N = zone.shape[2]
+    assert torch.equal(cache.codebook_gpu[0][:, :, :, :N].cpu(), cb)
+    assert torch.equal(cache.key_4bit_packed_gpu[0][:, :, :, :N].cpu(), pk)
+    assert torch.equal(cache.cluster_key_counts_gpu[0].cpu(), oracle.cluster_counts(cb))
