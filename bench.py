@@ -100,7 +100,10 @@ class DecoderHarness:
 class GraphedDecoder:
     """Replays the decode step as a CUDA graph.  Between two flushes of the update buffer every launch
     argument of the step is constant except the window position and the RoPE position, which the kernels
-    read from device words; the step that flushes runs eagerly and the graph is captured again after it."""
+    read from device words.  The zone length, the candidate count and the tier thresholds are launch arguments,
+    so there is one graph per zone length; graphs for the lengths that the coming flushes will produce can be
+    captured ahead of time (`precapture`), as a serving engine captures its graphs at start-up: capturing executes
+    nothing and only needs the launch arguments.  The step that flushes runs eagerly."""
 
     def __init__(self, model, cache):
         self.model, self.cache = model, cache
@@ -108,27 +111,31 @@ class GraphedDecoder:
         self.tok = torch.zeros(1, dtype=torch.int64, device=dev)   # static input, fed back by the graph
         self.nxt = torch.zeros(1, dtype=torch.int64, device=dev)   # static output
         self.pos = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.graph = None
-        self.stale = True
+        self.graphs = {}              # zone length -> (graph, launches of this repository's kernels per replay)
+        self.graph = None             # the graph replayed last (kept for callers that release it explicitly)
+        self.need_resync = True       # device-side positions are stale (start, or after an eager step)
         self.captures = 0
         self.kernel_launches = 0      # launches of this repository's kernels executed through step()
-        self.launches_per_replay = 0
         self.pool = torch.cuda.graph_pool_handle()
         self.side = torch.cuda.Stream(device=dev)
 
-    def _capture(self):
+    def _zone_length(self):
+        return getattr(self.cache, "cpu_valid_end", [0])[0]
+
+    def _capture(self, n_zone):
+        """Capture the step for a zone of n_zone keys per head (the current length, or one a later flush produces)."""
         cache = self.cache
-        cache.device_positions = True
-        cache.sync_device_state()
-        self.pos.fill_(float(cache.context))
         saved = cache.host_state()
+        if n_zone != self._zone_length():   # a future state: right after a flush the window holds the steady rows
+            L = cache.layer_num
+            cache.set_host_state(([cache.steady_size] * L, list(saved[1]), saved[2], [n_zone] * L))
+        cache.device_positions = True
         # plain capture_begin / capture_end on a side stream: the torch.cuda.graph context also runs the garbage
-        # collector and empties the allocator cache, which costs far more than the capture when it is repeated
-        # after every flush
+        # collector and empties the allocator cache, which costs far more than the capture itself
         from pariskv_b200 import _lib
         before = _lib.launch_count()
         main = torch.cuda.current_stream()
-        g = torch.cuda.CUDAGraph()    # the previous graph stays alive until this one holds the shared pool
+        g = torch.cuda.CUDAGraph()    # earlier graphs stay alive: they share the memory pool
         self.side.wait_stream(main)
         with torch.cuda.stream(self.side):
             g.capture_begin(pool=self.pool)
@@ -140,10 +147,16 @@ class GraphedDecoder:
             g.capture_end()
         main.wait_stream(self.side)
         cache.set_host_state(saved)   # capture ran the host bookkeeping of one step without executing it
-        self.launches_per_replay = _lib.launch_count() - before
-        self.graph = g
-        self.stale = False
+        self.graphs[n_zone] = (g, _lib.launch_count() - before)
         self.captures += 1
+
+    def precapture(self, flushes):
+        """Graphs for the current zone length and for the lengths after each of the next `flushes` flushes."""
+        n0, I = self._zone_length(), getattr(self.cache, "dynamic_update_interval", 0)
+        for j in range(flushes + 1):
+            n = n0 + j * I
+            if n not in self.graphs and (j == 0 or n <= getattr(self.cache, "zone_capacity", 0)):
+                self._capture(n)
 
     def step(self):
         """Advance one token; input in self.tok, result in self.nxt (and fed back into self.tok)."""
@@ -156,13 +169,24 @@ class GraphedDecoder:
             self.kernel_launches += _lib.launch_count() - before
             self.nxt.copy_(out)
             self.tok.copy_(out)
-            self.stale = True                            # the zone grew: launch arguments changed
+            self.need_resync = True                      # the eager step did not touch the device-side positions
             return
-        if self.graph is None or self.stale:
-            self._capture()
+        n = self._zone_length()
+        if n not in self.graphs:
+            self._capture(n)
+        if self.need_resync:
+            cache.sync_device_state()
+            self.pos.fill_(float(cache.context))
+            self.need_resync = False
+        self.graph, launches = self.graphs[n]
         self.graph.replay()
-        self.kernel_launches += self.launches_per_replay
+        self.kernel_launches += launches
         cache.note_replayed_step()
+
+    def release(self):
+        """Drop every captured graph (before a communicator whose collectives they hold is destroyed)."""
+        self.graphs.clear()
+        self.graph = None
 
 
 def synth_kv(gen, P, H, device):
@@ -666,7 +690,7 @@ def seqshard_mode(args, device, rank, world, local_rank):
         # first waits for ever); a timer ends the process if the teardown still does not return
         import gc
         import threading
-        runner.graph = None
+        runner.release()
         gc.collect()
         barrier()
         sys.stdout.flush()
@@ -786,6 +810,8 @@ def main():
     for _ in range(2):                       # eager first: library handles, workspaces
         token = model.step(cache, token)
     runner.tok.copy_(token)
+    if use_graph:    # graphs for every zone length the run will reach, captured before anything is timed
+        runner.precapture((W + 2 * K) // cfg["interval"] + 1)
     for _ in range(max(W - 2, 1)):
         advance()
     barrier()

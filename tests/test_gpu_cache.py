@@ -241,3 +241,43 @@ def test_long_generation_with_drifting_keys_one_kv_head(oracle):
     assert torch.equal(cache.codebook_gpu[0][:, :, :, :N].cpu(), cb)
     assert torch.equal(cache.key_4bit_packed_gpu[0][:, :, :, :N].cpu(), pk)
     assert torch.equal(cache.cluster_key_counts_gpu[0].cpu(), oracle.cluster_counts(cb))
+
+
+def test_graphed_decoder_with_precaptured_graphs_matches_eager():
+    """bench.GraphedDecoder: graphs for the zone lengths of the coming flushes are captured ahead of time; a run that
+    crosses three flushes must produce the same tokens as plain eager stepping (same weights, same cache content)."""
+    import bench
+    cfg = dict(layers=2, hidden=256, q_heads=8, kv_heads=2, head_dim=128, ffn=512, vocab=997, rope_theta=1.0e6,
+               context=2600, sink=4, local=16, interval=8, topk=32)
+    dev = torch.device(DEV)
+    model = bench.DecoderHarness(cfg, dev, seed=5)
+    steps = 30
+
+    def fresh():
+        return bench.build_cache(cfg, dev, steps + 40, seed=9)
+
+    cache = fresh()
+    tok = torch.tensor([3], device=dev)
+    eager = []
+    for _ in range(steps):
+        tok = model.step(cache, tok)
+        eager.append(int(tok))
+    assert cache.cpu_valid_end[0] == 2600 - 20 + 3 * 8
+
+    cache = fresh()
+    runner = bench.GraphedDecoder(model, cache)
+    tok = torch.tensor([3], device=dev)
+    got = []
+    for _ in range(2):                  # eager first, as the benchmark does
+        tok = model.step(cache, tok)
+        got.append(int(tok))
+    runner.tok.copy_(tok)
+    runner.precapture(3)
+    captured = runner.captures
+    assert captured == 4
+    for _ in range(steps - 2):
+        runner.step()
+        got.append(int(runner.nxt))
+    assert got == eager
+    assert runner.captures == captured, "a graph was captured inside the run although all lengths were prepared"
+    assert cache.cpu_valid_end[0] == 2600 - 20 + 3 * 8 and cache.context == 2600 + steps
