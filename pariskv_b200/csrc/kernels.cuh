@@ -22,8 +22,12 @@ int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* ou
                      int64_t* n_chunks_out, cudaStream_t st);
 
 // topk.cu: exact top-k of rows of 32-bit values; out[row][i] = map ? map[row*map_stride + pos] : pos
+// With `scratch` (topk_scratch_bytes(rows, L, k) bytes, 256-byte aligned; 0 = not needed) rows longer than 16384
+// elements are selected in two passes of the one-CTA kernel instead of the cluster kernel.
+int64_t topk_scratch_bytes(int64_t rows, int64_t L, int64_t k);
 int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride, int64_t L, int64_t k,
-                int64_t* out, const int64_t* map, int64_t map_stride, int order, cudaStream_t st, int stage);
+                int64_t* out, const int64_t* map, int64_t map_stride, int order, cudaStream_t st, int stage,
+                void* scratch = nullptr, int64_t scratch_bytes = 0);
 
 // rerank.cu
 struct RerankArgs {

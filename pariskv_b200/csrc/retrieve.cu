@@ -10,7 +10,7 @@ namespace {
 inline int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
 struct RetrieveLayout {
-  int64_t q_blocks, q_norm, lut, counts, hist, scores, cand, total;
+  int64_t q_blocks, q_norm, lut, counts, hist, scores, cand, topk, topk_bytes, total;
   int64_t u8_stride, n_chunks_max;
 };
 
@@ -28,6 +28,8 @@ RetrieveLayout make_layout(int64_t bs, int64_t H, int64_t N, int64_t C) {
   l.hist = off, off += align256(bh * l.n_chunks_max * 256 * 4);
   l.scores = off, off += align256(bh * C * 4);
   l.cand = off, off += align256(bh * C * 8);
+  l.topk_bytes = topk_scratch_bytes(bh, C, 2048);   // sized for any K up to 8192 (the size does not depend on K)
+  l.topk = off, off += align256(l.topk_bytes);
   l.total = off;
   return l;
 }
@@ -129,5 +131,6 @@ extern "C" int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, con
   if ((rc = launch_select_rerank(ra, bh, counts, lay.u8_stride, hist, n_chunks, chunk_keys, mis, N, cd, sc, st)))
     return rc;
   if (K == 0) return PK_OK;  // the caller ranks the candidates itself (adaptive-k)
-  return launch_topk(sc, true, bh, C, C, K, (int64_t*)final_indices->data, cd, C, 0, st, ST_FINAL_TOPK);
+  return launch_topk(sc, true, bh, C, C, K, (int64_t*)final_indices->data, cd, C, 0, st, ST_FINAL_TOPK,
+                     lay.topk_bytes ? ws + lay.topk : nullptr, lay.topk_bytes);
 }

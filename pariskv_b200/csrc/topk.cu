@@ -30,6 +30,10 @@ struct TopkParams {
   int64_t* out;
   const int64_t* map;
   int64_t map_stride;
+  // one-CTA kernel only: a launch row is segment (row % nseg) of input row (row / nseg), `seg` elements long (the last
+  // one shorter); out_val, when set, receives the raw 32-bit values of the selected elements next to `out`
+  int64_t nseg, seg;
+  uint32_t* out_val;
 };
 
 constexpr int TK_CACHE = 16384;  // elements of a CTA's slice kept in (dynamic) shared memory; the rest is re-read from L2
@@ -351,8 +355,9 @@ __global__ void __launch_bounds__(TS_THREADS) topk_small_kernel(TopkParams p) {
   __shared__ unsigned s_ntie;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t row = blockIdx.x;
-  const int L = (int)p.L;
-  const uint32_t* in = p.in + row * p.row_stride;
+  const int64_t in_row = row / p.nseg, seg_id = row % p.nseg;
+  const int L = (int)min(p.seg, p.L - seg_id * p.seg);
+  const uint32_t* in = p.in + in_row * p.row_stride + seg_id * p.seg;
   pdl_wait();
   pdl_trigger();
   float mn = INFINITY, mx = -INFINITY;
@@ -483,19 +488,24 @@ __global__ void __launch_bounds__(TS_THREADS) topk_small_kernel(TopkParams p) {
   const unsigned long long excl = base + sc - mine64;
   unsigned sel_before = (unsigned)(excl >> 32), tie_before = (unsigned)excl;
   int64_t* out = p.out + row * p.k;
-  const int64_t* map = p.map ? p.map + row * p.map_stride : nullptr;
+  uint32_t* out_val = p.out_val ? p.out_val + row * p.k : nullptr;
+  const int64_t* map = p.map ? p.map + in_row * p.map_stride + seg_id * p.seg : nullptr;
   int64_t mv[TS_MAX / TS_THREADS];  // the chunk's output values, fetched with independent loads (per <= 16)
 #pragma unroll
   for (int j = 0; j < TS_MAX / TS_THREADS; j++) {
     const int i = i0 + j;
-    mv[j] = (i < i1) ? (map ? __ldg(map + i) : (int64_t)i) : 0;
+    mv[j] = (i < i1) ? (map ? __ldg(map + i) : seg_id * p.seg + (int64_t)i) : 0;
   }
 #pragma unroll
   for (int j = 0; j < TS_MAX / TS_THREADS; j++) {
     const int i = i0 + j;
     if (i < i1) {
       const uint8_t f = flag[i];
-      if (f == 1 || (f == 2 && tie_before < rem)) out[sel_before + min(tie_before, rem)] = mv[j];
+      if (f == 1 || (f == 2 && tie_before < rem)) {
+        const unsigned o = sel_before + min(tie_before, rem);
+        out[o] = mv[j];
+        if (out_val) out_val[o] = raw[i];
+      }
       sel_before += f == 1;
       tie_before += f == 2;
     }
@@ -537,14 +547,21 @@ __global__ void __launch_bounds__(1024) sort_by_value_kernel(const uint32_t* in,
 
 }  // namespace
 
+int64_t topk_scratch_bytes(int64_t rows, int64_t L, int64_t k) {
+  if (L <= TS_MAX || k < 1 || k > TS_MAX / 2) return 0;
+  return rows * (int64_t)TS_MAX * 12;   // (value u32, index i64) of up to TS_MAX segment winners per row
+}
+
 int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride, int64_t L, int64_t k,
-                int64_t* out, const int64_t* map, int64_t map_stride, int order, cudaStream_t st, int stage) {
+                int64_t* out, const int64_t* map, int64_t map_stride, int order, cudaStream_t st, int stage,
+                void* scratch, int64_t scratch_bytes) {
   StageTimer tm(stage, st);
   TopkParams p;
   p.in = (const uint32_t*)in;
   p.is_float = is_float ? 1 : 0;
   p.row_stride = row_stride, p.L = L, p.k = k;
   p.out = out, p.map = map, p.map_stride = map_stride;
+  p.nseg = 1, p.seg = L, p.out_val = nullptr;
   static int use_small = -1;
   if (use_small < 0) {
     const char* e = getenv("PK_TOPK_SMALL");
@@ -563,6 +580,33 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
     while (kp < k) kp <<= 1;
     sort_by_value_kernel<<<(unsigned)rows, 1024, (size_t)kp * 8, st>>>(p.in, p.is_float, row_stride, k, kp, out);
     return check_launch("topk sort");
+  }
+  // Long rows with scratch from the caller: cut the row into nseg segments, take the top k of every segment with the
+  // one-CTA kernel (nseg CTAs per row), then the top k of the nseg*k winners.  Exact: the k best of the row are among
+  // the k best of their own segments, and the winners are listed segment by segment in ascending position, so the
+  // tie rule (value descending, position ascending) is the same in both passes.
+  if (use_small && order == 0 && L > TS_MAX && scratch && k >= 1) {
+    int64_t nseg = TS_MAX / k;
+    if (nseg > 16) nseg = 16;
+    if (nseg >= 2 && (L + nseg - 1) / nseg > TS_MAX) nseg = 0;   // segments must fit the one-CTA kernel
+    const int64_t seg = nseg >= 2 ? (L + nseg - 1) / nseg : 0;
+    const bool fits = nseg >= 2 && L - (nseg - 1) * seg >= k && scratch_bytes >= rows * (int64_t)TS_MAX * 12 &&
+                      rows * nseg < (1LL << 31);
+    if (fits) {
+      uint32_t* win_val = (uint32_t*)scratch;                                  // [rows][nseg*k]
+      int64_t* win_idx = (int64_t*)((char*)scratch + rows * (int64_t)TS_MAX * 4);  // [rows][nseg*k], 8-byte aligned
+      TopkParams a = p;
+      a.nseg = nseg, a.seg = seg;
+      a.out = win_idx, a.out_val = win_val;
+      launch_chain(topk_small_kernel, dim3((unsigned)(rows * nseg)), dim3(TS_THREADS), TS_SMEM, st, a);
+      int rc = check_launch("topk segments");
+      if (rc) return rc;
+      TopkParams b = p;
+      b.in = win_val, b.row_stride = nseg * k, b.L = nseg * k, b.seg = nseg * k, b.nseg = 1;
+      b.map = win_idx, b.map_stride = nseg * k;
+      launch_chain(topk_small_kernel, dim3((unsigned)rows), dim3(TS_THREADS), TS_SMEM, st, b);
+      return check_launch("topk merge");
+    }
   }
   // about 1024 elements per CTA, at most 16 CTAs per row (clusters above 8 need the non-portable opt-in)
   unsigned ncta = 1;

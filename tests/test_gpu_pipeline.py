@@ -34,7 +34,8 @@ def _build_index(ops, oracle, keys, signs, layout):
 
 
 @pytest.mark.parametrize("layout", ["key_major", "plane_major_offset"])
-@pytest.mark.parametrize("N,C,K,bs,H", [(700, 350, 100, 2, 2), (4099, 410, 64, 1, 3), (33000, 3300, 256, 1, 2)])
+@pytest.mark.parametrize("N,C,K,bs,H", [(700, 350, 100, 2, 2), (4099, 410, 64, 1, 3), (33000, 3300, 256, 1, 2),
+                                         (180000, 18000, 2048, 1, 2), (90000, 17001, 1000, 2, 1)])
 def test_retrieve_chain_bit_exact(ops, oracle, layout, N, C, K, bs, H):
     g = torch.Generator().manual_seed(N)
     keys = synth_keys(g, bs, H, N)
@@ -127,3 +128,5 @@ def test_full_size_properties(ops, N, C):
     assert bool((torch.gather(cand, 2, pos) == fin).all())
     assert bool((torch.gather(s, 2, pos) >= kth).all())
     assert torch.equal(ops.topk(cnt, C), cand)
+    # the chain's final selection (two passes of the one-CTA kernel on long rows) equals the stand-alone op
+    assert torch.equal(ops.final_topk(s, cand, K), fin)
