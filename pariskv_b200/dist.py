@@ -7,15 +7,18 @@ cache on one device):
   cache with `num_key_value_heads / world` heads and runs the unchanged single-GPU path.  No collective on the
   retrieval path; `head_shard()` gives the slice.
 * The sequence (million-token contexts): the searchable zone is cut into equal contiguous chunks, one per
-  rank, each with its codes / 4-bit records in its own HBM and its K/V rows in its own pinned host memory.
-  Per layer and step every rank runs the local chain (collision -> candidates -> rerank -> local top-K) with
-  GLOBAL tier thresholds and the GLOBAL cluster histogram, then `merge_local_topk` all-gathers
-  (fp32 score, global key index) and every rank selects the same global top-K; each rank attends only the
-  selected rows it owns (rank 0 also the window) and `merge_partial_attention` combines the partial results
-  through their log-sum-exp.  Two small all-gathers per layer (K * 12 bytes and Hq * 260 bytes per rank).
+  rank, each with its codes / 4-bit records in its own HBM and its K/V rows in its own HBM (when they fit) or
+  pinned host memory.  Per layer and step every rank runs the local chain (collision -> candidates -> rerank ->
+  local top-K) with GLOBAL tier thresholds and the GLOBAL cluster histogram; the ranks exchange (fp32 score,
+  global key index) of their local lists and every rank selects the same global top-K; each rank attends only
+  the selected rows it owns (rank 0 also the window) and a second exchange of (partial output, log2 denominator)
+  gives every rank the exact softmax over the union.  `SequenceShardedCache` / `sequence_sharded_attend` run the
+  exchanges either as two small NCCL all-gathers with CUDA packing / unpacking kernels around them, or as
+  stores into peer memory with flag words (`PeerExchange`).
 
-The selection inside `merge_local_topk` is pluggable so that the exchange can be tested with gloo ranks on
-CPU; on GPUs the default selector is the CUDA top-k of this library.
+`merge_local_topk`, `owned_rows` and `merge_partial_attention` are the same exchanges written with torch ops and a
+pluggable selector: they run on CPU tensors with gloo ranks and are what the host-side tests exercise; on GPUs
+the CUDA entry points (`pk_shard_*`) do this work.
 """
 import math
 
