@@ -122,13 +122,13 @@ class GraphedDecoder:
     def _zone_length(self):
         return getattr(self.cache, "cpu_valid_end", [0])[0]
 
-    def _capture(self, n_zone):
-        """Capture the step for a zone of n_zone keys per head (the current length, or one a later flush produces)."""
+    def _capture(self, n_zone, future=None):
+        """Capture the step for a zone of n_zone keys per head: the current state, or `future`, the host state right
+        after a coming flush."""
         cache = self.cache
         saved = cache.host_state()
-        if n_zone != self._zone_length():   # a future state: right after a flush the window holds the steady rows
-            L = cache.layer_num
-            cache.set_host_state(([cache.steady_size] * L, list(saved[1]), saved[2], [n_zone] * L))
+        if future is not None:
+            cache.set_host_state(future)
         cache.device_positions = True
         # plain capture_begin / capture_end on a side stream: the torch.cuda.graph context also runs the garbage
         # collector and empties the allocator cache, which costs far more than the capture itself
@@ -152,11 +152,15 @@ class GraphedDecoder:
 
     def precapture(self, flushes):
         """Graphs for the current zone length and for the lengths after each of the next `flushes` flushes."""
-        n0, I = self._zone_length(), getattr(self.cache, "dynamic_update_interval", 0)
-        for j in range(flushes + 1):
-            n = n0 + j * I
-            if n not in self.graphs and (j == 0 or n <= getattr(self.cache, "zone_capacity", 0)):
-                self._capture(n)
+        if self._zone_length() not in self.graphs:
+            self._capture(self._zone_length())
+        for j in range(1, flushes + 1):
+            future = self.cache.host_state_after_flushes(j)
+            if future is None:
+                break
+            n = future[3][0]
+            if n not in self.graphs:
+                self._capture(n, future)
 
     def step(self):
         """Advance one token; input in self.tok, result in self.nxt (and fed back into self.tok)."""
@@ -577,9 +581,6 @@ def seqshard_mode(args, device, rank, world, local_rank):
     if args.context:
         cfg["context"], debug = args.context, True
     K, W = args.steps, max(args.warmup, 3)
-    if K + W + 2 > cfg["interval"]:
-        raise SystemExit(f"--mode seqshard holds at most {cfg['interval'] - 2} steps (steps + warmup): the "
-                         "sequence-sharded form does not flush the update buffer yet")
     H, Lyr = cfg["kv_heads"], cfg["layers"]
     n_total = cfg["context"] - cfg["sink"] - cfg["local"]
     start, end = sequence_shard(n_total, rank, world)
@@ -602,7 +603,8 @@ def seqshard_mode(args, device, rank, world, local_rank):
     t_setup = time.time()
     model = DecoderHarness(cfg, device, seed=1234)
     cache = SequenceShardedCache(Lyr, H, cfg["q_heads"], n_total, cfg["sink"], cfg["local"], cfg["interval"],
-                                 cfg["topk"], device, rank, world, store=args.store, exchange=args.exchange)
+                                 cfg["topk"], device, rank, world, store=args.store, exchange=args.exchange,
+                                 max_new_length=W + K + 8)
     for l in range(Lyr):
         ks, vs = [], []
         for b in range(start // SHARD_BLOCK, (max(end, start + 1) - 1) // SHARD_BLOCK + 1):
@@ -638,6 +640,8 @@ def seqshard_mode(args, device, rank, world, local_rank):
     for _ in range(2):
         token = model.step(cache, token)
     runner.tok.copy_(token)
+    if use_graph:    # graphs for every zone length the run will reach, captured before anything is timed
+        runner.precapture((W + K) // cfg["interval"] + 1)
     for _ in range(W - 2):
         advance()
     barrier()

@@ -344,6 +344,15 @@ class polar_cache(KV_Cache):
     def set_host_state(self, st):
         self._window_len, self.current_seq_len, self.context, self.cpu_valid_end = list(st[0]), list(st[1]), st[2], list(st[3])
 
+    def host_state_after_flushes(self, j):
+        """The host state right after the j-th flush from now (None when the zone cannot grow that far): what a
+        step captured ahead of time needs, since capturing only records launch arguments."""
+        n = self.cpu_valid_end[0] + j * self.dynamic_update_interval
+        if n > self.zone_capacity:
+            return None
+        L = self.layer_num
+        return ([self.steady_size] * L, list(self.current_seq_len), self.context, [n] * L)
+
     def note_replayed_step(self):
         """Host-side bookkeeping of one decode step that ran as a graph replay."""
         for l in range(self.layer_num):

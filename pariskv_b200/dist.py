@@ -212,20 +212,30 @@ class PeerExchange:
 
 class SequenceShardedCache:
     """Decode-side cache of the sequence-sharded form: this rank holds one contiguous chunk of every layer's
-    zone (codes / 4-bit records / weights in HBM, K/V rows in pinned host memory) plus a full copy of the small
-    GPU window; rank 0 attends the window.  It exposes the calls a decode loop makes on the single-GPU cache
-    (`decode_update_kv_cache`, `compute`, `context`).  The zone is fixed after `load_layer`: the update buffer
-    must not overflow (no flush in this form yet), which holds for runs shorter than the buffer."""
+    zone (codes / 4-bit records / weights in HBM, K/V rows in HBM or pinned host memory) plus a full copy of the
+    small GPU window; rank 0 attends the window.  It exposes the calls a decode loop makes on the single-GPU cache
+    (`decode_update_kv_cache`, `compute`, `context`, and the hooks for replaying a captured step).
+
+    Flush: when the update buffer fills, every rank drops the oldest `interval` window rows (the windows are
+    replicas), the LAST rank codes them and appends them to its chunk — the zone grows at its end — and the
+    histogram of the new codes is all-reduced into every rank's global cluster histogram."""
 
     def __init__(self, layer_num, num_kv_heads, num_heads, n_total, sink_size, local_size, interval, final_topk,
                  device, rank, world, group=None, collision_ratio=0.2, candidate_ratio=0.1, srht_sign_vector=None,
-                 store="host", exchange="nccl"):
+                 store="host", exchange="nccl", max_new_length=0):
         from .cache_hub.polar_cache import srht_signs
         self.layer_num, self.kv_head, self.num_heads = layer_num, num_kv_heads, num_heads
-        self.n_total, self.sink_size, self.local_size, self.interval = n_total, sink_size, local_size, interval
+        self.sink_size, self.local_size, self.interval = sink_size, local_size, interval
+        self.dynamic_update_interval = interval
+        self.steady_size = sink_size + local_size
         self.final_topk, self.device, self.rank, self.world, self.group = final_topk, device, rank, world, group
         self.collision_ratio, self.candidate_ratio = collision_ratio, candidate_ratio
-        self.start, self.end = sequence_shard(n_total, rank, world)
+        self.start, end0 = sequence_shard(n_total, rank, world)
+        self._n_total = [n_total] * layer_num               # zone keys per head, all ranks together
+        self._n_local = [end0 - self.start] * layer_num     # zone keys per head held by this rank
+        self.last = rank == world - 1
+        # room for the keys that flushes append (they all go to the last rank)
+        self.growth = ((max_new_length + interval - 1) // interval * interval + interval) if self.last else 0
         self.signs = (srht_sign_vector.to(device, torch.bfloat16).contiguous() if srht_sign_vector is not None
                       else srht_signs(device))
         self.centers = torch.tensor([0.0420, 0.1266, 0.2130, 0.3025, 0.3973, 0.5001, 0.6169, 0.7633],
@@ -237,15 +247,13 @@ class SequenceShardedCache:
         self._window_len = [0] * layer_num
         self.meta = [None] * layer_num
         self.counts = [None] * layer_num
-        self.store_k = [None] * layer_num
-        self.store_v = [None] * layer_num
+        self.store_kv = [None] * layer_num
         self.context = 0
         self.last_topk_indices = None
         if store not in ("host", "hbm", "auto"):
             raise ValueError("store must be 'host', 'hbm' or 'auto'")
         if store == "auto":   # keep the shard's K/V rows in HBM when they fit beside the codes, else pinned host memory
-            n_local = self.end - self.start
-            need = layer_num * num_kv_heads * n_local * (512 + 112)
+            need = layer_num * num_kv_heads * (self._n_local[0] + self.growth) * (512 + 112)
             free, _ = torch.cuda.mem_get_info(device)
             store = "hbm" if need + (16 << 30) < free else "host"
         self.store = store
@@ -258,48 +266,92 @@ class SequenceShardedCache:
         self.device_positions = False     # window length read from a device word (captured steps)
         self._dev_state = torch.zeros(1, dtype=torch.int32, device=device)
 
+    # the names the single-GPU cache uses for the same quantities
+    @property
+    def n_total(self):
+        return self._n_total[0]
+
+    @property
+    def cpu_valid_end(self):
+        return self._n_total
+
+    @property
+    def end(self):
+        return self.start + self._n_local[0]
+
     def load_layer(self, layer, shard_keys, shard_values, window_keys, window_values):
         """shard_keys / shard_values: bf16 [1,H,n_local,128] on the device (this rank's chunk of the zone);
         window_*: bf16 [1,H,sink+local,128] (sink rows then the last `local` rows of the prompt)."""
         from . import ops
-        counts = torch.zeros(1, self.kv_head, 16, 256, dtype=torch.int32, device=self.device)
-        self.meta[layer] = ops.encode_keys(shard_keys, self.signs, cluster_counts=counts)
-        self.counts[layer] = allreduce_cluster_counts(counts, self.group)
         n_local = shard_keys.shape[2]
+        assert n_local == self._n_local[layer], "shard length differs from sequence_shard()"
+        cap = max(n_local + self.growth, 1)
+        cb, w, pk = ops.alloc_key_metadata(1, self.kv_head, cap, self.device)
+        counts = torch.zeros(1, self.kv_head, 16, 256, dtype=torch.int32, device=self.device)
+        ops.encode_keys(shard_keys, self.signs, cb[:, :, :, :n_local], w[:, :, :, :n_local], pk[:, :, :, :n_local, :],
+                        cluster_counts=counts)
+        self.meta[layer] = (cb, w, pk)
+        self.counts[layer] = allreduce_cluster_counts(counts, self.group)
         # K and V row of a key next to each other: one host address translation per selected key instead of two
         kv = torch.stack((shard_keys, shard_values), dim=3)          # [1,H,n,2,128] on the device
-        if self.store == "hbm" and n_local > 0:
-            skv = kv
+        if self.store == "hbm":
+            skv = torch.empty(1, self.kv_head, cap, 2, 128, dtype=torch.bfloat16, device=self.device)
         else:
-            skv = torch.empty(1, self.kv_head, max(n_local, 1), 2, 128, dtype=torch.bfloat16, pin_memory=True)
-            skv[:, :, :n_local].copy_(kv, non_blocking=True)
-        sk, sv = skv[:, :, :, 0], skv[:, :, :, 1]
-        self.store_k[layer], self.store_v[layer] = sk, sv
+            skv = torch.empty(1, self.kv_head, cap, 2, 128, dtype=torch.bfloat16, pin_memory=True)
+        skv[:, :, :n_local].copy_(kv, non_blocking=True)
+        self.store_kv[layer] = skv
         n = window_keys.shape[2]
         self.window_k[layer][:, :, :n] = window_keys
         self.window_v[layer][:, :, :n] = window_values
         self._window_len[layer] = n
         if layer == self.layer_num - 1:
-            self.context = self.sink_size + self.n_total + self.local_size
+            self.context = self.sink_size + self._n_total[layer] + self.local_size
 
     def decode_update_kv_cache(self, key_states, value_states, layer_idx):
         from . import ops
         pos = self._window_len[layer_idx]
-        if pos >= self.window_capacity:
-            raise RuntimeError("update buffer full: the sequence-sharded form has no flush yet")
         ops.append_kv(key_states, value_states, self.window_k[layer_idx], self.window_v[layer_idx], pos,
                       self._dev_state[0:1] if self.device_positions else None, 0)
         self._window_len[layer_idx] = pos + 1
         if layer_idx == 0:
             self.context += 1
+        if self._window_len[layer_idx] == self.window_capacity:
+            self._flush(layer_idx)
         return None, None
+
+    def _flush(self, layer):
+        """Move the oldest `interval` rows behind the sink out of the window and into the zone (last rank's chunk)."""
+        from . import ops
+        if self.device_positions:
+            raise RuntimeError("a flush cannot be part of a captured step: run the step that flushes eagerly")
+        I, sink, local = self.interval, self.sink_size, self.local_size
+        wk, wv = self.window_k[layer], self.window_v[layer]
+        delta = torch.zeros(1, self.kv_head, 16, 256, dtype=torch.int32, device=self.device)
+        if self.last:
+            n = self._n_local[layer]
+            cb, w, pk = self.meta[layer]
+            if n + I > cb.shape[3]:
+                raise RuntimeError("zone capacity exhausted: construct the cache with a larger max_new_length")
+            zk, zv = wk[:, :, sink:sink + I], wv[:, :, sink:sink + I]
+            ops.encode_keys(zk, self.signs, cb[:, :, :, n:n + I], w[:, :, :, n:n + I], pk[:, :, :, n:n + I, :],
+                            cluster_counts=delta)
+            self.store_kv[layer][:, :, n:n + I].copy_(torch.stack((zk, zv), dim=3), non_blocking=True)
+            self._n_local[layer] = n + I
+        self.counts[layer] += allreduce_cluster_counts(delta, self.group)
+        self._n_total[layer] += I
+        wk[:, :, sink:sink + local] = wk[:, :, sink + I:sink + I + local].clone()
+        wv[:, :, sink:sink + local] = wv[:, :, sink + I:sink + I + local].clone()
+        self._window_len[layer] = sink + local
 
     def compute(self, queries, layer_idx):
         cb, w, pk = self.meta[layer_idx]
+        n = self._n_local[layer_idx]
+        skv = self.store_kv[layer_idx]
         first = self.rank == 0
         out, final = sequence_sharded_attend(
-            queries.contiguous(), self.signs, self.centers, cb, w, pk, self.counts[layer_idx], self.store_k[layer_idx],
-            self.store_v[layer_idx], self.n_total, self.start, self.end, self.collision_ratio, self.candidate_ratio,
+            queries.contiguous(), self.signs, self.centers, cb[:, :, :, :n], w[:, :, :, :n], pk[:, :, :, :n, :],
+            self.counts[layer_idx], skv[:, :, :, 0], skv[:, :, :, 1], self._n_total[layer_idx], self.start,
+            self.start + n, self.collision_ratio, self.candidate_ratio,
             self.final_topk, window_k=self.window_k[layer_idx] if first else None,
             window_v=self.window_v[layer_idx] if first else None,
             n_window=(self.window_capacity if self.device_positions else self._window_len[layer_idx]) if first else 0,
@@ -310,7 +362,7 @@ class SequenceShardedCache:
 
     # ---- support for replaying a captured decode step (same calls as the single-GPU cache) ----
     def next_step_flushes(self) -> bool:
-        return False
+        return self._window_len[0] + 1 >= self.window_capacity
 
     def sync_device_state(self):
         self._dev_state[0] = self._window_len[0]
@@ -319,13 +371,19 @@ class SequenceShardedCache:
         self._dev_state[0:1] += 1
 
     def host_state(self):
-        return (list(self._window_len), self.context)
+        return (list(self._window_len), list(self._n_local), self.context, list(self._n_total))
 
     def set_host_state(self, st):
-        self._window_len, self.context = list(st[0]), st[1]
+        self._window_len, self._n_local, self.context, self._n_total = list(st[0]), list(st[1]), st[2], list(st[3])
+
+    def host_state_after_flushes(self, j):
+        """The host state right after the j-th flush from now (None when the zone cannot grow that far)."""
+        add = j * self.interval
+        n_local = [n + (add if self.last else 0) for n in self._n_local]
+        if self.last and self.meta[0] is not None and n_local[0] > self.meta[0][0].shape[3]:
+            return None
+        return ([self.steady_size] * self.layer_num, n_local, self.context, [n + add for n in self._n_total])
 
     def note_replayed_step(self):
-        if self._window_len[0] + 1 > self.window_capacity:
-            raise RuntimeError("update buffer full: the sequence-sharded form has no flush yet")
         self._window_len = [n + 1 for n in self._window_len]
         self.context += 1

@@ -25,10 +25,12 @@ def _oracle_select(scores, indices, k):
     return O.final_topk(scores, indices, k)
 
 
-def _shard_result(O, rank, world, keys, vals, q, signs, cen, coll, cand_ratio, K, counts_global):
+def _shard_result(O, rank, world, keys, vals, q, signs, cen, coll, cand_ratio, K, counts_global, span=None):
+    """One rank's part of the sharded formulation on the CPU; span = (start, end) when the chunks are not the equal
+    split (after flushes the last chunk has grown)."""
     from pariskv_b200 import dist as pkd
     N = keys.shape[2]
-    start, end = pkd.sequence_shard(N, rank, world)
+    start, end = span if span is not None else pkd.sequence_shard(N, rank, world)
     tiers, c_local, k_local = pkd.local_plan(N, world, coll, cand_ratio, K)
     cb, w, pk = O.encode(keys[:, :, start:end].contiguous(), signs)
     H = keys.shape[1]

@@ -57,27 +57,29 @@ def _worker(rank, world, port, tmp):
 
 
 def _cache_check(rank, world, dev, exchange="nccl"):
-    """SequenceShardedCache: load two layers, append two rows, attend; against the oracle on the whole zone."""
+    """SequenceShardedCache: load two layers, decode across one flush of the update buffer (the flushed rows go to the
+    last rank's chunk, the histogram delta is all-reduced), attend; against the oracle's sharded formulation."""
     from oracle import oracle as O
     from pariskv_b200 import dist as pkd
     g = torch.Generator().manual_seed(5)
-    H, N, K, sink, local, interval = 2, 7003, 96, 4, 16, 8
+    H, N0, K, sink, local, interval, steps = 2, 7003, 96, 4, 16, 4, 6
     signs = srht_signs()
     _, cen = O.constants()
-    cache = pkd.SequenceShardedCache(2, H, 8, N, sink, local, interval, K, dev, rank, world,
-                                     srht_sign_vector=signs, exchange=exchange)
-    start, end = pkd.sequence_shard(N, rank, world)
+    cache = pkd.SequenceShardedCache(2, H, 8, N0, sink, local, interval, K, dev, rank, world,
+                                     srht_sign_vector=signs, exchange=exchange, max_new_length=steps)
+    start, end = pkd.sequence_shard(N0, rank, world)
+    spans0 = [pkd.sequence_shard(N0, r, world) for r in range(world)]
     data = []
     for l in range(2):
-        keys = synth_keys(g, 1, H, N)
-        vals = torch.randn(1, H, N, 128, generator=g).to(torch.bfloat16)
+        keys = synth_keys(g, 1, H, N0)                      # the zone: token positions [sink, sink + N0)
+        vals = torch.randn(1, H, N0, 128, generator=g).to(torch.bfloat16)
         wk = torch.randn(1, H, sink + local, 128, generator=g).to(torch.bfloat16)
         wv = torch.randn(1, H, sink + local, 128, generator=g).to(torch.bfloat16)
         cache.load_layer(l, keys[:, :, start:end].contiguous().to(dev), vals[:, :, start:end].contiguous().to(dev),
                          wk.to(dev), wv.to(dev))
-        data.append((keys, vals, wk, wv))
-    assert cache.context == sink + N + local
-    for step in range(2):
+        data.append([keys, vals, wk, wv])
+    assert cache.context == sink + N0 + local
+    for step in range(steps):
         for l in range(2):
             keys, vals, wk, wv = data[l]
             nk = torch.randn(1, 1, H, 128, generator=g).to(torch.bfloat16)
@@ -91,15 +93,25 @@ def _cache_check(rank, world, dev, exchange="nccl"):
             out = cache.compute(qd, l)
             wk = torch.cat([wk, nk.transpose(1, 2)], 2)
             wv = torch.cat([wv, nv.transpose(1, 2)], 2)
-            data[l] = (keys, vals, wk, wv)
+            if wk.shape[2] == sink + local + interval:      # the same flush on the oracle side
+                keys = torch.cat([keys, wk[:, :, sink:sink + interval]], 2)
+                vals = torch.cat([vals, wv[:, :, sink:sink + interval]], 2)
+                wk = torch.cat([wk[:, :, :sink], wk[:, :, sink + interval:]], 2)
+                wv = torch.cat([wv[:, :, :sink], wv[:, :, sink + interval:]], 2)
+            data[l] = [keys, vals, wk, wv]
+            N = keys.shape[2]
+            assert cache.cpu_valid_end[l] == N
+            spans = [(a, b if r < world - 1 else N) for r, (a, b) in enumerate(spans0)]
             counts = O.cluster_counts(O.encode(keys, signs)[0])
-            parts = [_shard_result(O, r, world, keys, vals, q, signs, cen, 0.2, 0.1, K, counts) for r in range(world)]
+            assert torch.equal(cache.counts[l].cpu(), counts)
+            parts = [_shard_result(O, r, world, keys, vals, q, signs, cen, 0.2, 0.1, K, counts, span=spans[r])
+                     for r in range(world)]
             want = O.final_topk(torch.cat([p[0] for p in parts], -1), torch.cat([p[1] for p in parts], -1), K)
-            assert torch.equal(cache.last_topk_indices.cpu(), want)
+            assert torch.equal(cache.last_topk_indices.cpu(), want), (step, l)
             ref = O.attention(q, torch.cat([wk, O.gather(keys, want)], 2), torch.cat([wv, O.gather(vals, want)], 2))
             err = (out.float().cpu() - ref).abs().max().item()
             assert err <= 2e-2, err
-    assert cache.context == sink + N + local + 2
+    assert cache.context == sink + N0 + local + steps and cache.cpu_valid_end == [N0 + interval] * 2
     if cache.px is not None:
         cache.px.check()
 
