@@ -27,7 +27,7 @@ import os
 
 import torch
 
-from .. import ops
+from .. import hostmem, ops
 from .cache import KV_Cache
 
 USE_RABITQ_RERANK = True
@@ -105,9 +105,10 @@ class polar_cache(KV_Cache):
         # address translation of host memory instead of two; with zones of several GB per layer the row fetch of the
         # attention kernel ran 30 % faster on B200 this way.  unified_keys_cpu / unified_values_cpu are the two
         # strided halves, shaped as the reference's separate tensors.
-        if enable_offload:
-            self._store_kv = [torch.zeros(bs, H, self.zone_capacity, 2, 128, dtype=dtype, pin_memory=True)
+        if enable_offload:   # page-locked without the pinned allocator's power-of-two rounding
+            self._store_kv = [hostmem.pinned_empty(bs, H, self.zone_capacity, 2, 128, dtype=dtype)
                               for _ in range(layer_num)]
+            hostmem.release_on_collect(self, list(self._store_kv))
         else:
             self._store_kv = [torch.zeros(bs, H, self.zone_capacity, 2, 128, dtype=dtype, device=dev)
                               for _ in range(layer_num)]

@@ -248,6 +248,9 @@ class SequenceShardedCache:
         self.meta = [None] * layer_num
         self.counts = [None] * layer_num
         self.store_kv = [None] * layer_num
+        self._pinned = []                 # page-locked host tensors; their registrations end with this object
+        from . import hostmem
+        hostmem.release_on_collect(self, self._pinned)
         self.context = 0
         self.last_topk_indices = None
         if store not in ("host", "hbm", "auto"):
@@ -297,7 +300,9 @@ class SequenceShardedCache:
         if self.store == "hbm":
             skv = torch.empty(1, self.kv_head, cap, 2, 128, dtype=torch.bfloat16, device=self.device)
         else:
-            skv = torch.empty(1, self.kv_head, cap, 2, 128, dtype=torch.bfloat16, pin_memory=True)
+            from . import hostmem   # page-locked without the pinned allocator's power-of-two rounding
+            skv = hostmem.pinned_empty(1, self.kv_head, cap, 2, 128, dtype=torch.bfloat16)
+            self._pinned.append(skv)
         skv[:, :, :n_local].copy_(kv, non_blocking=True)
         self.store_kv[layer] = skv
         n = window_keys.shape[2]

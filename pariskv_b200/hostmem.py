@@ -1,0 +1,55 @@
+"""Page-locked host memory of exactly the requested size, backed by transparent huge pages.
+
+torch's pinned-memory allocator rounds every request up to the next power of two: a 4.3 GB K/V store becomes an
+8 GiB allocation, and thirty-two of them no longer fit a 196 GB host.  Here the memory is an anonymous mapping,
+advised to use huge pages, touched, and then registered with the CUDA driver (cudaHostRegister); with unified
+addressing the GPU reads it through the same pointer, exactly like memory from the pinned allocator.  The huge-page
+advice matters: rows fetched by SMs from registered 4 KB pages arrived 12 % slower on B200 than from the pinned
+allocator's memory, from registered huge-page memory as fast.
+
+The registration must end before the memory is unmapped.  The owner of the tensors (a cache object) passes them to
+`release_on_collect(owner, tensors)`: the registrations are dropped when the owner is collected, and the tensors
+are kept alive until then.
+"""
+import mmap
+import weakref
+
+import torch
+
+_HUGE = 2 << 20
+
+
+def pinned_empty(*shape, dtype):
+    """Uninitialised page-locked host tensor; raises RuntimeError when the driver refuses the registration."""
+    numel = 1
+    for s in shape:
+        numel *= int(s)
+    nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+    if nbytes == 0:
+        return torch.empty(*shape, dtype=dtype)
+    mm = mmap.mmap(-1, nbytes + _HUGE)                  # anonymous, private; room to start on a 2 MB boundary
+    if hasattr(mmap, "MADV_HUGEPAGE"):
+        try:
+            mm.madvise(mmap.MADV_HUGEPAGE)
+        except OSError:
+            pass                                         # huge pages are an optimisation, not a requirement
+    raw = torch.frombuffer(mm, dtype=torch.uint8)        # keeps the mapping alive
+    off = (-raw.data_ptr()) % _HUGE
+    flat = raw[off:off + nbytes]
+    flat[::4096] = 0                                     # fault the pages in (as huge pages where the kernel can)
+    err = torch.cuda.cudart().cudaHostRegister(flat.data_ptr(), nbytes, 0)
+    if int(err) != 0:
+        raise RuntimeError(f"cudaHostRegister of {nbytes} bytes failed with CUDA error {int(err)}")
+    return flat.view(dtype).view(*shape)
+
+
+def _release(tensors):
+    for t in tensors:
+        if t.numel():
+            torch.cuda.cudart().cudaHostUnregister(t.data_ptr())
+    tensors.clear()
+
+
+def release_on_collect(owner, tensors):
+    """Unregister `tensors` (a list, kept alive by this call) when `owner` is garbage-collected."""
+    return weakref.finalize(owner, _release, tensors)
