@@ -450,3 +450,38 @@ def test_shard_pack_unpack_owned_merge(ops):
     out = parts[0, :, :, :128].to(torch.bfloat16).unsqueeze(1).contiguous()
     pp = ops.shard_pack_partial(out.cuda(), parts[0, :, :, 128].contiguous().cuda()).cpu()
     assert torch.equal(pp[..., :128], out[:, 0].float()) and torch.equal(pp[..., 128], parts[0, :, :, 128])
+
+
+def test_peer_exchange_wait_runs_out_and_reports():
+    """The flag wait of the peer-memory exchange is bounded: with a flag word that no rank ever publishes the
+    collecting kernel gives up after about a second, raises the status word of the control block and returns —
+    the context stays usable and the host can tell."""
+    import ctypes
+    import time
+    from pariskv_b200 import _lib as L
+    world, bs, H, Kl = 2, 1, 2, 64
+    gather_off, flags_off = 0, world * bs * H * Kl * 16
+    buf = torch.zeros(flags_off + 256, dtype=torch.uint8, device=DEV)        # gather area and flags of "this rank"
+    ctl = torch.zeros(8, dtype=torch.int32, device=DEV)
+    ctl[0] = 1                                                              # exchange 1 was started locally ...
+    buf[flags_off:flags_off + 4] = torch.tensor([1, 0, 0, 0], dtype=torch.uint8, device=DEV)   # ... rank 0 published,
+    scores = torch.empty(bs, H, world * Kl, dtype=torch.float32, device=DEV)                    # rank 1 never does
+    indices = torch.empty(bs, H, world * Kl, dtype=torch.int64, device=DEV)
+    ds, di = L.desc(scores), L.desc(indices)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    rc = L.load().pk_shard_collect_topk(buf.data_ptr(), gather_off, flags_off, ctl.data_ptr(), world, Kl,
+                                        L.ref(ds), L.ref(di), L.stream_ptr(torch.device(DEV)))
+    assert rc == 0
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert int(ctl[2]) == 1, "the expired wait was not reported"
+    assert 0.05 < waited < 20.0, waited
+    # the context is intact: the same call with both flags published returns at once and leaves the status alone
+    ctl[2] = 0
+    buf[flags_off + 4:flags_off + 8] = torch.tensor([1, 0, 0, 0], dtype=torch.uint8, device=DEV)
+    rc = L.load().pk_shard_collect_topk(buf.data_ptr(), gather_off, flags_off, ctl.data_ptr(), world, Kl,
+                                        L.ref(ds), L.ref(di), L.stream_ptr(torch.device(DEV)))
+    torch.cuda.synchronize()
+    assert rc == 0 and int(ctl[2]) == 0
+    assert int(indices.abs().sum()) == 0 and float(scores.abs().sum()) == 0.0   # the zeroed gather area, unpacked
