@@ -123,3 +123,16 @@ def test_owned_rows_split():
     sel = torch.tensor([[[2, 5, 9, 14, 20]]])
     local, n = pkd.owned_rows(sel, 5, 15)
     assert n.tolist() == [[3]] and local[0, 0, :3].tolist() == [0, 4, 9]
+
+
+def test_tier_thresholds_match_the_reference_arithmetic():
+    """ceil(N * collision_ratio * rho) in Python floats, rho in (.05, .15, .30, .50, .75, 1): for N = 32768 and ratio
+    0.2 the reference's own arithmetic (cache_hub/polar_cache.py:1221-1222) gives 328, 984, 1967, 3277, 4916, 6554."""
+    from oracle import oracle as O
+    from pariskv_b200 import dist as pkd
+    want = [328, 984, 1967, 3277, 4916, 6554]
+    assert list(O.tier_counts(32768, 0.2)) == want
+    tiers, c_local, k_local = pkd.local_plan(32768, 1, 0.2, 4096 / 32768, 256)
+    assert tiers == want and c_local == 4096 and k_local == 256
+    # per-shard budgets: ceil of the global candidate count over the ranks, the final K capped by it
+    assert pkd.local_plan(32768, 4, 0.2, 4096 / 32768, 2048)[1:] == (1024, 1024)
