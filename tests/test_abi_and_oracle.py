@@ -151,6 +151,18 @@ def test_library_exports_every_declared_symbol():
     assert lib.pk_retrieve_workspace_bytes(1, 8, 131004, 13101) > 0
 
 
+def test_public_header_is_plain_c():
+    """include/pariskv_b200.h must compile on its own as C and as C++ (no torch types, no CUDA headers)."""
+    import shutil
+    import subprocess
+    hdr = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "pariskv_b200.h")
+    for cc, args in (("gcc", ["-x", "c", "-std=c11"]), ("g++", ["-x", "c++", "-std=c++17"])):
+        if shutil.which(cc) is None:
+            pytest.skip(f"{cc} not installed")
+        r = subprocess.run([cc, "-fsyntax-only", "-Wall", *args, hdr], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+
+
 def test_argument_errors_surface_as_exceptions():
     """Validation runs before any CUDA call, so it can be exercised without a GPU."""
     from pariskv_b200 import _lib
