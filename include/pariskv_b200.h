@@ -59,6 +59,11 @@ int64_t pk_launch_count(void);
 int pk_timing_enable(int on);
 int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages);
 
+/* Process-wide option, no counterpart in the reference: launch the kernels of the decode chain with programmatic
+ * dependent launch (a kernel's prologue may overlap the tail of its predecessor).  Off by default: with the decode
+ * step replayed as a CUDA graph it measured neutral on B200. */
+int pk_set_pdl(int on);
+
 /* ---- (a) key coding ---------------------------------------------------------------------- */
 
 /* SRHT normalise-rotate + 8-bit sign code + 4-bit (sign | 3-bit level) code + fused rerank weight
@@ -245,13 +250,17 @@ int pk_append_kv(const pk_tensor* k_row, const pk_tensor* v_row, const pk_tensor
 /* ---- the whole retrieval chain in one call ------------------------------------------------------- */
 
 /* queries -> final top-K key indices for one layer and one decode step: the body of
- * polar_cache.collision_based_topk_batch (cache_hub/polar_cache.py:1126-1162, :1207-1304).
+ * polar_cache.collision_based_topk_batch (cache_hub/polar_cache.py:1126-1162, :1207-1304), as TWO launches:
+ * (1) query preparation + cluster ranking + tier table + collision count, (2) candidate selection + 4-bit rerank +
+ * final top-K.
  *   codebook / key_block_weight / key_4bit: views of the N searchable keys (as pk_collision_fused /
- *   pk_rerank); cluster_key_counts i32 [bs,H,16,256]; tier_counts host array (6);
+ *   pk_rerank); cluster_key_counts i32 [bs,H,16,256]; tier_counts host array (1..8 thresholds);
  *   C candidates, K final; final_indices i64 [bs,H,K] ascending key index.  K = 0 stops after the rerank
  *   (final_indices may be NULL): the adaptive-k variants rank the C candidates themselves.
  *   Optional outputs (NULL to skip): cand i64 [bs,H,C], scores_f32 f32 [bs,H,C],
- *   q_blocks bf16 [bs,H,16,8], q_norm bf16 [bs,H,1], query_avg bf16 [bs,H,128]. */
+ *   q_blocks bf16 [bs,H,16,8], q_norm bf16 [bs,H,1], query_avg bf16 [bs,H,128].
+ *   workspace: pk_retrieve_workspace_bytes(bs,H,N,C) bytes, device, 256-byte aligned; nothing in it has to be
+ *   cleared by the caller and nothing in it carries over between calls. */
 int64_t pk_retrieve_workspace_bytes(int64_t bs, int64_t H, int64_t N, int64_t C);
 int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, const pk_tensor* mag_centers,
                 const pk_tensor* codebook, const pk_tensor* key_block_weight, const pk_tensor* key_4bit,
@@ -259,6 +268,72 @@ int pk_retrieve(const pk_tensor* queries, const pk_tensor* signs, const pk_tenso
                 int64_t K, const pk_tensor* final_indices, const pk_tensor* cand,
                 const pk_tensor* scores_f32, const pk_tensor* q_blocks, const pk_tensor* q_norm,
                 const pk_tensor* query_avg, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* How the tier thresholds and the candidate count follow from the zone length N: the ratio schedule of
+ * polar_cache._get_adaptive_ratios (cache_hub/polar_cache.py:1113-1124) with the arithmetic of :1221-1222 and
+ * :1239-1240.  Row i applies when N < bound[i] (bounds ascending), the last row otherwise:
+ *   tier t  = ceil(N * collision_ratio[row] * tier_ratio[t])     (IEEE double, left to right, as Python computes it)
+ *   C       = max(1, ceil(N * candidate_ratio[row])) */
+typedef struct pk_zone_schedule {
+  int32_t n_rows;   /* 1..4 */
+  int32_t n_tiers;  /* 1..8 */
+  int64_t bound[3];
+  double candidate_ratio[4];
+  double collision_ratio[4];
+  double tier_ratio[8];
+} pk_zone_schedule;
+
+/* The same chain with the options that the reference, a single-sequence single-GPU cache, does not have.  Fields
+ * left zero / NULL give exactly pk_retrieve.
+ *   kv_len + schedule   per-sample zone lengths read ON THE DEVICE: sample b searches the first kv_len[b] keys of
+ *                       the views (1 <= kv_len[b] <= N; values outside are clamped) with thresholds and candidate
+ *                       count from `schedule`; tier_counts is ignored, C is the row stride of cand / scores_f32
+ *                       and must be >= pk_zone_max_candidates(schedule, N), K an upper bound: sample b gets
+ *                       min(K, its candidates) final indices, reported in n_sel.  One captured launch sequence
+ *                       then serves a zone that grows, and a batch of sequences of different lengths
+ *                       (the reference asserts equal lengths: cache_hub/polar_cache.py:396-403).
+ *   phase / shard_hist  exact selection when the zone is cut into contiguous shards, one per rank: phase 1 runs
+ *                       launch (1) and writes local_hist u32 [bs,H,256] (how many local keys have each count);
+ *                       the caller all-gathers these rank-major into shard_hist [world,bs,H,256]; phase 2 runs
+ *                       launch (2): the threshold count and the tie quota are taken from the SUM of the shards'
+ *                       histograms, ties go to the shards in rank order, so the union of the shards' candidate
+ *                       lists is exactly the single-GPU candidate set.  C is then the GLOBAL candidate count
+ *                       and the row stride; n_cand reports the local count.  tier_counts must come from the
+ *                       global zone length.  phase 0 = both launches, no sharding.
+ *   n_sel  i32 [bs,H]   valid entries of final_indices;  n_cand i32 [bs,H]  valid entries of cand / scores_f32 */
+typedef struct pk_retrieve_args {
+  const pk_tensor* queries;
+  const pk_tensor* signs;
+  const pk_tensor* mag_centers;
+  const pk_tensor* codebook;
+  const pk_tensor* key_block_weight;
+  const pk_tensor* key_4bit;
+  const pk_tensor* cluster_key_counts;
+  const int64_t* tier_counts;
+  int32_t n_tiers;
+  int32_t phase;
+  int64_t C;
+  int64_t K;
+  const pk_tensor* kv_len;
+  const pk_zone_schedule* schedule;
+  const pk_tensor* local_hist;
+  const pk_tensor* shard_hist;
+  int32_t world;
+  int32_t rank;
+  const pk_tensor* final_indices;
+  const pk_tensor* n_sel;
+  const pk_tensor* cand;
+  const pk_tensor* n_cand;
+  const pk_tensor* scores_f32;
+  const pk_tensor* q_blocks;
+  const pk_tensor* q_norm;
+  const pk_tensor* query_avg;
+  void* workspace;
+  int64_t workspace_bytes;
+} pk_retrieve_args;
+int pk_retrieve_ex(const pk_retrieve_args* args, void* stream);
+/* Largest candidate count the schedule gives for any zone length in 1..N. */
+int64_t pk_zone_max_candidates(const pk_zone_schedule* schedule, int64_t N);
 
 /* ---- sequence-sharded form: the glue on either side of the two all-gathers ------------------------- */
 

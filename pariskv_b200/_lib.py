@@ -23,7 +23,25 @@ class PkTensor(ctypes.Structure):
                 ("shape", ctypes.c_int64 * PK_MAX_DIMS), ("stride", ctypes.c_int64 * PK_MAX_DIMS)]
 
 
+class PkZoneSchedule(ctypes.Structure):
+    _fields_ = [("n_rows", ctypes.c_int32), ("n_tiers", ctypes.c_int32), ("bound", ctypes.c_int64 * 3),
+                ("candidate_ratio", ctypes.c_double * 4), ("collision_ratio", ctypes.c_double * 4),
+                ("tier_ratio", ctypes.c_double * 8)]
+
+
 TP = ctypes.POINTER(PkTensor)
+
+
+class PkRetrieveArgs(ctypes.Structure):
+    _fields_ = [("queries", TP), ("signs", TP), ("mag_centers", TP), ("codebook", TP), ("key_block_weight", TP),
+                ("key_4bit", TP), ("cluster_key_counts", TP), ("tier_counts", ctypes.POINTER(ctypes.c_int64)),
+                ("n_tiers", ctypes.c_int32), ("phase", ctypes.c_int32), ("C", ctypes.c_int64), ("K", ctypes.c_int64),
+                ("kv_len", TP), ("schedule", ctypes.POINTER(PkZoneSchedule)), ("local_hist", TP), ("shard_hist", TP),
+                ("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("final_indices", TP), ("n_sel", TP),
+                ("cand", TP), ("n_cand", TP), ("scores_f32", TP), ("q_blocks", TP), ("q_norm", TP),
+                ("query_avg", TP), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64)]
+
+
 _I64, _INT, _F32, _VP = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 _I64P = ctypes.POINTER(ctypes.c_int64)
 _U64 = ctypes.c_uint64
@@ -34,6 +52,7 @@ SIGNATURES = {
     "pk_version": (_INT, []),
     "pk_last_error": (ctypes.c_char_p, []),
     "pk_launch_count": (_I64, []),
+    "pk_set_pdl": (_INT, [_INT]),
     "pk_timing_enable": (_INT, [_INT]),
     "pk_timing_read": (_INT, [ctypes.POINTER(ctypes.c_double), _I64P, _INT]),
     "pk_encode_keys": (_INT, [TP, TP, TP, TP, TP, TP, _VP]),
@@ -58,6 +77,8 @@ SIGNATURES = {
     "pk_retrieve_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
     "pk_retrieve": (_INT, [TP, TP, TP, TP, TP, TP, TP, _I64P, _INT, _I64, _I64, TP, TP, TP, TP, TP, TP, _VP, _I64,
                            _VP]),
+    "pk_retrieve_ex": (_INT, [ctypes.POINTER(PkRetrieveArgs), _VP]),
+    "pk_zone_max_candidates": (_I64, [ctypes.POINTER(PkZoneSchedule), _I64]),
     "pk_shard_pack_topk": (_INT, [TP, TP, TP, _I64, TP, _VP]),
     "pk_shard_unpack_topk": (_INT, [TP, TP, TP, _VP]),
     "pk_shard_owned_rows": (_INT, [TP, _I64, _I64, TP, TP, _VP]),
@@ -109,6 +130,26 @@ def desc(t):
 
 def ref(d):
     return ctypes.byref(d) if d is not None else None
+
+
+def ptr(d):
+    """pk_tensor (or None) -> a typed pointer for a structure field (NULL for None)."""
+    return ctypes.pointer(d) if d is not None else None
+
+
+def zone_schedule(bounds, candidate_ratios, collision_ratios, tier_ratios):
+    """The ratio schedule as the C structure: row i applies to zones shorter than bounds[i], the last row to the rest."""
+    s = PkZoneSchedule()
+    s.n_rows, s.n_tiers = len(candidate_ratios), len(tier_ratios)
+    if len(bounds) != s.n_rows - 1 or len(collision_ratios) != s.n_rows or not 1 <= s.n_rows <= 4 or not 1 <= s.n_tiers <= 8:
+        raise ValueError("schedule: need n-1 bounds for n <= 4 rows and 1..8 tier ratios")
+    for i, b in enumerate(bounds):
+        s.bound[i] = int(b)
+    for i in range(s.n_rows):
+        s.candidate_ratio[i], s.collision_ratio[i] = float(candidate_ratios[i]), float(collision_ratios[i])
+    for i, r in enumerate(tier_ratios):
+        s.tier_ratio[i] = float(r)
+    return s
 
 
 def stream_ptr(device=None):

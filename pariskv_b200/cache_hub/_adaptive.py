@@ -18,14 +18,11 @@ from .polar_cache import polar_cache as _base_cache
 class AdaptiveKCache(_base_cache):
     # (candidate_ratio, collision_ratio) by zone length, adaptive variants
     # (cache_hub/polar_cache_adaptivek_varlen.py:2115-2126)
-    def _get_adaptive_ratios(self, retrieval_len):
-        if retrieval_len < 5000:
-            return 0.5, 0.5
-        if retrieval_len < 10000:
-            return 0.25, 0.3
-        if retrieval_len < 30000:
-            return 0.2, 0.25
-        return 0.05, 0.2
+    def _ratio_rows(self):
+        return [(0.5, 0.5), (0.25, 0.3), (0.2, 0.25), (0.05, 0.2)]
+
+    def _max_selected_rows(self):
+        return max(super()._max_selected_rows(), 4096)   # the adaptive selection may attend up to 4096 rows per head
 
     def _init_adaptive(self, threshold, min_k, max_k, per_head):
         self.adaptive_topk_threshold = float(threshold)
@@ -85,7 +82,7 @@ class AdaptiveKCache(_base_cache):
         _, ex = ops.retrieve(queries, self.srht_diagonal_signs, self._mag_centers,
                              self.codebook_gpu[layer_idx][:, :, :, :N], self.key_block_weight_gpu[layer_idx][:, :, :, :N],
                              self.key_4bit_packed_gpu[layer_idx][:, :, :, :N, :], self.cluster_key_counts_gpu[layer_idx],
-                             tiers, C, 0, want=("cand", "scores_f32", "query_avg"))
+                             tiers, C, 0, want=("cand", "scores_f32", "query_avg"), scratch=self._retrieve_scratch)
         cand, cand_scores = ex["cand"], ex["scores_f32"].to(torch.bfloat16)   # the reference ranks bf16 scores
         # window logits: a small dense product, left to the library as the reference does
         sl_logits = torch.einsum("bhd,bhkd->bhk", ex["query_avg"], wk[:, :, :n_win]).to(torch.float32) * self._attn_scale
@@ -102,5 +99,5 @@ class AdaptiveKCache(_base_cache):
             n_sel = adaptive_k.max().to(torch.int32).expand_as(adaptive_k).contiguous()
         self.last_adaptive = (adaptive_k, topk, n_sel, sl_logits, cand, cand_scores)
         self.last_topk_indices = topk
-        return ops.sparse_attention(queries, wk, wv, n_win, self._store_k[layer_idx], self._store_v[layer_idx], topk,
-                                    n_sel=n_sel)
+        return self._attend(queries, wk, wv, n_win, self._store_k[layer_idx], self._store_v[layer_idx], topk,
+                            n_sel=n_sel)

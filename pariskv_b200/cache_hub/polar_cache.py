@@ -21,17 +21,19 @@ model runtime written for the reference decodes through it unchanged.  The body 
   the oldest ``dynamic_update_interval`` local rows are coded, added to the cluster histogram, copied to the
   zone store on the same stream, and the window slides.
 """
+import ctypes
 import json
 import math
 import os
 
 import torch
 
-from .. import hostmem, ops
+from .. import _lib, hostmem, ops
 from .cache import KV_Cache
 
 USE_RABITQ_RERANK = True
 TIER_RATIOS = (0.05, 0.15, 0.30, 0.50, 0.75, 1.0)  # reference: cache_hub/polar_cache.py:1221
+ZONE_BOUNDS = (5000, 10000, 30000)                 # zone lengths at which the ratios change (:1113-1124)
 
 
 def srht_signs(device, seed=42):
@@ -141,6 +143,32 @@ class polar_cache(KV_Cache):
         self.device_positions = False
         self.context = 0
         self.last_topk_indices = None               # [bs,H,K] of the most recent compute (for inspection)
+        # Scratch of the retrieval chain and of the attention kernel, sized once for the zone's capacity: the
+        # addresses never change, so decode steps captured in CUDA graphs stay valid however the zone grows.
+        self._zone_schedule = _lib.zone_schedule(ZONE_BOUNDS, [r[0] for r in self._ratio_rows()],
+                                                 [r[1] for r in self._ratio_rows()], TIER_RATIOS)
+        c_max = int(_lib.load().pk_zone_max_candidates(ctypes.byref(self._zone_schedule), max(self.zone_capacity, 1)))
+        self._c_max = max(c_max, 1)
+        self._retrieve_scratch = ops.Scratch(dev, ops.retrieve_scratch_bytes(bs, H, max(self.zone_capacity, 1), self._c_max))
+        self._attn_rows_max = self.window_capacity + max(self.final_topk, self._max_selected_rows())
+        self._attn_scratch = ops.Scratch(dev, ops.attention_scratch_bytes(bs, num_heads, self._attn_rows_max))
+
+    def _max_selected_rows(self):
+        """Most zone rows one attention call can be given besides the window: the full-attention regime attends every
+        zone row while the sequence is shorter than the threshold."""
+        return max(self.FULL_ATTENTION_THRESHOLD, self.steady_size + 2 * self.final_topk)
+
+    def _attend(self, queries, wk, wv, n_win, *args, **kw):
+        """ops.sparse_attention on the cache's own scratch (the shared, growable one for an oversized eager call)."""
+        sel = args[2] if len(args) > 2 else kw.get("selected")
+        rows = n_win + (sel.shape[2] if sel is not None else 0)
+        scratch = self._attn_scratch if rows <= self._attn_rows_max else None
+        return ops.sparse_attention(queries, wk, wv, n_win, *args, scratch=scratch, **kw)
+
+    def check_status(self):
+        """Raise if a kernel reported a bounded wait that ran out (a host synchronisation: call it between decode
+        loops, not inside one)."""
+        ops.check_attention_status(self._attn_scratch, self.batch_size, self.num_heads)
 
     # ------------------------------------------------------------------------------------------------
     # prefill
@@ -277,15 +305,17 @@ class polar_cache(KV_Cache):
     # ------------------------------------------------------------------------------------------------
     # attention
     # ------------------------------------------------------------------------------------------------
+    def _ratio_rows(self):
+        """(candidate_ratio, collision_ratio) for zones shorter than ZONE_BOUNDS[i], and for the rest:
+        cache_hub/polar_cache.py:1113-1124."""
+        return [(0.5, 0.5), (0.25, 0.3), (0.2, 0.25), (0.1, 0.2)]
+
     def _get_adaptive_ratios(self, retrieval_len):
-        """(candidate_ratio, collision_ratio) by zone length: cache_hub/polar_cache.py:1113-1124."""
-        if retrieval_len < 5000:
-            return 0.5, 0.5
-        if retrieval_len < 10000:
-            return 0.25, 0.3
-        if retrieval_len < 30000:
-            return 0.2, 0.25
-        return 0.1, 0.2
+        rows = self._ratio_rows()
+        for bound, row in zip(ZONE_BOUNDS, rows):
+            if retrieval_len < bound:
+                return row
+        return rows[-1]
 
     def retrieval_plan(self, N):
         """(tier thresholds, candidate count C, final K) for a zone of N keys
@@ -307,22 +337,22 @@ class polar_cache(KV_Cache):
         full = total < max(self.FULL_ATTENTION_THRESHOLD, self.steady_size + 2 * self.final_topk) or N <= 0
         if full:  # cache_hub/polar_cache.py:1033-1045: attend everything
             if N <= 0:
-                return ops.sparse_attention(queries, wk, wv, n_win)
+                return self._attend(queries, wk, wv, n_win)
             if self._all_rows is None or self._all_rows.shape[-1] < N:
                 self._all_rows = torch.arange(self.zone_capacity, device=self.device).expand(
                     self.batch_size, self.kv_head, -1).contiguous()
             sel = self._all_rows[:, :, :N].contiguous() if N != self._all_rows.shape[-1] else self._all_rows
-            return ops.sparse_attention(queries, wk, wv, n_win, sk, sv, sel)
+            return self._attend(queries, wk, wv, n_win, sk, sv, sel)
         tiers, C, K = self.retrieval_plan(N)
         final, _ = ops.retrieve(queries, self.srht_diagonal_signs, self._mag_centers,
                                 self.codebook_gpu[layer_idx][:, :, :, :N], self.key_block_weight_gpu[layer_idx][:, :, :, :N],
                                 self.key_4bit_packed_gpu[layer_idx][:, :, :, :N, :], self.cluster_key_counts_gpu[layer_idx],
-                                tiers, C, K)
+                                tiers, C, K, scratch=self._retrieve_scratch)
         self.last_topk_indices = final
         if self.device_positions:  # rows = (window length at step start) + this step's row, read on the device
-            return ops.sparse_attention(queries, wk, wv, self.window_capacity, sk, sv, final,
-                                        n_window_dev=self._dev_state[0:1], n_window_add=1)
-        return ops.sparse_attention(queries, wk, wv, n_win, sk, sv, final)
+            return self._attend(queries, wk, wv, self.window_capacity, sk, sv, final,
+                                n_window_dev=self._dev_state[0:1], n_window_add=1)
+        return self._attend(queries, wk, wv, n_win, sk, sv, final)
 
     # ------------------------------------------------------------------------------------------------
     # support for replaying a captured decode step

@@ -80,14 +80,14 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
   const int tid = threadIdx.x;
   const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int64_t bh = (int64_t)b * p.H + h;
+  const unsigned mb = (unsigned)__cvta_generic_to_shared(&mbar);
+  pdl_wait();  // the selected indices and the per-head row counts come from the kernels before this one
   const int64_t n_sel = p.n_sel ? min((int64_t)p.n_sel[bh], p.K) : p.K;
   const int64_t n_window =
       p.n_window_dev ? min(p.n_window, max((int64_t)0, (int64_t)p.n_window_dev[0] + p.n_window_add)) : p.n_window;
   const int64_t n_rows = n_window + n_sel;
   const int64_t r0 = (int64_t)tile * ATT_TILE;
   const int n_tile = (int)max((int64_t)0, min((int64_t)ATT_TILE, n_rows - r0));
-  const unsigned mb = (unsigned)__cvta_generic_to_shared(&mbar);
-  pdl_wait();  // the selected indices come from the top-k kernel
 
   // ---- stage the tile: thread t copies row t/2, K for even t and V for odd t ----
   {
@@ -122,12 +122,15 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
     }
   }
   const int s = tid & 7, grp = tid >> 3;
-  if (!__syncthreads_and(mbar_wait(mb, 0, ATT_WAIT_LIMIT))) {
-    // the copies never completed: report, give them one more bounded chance to land, and leave
+  // The copies never completed: report it, give them one more bounded chance to land, and go on with an EMPTY
+  // tile (partials m = -inf, l = 0), so that this block still arrives on the counter of its (batch, KV head), the
+  // merge runs and the counter returns to zero.  The host must treat a raised status word as fatal.
+  const bool landed = __syncthreads_and(mbar_wait(mb, 0, ATT_WAIT_LIMIT));
+  if (!landed) {
     if (tid == 0) atomicExch(p.status, 1);
     mbar_wait(mb, 0, ATT_WAIT_LIMIT);
-    return;
   }
+  const int n_live = landed ? n_tile : 0;
 
   for (int qg = 0; qg < p.n_qgroups; qg++) {
     const int n_heads = min(ATT_GQ, p.G - qg * ATT_GQ);
@@ -153,7 +156,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
       for (int i = 0; i < 16; i++) o[g][i] = 0.0f;
     }
     for (int i = grp; i < ATT_TILE; i += 16) {  // uniform trip count per warp: shuffles need all lanes
-      const bool live = i < n_tile && s_valid[i];
+      const bool live = i < n_live && s_valid[i];
       float kf[16], vf[16];
       if (live) {
         const uint4* kp = reinterpret_cast<const uint4*>(Ks + i * 128 + 16 * s);
@@ -389,12 +392,12 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
     p.lse = (float*)lse->data;
   }
   cudaStream_t st = (cudaStream_t)stream;
-  static bool attr_done = false;
   constexpr int kSmem = 2 * ATT_TILE * 256 + 16 * ATT_GQ * 128 * 4;
-  if (!attr_done) {
+  static PerDevice smem_attr;  // the opt-in to more than 48 KB of dynamic shared memory is per device
+  if (const unsigned long long bit = first_on_device(smem_attr)) {
     if (cudaFuncSetAttribute(sparse_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
       return check_launch("sparse_attention smem");
-    attr_done = true;
+    mark_on_device(smem_attr, bit);
   }
   dim3 grid((unsigned)n_tiles, (unsigned)H, (unsigned)bs);
   StageTimer tm(ST_ATTENTION, st);

@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(256) rank_kernel(RankParams p) {
 struct CollParams {
   const uint8_t* codes;          // element (b,h,s,k) at codes[b*c_b + h*c_h + s*c_s + k*c_l]
   int64_t c_b, c_h, c_s, c_l;
-  const uint32_t* lut;           // [bs*H][B][64] words = 256 byte entries per subspace
+  const uint32_t* lut;           // [bs*H][B][64] words = 256 byte entries per subspace (FUSED == false)
   int32_t* out_i32;              // [bs*H][N]            (OUT_U8 == false)
   uint8_t* out_u8;               // [bs*H][u8_stride], indexed by virtual key (OUT_U8 == true)
   uint32_t* chunk_hist;          // [bs*H][n_chunks][256] (OUT_U8 == true)
@@ -180,23 +180,64 @@ struct CollParams {
   int H, B;
   int64_t N;                     // keys per head
   int mis;                       // virtual key v = key + mis; loads are 16-byte aligned in v
-  int64_t chunk_keys;            // virtual keys per block (multiple of 4096)
+  int64_t chunk_keys;            // virtual keys per block
+  int64_t n_hist;                // histogram rows per (batch, head) of chunk_hist (chain kernel)
+  ChainQuery q;                  // FUSED == true: the table is built in the block from the query
+  int G;
+  float inv_g;
 };
 
 // byte k (0..3) of w, zero-extended: one PRMT
 __device__ __forceinline__ unsigned byte_of(uint32_t w, int k) { return __byte_perm(w, 0, 0x4440 | k); }
 
+// Sorts the 256 keys of a warp (8 per lane, element index e = 8 * lane + r) into DESCENDING order of e with a
+// bitonic network: exchanges at distance < 8 stay inside a lane, the others are xor shuffles.  Keys are distinct.
+__device__ __forceinline__ void warp_sort_desc_256(unsigned (&v)[8], int lane) {
+#pragma unroll
+  for (int k = 2; k <= 256; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j >= 8) {
+        const int lj = j >> 3;
+        // block direction: "up" blocks end descending; the lower element of a pair keeps the maximum there
+        const bool up = ((lane << 3) & k) == 0;
+        const bool lower = (lane & lj) == 0;
+        const bool take_max = up == lower;
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+          const unsigned o = __shfl_xor_sync(0xffffffffu, v[r], lj);
+          v[r] = take_max ? max(v[r], o) : min(v[r], o);
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+          const int l = r ^ j;
+          if (l > r) {
+            const bool up = ((((lane << 3) | r) & k) == 0);
+            const unsigned a = v[r], b = v[l];
+            const unsigned mx = max(a, b), mn = min(a, b);
+            v[r] = up ? mx : mn;
+            v[l] = up ? mn : mx;
+          }
+        }
+      }
+    }
+  }
+}
+
+// The stand-alone op (tier table from global memory, int32 counts out), 256 threads.
 // LAYOUT 0: plane-major ([.., 16, N], key stride 1): a thread owns 16 consecutive keys.
 // LAYOUT 1: key-major ([.., N, 16], subspace stride 1): a warp owns 512 consecutive keys, lane-strided.
 // LAYOUT 2: any strides, any B <= 32: a thread owns one key at a time.
 template <int LAYOUT, bool OUT_U8>
-__global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
+__global__ void __launch_bounds__(256, 2) collision_kernel(CollParams p) {
   __shared__ __align__(16) uint8_t s_lut[32 * 256];
-  __shared__ unsigned hist[8 * 256];  // eight replicas (lane & 7) cut same-bin collisions inside a warp
+  __shared__ __align__(16) unsigned hist[8 * 256];  // eight replicas (lane & 7) cut same-bin collisions inside a warp
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   unsigned* my_hist = hist + ((lane & 7) << 8);
-  const int64_t Nv = p.N + p.mis;
+  const int64_t N = p.N;
+  const int64_t Nv = N + p.mis;
   const int64_t v_begin = (int64_t)blockIdx.x * p.chunk_keys;
   const int64_t v_end = min(Nv, v_begin + p.chunk_keys);
   const uint8_t* base = p.codes + b * p.c_b + h * p.c_h - p.mis * p.c_l;
@@ -220,8 +261,6 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
   }
   if (OUT_U8)
     for (int i = tid; i < 8 * 256; i += 256) hist[i] = 0;
-  pdl_wait();     // the code loads above do not depend on the ranking kernel; the table below does
-  pdl_trigger();
   {
     const uint4* src = reinterpret_cast<const uint4*>(p.lut + (int64_t)bh * p.B * 64);
     uint4* dst = reinterpret_cast<uint4*>(s_lut);
@@ -253,11 +292,11 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
 #pragma unroll
         for (int k = 0; k < 16; k++) {
           pk4[k >> 2] |= (uint32_t)cnt[k] << (8 * (k & 3));
-          if (live && key0 + k >= 0 && key0 + k < p.N) atomicAdd(&my_hist[cnt[k]], 1u);
+          if (live && key0 + k >= 0 && key0 + k < N) atomicAdd(&my_hist[cnt[k]], 1u);
         }
         if (live) *reinterpret_cast<uint4*>(out8 + v0) = make_uint4(pk4[0], pk4[1], pk4[2], pk4[3]);
       } else if (live) {
-        if (key0 >= 0 && key0 + 16 <= p.N && ((reinterpret_cast<uintptr_t>(out32 + key0) & 15) == 0)) {
+        if (key0 >= 0 && key0 + 16 <= N && ((reinterpret_cast<uintptr_t>(out32 + key0) & 15) == 0)) {
 #pragma unroll
           for (int q = 0; q < 4; q++)
             *reinterpret_cast<int4*>(out32 + key0 + 4 * q) =
@@ -265,7 +304,7 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
         } else {
 #pragma unroll
           for (int k = 0; k < 16; k++)
-            if (key0 + k >= 0 && key0 + k < p.N) out32[key0 + k] = cnt[k];
+            if (key0 + k >= 0 && key0 + k < N) out32[key0 + k] = cnt[k];
         }
       }
     }
@@ -322,6 +361,292 @@ __global__ void __launch_bounds__(256) collision_kernel(CollParams p) {
     for (int r = 0; r < 8; r++) t += hist[r * 256 + tid];
     p.chunk_hist[((int64_t)bh * gridDim.x + blockIdx.x) * 256 + tid] = t;
   }
+}
+
+// ---- the collision kernel of the decode chain -------------------------------------------------------------------
+// 512 threads, one block per SM.  While its first code loads are in flight every block builds the tier table itself:
+// warp 0 prepares the query (group mean, normalise, rotate: 4 dimensions per lane, the arithmetic and the fixed
+// operation order of rotate16 / query_prep_kernel), then warp w ranks the 256 clusters of subspace w by (score
+// descending, id ascending) with a register bitonic sort, takes the exclusive prefix sum of the cluster sizes in
+// that order and writes, per cluster, the number of tiers whose threshold the prefix is below.  Output: one u8 count
+// per virtual key and 256-bin histograms of the counts, one per `hist_keys` keys (two per block when the block covers
+// its chunk in one pass), from which the selection kernel derives thresholds and output offsets.
+constexpr int CC_THREADS = 512;
+constexpr int CC_PASS = 8192;  // keys a block covers per pass: 16 warps x 512
+
+// x: dims [4*lane, 4*lane+4) of the group-mean query (bf16 values as floats); sg: their SRHT signs.
+// Same pairwise trees and butterflies as rotate16, spread over 32 lanes.  Returns the bf16 norm.
+__device__ __forceinline__ float rotate4(float (&x)[4], const float (&sg)[4], int lane) {
+  float t0 = __fadd_rn(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]));
+  float t1 = __fadd_rn(__fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
+  float sum = __fadd_rn(t0, t1);
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, off));
+  const float n = bfround(__fsqrt_rn(sum));
+  const float den = fmaxf(n, bfround(1e-8f));
+#pragma unroll
+  for (int i = 0; i < 4; i++) x[i] = __fmul_rn(bfround(__fdiv_rn(x[i], den)), sg[i]);
+  {  // h = 1, 2 inside the lane
+    float a = x[0], b = x[1], c = x[2], d = x[3];
+    x[0] = __fadd_rn(a, b), x[1] = __fsub_rn(a, b), x[2] = __fadd_rn(c, d), x[3] = __fsub_rn(c, d);
+    a = x[0], b = x[1], c = x[2], d = x[3];
+    x[0] = __fadd_rn(a, c), x[2] = __fsub_rn(a, c), x[1] = __fadd_rn(b, d), x[3] = __fsub_rn(b, d);
+  }
+#pragma unroll
+  for (int bit = 1; bit < 32; bit <<= 1)  // h = 4 .. 64 across lanes
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float pv = __shfl_xor_sync(0xffffffffu, x[i], bit);
+      x[i] = (lane & bit) ? __fsub_rn(pv, x[i]) : __fadd_rn(x[i], pv);
+    }
+#pragma unroll
+  for (int i = 0; i < 4; i++) x[i] = bfround(__fmul_rn(x[i], 0.08838834764831845f));
+  return n;
+}
+
+__device__ __forceinline__ void unpack4(uint2 v, float* out) {
+  out[0] = __uint_as_float(v.x << 16), out[1] = __uint_as_float(v.x & 0xffff0000u);
+  out[2] = __uint_as_float(v.y << 16), out[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+
+template <int LAYOUT>
+__global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollParams p) {
+  __shared__ __align__(16) uint8_t s_lut[16 * 256];
+  // prologue: cluster sizes, 256 words per warp; afterwards: two histograms (one per half of a single-pass chunk) of
+  // eight replicas each (lane & 7 picks the replica, which cuts same-bin collisions inside a warp)
+  __shared__ __align__(16) unsigned hist[16 * 256];
+  __shared__ float s_q[128];
+  __shared__ unsigned s_tiers[9];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const ChainQuery& cq = p.q;
+#ifdef PK_PHASES
+  const bool mk = blockIdx.x == 1 && blockIdx.y == 0;
+#endif
+  PK_MARK(0, mk);
+  if (cq.n_dev) pdl_wait();  // the zone length may have been written by the kernel just before this one
+  const int64_t N = cq.n_dev ? min(max((int64_t)cq.n_dev[b], (int64_t)1), p.N) : p.N;
+  const int64_t Nv = N + p.mis;
+  const int64_t v_begin = (int64_t)blockIdx.x * p.chunk_keys;
+  if (v_begin >= Nv) return;  // beyond this sample's zone (whole block, before any barrier)
+  const int64_t v_end = min(Nv, v_begin + p.chunk_keys);
+  const uint8_t* base = p.codes + b * p.c_b + h * p.c_h - p.mis * p.c_l;
+  uint8_t* out8 = p.out_u8 + (int64_t)bh * p.u8_stride;
+  const int pass_keys = (int)min(p.chunk_keys, (int64_t)CC_PASS);
+  const int tile = pass_keys >> 4;  // keys per warp and pass (LAYOUT 1), a multiple of 32
+  const int kpl = tile >> 5;        // keys per lane and pass, 1..16
+  const bool publish = blockIdx.x == 0;
+
+  // the first batch of code loads is issued before anything else, so their latency overlaps the prologue
+  uint4 r[16];
+  if (LAYOUT == 1) {
+    const int64_t w0 = v_begin + (int64_t)tile * warp;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int64_t v = w0 + 32 * j + lane;
+      r[j] = (j < kpl && v < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + v * 16)) : make_uint4(0, 0, 0, 0);
+    }
+  } else if (LAYOUT == 0) {
+    const int64_t v0 = v_begin + 16 * (int64_t)tid;
+#pragma unroll
+    for (int s = 0; s < 16; s++)
+      r[s] = (16 * tid < pass_keys && v0 < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + s * p.c_s + v0))
+                                                   : make_uint4(0, 0, 0, 0);
+  }
+  pdl_wait();     // the code loads above do not depend on the kernel before this one; the query below does
+  pdl_trigger();
+  PK_MARK(1, mk);
+
+  // ---- prologue: query, cluster ranking, tier table ----
+  {
+    const int sub = warp;
+    unsigned* my = hist + warp * 256;
+    // cluster sizes of this warp's subspace: 8 consecutive clusters per lane
+    const int4* cp = reinterpret_cast<const int4*>(cq.counts + ((int64_t)bh * 16 + sub) * 256 + lane * 8);
+    const int4 c0 = __ldg(cp), c1 = __ldg(cp + 1);
+    if (warp == 0) {
+      const uint16_t* q = cq.queries + ((int64_t)b * cq.Hq + (int64_t)h * p.G) * 128 + 4 * lane;
+      float x[4], sg[4], acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      unpack4(__ldg(reinterpret_cast<const uint2*>(cq.signs + 4 * lane)), sg);
+      for (int g = 0; g < p.G; g++) {  // fp32 sum over the group, g ascending
+        float v[4];
+        unpack4(__ldg(reinterpret_cast<const uint2*>(q + g * 128)), v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[i] = __fadd_rn(acc[i], v[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) x[i] = bfround(__fmul_rn(acc[i], p.inv_g));
+      if (publish && cq.query_avg)
+        *reinterpret_cast<uint2*>(cq.query_avg + (int64_t)bh * 128 + 4 * lane) =
+            make_uint2((uint32_t)f2bf(x[0]) | ((uint32_t)f2bf(x[1]) << 16), (uint32_t)f2bf(x[2]) | ((uint32_t)f2bf(x[3]) << 16));
+      const float n = rotate4(x, sg, lane);
+#pragma unroll
+      for (int i = 0; i < 4; i++) s_q[4 * lane + i] = x[i];
+      if (publish) {
+        *reinterpret_cast<uint2*>(cq.q_blocks + (int64_t)bh * 128 + 4 * lane) =
+            make_uint2((uint32_t)f2bf(x[0]) | ((uint32_t)f2bf(x[1]) << 16), (uint32_t)f2bf(x[2]) | ((uint32_t)f2bf(x[3]) << 16));
+        if (lane == 0) cq.q_norm[bh] = f2bf(n);
+      }
+    }
+    if (tid == 32) {  // thresholds of this sample
+      if (cq.n_dev || cq.n_plan > 0) {
+        unsigned t[8];
+        zone_tiers(cq.sched, cq.n_dev ? (long long)N : cq.n_plan, t);
+        for (int i = 0; i < cq.sched.n_tiers; i++) s_tiers[i] = t[i];
+        s_tiers[8] = (unsigned)cq.sched.n_tiers;
+      } else {
+        for (int i = 0; i < cq.n_tiers; i++) s_tiers[i] = cq.tiers[i];
+        s_tiers[8] = (unsigned)cq.n_tiers;
+      }
+      if (publish && cq.zero_words) cq.zero_words[bh] = 0u;
+    }
+    *reinterpret_cast<int4*>(my + lane * 8) = c0;
+    *reinterpret_cast<int4*>(my + lane * 8 + 4) = c1;
+    __syncthreads();
+    PK_MARK(2, mk);
+    const int n_tiers = (int)s_tiers[8];
+    unsigned tier[8];
+#pragma unroll
+    for (int t = 0; t < 8; t++) tier[t] = t < n_tiers ? s_tiers[t] : 0u;
+    // register r of a lane starts with cluster c = 32 * r + lane: the first five terms of the score (bits 0..4 of c)
+    // are the lane's, the last three (bits 5..7) the register's; the sum is taken in the order j = 0..7
+    float qv[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) qv[j] = s_q[sub * 8 + j];
+    float s5 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 5; j++) s5 = __fadd_rn(s5, ((lane >> j) & 1) ? qv[j] : -qv[j]);
+    unsigned key[8];
+#pragma unroll
+    for (int rr = 0; rr < 8; rr++) {
+      float sc = s5;
+#pragma unroll
+      for (int j = 5; j < 8; j++) sc = __fadd_rn(sc, ((rr >> (j - 5)) & 1) ? qv[j] : -qv[j]);
+      // order of (score descending, id ascending) as one unsigned compare; -0 counts as +0 like a float compare
+      unsigned bits = f2bf(sc);
+      if (bits == 0x8000u) bits = 0u;
+      const unsigned ord = (bits & 0x8000u) ? (~bits & 0xFFFFu) : (bits | 0x8000u);
+      key[rr] = (ord << 8) | (unsigned)(255 - (32 * rr + lane));
+    }
+    warp_sort_desc_256(key, lane);
+    unsigned cnt[8], run = 0;
+#pragma unroll
+    for (int rr = 0; rr < 8; rr++) {
+      cnt[rr] = my[255u - (key[rr] & 255u)];
+      run += cnt[rr];
+    }
+    unsigned incl = run;  // inclusive prefix over lanes
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    unsigned excl = incl - run;
+#pragma unroll
+    for (int rr = 0; rr < 8; rr++) {
+      unsigned wgt = 0;
+#pragma unroll
+      for (int t = 0; t < 8; t++) wgt += (t < n_tiers && excl < tier[t]) ? 1u : 0u;
+      s_lut[sub * 256 + (255u - (key[rr] & 255u))] = (uint8_t)wgt;
+      excl += cnt[rr];
+    }
+    __syncthreads();  // the table is complete and the staging area is free again
+    PK_MARK(3, mk);
+    for (int i = tid; i < 16 * 256; i += CC_THREADS) hist[i] = 0;
+    __syncthreads();
+  }
+  PK_MARK(4, mk);
+
+  // a chunk covered in one pass gets two histograms (its halves), so the selection kernel can run two blocks on it
+  const bool split = p.chunk_keys <= CC_PASS;
+  const int64_t hist_keys = split ? (p.chunk_keys >> 1) : p.chunk_keys;
+  unsigned* hist_rep = hist + ((lane & 7) << 8);
+  if (LAYOUT == 0) {
+    for (int64_t t0 = v_begin; t0 < v_end; t0 += CC_PASS) {  // block-uniform trip count
+      const int64_t v0 = t0 + 16 * (int64_t)tid;
+      const bool live = 16 * tid < pass_keys && v0 < v_end;
+      int cnt[16];
+#pragma unroll
+      for (int k = 0; k < 16; k++) cnt[k] = 0;
+#pragma unroll
+      for (int s = 0; s < 16; s++) {
+        const uint32_t w4[4] = {r[s].x, r[s].y, r[s].z, r[s].w};
+#pragma unroll
+        for (int k = 0; k < 16; k++) cnt[k] += s_lut[s * 256 + byte_of(w4[k >> 2], k & 3)];
+      }
+      const int64_t vn = v0 + CC_PASS;
+      if (16 * tid < pass_keys && vn < v_end) {
+#pragma unroll
+        for (int s = 0; s < 16; s++) r[s] = __ldg(reinterpret_cast<const uint4*>(base + s * p.c_s + vn));
+      }
+      if (live) {
+        const int64_t key0 = v0 - p.mis;
+        unsigned* hh = hist_rep + ((split && v0 - v_begin >= hist_keys) ? 8 * 256 : 0);
+        uint32_t pk4[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+          pk4[k >> 2] |= (uint32_t)cnt[k] << (8 * (k & 3));
+          if (key0 + k >= 0 && key0 + k < N) atomicAdd(&hh[cnt[k]], 1u);
+        }
+        *reinterpret_cast<uint4*>(out8 + v0) = make_uint4(pk4[0], pk4[1], pk4[2], pk4[3]);
+      }
+    }
+  } else if (LAYOUT == 1) {
+    for (int64_t t0 = v_begin; t0 < v_end; t0 += CC_PASS) {
+      const int64_t w0 = t0 + (int64_t)tile * warp;
+      int cnt[16];
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        int c = 0;
+        if (j < kpl) {
+          const uint32_t w4[4] = {r[j].x, r[j].y, r[j].z, r[j].w};
+#pragma unroll
+          for (int s = 0; s < 16; s++) c += s_lut[s * 256 + byte_of(w4[s >> 2], s & 3)];
+        }
+        cnt[j] = c;
+      }
+      const int64_t wn = w0 + CC_PASS;
+      if (wn < v_end) {
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          const int64_t v = wn + 32 * j + lane;
+          r[j] = (j < kpl && v < v_end) ? __ldg(reinterpret_cast<const uint4*>(base + v * 16)) : make_uint4(0, 0, 0, 0);
+        }
+      }
+      unsigned* hh = hist_rep + ((split && w0 - v_begin >= hist_keys) ? 8 * 256 : 0);
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        const int64_t v = w0 + 32 * j + lane;
+        if (j < kpl && v < v_end) {
+          out8[v] = (uint8_t)cnt[j];
+          atomicAdd(&hh[cnt[j]], 1u);
+        }
+      }
+    }
+  } else {
+    for (int64_t v = v_begin + tid; v < v_end; v += CC_THREADS) {
+      const int64_t key = v - p.mis;
+      if (key < 0) continue;
+      int cnt = 0;
+      for (int s = 0; s < 16; s++) cnt += s_lut[s * 256 + base[s * p.c_s + v * p.c_l]];
+      out8[v] = (uint8_t)cnt;
+      atomicAdd(&hist_rep[((split && v - v_begin >= hist_keys) ? 8 * 256 : 0) + cnt], 1u);
+    }
+  }
+  __syncthreads();
+  PK_MARK(5, mk);
+  {
+    const int half = tid >> 8, bin = tid & 255;
+    if (half == 0 || split) {
+      unsigned t = 0;
+#pragma unroll
+      for (int rep = 0; rep < 8; rep++) t += hist[(half * 8 + rep) * 256 + bin];
+      const int64_t row = split ? 2 * (int64_t)blockIdx.x + half : (int64_t)blockIdx.x;
+      if (row < p.n_hist)  // the second half of the last block may lie beyond the zone: it has no row
+        p.chunk_hist[((int64_t)bh * p.n_hist + row) * 256 + bin] = t;
+    }
+  }
+  PK_MARK(6, mk);
 }
 
 // Unfused single-tier op: codes are int32 [bs,H,N,B] contiguous; one thread per key.
@@ -400,20 +725,33 @@ int launch_rank(const uint16_t* queries, const uint16_t* signs, int Hq, int H, u
   return check_launch("rank_clusters");
 }
 
-// Streams the codes of N keys per (batch, head) and writes counts.  counts_u8 / chunk_hist non-null
-// selects the compact internal output (u8 per virtual key + one 256-bin histogram per block).
-int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* out_i32, uint8_t* counts_u8,
-                     int64_t u8_stride, uint32_t* chunk_hist, int* mis_out, int64_t* chunk_keys_out,
-                     int64_t* n_chunks_out, cudaStream_t st) {
+// Launch geometry of the chain's collision kernel: about one block per SM over the whole grid.  A block covers
+// chunk_keys virtual keys: a multiple of 512 up to 8192 (one pass), else a multiple of 8192 up to 32768 (the selection
+// kernel keeps one int per key of a histogram row in shared memory).
+void chain_geometry(int64_t bs_h, int64_t Nv, int64_t* chunk_keys, int64_t* hist_keys, int64_t* n_hist) {
+  int64_t target = (int64_t)sm_count() / (bs_h > 0 ? bs_h : 1);
+  if (target < 1) target = 1;
+  int64_t chunk = (Nv + target - 1) / target;
+  if (chunk < 2048) chunk = 2048;  // every block of the selection kernel reads all histogram rows: keep them few
+  if (chunk <= CC_PASS) {
+    chunk = (chunk + 511) / 512 * 512;
+  } else {
+    chunk = (chunk + CC_PASS - 1) / CC_PASS * CC_PASS;
+    if (chunk > 32768) chunk = 32768;
+  }
+  *chunk_keys = chunk;
+  *hist_keys = chunk <= CC_PASS ? chunk / 2 : chunk;
+  *n_hist = (Nv + *hist_keys - 1) / *hist_keys;
+}
+
+// The stand-alone op: streams the codes of N keys per (batch, head) and writes int32 counts; table from `lut`.
+int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* out_i32, cudaStream_t st) {
   const int64_t bs = codebook->shape[0], H = codebook->shape[1], B = codebook->shape[2], N = codebook->shape[3];
-  CollParams p;
+  CollParams p = {};
   p.codes = (const uint8_t*)codebook->data;
   p.c_b = codebook->stride[0], p.c_h = codebook->stride[1], p.c_s = codebook->stride[2], p.c_l = codebook->stride[3];
   p.lut = lut;
   p.out_i32 = out_i32;
-  p.out_u8 = counts_u8;
-  p.chunk_hist = chunk_hist;
-  p.u8_stride = u8_stride;
   p.H = (int)H, p.B = (int)B, p.N = N;
   const uintptr_t addr = reinterpret_cast<uintptr_t>(p.codes);
   int layout = 2, mis = 0;
@@ -427,23 +765,93 @@ int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* ou
   const int64_t Nv = N + mis;
   p.chunk_keys = collision_chunk_keys(bs * H, Nv);
   const int64_t n_chunks = (Nv + p.chunk_keys - 1) / p.chunk_keys;
-  if (mis_out) *mis_out = mis;
-  if (chunk_keys_out) *chunk_keys_out = p.chunk_keys;
-  if (n_chunks_out) *n_chunks_out = n_chunks;
   dim3 grid((unsigned)n_chunks, (unsigned)(bs * H));
-  const size_t smem = 0;
-  const bool u8 = counts_u8 != nullptr;
   StageTimer tm(ST_COLLISION, st);
-#define PK_LAUNCH_COLL(L, U) launch_chain(collision_kernel<L, U>, grid, dim3(256), smem, st, p)
-  if (layout == 0) {
-    if (u8) PK_LAUNCH_COLL(0, true); else PK_LAUNCH_COLL(0, false);
-  } else if (layout == 1) {
-    if (u8) PK_LAUNCH_COLL(1, true); else PK_LAUNCH_COLL(1, false);
-  } else {
-    if (u8) PK_LAUNCH_COLL(2, true); else PK_LAUNCH_COLL(2, false);
-  }
-#undef PK_LAUNCH_COLL
+  if (layout == 0) collision_kernel<0, false><<<grid, 256, 0, st>>>(p);
+  else if (layout == 1) collision_kernel<1, false><<<grid, 256, 0, st>>>(p);
+  else collision_kernel<2, false><<<grid, 256, 0, st>>>(p);
   return check_launch("collision");
+}
+
+// The decode chain: query preparation, cluster ranking, tier table and the count in one kernel; compact output
+// (u8 per virtual key + 256-bin histograms, one per hist_keys keys).
+int launch_chain_collision(const pk_tensor* codebook, const ChainQuery& cq, uint8_t* counts_u8, int64_t u8_stride,
+                           uint32_t* chunk_hist, int* mis_out, int64_t* hist_keys_out, int64_t* n_hist_out,
+                           cudaStream_t st) {
+  const int64_t bs = codebook->shape[0], H = codebook->shape[1], B = codebook->shape[2], N = codebook->shape[3];
+  if (B != 16) return fail(PK_ERR_ARG, "the fused chain supports 16 subspaces");
+  CollParams p = {};
+  p.codes = (const uint8_t*)codebook->data;
+  p.c_b = codebook->stride[0], p.c_h = codebook->stride[1], p.c_s = codebook->stride[2], p.c_l = codebook->stride[3];
+  p.out_u8 = counts_u8;
+  p.chunk_hist = chunk_hist;
+  p.u8_stride = u8_stride;
+  p.H = (int)H, p.B = 16, p.N = N;
+  p.q = cq;
+  p.G = H > 0 ? cq.Hq / (int)H : 1;
+  p.inv_g = 1.0f / (float)p.G;
+  int layout = 2;
+  p.mis = chain_layout(codebook, &layout);
+  int64_t hist_keys = 0;
+  chain_geometry(bs * H, N + p.mis, &p.chunk_keys, &hist_keys, &p.n_hist);
+  const int64_t n_blocks = (N + p.mis + p.chunk_keys - 1) / p.chunk_keys;
+  if (mis_out) *mis_out = p.mis;
+  if (hist_keys_out) *hist_keys_out = hist_keys;
+  if (n_hist_out) *n_hist_out = p.n_hist;
+  dim3 grid((unsigned)n_blocks, (unsigned)(bs * H));
+  StageTimer tm(ST_COLLISION, st);
+  if (layout == 0) launch_chain(chain_collision_kernel<0>, grid, dim3(CC_THREADS), 0, st, p);
+  else if (layout == 1) launch_chain(chain_collision_kernel<1>, grid, dim3(CC_THREADS), 0, st, p);
+  else launch_chain(chain_collision_kernel<2>, grid, dim3(CC_THREADS), 0, st, p);
+  return check_launch("chain collision");
+}
+
+// Which code path a codebook view takes in the chain kernel (0 plane-major, 1 key-major, 2 generic) and, for the
+// plane-major one, how many bytes its first key lies past a 16-byte boundary.
+int chain_layout(const pk_tensor* codebook, int* layout) {
+  const int64_t c_b = codebook->stride[0], c_h = codebook->stride[1], c_s = codebook->stride[2], c_l = codebook->stride[3];
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(codebook->data);
+  *layout = 2;
+  if (c_l == 1 && c_s % 16 == 0 && c_h % 16 == 0 && c_b % 16 == 0) {
+    *layout = 0;
+    return (int)(addr & 15);
+  }
+  if (c_s == 1 && c_l == 16 && (addr & 15) == 0 && c_h % 16 == 0 && c_b % 16 == 0) *layout = 1;
+  return 0;
+}
+
+namespace {
+// One block per (batch, head): bin `tid` summed over the chunks that hold keys of this sample.
+__global__ void __launch_bounds__(256) hist_reduce_kernel(const uint32_t* __restrict__ chunk_hist, int64_t n_chunks,
+                                                          int64_t chunk_keys, int mis, int H, int64_t N,
+                                                          const int32_t* __restrict__ n_dev,
+                                                          uint32_t* __restrict__ local_hist) {
+  const int64_t bh = blockIdx.x;
+  const int tid = threadIdx.x;
+  pdl_wait();
+  pdl_trigger();
+  const int64_t n = n_dev ? min(max((int64_t)n_dev[bh / H], (int64_t)1), N) : N;
+  const int64_t live = min(n_chunks, (n + mis + chunk_keys - 1) / chunk_keys);
+  const uint32_t* hp = chunk_hist + bh * n_chunks * 256 + tid;
+  unsigned t = 0;
+  int64_t c = 0;
+  for (; c + 8 <= live; c += 8) {
+    unsigned v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __ldg(hp + (c + i) * 256);
+#pragma unroll
+    for (int i = 0; i < 8; i++) t += v[i];
+  }
+  for (; c < live; c++) t += __ldg(hp + c * 256);
+  local_hist[bh * 256 + tid] = t;
+}
+}  // namespace
+
+int launch_hist_reduce(const uint32_t* chunk_hist, int64_t bs_h, int64_t n_chunks, int64_t chunk_keys, int mis, int H,
+                       int64_t N, const int32_t* n_dev, uint32_t* local_hist, cudaStream_t st) {
+  launch_chain(hist_reduce_kernel, dim3((unsigned)bs_h), dim3(256), 0, st, chunk_hist, n_chunks, chunk_keys, mis, H, N,
+               n_dev, local_hist);
+  return check_launch("shard histogram");
 }
 
 }  // namespace pk
@@ -514,7 +922,7 @@ extern "C" int pk_collision_fused(const pk_tensor* sorted_cluster_ids, const pk_
     rc = check_launch("collision table");
   }
   if (rc) return rc;
-  return launch_collision(codebook, lut, (int32_t*)cache_cnt->data, nullptr, 0, nullptr, nullptr, nullptr, nullptr, st);
+  return launch_collision(codebook, lut, (int32_t*)cache_cnt->data, st);
 }
 
 extern "C" int pk_collision(const pk_tensor* sorted_cluster_ids, const pk_tensor* topk_cluster_cnt,
@@ -593,7 +1001,11 @@ extern "C" int64_t pk_collision_fused_static_max_triples(void) { return kStaticT
 extern "C" int pk_collision_fused_static(const pk_tensor* sorted_cluster_ids, const pk_tensor* cluster_key_counts,
                                          const pk_tensor* codebook, const int64_t* tier_counts, int n_tiers,
                                          const pk_tensor* cache_cnt, void* stream) {
-  PK_REQUIRE(codebook != nullptr && codebook->ndim == 4, "codebook must be a 4-D tensor");
+  PK_CHECK_TENSOR(codebook, PK_U8, 4);
+  PK_CHECK_TENSOR(cluster_key_counts, PK_I32, 4);
+  PK_CHECK_TENSOR(cache_cnt, PK_I32, 3);
+  PK_REQUIRE(sorted_cluster_ids && sorted_cluster_ids->data && sorted_cluster_ids->ndim == 4,
+             "sorted_cluster_ids must be a 4-D tensor");
   const int64_t triples = codebook->shape[0] * codebook->shape[1] * codebook->shape[2];
   if (triples * 256 > kStaticTableBytes)
     return fail(PK_ERR_WORKSPACE,
@@ -608,3 +1020,9 @@ extern "C" int pk_collision_fused_static(const pk_tensor* sorted_cluster_ids, co
   return pk_collision_fused(sorted_cluster_ids, cluster_key_counts, codebook, tier_counts, n_tiers, cache_cnt, table,
                             kStaticTableBytes, stream);
 }
+
+#ifdef PK_PHASES
+extern "C" int pk_debug_phases_collision(unsigned long long* out64) {
+  return cudaMemcpyFromSymbol(out64, pk::g_pk_phase, sizeof(unsigned long long) * 64) == cudaSuccess ? PK_OK : PK_ERR_CUDA;
+}
+#endif

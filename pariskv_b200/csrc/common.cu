@@ -57,13 +57,20 @@ StageTimer::~StageTimer() {
   if (b && cudaEventRecord(b, st_) == cudaSuccess) g_spans.push_back({stage_, a_, b});
 }
 
-bool pdl_enabled() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("PK_PDL");
-    on = (e && e[0] == '1') ? 1 : 0;  // off unless asked for: measured neutral when the step is replayed as a graph
-  }
-  return on == 1;
+static std::atomic<int> g_pdl{0};  // off unless asked for: measured neutral when the step is replayed as a graph
+bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+
+static std::mutex g_dev_mu;
+unsigned long long first_on_device(PerDevice& p) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  const unsigned long long bit = 1ull << dev;
+  return (p.done & bit) ? 0ull : bit;
+}
+void mark_on_device(PerDevice& p, unsigned long long bit) {
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  p.done |= bit;
 }
 
 int sm_count() {
@@ -83,6 +90,11 @@ extern "C" {
 int pk_version(void) { return 1; }
 const char* pk_last_error(void) { return pk::g_err; }
 int64_t pk_launch_count(void) { return pk::g_launches.load(std::memory_order_relaxed); }
+
+int pk_set_pdl(int on) {
+  pk::g_pdl.store(on ? 1 : 0, std::memory_order_relaxed);
+  return PK_OK;
+}
 
 int pk_timing_enable(int on) {
   std::lock_guard<std::mutex> lk(pk::g_tmu);

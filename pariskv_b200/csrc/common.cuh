@@ -69,9 +69,18 @@ inline int elem_size(int dtype) {
 // may be scheduled while its predecessor is still running, does the part of its prologue that does not read the
 // predecessor's output, and then blocks in pdl_wait() until the predecessor has completed and flushed.  Every
 // kernel signals pdl_trigger() only AFTER its own pdl_wait(), so completion is transitive along the chain.
-// Without the launch attribute both instructions do nothing.  The attribute is set only when PK_PDL=1 is in the
-// environment: with the decode step replayed as a CUDA graph it measured neutral on B200.
+// Without the launch attribute both instructions do nothing.  The attribute is set only after pk_set_pdl(1):
+// with the decode step replayed as a CUDA graph it measured neutral on B200.
 bool pdl_enabled();
+
+// Per-device "done once" flags for settings that belong to a device (cudaFuncSetAttribute opt-ins): bit d is set
+// once the setting has been applied with device d current.  first_on_device() returns the bit to set, or 0 when
+// the current device already has it.
+struct PerDevice {
+  unsigned long long done = 0;  // guarded by per_device_mutex()
+};
+unsigned long long first_on_device(PerDevice& p);
+void mark_on_device(PerDevice& p, unsigned long long bit);
 
 #ifdef __CUDACC__
 template <typename... KArgs, typename... Args>
@@ -93,6 +102,21 @@ inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block,
 
 // ---- device side ----
 #ifdef __CUDACC__
+#ifdef PK_PHASES
+// Development aid (never part of a normal build): thread 0 of one chosen block stores the global timer at numbered
+// points of a kernel, so the phases of a single block can be laid out on a time line.
+static __device__ unsigned long long g_pk_phase[64];  // one copy per translation unit
+__device__ __forceinline__ void pk_mark(int i, bool on) {
+  if (on && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_pk_phase[i] = t;
+  }
+}
+#define PK_MARK(i, on) pk::pk_mark(i, on)
+#else
+#define PK_MARK(i, on) ((void)0)
+#endif
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -104,63 +104,385 @@ __global__ void __launch_bounds__(RR_THREADS) rerank_kernel(RerankArgs a, uint16
   }
 }
 
-// ---- candidate selection from u8 counts fused with the rerank of the selected keys -----------------
+// ---- candidate selection from u8 counts, rerank of the selected keys and the final top-K, one launch -----------
 // One block per (chunk of keys, batch*head).  The per-chunk histograms written by the collision kernel
-// give every block the global threshold bin, the tie quota and its own output offset, so the candidate
-// list comes out in ascending key order with no atomics and no second pass.
+// give every block the global threshold count, the tie quota and its own output offset, so the candidate
+// list comes out in ascending key order with no atomics and no second pass.  The block that finishes last for a
+// (batch, head) then selects the final top-K of that head's fp32 scores (an arrival counter per head; the scores
+// of the other blocks are read back from L2), so the chain needs no further launch.
 constexpr int SEL_THREADS = 512;  // the first 256 threads own the 256 count bins
+constexpr int FT_BINS = 4096;     // histogram bins of one radix pass of the final selection
+constexpr int FT_KEYS_MAX = 16384;  // scores kept in shared memory by the final selection (the rest is re-read from L2)
 
 struct SelParams {
-  const uint8_t* counts;  // [bs*H][u8_stride], virtual keys
-  int64_t u8_stride;
-  const uint32_t* chunk_hist;  // [bs*H][n_chunks][256]
-  int64_t n_chunks, chunk_keys, N, C;
-  int mis;
-  int64_t* cand_out;   // [bs*H][C]
-  float* scores_f32;   // [bs*H][C]
+  SelectArgs s;
+  int small_cap;  // longest row that the all-in-shared-memory final selection takes (a multiple of 16)
+  int key_cache;  // words of the shared-memory key cache of the general final selection
 };
 
+// ---- final top-K of one (batch, head) by one block ------------------------------------------------------------------
+// Selected set = first K of (score descending, position ascending), emitted as cand[position] in ascending position
+// (positions are ascending key indices).  Two forms: rows that fit the shared-memory cache, and longer ones.
+
+// Block-wide exclusive scan of a packed pair of counters; returns (exclusive prefix, block total).
+template <int NT>
+__device__ __forceinline__ unsigned long long block_scan_excl(unsigned long long mine, unsigned long long* s_scan,
+                                                              unsigned long long* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long sc = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const unsigned long long o = __shfl_up_sync(0xffffffffu, sc, off);
+    if (lane >= off) sc += o;
+  }
+  if (lane == 31) s_scan[warp] = sc;
+  __syncthreads();
+  unsigned long long before = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < NT / 32; w++) {
+    const unsigned long long v = s_scan[w];
+    if (w < warp) before += v;
+    tot += v;
+  }
+  *total = tot;
+  return before + sc - mine;
+}
+
+// Threshold bin of hist[0..nb): the highest bin d with (elements in bins >= d) >= rem.  Result in res[0..2] =
+// (d, elements in higher bins, elements in d); every thread returns after the result is visible.
+template <int NT>
+__device__ __forceinline__ void block_threshold_bin(const unsigned* hist, int nb, unsigned rem, unsigned* s_w, unsigned* res) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int per = nb >= NT ? nb / NT : 1;
+  unsigned mine = 0;
+  if (tid * per < nb)
+    for (int j = 0; j < per; j++) mine += hist[tid * per + j];
+  unsigned suf = mine;  // inclusive suffix sum over threads (higher thread = higher bins)
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const unsigned o = __shfl_down_sync(0xffffffffu, suf, off);
+    if (lane + off < 32) suf += o;
+  }
+  if (lane == 0) s_w[warp] = suf;
+  __syncthreads();
+  unsigned higher_w = 0;
+  for (int w = warp + 1; w < NT / 32; w++) higher_w += s_w[w];
+  const unsigned incl = suf + higher_w, higher = incl - mine;
+  if (mine && higher < rem && incl >= rem) {  // the crossing lies inside this thread's bins
+    unsigned acc = higher;
+    for (int j = per - 1; j >= 0; j--) {
+      const unsigned hv = hist[tid * per + j];
+      if (acc + hv >= rem) {
+        res[0] = (unsigned)(tid * per + j), res[1] = acc, res[2] = hv;
+        break;
+      }
+      acc += hv;
+    }
+  }
+  __syncthreads();
+}
+
+constexpr int FT_TIES = 1024;  // elements of the threshold bin that are ranked among themselves
+
+// Rows of at most `cap` scores, everything in shared memory: one histogram over FT_BINS equal-width VALUE bins between
+// the row's minimum and maximum (a monotone map, and spread out, so shared-memory atomics rarely collide), the
+// threshold bin, then the few elements of that bin ranked among themselves by (key descending, position ascending).
+// Returns false (nothing written) when the threshold bin holds more than FT_TIES elements - a flat row; the caller
+// then uses the general form.  raw: n words, hist: FT_BINS words, flag: n bytes, tie: FT_TIES uint2.
+template <int NT>
+__device__ bool final_select_cached(const float* __restrict__ scores, const int64_t* __restrict__ cand, int n, int K,
+                                    int64_t* __restrict__ out, uint32_t* raw, unsigned* hist, uint8_t* flag, uint2* tie,
+                                    unsigned* s_w, unsigned long long* s_scan) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int NW = NT / 32;
+  float mn = INFINITY, mx = -INFINITY;
+  for (int base = tid; base < n; base += NT * 16) {  // sixteen independent loads in flight per thread
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int i = base + j * NT;
+      v[j] = i < n ? __ldcg(scores + i) : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int i = base + j * NT;
+      if (i < n) {
+        raw[i] = __float_as_uint(v[j]);
+        mn = fminf(mn, v[j]), mx = fmaxf(mx, v[j]);
+      }
+    }
+  }
+  for (int i = tid; i < FT_BINS; i += NT) hist[i] = 0;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  if (lane == 0) s_w[warp] = __float_as_uint(mn), s_w[NW + warp] = __float_as_uint(mx);
+  if (tid == 0) s_w[2 * NW + 3] = 0;  // tie counter
+  __syncthreads();
+  mn = __uint_as_float(s_w[lane < NW ? lane : 0]), mx = __uint_as_float(s_w[NW + (lane < NW ? lane : 0)]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  }
+  float scale = (float)(FT_BINS - 1) / (mx - mn);
+  if (!(scale > 0.0f) || !(scale < INFINITY)) return false;  // flat or non-finite range (the same for every thread)
+  auto bin_of = [&](uint32_t u) -> unsigned {
+    return min((unsigned)(FT_BINS - 1), (unsigned)((__uint_as_float(u) - mn) * scale));
+  };
+  for (int i = tid; i < n; i += NT) atomicAdd(&hist[bin_of(raw[i])], 1u);
+  __syncthreads();
+  block_threshold_bin<NT>(hist, FT_BINS, (unsigned)K, s_w, s_w + 2 * NW);
+  const unsigned T = s_w[2 * NW], above = s_w[2 * NW + 1], in_bin = s_w[2 * NW + 2];
+  if (in_bin > (unsigned)FT_TIES) return false;
+  const unsigned rem = (unsigned)K - above;  // taken from the threshold bin
+  for (int i = tid; i < n; i += NT) {
+    const uint32_t u = raw[i];
+    const unsigned bn = bin_of(u);
+    uint8_t f = bn > T ? 1 : 0;
+    if (bn == T) {
+      f = 2;
+      tie[atomicAdd(&s_w[2 * NW + 3], 1u)] = make_uint2(ord_key(__uint_as_float(u)), (unsigned)i);
+    }
+    flag[i] = f;
+  }
+  __syncthreads();
+  const int n_tie = (int)s_w[2 * NW + 3];
+  for (int t = tid; t < n_tie; t += NT) {
+    const uint2 me = tie[t];
+    unsigned rk = 0;
+    for (int j = 0; j < n_tie; j++) {
+      const uint2 o = tie[j];
+      rk += (o.x > me.x || (o.x == me.x && o.y < me.y)) ? 1u : 0u;
+    }
+    flag[me.y] = rk < rem ? 1 : 0;
+  }
+  __syncthreads();
+  // ordered compaction: a contiguous span of positions per thread, one scan; the selected positions go to a list in
+  // shared memory (over the histogram, K <= FT_BINS), so that the candidate ids are then fetched in one batch
+  const int per = (n + NT - 1) / NT;
+  const int i0 = min(n, tid * per), i1 = min(n, i0 + per);
+  unsigned cnt = 0;
+  for (int i = i0; i < i1; i++) cnt += flag[i];
+  unsigned long long total;
+  unsigned pos = (unsigned)block_scan_excl<NT>((unsigned long long)cnt, s_scan, &total);
+  if (K <= FT_BINS) {
+    unsigned* sel = hist;
+    for (int i = i0; i < i1; i++)
+      if (flag[i]) sel[pos++] = (unsigned)i;
+    __syncthreads();
+    for (int base = tid; base < K; base += NT * 8) {
+      int64_t cv[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) cv[j] = base + j * NT < K ? __ldcg(cand + sel[base + j * NT]) : 0;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (base + j * NT < K) out[base + j * NT] = cv[j];
+    }
+  } else {
+    for (int i = i0; i < i1; i += 8) {  // the candidate ids of up to eight selected positions are fetched together
+      int64_t cv[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) cv[j] = (i + j < i1 && flag[i + j]) ? __ldcg(cand + i + j) : 0;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (i + j < i1 && flag[i + j]) out[pos++] = cv[j];
+    }
+  }
+  return true;
+}
+
+// Any row length: scores are mapped to order-preserving 32-bit keys; radix passes of up to 12 bits, starting at the
+// highest bit in which the keys differ at all, narrow the threshold key down; ties of the full key go to the lowest
+// positions.  keys: shared-memory cache of the first `cap` keys (the rest is re-read from L2); hist: FT_BINS words.
+template <int NT>
+__device__ void final_select_general(const float* __restrict__ scores, const int64_t* __restrict__ cand, int n, int K,
+                                     int64_t* __restrict__ out, uint32_t* keys, int cap, unsigned* hist,
+                                     unsigned* s_w /*[NT/32 * 2 + 4]*/, unsigned long long* s_scan /*[NT/32]*/) {
+  constexpr int NW = NT / 32;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // pass 0: keys into shared memory, range of the keys
+  unsigned kmin = 0xffffffffu, kmax = 0u;
+  for (int base = tid; base < n; base += NT * 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int i = base + j * NT;
+      v[j] = i < n ? __ldcg(scores + i) : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int i = base + j * NT;
+      if (i < n) {
+        const unsigned k = ord_key(v[j]);
+        if (i < cap) keys[i] = k;
+        kmin = min(kmin, k), kmax = max(kmax, k);
+      }
+    }
+  }
+  kmin = __reduce_min_sync(0xffffffffu, kmin);
+  kmax = __reduce_max_sync(0xffffffffu, kmax);
+  if (lane == 0) s_w[warp] = kmin, s_w[NW + warp] = kmax;
+  __syncthreads();
+  kmin = s_w[lane < NW ? lane : 0], kmax = s_w[NW + (lane < NW ? lane : 0)];
+  kmin = __reduce_min_sync(0xffffffffu, kmin);
+  kmax = __reduce_max_sync(0xffffffffu, kmax);
+  __syncthreads();  // s_w is reused below
+  auto key_at = [&](int i) -> unsigned { return i < cap ? keys[i] : ord_key(__ldcg(scores + i)); };
+
+  // bits above the highest differing bit are common to all keys: decided from the start
+  int top = (kmin == kmax) ? -1 : 31 - __clz(kmin ^ kmax);
+  unsigned dm = top >= 31 ? 0u : (top < 0 ? 0xffffffffu : ~((2u << top) - 1u));  // mask of decided bits
+  unsigned prefix = kmax & dm;
+  unsigned rem = (unsigned)K;
+  while (top >= 0) {
+    const int lo = max(top - 11, 0);
+    const int nb = 1 << (top - lo + 1);
+    for (int i = tid; i < nb; i += NT) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n; i += NT) {
+      const unsigned k = key_at(i);
+      if ((k & dm) == prefix) atomicAdd(&hist[(k >> lo) & (unsigned)(nb - 1)], 1u);
+    }
+    __syncthreads();
+    block_threshold_bin<NT>(hist, nb, rem, s_w, s_w + 2 * NW);
+    const unsigned d = s_w[2 * NW], above = s_w[2 * NW + 1], cnt = s_w[2 * NW + 2];
+    __syncthreads();
+    rem -= above;
+    prefix |= d << lo;
+    dm |= (unsigned)(nb - 1) << lo;
+    top = lo - 1;
+    if (cnt == rem) break;  // the whole digit bin is taken
+  }
+  const unsigned quota = rem;  // elements with (key & dm) == prefix that are taken, lowest positions first
+
+  // ordered emission: 16 consecutive positions per thread and round
+  unsigned long long run = 0;  // (selected outright << 32 | ties) before this round
+  for (int base = 0; base < n; base += NT * 16) {
+    const int i0 = base + tid * 16;
+    unsigned gt_mask = 0, eq_mask = 0;
+#pragma unroll
+    for (int q4 = 0; q4 < 4; q4++) {
+      const int i = i0 + 4 * q4;
+      unsigned k4[4];
+      if (i + 4 <= n && i + 4 <= cap) {
+        const uint4 a = *reinterpret_cast<const uint4*>(keys + i);
+        k4[0] = a.x, k4[1] = a.y, k4[2] = a.z, k4[3] = a.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++) k4[j] = i + j < n ? key_at(i + j) : 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const bool ok = i + j < n;
+        const unsigned kh = k4[j] & dm;
+        gt_mask |= (unsigned)(ok && kh > prefix) << (4 * q4 + j);
+        eq_mask |= (unsigned)(ok && kh == prefix) << (4 * q4 + j);
+      }
+    }
+    const unsigned long long mine = ((unsigned long long)__popc(gt_mask) << 32) | (unsigned)__popc(eq_mask);
+    unsigned long long total;
+    const unsigned long long before = run + block_scan_excl<NT>(mine, s_scan, &total);
+    unsigned g = (unsigned)(before >> 32), e = (unsigned)before;
+    // which of my sixteen are taken: everything above the threshold, ties while the quota lasts
+    unsigned take = gt_mask;
+    {
+      unsigned em = eq_mask, ee = e;
+      while (em && ee < quota) {
+        const int j = __ffs(em) - 1;
+        take |= 1u << j;
+        em &= em - 1;
+        ee++;
+      }
+    }
+    unsigned o = g + min(e, quota);
+#pragma unroll
+    for (int h8 = 0; h8 < 2; h8++) {
+      int64_t cv[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) cv[j] = ((take >> (8 * h8 + j)) & 1u) ? __ldcg(cand + i0 + 8 * h8 + j) : 0;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if ((take >> (8 * h8 + j)) & 1u) out[o++] = cv[j];
+    }
+    run += total;
+    __syncthreads();
+  }
+}
+
 template <bool FAST>
-__global__ void __launch_bounds__(SEL_THREADS) select_rerank_kernel(RerankArgs a, SelParams p) {
+__global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kernel(RerankArgs a, SelParams pp) {
   extern __shared__ __align__(16) unsigned char dyn[];
+  const SelectArgs& p = pp.s;
   RerankSmem& sm = *reinterpret_cast<RerankSmem*>(dyn);
   int* list = reinterpret_cast<int*>(dyn + sizeof(RerankSmem));  // selected keys of this chunk, in order
   __shared__ unsigned tot[256], pre[256];
-  __shared__ unsigned s_warp[8];
-  __shared__ unsigned s_misc[4];  // t, quota, gt_before, eq_before
+  __shared__ unsigned s_warp[2 * (SEL_THREADS / 32) + 4];
+  __shared__ unsigned s_misc[8];  // t, quota, gt_base, eq_base, gt_total, last-block flag
   __shared__ unsigned long long s_scan[SEL_THREADS / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t bh = blockIdx.y, chunk = blockIdx.x;
   const int b = (int)(bh / a.H), h = (int)(bh % a.H);
-  rerank_setup(sm, a, bh, tid, SEL_THREADS);  // query blocks: written two kernels back, complete by now
-  pdl_wait();                                   // counts and block histograms come from the collision kernel
+#ifdef PK_PHASES
+  const bool mk = blockIdx.x == 1 && blockIdx.y == 0;
+#endif
+  PK_MARK(0, mk);
+  pdl_wait();  // counts, block histograms, query blocks and the zeroed arrival counters come from the collision kernel
   pdl_trigger();
-  if (tid < 256) {
-    const uint32_t* hp = p.chunk_hist + bh * p.n_chunks * 256 + tid;
+  const int64_t N = p.n_dev ? min(max((int64_t)p.n_dev[b], (int64_t)1), p.N) : p.N;
+  const int64_t Nv = N + p.mis;
+  const int64_t v_begin = chunk * p.chunk_keys;
+  if (v_begin >= Nv) return;  // beyond this sample's zone (whole block, before any barrier)
+  const int64_t v_end = min(Nv, v_begin + p.chunk_keys);
+  const int64_t live_chunks = (Nv + p.chunk_keys - 1) / p.chunk_keys;
+  // candidates wanted over the whole zone (all shards together)
+  const int64_t C_want = p.n_dev ? min((int64_t)zone_candidates(p.sched, N), p.C) : p.C_want;
+  // this block's counts (one 16-byte load per thread and round of the scan below): issued first, needed last
+  const uint8_t* cnt = p.counts_u8 + bh * p.u8_stride;
+  uint4 cnt0 = make_uint4(0, 0, 0, 0);
+  if (v_begin + 16 * (int64_t)tid < v_end) cnt0 = __ldcg(reinterpret_cast<const uint4*>(cnt + v_begin + 16 * (int64_t)tid));
+  rerank_setup(sm, a, bh, tid, SEL_THREADS);
+  // Bin `tid & 255` of the histogram rows: the two halves of the block take alternate rows, sixteen loads in flight
+  // per thread, so a few dozen rows cost one round trip to L2.
+  unsigned g_tot = 0, g_before = 0;  // sharded: bin totals over all shards / over the shards before this one
+  {
+    const int bin = tid & 255, par = tid >> 8;
+    const uint32_t* hp = p.chunk_hist + bh * p.n_chunks * 256 + bin;
     unsigned t = 0, pr = 0;
-    int64_t c = 0;
-    for (; c + 8 <= p.n_chunks; c += 8) {  // eight independent loads in flight
-      unsigned v[8];
+    for (int64_t c0 = par; c0 < live_chunks; c0 += 32) {
+      unsigned v[16];
 #pragma unroll
-      for (int i = 0; i < 8; i++) v[i] = __ldg(hp + (c + i) * 256);
+      for (int i = 0; i < 16; i++) v[i] = (c0 + 2 * i < live_chunks) ? __ldcg(hp + (c0 + 2 * i) * 256) : 0u;
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
+      for (int i = 0; i < 16; i++) {
         t += v[i];
-        if (c + i < chunk) pr += v[i];
+        if (c0 + 2 * i < chunk) pr += v[i];
       }
     }
-    for (; c < p.n_chunks; c++) {
-      const unsigned v = __ldg(hp + c * 256);
-      t += v;
-      if (c < chunk) pr += v;
+    if (par) tot[bin] = t, pre[bin] = pr;
+    __syncthreads();
+    if (!par) {
+      t += tot[bin], pr += pre[bin];
+      tot[bin] = t, pre[bin] = pr;
+      g_tot = t;
+      if (p.shard_hist) {
+        g_tot = 0;
+        const int64_t rows = (int64_t)gridDim.y;  // bs*H
+        for (int r = 0; r < p.world; r++) {
+          const unsigned v = __ldg(p.shard_hist + ((int64_t)r * rows + bh) * 256 + bin);
+          g_tot += v;
+          if (r < p.rank) g_before += v;
+        }
+      }
     }
-    tot[tid] = t;
-    pre[tid] = pr;
   }
-  if (tid < 4) s_misc[tid] = 0;
+  if (tid < 8) s_misc[tid] = 0;
   __syncthreads();
+  PK_MARK(1, mk);
   // threshold bin: suffix sums over 256 bins (8 warps x 32 bins)
-  unsigned v = tid < 256 ? tot[tid] : 0u, incl = v;
+  unsigned v = tid < 256 ? g_tot : 0u, incl = v;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
     unsigned o = __shfl_down_sync(0xffffffffu, incl, off);
@@ -172,29 +494,38 @@ __global__ void __launch_bounds__(SEL_THREADS) select_rerank_kernel(RerankArgs a
     unsigned higher = 0;
     for (int w = warp + 1; w < 8; w++) higher += s_warp[w];
     const unsigned suf = incl + higher, above = suf - v;
-    if (suf >= (unsigned)p.C && above < (unsigned)p.C) {
+    if (suf >= (unsigned)C_want && above < (unsigned)C_want) {
       s_misc[0] = (unsigned)tid;
-      s_misc[1] = (unsigned)p.C - above;
+      // ties of the threshold count taken over the whole zone; a shard takes what the shards before it left
+      const unsigned q_all = (unsigned)C_want - above;
+      const unsigned left = q_all > g_before ? q_all - g_before : 0u;
+      s_misc[1] = p.shard_hist ? min(left, tot[tid]) : q_all;
     }
   }
   __syncthreads();
   const unsigned T = s_misc[0], quota = s_misc[1];
-  if (tid < 256 && (unsigned)tid > T && pre[tid]) atomicAdd(&s_misc[2], pre[tid]);
+  if (tid < 256 && (unsigned)tid > T) {
+    if (pre[tid]) atomicAdd(&s_misc[2], pre[tid]);
+    if (tot[tid]) atomicAdd(&s_misc[4], tot[tid]);
+  }
   if ((unsigned)tid == T) s_misc[3] = pre[tid];
   __syncthreads();
   const unsigned gt_base = s_misc[2], eq_base = s_misc[3];
+  // candidates of this (batch, head) held by this shard
+  const int64_t C_here = min((int64_t)s_misc[4] + (int64_t)min(tot[T], quota), p.C);
 
-  const int64_t Nv = p.N + p.mis;
-  const int64_t v_begin = chunk * p.chunk_keys, v_end = min(Nv, v_begin + p.chunk_keys);
-  const uint8_t* cnt = p.counts + bh * p.u8_stride;
+  PK_MARK(2, mk);
   unsigned gt_run = 0, eq_run = 0;  // running counts over this chunk (all threads hold the same values)
   unsigned n_list = 0;
   for (int64_t t0 = v_begin; t0 < v_end; t0 += 16 * SEL_THREADS) {
     const int64_t v0 = t0 + 16 * (int64_t)tid;
-    uint32_t w4[4] = {0, 0, 0, 0};
-    if (v0 < v_end) {
-      const uint4 r = *reinterpret_cast<const uint4*>(cnt + v0);
-      w4[0] = r.x, w4[1] = r.y, w4[2] = r.z, w4[3] = r.w;
+    uint32_t w4[4] = {cnt0.x, cnt0.y, cnt0.z, cnt0.w};  // first round: loaded at the top of the kernel
+    if (t0 != v_begin) {
+      w4[0] = w4[1] = w4[2] = w4[3] = 0;
+      if (v0 < v_end) {
+        const uint4 r = __ldcg(reinterpret_cast<const uint4*>(cnt + v0));
+        w4[0] = r.x, w4[1] = r.y, w4[2] = r.z, w4[3] = r.w;
+      }
     }
     unsigned gt_mask = 0, eq_mask = 0;
 #pragma unroll
@@ -238,16 +569,54 @@ __global__ void __launch_bounds__(SEL_THREADS) select_rerank_kernel(RerankArgs a
     __syncthreads();
   }
   n_list = gt_run + (min(eq_base + eq_run, quota) - min(eq_base, quota));
-  const int64_t out_base = bh * p.C + gt_base + min(eq_base, quota);
+  PK_MARK(3, mk);
+  const int64_t row_base = bh * p.C;
+  const int64_t out_pos = (int64_t)gt_base + min(eq_base, quota);
   const float qn = bf2f(a.q_norm[bh]);
   const uint8_t* k4 = a.k4 + b * a.k4_b + h * a.k4_h;
   const uint16_t* w = a.w + b * a.w_b + h * a.w_h;
   for (unsigned i = tid; i < n_list; i += SEL_THREADS) {
+    if (out_pos + i >= p.C) break;  // cannot happen with consistent histograms; keeps a bad input inside the row
     const int64_t key = list[i];
     const float s = rerank_one<FAST>(sm, a, k4, w, key, qn, lane, nullptr, 0);
-    p.scores_f32[out_base + i] = s;
-    if (p.cand_out) p.cand_out[out_base + i] = key;
+    p.scores_f32[row_base + out_pos + i] = s;
+    p.cand_out[row_base + out_pos + i] = key;
   }
+  if (chunk == 0 && tid == 0 && p.n_cand_out) p.n_cand_out[bh] = (int32_t)C_here;
+  PK_MARK(4, mk);
+  if (p.K <= 0) return;
+
+  // ---- the block that arrives last for this (batch, head) selects the final top-K ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_misc[5] = atomicAdd(p.counters + bh, 1u) + 1u == (unsigned)live_chunks;
+  __syncthreads();
+  if (!s_misc[5]) return;
+  __threadfence();
+  PK_MARK(8, blockIdx.y == 0);
+  const int K_here = (int)min(p.K, C_here);
+  if (K_here > 0) {
+    // shared memory of the final stage (over the candidate list, no longer needed):
+    // [histogram FT_BINS words | scores / keys | flags | tie list]
+    unsigned* hist = reinterpret_cast<unsigned*>(list);
+    uint32_t* keys = reinterpret_cast<uint32_t*>(list) + FT_BINS;
+    bool done = false;
+    if (C_here <= pp.small_cap) {
+      uint8_t* flag = reinterpret_cast<uint8_t*>(keys + pp.small_cap);
+      uint2* tie = reinterpret_cast<uint2*>(flag + pp.small_cap);
+      done = final_select_cached<SEL_THREADS>(p.scores_f32 + row_base, p.cand_out + row_base, (int)C_here, K_here,
+                                              p.final_out + bh * p.K, keys, hist, flag, tie, s_warp, s_scan);
+      __syncthreads();
+    }
+    if (!done)
+      final_select_general<SEL_THREADS>(p.scores_f32 + row_base, p.cand_out + row_base, (int)C_here, K_here,
+                                        p.final_out + bh * p.K, keys, pp.key_cache, hist, s_warp, s_scan);
+  }
+  if (tid == 0) {
+    if (p.n_sel_out) p.n_sel_out[bh] = K_here;
+    p.counters[bh] = 0;
+  }
+  PK_MARK(15, blockIdx.y == 0);
 }
 
 bool rerank_fast_layout(const RerankArgs& a) {
@@ -287,23 +656,38 @@ int launch_rerank(const RerankArgs& a, int64_t bs_h, uint16_t* scores_bf16, floa
   return check_launch("rerank");
 }
 
-int launch_select_rerank(const RerankArgs& a, int64_t bs_h, const uint8_t* counts_u8, int64_t u8_stride,
-                         const uint32_t* chunk_hist, int64_t n_chunks, int64_t chunk_keys, int mis, int64_t N,
-                         int64_t* cand_out, float* scores_f32, cudaStream_t st) {
+namespace {
+inline int64_t final_small_cap(int64_t C) { return (C < FT_KEYS_MAX ? (C + 15) / 16 * 16 : (int64_t)FT_KEYS_MAX); }
+}  // namespace
+
+int64_t select_final_max_row() { return FT_KEYS_MAX; }
+
+int64_t select_smem_bytes(int64_t chunk_keys, int64_t C, int64_t K) {
+  int64_t body = chunk_keys * (int64_t)sizeof(int);  // the chunk's candidate list
+  if (K > 0) {
+    const int64_t cap = final_small_cap(C);
+    const int64_t ft = ((int64_t)FT_BINS + cap) * 4 + cap + (int64_t)FT_TIES * 8;
+    if (ft > body) body = ft;
+  }
+  return (int64_t)sizeof(RerankSmem) + body;
+}
+
+int launch_select_rerank(const RerankArgs& a, int64_t bs_h, const SelectArgs& sa, cudaStream_t st) {
   SelParams p;
-  p.counts = counts_u8, p.u8_stride = u8_stride, p.chunk_hist = chunk_hist;
-  p.n_chunks = n_chunks, p.chunk_keys = chunk_keys, p.N = N, p.C = a.C, p.mis = mis;
-  p.cand_out = cand_out, p.scores_f32 = scores_f32;
-  const size_t smem = sizeof(RerankSmem) + (size_t)chunk_keys * sizeof(int);
-  dim3 grid((unsigned)n_chunks, (unsigned)bs_h);
+  p.s = sa;
+  const int64_t smem = select_smem_bytes(sa.chunk_keys, sa.C, sa.K);
+  p.small_cap = sa.K > 0 ? (int)final_small_cap(sa.C) : 0;
+  p.key_cache = sa.K > 0 ? (int)((smem - (int64_t)sizeof(RerankSmem)) / 4 - FT_BINS) : 0;
+  if (sa.C >= (1ll << 31) || sa.N >= (1ll << 31)) return fail(PK_ERR_ARG, "zone too long for the selection kernel");
+  dim3 grid((unsigned)sa.n_chunks, (unsigned)bs_h);
   const bool fast = rerank_fast_layout(a);
   auto kern = fast ? select_rerank_kernel<true> : select_rerank_kernel<false>;
-  if (smem > 48 * 1024) {
+  if (smem > 48 * 1024) {  // an opt-in per device: set on every launch that needs it
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return check_launch("select_rerank smem");
   }
   StageTimer tm(ST_SELECT_RERANK, st);
-  launch_chain(kern, grid, dim3(SEL_THREADS), smem, st, a, p);
+  launch_chain(kern, grid, dim3(SEL_THREADS), (size_t)smem, st, a, p);
   return check_launch("select_rerank");
 }
 
@@ -363,3 +747,9 @@ extern "C" int pk_rerank(const pk_tensor* coarse_indices, const pk_tensor* key_4
   a.C = C;
   return launch_rerank(a, bs * H, sbf, s32, v, (cudaStream_t)stream);
 }
+
+#ifdef PK_PHASES
+extern "C" int pk_debug_phases_select(unsigned long long* out64) {
+  return cudaMemcpyFromSymbol(out64, pk::g_pk_phase, sizeof(unsigned long long) * 64) == cudaSuccess ? PK_OK : PK_ERR_CUDA;
+}
+#endif

@@ -10,8 +10,6 @@
 // Selected set: first k of (value descending, index ascending); emitted in ascending index.
 #include <cooperative_groups.h>
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -562,14 +560,15 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
   p.row_stride = row_stride, p.L = L, p.k = k;
   p.out = out, p.map = map, p.map_stride = map_stride;
   p.nseg = 1, p.seg = L, p.out_val = nullptr;
-  static int use_small = -1;
-  if (use_small < 0) {
-    const char* e = getenv("PK_TOPK_SMALL");
-    use_small = (e && atoi(e) == 0) ? 0 : 1;
-    if (use_small && cudaFuncSetAttribute(topk_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TS_SMEM) !=
-                         cudaSuccess) {
+  // dynamic shared memory above 48 KB is an opt-in per kernel AND per device
+  static PerDevice small_attr;
+  bool use_small = true;
+  if (const unsigned long long bit = first_on_device(small_attr)) {
+    if (cudaFuncSetAttribute(topk_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TS_SMEM) == cudaSuccess) {
+      mark_on_device(small_attr, bit);
+    } else {
       cudaGetLastError();
-      use_small = 0;
+      use_small = false;  // this device refuses the opt-in: the cluster kernel below handles every row length
     }
   }
   if (use_small && L <= TS_MAX) {  // short rows: one CTA per row, no cluster barriers
@@ -608,40 +607,21 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
       return check_launch("topk merge");
     }
   }
-  // about 1024 elements per CTA, at most 16 CTAs per row (clusters above 8 need the non-portable opt-in)
+  // about 1024 elements per CTA, at most 8 CTAs per row (the portable cluster size)
   unsigned ncta = 1;
-  static int max_cta = 0;
-  if (max_cta == 0) {
-    const char* e = getenv("PK_TOPK_MAX_CTA");
-    max_cta = e ? atoi(e) : 8;  // measured on B200: 8 CTAs per row is the fastest for rows of ~13 K
-    if (max_cta < 1) max_cta = 1;
-  }
-  while (ncta < 16 && ncta < (unsigned)max_cta && (int64_t)ncta * 1024 < L) ncta <<= 1;
-  static int nonportable = -1;  // -1 unknown, 0 refused, 1 allowed
-  if (ncta > 8) {
-    if (nonportable < 0)
-      nonportable = cudaFuncSetAttribute(topk_cluster_kernel<16>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) ==
-                            cudaSuccess
-                        ? 1
-                        : 0;
-    if (nonportable == 0) {
-      cudaGetLastError();
-      ncta = 8;
-    }
-  }
+  while (ncta < 8 && (int64_t)ncta * 1024 < L) ncta <<= 1;  // measured on B200: 8 CTAs per row is the fastest for rows of ~13 K
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(ncta, (unsigned)rows);
   cfg.blockDim = dim3(TK_THREADS);
   const int64_t slice = (L + ncta - 1) / ncta;
   cfg.dynamicSmemBytes = (size_t)(slice < TK_CACHE ? slice : TK_CACHE) * 4;
-  static bool smem_attr = false;
-  if (!smem_attr) {
+  static PerDevice cluster_attr;
+  if (const unsigned long long bit = first_on_device(cluster_attr)) {
     cudaFuncSetAttribute(topk_cluster_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
     cudaFuncSetAttribute(topk_cluster_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
     cudaFuncSetAttribute(topk_cluster_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
     cudaFuncSetAttribute(topk_cluster_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
-    cudaFuncSetAttribute(topk_cluster_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, TK_CACHE * 4);
-    smem_attr = true;
+    if (cudaGetLastError() == cudaSuccess) mark_on_device(cluster_attr, bit);
   }
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -658,8 +638,7 @@ int launch_topk(const void* in, bool is_float, int64_t rows, int64_t row_stride,
     case 1: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<1>, p); break;
     case 2: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<2>, p); break;
     case 4: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<4>, p); break;
-    case 8: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<8>, p); break;
-    default: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<16>, p); break;
+    default: e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<8>, p); break;
   }
   if (e != cudaSuccess) return fail(PK_ERR_CUDA, "topk launch: %s", cudaGetErrorString(e));
   int rc = check_launch("topk");

@@ -6,6 +6,7 @@ block weights ``[bs,H,16,N]``, packed 4-bit ``[bs,H,16,N,4]``) with any strides.
 here are key-major in memory (``[bs,H,N,16(,4)]``) and returned as permuted views with those shapes;
 that layout turns a rerank candidate into one 64-byte plus one 32-byte record.
 """
+import ctypes
 import math
 
 import torch
@@ -16,14 +17,58 @@ _WS = {}
 
 
 def workspace(device, nbytes, tag="default"):
-    """A cached, growable scratch buffer per (device, tag).  Calls on one stream reuse it safely."""
+    """A cached scratch buffer per (device, tag) for eager calls that do not bring their own.  It grows by
+    replacement, so it must not grow while a CUDA graph is being captured (a graph captured earlier would keep
+    the address of the buffer that was dropped): callers that capture pass a Scratch they own instead."""
     key = (torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device(), tag)
     buf = _WS.get(key)
     if buf is None or buf.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(f"the shared '{tag}' scratch buffer would have to grow to {int(nbytes)} bytes during a "
+                               "stream capture; give the op a Scratch sized before the capture")
         # zero-filled: the attention kernel keeps arrival counters in its workspace header
         buf = torch.zeros(max(int(nbytes), 1 << 16), dtype=torch.uint8, device=device)
         _WS[key] = buf
     return buf
+
+
+class Scratch:
+    """A fixed scratch buffer that its owner sizes once (for the largest problem it will run) and passes to every
+    call: its address never changes, so launches captured in a CUDA graph stay valid for the owner's lifetime.
+    Zero-filled at allocation (the attention kernel's arrival counters live in its header)."""
+
+    def __init__(self, device, nbytes):
+        self.buf = torch.zeros(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+    def take(self, nbytes, what):
+        if self.buf.numel() < nbytes:
+            raise RuntimeError(f"{what}: the owned scratch buffer holds {self.buf.numel()} bytes, {int(nbytes)} needed")
+        return self.buf
+
+
+def _scratch(device, nbytes, tag, scratch):
+    return scratch.take(nbytes, tag) if scratch is not None else workspace(device, nbytes, tag)
+
+
+def retrieve_scratch_bytes(bs, H, N, C):
+    return int(L.load().pk_retrieve_workspace_bytes(int(bs), int(H), int(N), int(C)))
+
+
+def attention_scratch_bytes(bs, Hq, max_rows):
+    return int(L.load().pk_attention_workspace_bytes(int(bs), int(Hq), int(max_rows)))
+
+
+def attention_status(scratch_or_buf, bs, Hq):
+    """The status word of an attention scratch buffer (a host synchronisation: call it outside the decode loop).
+    Non-zero means that a block gave up waiting for its row copies; the results since then are invalid."""
+    buf = scratch_or_buf.buf if isinstance(scratch_or_buf, Scratch) else scratch_or_buf
+    return int(buf[: (bs * Hq + 1) * 4].view(torch.int32)[bs * Hq].item())
+
+
+def check_attention_status(scratch_or_buf, bs, Hq):
+    if attention_status(scratch_or_buf, bs, Hq) != 0:
+        raise RuntimeError("sparse attention: a block gave up waiting for its K/V row copies (status word set); "
+                           "the attention outputs since then are invalid")
 
 
 def _call(name, *args):
@@ -236,7 +281,7 @@ def append_kv(k_row, v_row, window_k, window_v, pos, pos_dev=None, pos_add=0):
 
 
 def sparse_attention(queries, window_k, window_v, n_window, store_k=None, store_v=None, selected=None, n_sel=None,
-                     index_offset=0, scale=None, out=None, n_window_dev=None, n_window_add=0, lse=None):
+                     index_offset=0, scale=None, out=None, n_window_dev=None, n_window_add=0, lse=None, scratch=None):
     """Decode attention over window rows [0, n_window) plus the selected rows of the K/V store (device or
     pinned host memory); see pk_sparse_attention."""
     _require_cuda(queries, window_k, window_v, selected)
@@ -248,7 +293,7 @@ def sparse_attention(queries, window_k, window_v, n_window, store_k=None, store_
         scale = 1.0 / math.sqrt(D)
     K = selected.shape[2] if selected is not None else 0
     nb = L.load().pk_attention_workspace_bytes(bs, Hq, n_window + K)
-    ws = workspace(dev, nb, "attention")
+    ws = _scratch(dev, nb, "attention", scratch)
     d = [L.desc(t) for t in (queries, window_k, window_v, store_k, store_v, selected, n_sel, out, n_window_dev, lse)]
     _call("pk_sparse_attention", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(n_window), L.ref(d[8]), int(n_window_add),
           L.ref(d[3]), L.ref(d[4]), L.ref(d[5]), L.ref(d[6]), int(index_offset), float(scale), L.ref(d[7]), L.ref(d[9]),
@@ -260,7 +305,7 @@ def sparse_attention(queries, window_k, window_v, n_window, store_k=None, store_
 # the fused retrieval chain
 # --------------------------------------------------------------------------------------------------
 def retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, cluster_key_counts, tier_counts,
-             C, K, final_indices=None, want=()):
+             C, K, final_indices=None, want=(), scratch=None):
     """queries -> final top-K key indices (ascending) in one call.  `want` may name extra outputs among
     {"cand", "scores_f32", "q_blocks", "q_norm", "query_avg"}; returns (final_indices, extras dict)."""
     _require_cuda(queries, codebook, key_block_weight, key_4bit, cluster_key_counts)
@@ -280,7 +325,7 @@ def retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, 
     if "query_avg" in want:
         extras["query_avg"] = torch.empty(bs, H, 128, dtype=torch.bfloat16, device=dev)
     nb = L.load().pk_retrieve_workspace_bytes(bs, H, N, C)
-    ws = workspace(dev, nb, "retrieve")
+    ws = _scratch(dev, nb, "retrieve", scratch)
     tiers = L.i64_array(list(tier_counts))
     d = [L.desc(t) for t in (queries, signs, mag_centers, codebook, key_block_weight, key_4bit, cluster_key_counts,
                              final_indices, extras.get("cand"), extras.get("scores_f32"), extras.get("q_blocks"),
@@ -289,6 +334,66 @@ def retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, 
           tiers, len(tier_counts), int(C), int(K), L.ref(d[7]), L.ref(d[8]), L.ref(d[9]), L.ref(d[10]),
           L.ref(d[11]), L.ref(d[12]), ws.data_ptr(), ws.numel(), L.stream_ptr(dev))
     return final_indices, extras
+
+
+def retrieve_ex(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, cluster_key_counts, C, K,
+                tier_counts=None, kv_len=None, schedule=None, phase=0, local_hist=None, shard_hist=None, world=1,
+                rank=0, final_indices=None, n_sel=None, n_cand=None, want=(), outputs=None, scratch=None):
+    """The retrieval chain with per-sample zone lengths read on the device (`kv_len` i32 [bs] + `schedule`, a
+    _lib.zone_schedule) or in its two-phase form for a zone sharded over ranks (phase 1 -> local_hist; phase 2 with
+    the all-gathered shard_hist); see pk_retrieve_ex.  `outputs` may hold preallocated tensors for the names in
+    `want` (reused between the two phases).  Returns (final_indices, n_sel, extras dict)."""
+    _require_cuda(queries, codebook, key_block_weight, key_4bit, cluster_key_counts)
+    bs, H, B, N = codebook.shape
+    dev = codebook.device
+    row = min(int(C), N) if phase else int(C)
+    extras = dict(outputs or {})
+    shapes = {"cand": ((bs, H, row), torch.int64), "scores_f32": ((bs, H, row), torch.float32),
+              "q_blocks": ((bs, H, 16, 8), torch.bfloat16), "q_norm": ((bs, H, 1), torch.bfloat16),
+              "query_avg": ((bs, H, 128), torch.bfloat16)}
+    for name in want:
+        if name not in extras:
+            shape, dt = shapes[name]
+            extras[name] = torch.empty(*shape, dtype=dt, device=dev)
+    if phase != 1:
+        if final_indices is None and K > 0:
+            final_indices = torch.empty(bs, H, K, dtype=torch.int64, device=dev)
+        if n_sel is None and K > 0:
+            n_sel = torch.empty(bs, H, dtype=torch.int32, device=dev)
+        if n_cand is None:
+            n_cand = torch.empty(bs, H, dtype=torch.int32, device=dev)
+    if phase == 1 and local_hist is None:
+        local_hist = torch.empty(bs, H, 256, dtype=torch.int32, device=dev)
+    nb = retrieve_scratch_bytes(bs, H, N, row)
+    ws = _scratch(dev, nb, "retrieve", scratch)
+    a = L.PkRetrieveArgs()
+    keep = []
+
+    def put(field, t):
+        if t is not None:
+            d = L.desc(t)
+            keep.append(d)
+            setattr(a, field, L.ptr(d))
+
+    for field, t in (("queries", queries), ("signs", signs), ("mag_centers", mag_centers), ("codebook", codebook),
+                     ("key_block_weight", key_block_weight), ("key_4bit", key_4bit),
+                     ("cluster_key_counts", cluster_key_counts), ("kv_len", kv_len), ("local_hist", local_hist),
+                     ("shard_hist", shard_hist), ("final_indices", final_indices), ("n_sel", n_sel),
+                     ("cand", extras.get("cand")), ("n_cand", n_cand), ("scores_f32", extras.get("scores_f32")),
+                     ("q_blocks", extras.get("q_blocks")), ("q_norm", extras.get("q_norm")),
+                     ("query_avg", extras.get("query_avg"))):
+        put(field, t)
+    if tier_counts is not None:
+        tiers = L.i64_array(list(tier_counts))
+        a.tier_counts, a.n_tiers = tiers, len(tier_counts)
+    if schedule is not None:
+        a.schedule = ctypes.pointer(schedule)
+    a.phase, a.C, a.K, a.world, a.rank = int(phase), int(C), int(K), int(world), int(rank)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    _call("pk_retrieve_ex", ctypes.byref(a), L.stream_ptr(dev))
+    extras["n_cand"] = n_cand
+    extras["local_hist"] = local_hist
+    return final_indices, n_sel, extras
 
 
 # --------------------------------------------------------------------------------------------------

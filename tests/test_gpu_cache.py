@@ -281,3 +281,84 @@ def test_graphed_decoder_with_precaptured_graphs_matches_eager():
     assert got == eager
     assert runner.captures == captured, "a graph was captured inside the run although all lengths were prepared"
     assert cache.cpu_valid_end[0] == 2600 - 20 + 3 * 8 and cache.context == 2600 + steps
+
+
+def test_first_captured_graph_survives_later_captures_and_unrelated_allocations():
+    """Scratch owned by the cache: the graph captured FIRST is replayed after graphs for longer zones were captured
+    and after a few hundred MB of unrelated tensors were allocated, filled and freed.  Its tokens must be those of
+    eager stepping, and the scratch addresses must not have moved."""
+    import bench
+    cfg = dict(layers=2, hidden=256, q_heads=8, kv_heads=2, head_dim=128, ffn=512, vocab=997, rope_theta=1.0e6,
+               context=2600, sink=4, local=16, interval=8, topk=32)
+    dev = torch.device(DEV)
+    model = bench.DecoderHarness(cfg, dev, seed=6)
+    cache = bench.build_cache(cfg, dev, 80, seed=10)
+    tok = torch.tensor([5], device=dev)
+    eager = []
+    for _ in range(6):
+        tok = model.step(cache, tok)
+        eager.append(int(tok))
+    cache = bench.build_cache(cfg, dev, 80, seed=10)
+    addr = (cache._retrieve_scratch.buf.data_ptr(), cache._attn_scratch.buf.data_ptr())
+    runner = bench.GraphedDecoder(model, cache)
+    tok = torch.tensor([5], device=dev)
+    got = []
+    for _ in range(2):
+        tok = model.step(cache, tok)
+        got.append(int(tok))
+    runner.tok.copy_(tok)
+    runner.precapture(4)                      # graph(N) first, then graph(N + I) ... graph(N + 4 I)
+    junk = [torch.full((64 << 20,), 0x7f, dtype=torch.uint8, device=dev) for _ in range(5)]
+    torch.cuda.synchronize()
+    del junk
+    junk = [torch.full((8 << 20,), 0x55, dtype=torch.uint8, device=dev) for _ in range(24)]
+    torch.cuda.synchronize()
+    del junk
+    for _ in range(4):                        # still before the first flush: these replay the first graph
+        runner.step()
+        got.append(int(runner.nxt))
+    assert got == eager
+    assert addr == (cache._retrieve_scratch.buf.data_ptr(), cache._attn_scratch.buf.data_ptr())
+    cache.check_status()
+
+
+def test_shared_scratch_refuses_to_grow_inside_a_capture():
+    from pariskv_b200 import ops
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        g.capture_begin()
+        try:
+            with pytest.raises(RuntimeError, match="during a stream capture"):
+                ops.workspace(DEV, 1 << 30, "test-capture-growth")
+        finally:
+            g.capture_end()
+    torch.cuda.current_stream().wait_stream(s)
+
+
+def test_attention_status_word_is_read_and_raised(oracle):
+    """The attention kernel reports a copy wait that ran out through a status word in its scratch header.  Nothing is
+    made to time out here: the word is set by hand and the host-side reader must raise; with the word cleared the
+    same cache goes on giving correct results (the arrival counters in the same header were left at zero)."""
+    g = torch.Generator().manual_seed(31)
+    bs, H, Hq, sink, local, I, topk, P = 1, 2, 8, 4, 16, 8, 32, 2300
+    cache = _make_cache(P, 32, bs, H, Hq, sink, local, I, topk, True, 1)
+    K = synth_keys(g, bs, H, P)
+    V = torch.randn(bs, H, P, 128, generator=g).to(torch.bfloat16)
+    cache.prefill_update_kv_cache(None, K.transpose(1, 2).contiguous().to(DEV), V.transpose(1, 2).contiguous().to(DEV), 0, 0)
+    nk = torch.randn(bs, H, 1, 128, generator=g).to(torch.bfloat16)
+    nv = torch.randn(bs, H, 1, 128, generator=g).to(torch.bfloat16)
+    cache.decode_update_kv_cache(nk.transpose(1, 2).contiguous().to(DEV), nv.transpose(1, 2).contiguous().to(DEV), 0)
+    q = torch.randn(bs, 1, Hq, 128, generator=g).to(torch.bfloat16)
+    out = cache.compute(q.to(DEV), 0)
+    cache.check_status()                                          # clean run: no complaint
+    header = cache._attn_scratch.buf[: (bs * Hq + 1) * 4].view(torch.int32)
+    assert int(header[: bs * Hq].abs().sum()) == 0                # every call leaves the counters at zero
+    header[bs * Hq] = 1
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        cache.check_status()
+    header[bs * Hq] = 0
+    out2 = cache.compute(q.to(DEV), 0)
+    assert torch.equal(out, out2)
+    cache.check_status()

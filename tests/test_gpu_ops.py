@@ -485,3 +485,39 @@ def test_peer_exchange_wait_runs_out_and_reports():
     torch.cuda.synchronize()
     assert rc == 0 and int(ctl[2]) == 0
     assert int(indices.abs().sum()) == 0 and float(scores.abs().sum()) == 0.0   # the zeroed gather area, unpacked
+
+
+def test_mirror_rerank_v4b_is_optional_and_correct(ops, oracle):
+    """Documented difference from the reference wrapper (cache_hub/rerank/rerank.py:214-263): the debug tensor v4b
+    is produced only on request.  Without want_v4b the second return value is None; with it the tensor holds the
+    signed magnitude levels of every candidate, the values the reference writes."""
+    from pariskv_b200.cache_hub.rerank.rerank import partial_rerank_cuda
+    g = torch.Generator().manual_seed(3)
+    pk, w, qb, qn = (t.to(DEV) for t in _rerank_inputs(g, 1, 2, 900))
+    cen = oracle.constants()[1].to(DEV)
+    cand = torch.stack([torch.randperm(900, generator=g)[:130].sort().values for _ in range(2)]).view(1, 2, 130).to(DEV)
+    s0, none = partial_rerank_cuda(cand, pk, w, qb, qn, cen, 16, 8)
+    assert none is None
+    s1, v4b = partial_rerank_cuda(cand, pk, w, qb, qn, cen, 16, 8, want_v4b=True)
+    assert torch.equal(s0, s1) and v4b.shape == (1, 2, 16, 130, 8)
+    codes = torch.gather(pk.cpu(), 3, cand.cpu()[:, :, None, :, None].expand(1, 2, 16, 130, 4)).to(torch.int32)
+    nib = torch.stack([codes & 0xF, codes >> 4], -1).view(1, 2, 16, 130, 8)
+    lev = cen.cpu().float()[(nib & 7).long()] * torch.where((nib & 8) != 0, 1.0, -1.0)
+    assert torch.equal(v4b.float().cpu(), lev)
+
+
+def test_mirror_rerank_fused_returns_ascending_indices(ops, oracle):
+    """Documented difference from cache_hub/rerank/rerank.py:266-294: rerank_rabitq_fused returns the final indices in
+    ascending key order (the reference returns them ordered by score); the SET is the top-K by fp32 score."""
+    from pariskv_b200.cache_hub.rerank.rerank import rerank_rabitq_fused
+    g = torch.Generator().manual_seed(4)
+    pk, w, qb, qn = (t.to(DEV) for t in _rerank_inputs(g, 1, 2, 3000))
+    cen = oracle.constants()[1].to(DEV)
+    cnt = torch.randint(0, 97, (1, 2, 3000), generator=g, dtype=torch.int32).to(DEV)
+    fin, sbf, _ = rerank_rabitq_fused(cnt, pk, w, qb, qn, cen, 0.2, 100, 16, 8)
+    assert fin.shape == (1, 2, 100) and bool((fin[..., 1:] > fin[..., :-1]).all())
+    cand = ops.topk(cnt, 600)
+    _, s32 = ops.rerank(cand, pk, w, qb, qn, cen, want_f32=True)
+    for h in range(2):
+        order = sorted(range(600), key=lambda i: (-float(s32[0, h, i]), i))[:100]
+        assert sorted(int(cand[0, h, i]) for i in order) == fin[0, h].tolist()
