@@ -385,6 +385,24 @@ int pk_shard_exchange_partial(const pk_tensor* out, const pk_tensor* lse, const 
 int pk_shard_collect_partial(uint64_t local_base, int64_t gather_offset, int64_t flags_offset, void* control, int world,
                              const pk_tensor* out, void* stream);
 
+/* ---- KV-head-sharded (tensor-parallel) form ------------------------------------------------------------ */
+
+/* With the KV heads split over ranks every stage of the retrieval path is independent per rank: a rank builds its
+ * cache with H / world heads (the reference puts the whole cache on one device, cache_hub/polar_cache.py:171) and no
+ * collective touches the path.  What a tensor-parallel model adds around it is the reduction of its row-parallel
+ * projections; at decode time that is one short vector, and this entry point does it in ONE launch over peer memory:
+ *   out = residual + sum over ranks of partial          (bf16 [1,n] each, fp32 accumulation in rank order, so the
+ *                                                        result is bit-identical on every rank)
+ * Layout of every rank's symmetric buffer (peer_bases[r] as seen from this process): two gather areas of area_bytes
+ * (>= world * n * 2) each, one after the other from gather_offset, used alternately, and `world` u32 flag words at
+ * flags_offset, zero before the first use; `control` = 16 bytes of LOCAL device memory (exchange number, unused,
+ * status, pad), zero before the first use.  All ranks must issue the same sequence of reductions.  The wait is
+ * bounded (about a second); on expiry control[2] becomes 1 and the result is invalid.  One rank per GPU.
+ * No counterpart in the reference. */
+int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residual, const pk_tensor* out,
+                    const uint64_t* peer_bases, int world, int rank, int64_t gather_offset, int64_t area_bytes,
+                    int64_t flags_offset, void* control, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

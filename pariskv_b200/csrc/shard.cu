@@ -219,6 +219,74 @@ __global__ void __launch_bounds__(128) shard_merge_partial_peer_kernel(const flo
   out[(int64_t)row * 128 + d] = __float2bfloat16(den > 0.f ? acc / den : 0.f);
 }
 
+// ---- row-parallel reduce of a tensor-parallel layer over peer memory, one launch ---------------------------------
+// out = residual + sum over ranks of partial, for one short vector (the [1, hidden] output of a row-parallel
+// projection at decode time).  One block: every thread stores its 16 bytes of this rank's partial into slot `rank` of
+// EVERY peer's gather area, the block publishes the exchange number into word `rank` of every peer's flags, waits
+// (bounded) until its own flag words carry that number, then sums the `world` slots of its own area in rank order in
+// fp32, so every rank computes bit-identical results.  Consecutive reductions alternate between two gather areas
+// (exchange number parity): a rank can reach the reduction after the next one only after every peer has published
+// the next one, i.e. has finished reading this one.
+__global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restrict__ partial, const uint4* __restrict__ residual,
+                                                           uint4* __restrict__ out, int n16, PeerSet peers, int64_t gather_off,
+                                                           int64_t area_bytes, int64_t flags_off, int rank, int world,
+                                                           PeerCtl* ctl) {
+  const int tid = threadIdx.x;
+  __shared__ unsigned s_epoch;
+  if (tid == 0) s_epoch = ctl->epoch + 1;
+  __syncthreads();
+  const unsigned epoch = s_epoch;
+  const int64_t area = gather_off + (int64_t)(epoch & 1u) * area_bytes;
+  for (int i = tid; i < n16; i += blockDim.x) {
+    const uint4 v = partial[i];
+    for (int q = 0; q < world; q++)
+      reinterpret_cast<uint4*>(peers.base[q] + area)[(int64_t)rank * n16 + i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    for (int q = 0; q < world; q++) st_release_sys(reinterpret_cast<unsigned*>(peers.base[q] + flags_off) + rank, epoch);
+    ctl->epoch = epoch;
+    const unsigned* flags = reinterpret_cast<const unsigned*>(peers.base[rank] + flags_off);
+    for (int r = 0; r < world; r++) {
+      long long polls = 0;
+      while ((int)(ld_acquire_sys(flags + r) - epoch) < 0) {
+        if (++polls > SHARD_WAIT_POLLS) {
+          atomicExch(&ctl->status, 1u);
+          break;
+        }
+        __nanosleep(100);
+      }
+    }
+  }
+  __syncthreads();
+  const uint4* mine = reinterpret_cast<const uint4*>(peers.base[rank] + area);
+  for (int i = tid; i < n16; i += blockDim.x) {
+    float acc[8];
+    {
+      const uint4 v = residual ? residual[i] : make_uint4(0, 0, 0, 0);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; k++) acc[2 * k] = __uint_as_float(w[k] << 16), acc[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+    for (int r = 0; r < world; r++) {
+      const uint4 v = __ldcg(mine + (int64_t)r * n16 + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        acc[2 * k] = __fadd_rn(acc[2 * k], __uint_as_float(w[k] << 16));
+        acc[2 * k + 1] = __fadd_rn(acc[2 * k + 1], __uint_as_float(w[k] & 0xffff0000u));
+      }
+    }
+    uint4 o;
+    o.x = (uint32_t)f2bf(acc[0]) | ((uint32_t)f2bf(acc[1]) << 16);
+    o.y = (uint32_t)f2bf(acc[2]) | ((uint32_t)f2bf(acc[3]) << 16);
+    o.z = (uint32_t)f2bf(acc[4]) | ((uint32_t)f2bf(acc[5]) << 16);
+    o.w = (uint32_t)f2bf(acc[6]) | ((uint32_t)f2bf(acc[7]) << 16);
+    out[i] = o;
+  }
+}
+
 }  // namespace pk
 
 using namespace pk;
@@ -389,4 +457,32 @@ extern "C" int pk_shard_collect_partial(uint64_t local_base, int64_t gather_offs
       (const float*)(base + gather_offset), (const unsigned*)(base + flags_offset), (PeerCtl*)control,
       (__nv_bfloat16*)out->data, world, (int)(bs * Hq));
   return check_launch("shard_collect_partial");
+}
+
+extern "C" int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residual, const pk_tensor* out,
+                               const uint64_t* peer_bases, int world, int rank, int64_t gather_offset, int64_t area_bytes,
+                               int64_t flags_offset, void* control, void* stream) {
+  PK_CHECK_TENSOR(partial, PK_BF16, 2);
+  PK_CHECK_TENSOR(out, PK_BF16, 2);
+  const int64_t n = numel(partial);
+  PK_REQUIRE(is_contig(partial) && is_contig(out) && numel(out) == n && n >= 8 && n % 8 == 0 && n <= (1 << 20),
+             "partial / out must be contiguous bf16 with the same number of elements, a multiple of 8, at most 2^20");
+  PK_REQUIRE((reinterpret_cast<uintptr_t>(partial->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(out->data) & 15) == 0,
+             "partial / out must be 16-byte aligned");
+  const uint4* res = nullptr;
+  if (residual) {
+    PK_CHECK_TENSOR(residual, PK_BF16, 2);
+    PK_REQUIRE(is_contig(residual) && numel(residual) == n && (reinterpret_cast<uintptr_t>(residual->data) & 15) == 0,
+               "residual must match partial and be 16-byte aligned");
+    res = (const uint4*)residual->data;
+  }
+  PK_REQUIRE(control != nullptr && gather_offset >= 0 && gather_offset % 16 == 0 && flags_offset >= 0 && flags_offset % 4 == 0 &&
+                 area_bytes >= (int64_t)world * n * 2 && area_bytes % 16 == 0,
+             "control block, offsets or area size invalid (one area holds world x n bf16; two areas follow each other)");
+  PeerSet ps;
+  int rc;
+  if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
+  tp_allreduce_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const uint4*)partial->data, res, (uint4*)out->data, (int)(n / 8), ps,
+                                                           gather_offset, area_bytes, flags_offset, rank, world, (PeerCtl*)control);
+  return check_launch("tp_allreduce");
 }

@@ -168,6 +168,56 @@ def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_wei
     return ops.shard_merge_partial(flat2.view(world, bs, Hq, 129)), final
 
 
+class TPReducer:
+    """The reduction of a tensor-parallel model's row-parallel projections at decode time: out = residual + sum over
+    ranks of partial, for bf16 vectors of n elements.  With KV heads split over ranks (head_shard) this is the only
+    exchange the model needs; the retrieval path itself has none.
+
+    mode "peer": one launch over peer memory (pk_tp_allreduce): stores into every peer's symmetric buffer, flag
+    words, fp32 sum in rank order, bit-identical on every rank; no NVLink multicast objects are created.
+    mode "nccl": torch.distributed.all_reduce followed by the residual add.  A single rank needs neither."""
+
+    def __init__(self, n, device, group=None, mode="peer"):
+        self.n, self.device = int(n), device
+        self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
+        self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
+        if mode not in ("peer", "nccl"):
+            raise ValueError("mode must be 'peer' or 'nccl'")
+        self.mode = mode if self.world > 1 else "none"
+        if self.mode == "peer":
+            import os
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+            from . import _lib
+            if self.world > 16:
+                raise ValueError("at most 16 ranks")
+            self.area_bytes = (self.world * self.n * 2 + 255) // 256 * 256
+            self.flags_off = 2 * self.area_bytes
+            self.buf = symm.empty(self.flags_off + 256, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            self.handle = symm.rendezvous(self.buf, self.group.group_name)
+            self.peer_array = _lib.u64_array([int(p) for p in self.handle.buffer_ptrs])
+            self.ctl = torch.zeros(4, dtype=torch.int32, device=device)
+            torch.cuda.synchronize(device)
+            dist.barrier(group=self.group)        # every rank's flags are zero before any store
+
+    def reduce(self, partial, residual):
+        """partial, residual: bf16 [1, n] -> bf16 [1, n], identical on every rank."""
+        if self.mode == "none":
+            return residual + partial
+        if self.mode == "nccl":
+            dist.all_reduce(partial, group=self.group)
+            return residual + partial
+        from . import ops
+        return ops.tp_allreduce(partial.contiguous(), residual.contiguous(), self)
+
+    def check(self):
+        """Raise if a bounded wait ran out (host synchronisation: call it outside the decode loop)."""
+        if self.mode == "peer" and int(self.ctl.cpu()[2]):
+            raise RuntimeError("tensor-parallel reduce: a peer's data did not arrive within the wait limit")
+
+
 class PeerExchange:
     """Symmetric buffers for the two per-layer exchanges of the sequence-sharded form, so that they run as stores
     into peer memory plus flag words instead of two collectives (pk_shard_exchange_* / pk_shard_collect_*).

@@ -487,3 +487,15 @@ def shard_collect_partial(px, bs, Hq):
     _call("pk_shard_collect_partial", px.local_base, px.gather2_off, px.flags2_off, px.ctl.data_ptr() + 16, px.world,
           L.ref(d), L.stream_ptr(px.device))
     return out
+
+
+def tp_allreduce(partial, residual, px, out=None):
+    """out = residual + sum over ranks of partial, one launch over peer memory; px: a dist.TPReducer in peer mode.
+    See pk_tp_allreduce."""
+    _require_cuda(partial, residual)
+    if out is None:
+        out = torch.empty_like(partial)
+    d = [L.desc(t) for t in (partial, residual, out)]
+    _call("pk_tp_allreduce", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), px.peer_array, px.world, px.rank, 0, px.area_bytes,
+          px.flags_off, px.ctl.data_ptr(), L.stream_ptr(partial.device))
+    return out

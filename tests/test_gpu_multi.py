@@ -151,3 +151,73 @@ def test_sequence_sharded_on_two_gpus(tmp_path):
     a = torch.load(os.path.join(tmp_path, "out_0.pt"))
     b = torch.load(os.path.join(tmp_path, "out_1.pt"))
     assert torch.equal(a, b)
+
+
+# ---- KV-head-sharded (tensor-parallel) form ------------------------------------------------------------------------
+def test_head_sharded_caches_reproduce_the_full_cache():
+    """Each of W caches built with H / W KV heads (the tensor-parallel split) must retrieve exactly the indices that
+    the full-width cache retrieves for those heads, and produce the same attention output for their query heads."""
+    from pariskv_b200 import dist as pkd
+    from pariskv_b200.cache_hub.polar_cache import polar_cache
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(12)
+    H, Hq, P, sink, local, I, K = 8, 32, 4200, 4, 16, 8, 64
+    keys = synth_keys(g, 1, H, P)
+    vals = torch.randn(1, H, P, 128, generator=g).to(torch.bfloat16)
+    q = (torch.randn(1, 1, Hq, 128, generator=g) * 0.5).to(torch.bfloat16)
+
+    def run(heads, qheads):
+        c = polar_cache(valid_start=[0], layer_num=1, batch_size=1, max_length=P + 16, num_key_value_heads=heads.stop - heads.start,
+                        num_heads=qheads.stop - qheads.start, head_dim=128, dtype=torch.bfloat16, layer_mapping={"0": dev},
+                        max_new_length=16, sink_size=sink, local_size=local, core=0, nprobe=0, cache_unit_size=0,
+                        cache_cluster_num=0, num_gpus=1, model_size=8, final_topk=K, dynamic_update_interval=I,
+                        enable_offload=True)
+        c.prefill_update_kv_cache(None, keys[:, heads].transpose(1, 2).contiguous().to(dev),
+                                  vals[:, heads].transpose(1, 2).contiguous().to(dev), 0, 0)
+        out = c.compute(q[:, :, qheads].contiguous().to(dev), 0)
+        return c.last_topk_indices.cpu(), out.cpu()
+
+    full_idx, full_out = run(slice(0, H), slice(0, Hq))
+    for world in (2, 8):
+        for r in range(world):
+            hs = pkd.head_shard(H, r, world)
+            qs = slice(hs.start * 4, hs.stop * 4)
+            idx, out = run(hs, qs)
+            assert torch.equal(idx, full_idx[:, hs]), (world, r)
+            assert torch.equal(out, full_out[:, :, qs]), (world, r)
+
+
+def _tp_worker(rank, world, port):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from pariskv_b200.dist import TPReducer
+        for mode in ("peer", "nccl"):
+            red = TPReducer(4096, dev, mode=mode)
+            g = torch.Generator().manual_seed(7)
+            for it in range(60):      # back to back: consecutive reductions alternate between the two gather areas
+                parts = [torch.randn(1, 4096, generator=g).to(torch.bfloat16) for _ in range(world)]
+                res = torch.randn(1, 4096, generator=g).to(torch.bfloat16)
+                want = res.float()
+                for p in parts:
+                    want = want + p.float()
+                got = red.reduce(parts[rank].clone().to(dev), res.to(dev)).float().cpu()
+                if mode == "peer":
+                    assert torch.equal(got, want.to(torch.bfloat16).float()), (mode, it)
+                else:
+                    assert (got - want).abs().max().item() <= 0.25, (mode, it)
+            red.check()
+            torch.cuda.synchronize()
+            dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_reduce_on_two_gpus():
+    mp.spawn(_tp_worker, args=(2, _free_port()), nprocs=2, join=True)
