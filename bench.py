@@ -864,8 +864,8 @@ def seqshard_mode(args, device, rank, world, local_rank):
         dist.all_gather_into_tensor(toks, last)
         agree = bool((toks == toks[0]).all().item())
     if rank == 0:
-        from pariskv_b200.dist import local_plan
-        tiers, c_local, k_local = local_plan(n_total, world, 0.2, 0.1, cfg["topk"])
+        from pariskv_b200.dist import global_plan
+        tiers, c_total, k_final = global_plan(n_total, 0.2, 0.1, cfg["topk"])
         line = {
             "metric": "decode_tokens_per_s", "value": K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -878,7 +878,8 @@ def seqshard_mode(args, device, rank, world, local_rank):
             "clocks": clocks, "gpu_launches": int(launches), "ranks_agree": agree, "exchange": args.exchange,
             "cuda_graph": {"used": use_graph, "captures": runner.captures},
             "setup_s": round(setup_s, 1), "zone_keys_per_head": n_total, "shard_keys_per_head": end - start,
-            "candidates_per_shard": c_local, "local_topk": k_local,
+            "candidates_total": c_total, "final_topk": k_final,
+            "selection": "exact: global threshold count from all-gathered count histograms, ties in rank order",
         }
         if debug:
             line["invalid"] = "debug run with reduced layers/context"

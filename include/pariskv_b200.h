@@ -342,7 +342,9 @@ int64_t pk_zone_max_candidates(const pk_zone_schedule* schedule, int64_t N);
  * contiguous chunk [start, end) of the zone, runs pk_retrieve over it (local indices), and then:
  *   pk_shard_pack_topk     cand i64 [bs,H,C] ascending, scores f32 [bs,H,C], local_final i64 [bs,H,Kl] (a subset
  *                          of cand) -> packed i64 [bs,H,Kl,2] = (fp32 score bits, global index = local + start);
- *                          the host all-gathers `packed` rank-major into [world,bs,H,Kl,2];
+ *                          n_cand / n_sel (i32 [bs,H], or NULL = all) give the valid entries of the cand / local_final
+ *                          rows (the outputs of pk_retrieve_ex phase 2); entries past n_sel become (-inf, -1) and
+ *                          never win the merge; the host all-gathers `packed` rank-major into [world,bs,H,Kl,2];
  *   pk_shard_unpack_topk   gathered -> scores f32 / indices i64 [bs,H,world*Kl], rank-major per row (ascending
  *                          global index, because the chunks are ascending), ready for pk_final_topk;
  *   pk_shard_owned_rows    final i64 [bs,H,K] ascending global -> local i64 [bs,H,K] (the rows inside
@@ -353,7 +355,7 @@ int64_t pk_zone_max_candidates(const pk_zone_schedule* schedule, int64_t N);
  *   pk_shard_merge_partial gathered -> out bf16 [bs,1,Hq,128]: sum_r 2^(lse_r - max) out_r / sum_r 2^(lse_r - max),
  *                          ranks with lse = -inf (no rows) skipped. */
 int pk_shard_pack_topk(const pk_tensor* cand, const pk_tensor* scores, const pk_tensor* local_final, int64_t start,
-                       const pk_tensor* packed, void* stream);
+                       const pk_tensor* n_sel, const pk_tensor* n_cand, const pk_tensor* packed, void* stream);
 int pk_shard_unpack_topk(const pk_tensor* gathered, const pk_tensor* scores, const pk_tensor* indices, void* stream);
 int pk_shard_owned_rows(const pk_tensor* final_indices, int64_t start, int64_t end, const pk_tensor* local,
                         const pk_tensor* n_owned, void* stream);
@@ -376,6 +378,7 @@ int pk_shard_merge_partial(const pk_tensor* gathered, const pk_tensor* out, void
  * order; the two exchanges of a layer use different areas, flags and control blocks.  At most 16 ranks.
  * No counterpart in the reference. */
 int pk_shard_exchange_topk(const pk_tensor* cand, const pk_tensor* scores, const pk_tensor* local_final, int64_t start,
+                           const pk_tensor* n_sel, const pk_tensor* n_cand,
                            const uint64_t* peer_bases, int world, int rank, int64_t gather_offset,
                            int64_t flags_offset, void* control, void* stream);
 int pk_shard_collect_topk(uint64_t local_base, int64_t gather_offset, int64_t flags_offset, void* control, int world,

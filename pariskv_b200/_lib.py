@@ -79,12 +79,12 @@ SIGNATURES = {
                            _VP]),
     "pk_retrieve_ex": (_INT, [ctypes.POINTER(PkRetrieveArgs), _VP]),
     "pk_zone_max_candidates": (_I64, [ctypes.POINTER(PkZoneSchedule), _I64]),
-    "pk_shard_pack_topk": (_INT, [TP, TP, TP, _I64, TP, _VP]),
+    "pk_shard_pack_topk": (_INT, [TP, TP, TP, _I64, TP, TP, TP, _VP]),
     "pk_shard_unpack_topk": (_INT, [TP, TP, TP, _VP]),
     "pk_shard_owned_rows": (_INT, [TP, _I64, _I64, TP, TP, _VP]),
     "pk_shard_pack_partial": (_INT, [TP, TP, TP, _VP]),
     "pk_shard_merge_partial": (_INT, [TP, TP, _VP]),
-    "pk_shard_exchange_topk": (_INT, [TP, TP, TP, _I64, _U64P, _INT, _INT, _I64, _I64, _VP, _VP]),
+    "pk_shard_exchange_topk": (_INT, [TP, TP, TP, _I64, TP, TP, _U64P, _INT, _INT, _I64, _I64, _VP, _VP]),
     "pk_shard_collect_topk": (_INT, [_U64, _I64, _I64, _VP, _INT, _I64, TP, TP, _VP]),
     "pk_shard_exchange_partial": (_INT, [TP, TP, _U64P, _INT, _INT, _I64, _I64, _VP, _VP]),
     "pk_shard_collect_partial": (_INT, [_U64, _I64, _I64, _VP, _INT, TP, _VP]),

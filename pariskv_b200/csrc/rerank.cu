@@ -196,21 +196,39 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int NW = NT / 32;
   float mn = INFINITY, mx = -INFINITY;
-  for (int base = tid; base < n; base += NT * 16) {  // sixteen independent loads in flight per thread
-    float v[16];
+  // The row starts anywhere (its stride may be odd): a few scalar loads up to the first 16-byte boundary, then
+  // 16-byte loads, eight in flight per thread, so a row of 13 K scores is one round trip to L2.
+  const int head = min(n, (int)((4 - ((reinterpret_cast<uintptr_t>(scores) >> 2) & 3)) & 3));
+  if (tid < head) {
+    const float v = __ldcg(scores + tid);
+    raw[tid] = __float_as_uint(v);
+    mn = fminf(mn, v), mx = fmaxf(mx, v);
+  }
+  const float4* s4 = reinterpret_cast<const float4*>(scores + head);
+  const int n4 = (n - head) >> 2;
+  for (int base = tid; base < n4; base += NT * 8) {
+    float4 v[8];
 #pragma unroll
-    for (int j = 0; j < 16; j++) {
+    for (int j = 0; j < 8; j++) {
       const int i = base + j * NT;
-      v[j] = i < n ? __ldcg(scores + i) : 0.0f;
+      v[j] = i < n4 ? __ldcg(s4 + i) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
 #pragma unroll
-    for (int j = 0; j < 16; j++) {
+    for (int j = 0; j < 8; j++) {
       const int i = base + j * NT;
-      if (i < n) {
-        raw[i] = __float_as_uint(v[j]);
-        mn = fminf(mn, v[j]), mx = fmaxf(mx, v[j]);
+      if (i < n4) {
+        uint32_t* r4 = raw + head + 4 * i;
+        r4[0] = __float_as_uint(v[j].x), r4[1] = __float_as_uint(v[j].y);
+        r4[2] = __float_as_uint(v[j].z), r4[3] = __float_as_uint(v[j].w);
+        mn = fminf(fminf(mn, v[j].x), fminf(fminf(v[j].y, v[j].z), v[j].w));
+        mx = fmaxf(fmaxf(mx, v[j].x), fmaxf(fmaxf(v[j].y, v[j].z), v[j].w));
       }
     }
+  }
+  for (int i = head + 4 * n4 + tid; i < n; i += NT) {
+    const float v = __ldcg(scores + i);
+    raw[i] = __float_as_uint(v);
+    mn = fminf(mn, v), mx = fmaxf(mx, v);
   }
   for (int i = tid; i < FT_BINS; i += NT) hist[i] = 0;
 #pragma unroll
@@ -227,6 +245,7 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
     mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
   }
+  PK_MARK(9, blockIdx.y == 0);
   float scale = (float)(FT_BINS - 1) / (mx - mn);
   if (!(scale > 0.0f) || !(scale < INFINITY)) return false;  // flat or non-finite range (the same for every thread)
   auto bin_of = [&](uint32_t u) -> unsigned {
@@ -234,7 +253,9 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
   };
   for (int i = tid; i < n; i += NT) atomicAdd(&hist[bin_of(raw[i])], 1u);
   __syncthreads();
+  PK_MARK(10, blockIdx.y == 0);
   block_threshold_bin<NT>(hist, FT_BINS, (unsigned)K, s_w, s_w + 2 * NW);
+  PK_MARK(11, blockIdx.y == 0);
   const unsigned T = s_w[2 * NW], above = s_w[2 * NW + 1], in_bin = s_w[2 * NW + 2];
   if (in_bin > (unsigned)FT_TIES) return false;
   const unsigned rem = (unsigned)K - above;  // taken from the threshold bin
@@ -249,6 +270,7 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
     flag[i] = f;
   }
   __syncthreads();
+  PK_MARK(12, blockIdx.y == 0);
   const int n_tie = (int)s_w[2 * NW + 3];
   for (int t = tid; t < n_tie; t += NT) {
     const uint2 me = tie[t];
@@ -260,6 +282,7 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
     flag[me.y] = rk < rem ? 1 : 0;
   }
   __syncthreads();
+  PK_MARK(13, blockIdx.y == 0);
   // ordered compaction: a contiguous span of positions per thread, one scan; the selected positions go to a list in
   // shared memory (over the histogram, K <= FT_BINS), so that the candidate ids are then fetched in one batch
   const int per = (n + NT - 1) / NT;
@@ -273,6 +296,7 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
     for (int i = i0; i < i1; i++)
       if (flag[i]) sel[pos++] = (unsigned)i;
     __syncthreads();
+    PK_MARK(14, blockIdx.y == 0);
     for (int base = tid; base < K; base += NT * 8) {
       int64_t cv[8];
 #pragma unroll

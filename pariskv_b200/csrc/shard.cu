@@ -17,21 +17,37 @@ __device__ __forceinline__ int lower_bound_i64(const int64_t* __restrict__ a, in
   return lo;
 }
 
+// One entry of a rank's local top list: (fp32 score bits, global key index), or (-inf, -1) past the row's valid
+// entries.  cand / scores rows have stride C and n_cand[row] (default C) valid entries; local_final rows have n_sel[row]
+// (default Kl) valid entries.
+__device__ __forceinline__ longlong2 shard_entry(const int64_t* __restrict__ cand, const float* __restrict__ scores,
+                                                 const int64_t* __restrict__ local_final, const int32_t* __restrict__ n_sel,
+                                                 const int32_t* __restrict__ n_cand, int row, int j, int C, int Kl, int64_t start) {
+  longlong2 v;
+  v.x = (int64_t)__float_as_int(-INFINITY);
+  v.y = -1;
+  const int valid = n_sel ? min(max(n_sel[row], 0), Kl) : Kl;
+  const int nc = n_cand ? min(max(n_cand[row], 0), C) : C;
+  if (j < valid && nc > 0) {
+    const int64_t idx = local_final[(int64_t)row * Kl + j];
+    int p = lower_bound_i64(cand + (int64_t)row * C, nc, idx);
+    if (p >= nc) p = nc - 1;
+    v.x = (int64_t)__float_as_int(scores[(int64_t)row * C + p]);
+    v.y = idx + start;
+  }
+  return v;
+}
+
 // packed[row][j] = (score bits of local_final[row][j] as int64, local_final[row][j] + start)
 __global__ void __launch_bounds__(256) shard_pack_kernel(const int64_t* __restrict__ cand, const float* __restrict__ scores,
                                                          const int64_t* __restrict__ local_final, int64_t* __restrict__ packed,
-                                                         int C, int Kl, int64_t start) {
+                                                         int C, int Kl, int64_t start, const int32_t* __restrict__ n_sel,
+                                                         const int32_t* __restrict__ n_cand) {
   const int row = blockIdx.y;
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= Kl) return;
-  const int64_t idx = local_final[(int64_t)row * Kl + j];
-  const int64_t* c = cand + (int64_t)row * C;
-  int p = lower_bound_i64(c, C, idx);
-  if (p >= C) p = C - 1;
-  const float s = scores[(int64_t)row * C + p];
-  int64_t* o = packed + ((int64_t)row * Kl + j) * 2;
-  o[0] = (int64_t)__float_as_int(s);
-  o[1] = idx + start;
+  *reinterpret_cast<longlong2*>(packed + ((int64_t)row * Kl + j) * 2) =
+      shard_entry(cand, scores, local_final, n_sel, n_cand, row, j, C, Kl, start);
 }
 
 // gathered [world][rows][Kl][2] -> scores [rows][world*Kl], indices [rows][world*Kl] (rank-major within a row)
@@ -157,17 +173,13 @@ __device__ __forceinline__ void peer_wait(PeerCtl* ctl, const unsigned* flags, i
 __global__ void __launch_bounds__(256) shard_pack_peer_kernel(const int64_t* __restrict__ cand, const float* __restrict__ scores,
                                                               const int64_t* __restrict__ local_final, int C, int Kl,
                                                               int64_t start, PeerSet peers, int64_t gather_off,
-                                                              int64_t flags_off, int rank, int world, int rows, PeerCtl* ctl) {
+                                                              int64_t flags_off, int rank, int world, int rows, PeerCtl* ctl,
+                                                              const int32_t* __restrict__ n_sel,
+                                                              const int32_t* __restrict__ n_cand) {
   const int row = blockIdx.y;
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j < Kl) {
-    const int64_t idx = local_final[(int64_t)row * Kl + j];
-    const int64_t* c = cand + (int64_t)row * C;
-    int p = lower_bound_i64(c, C, idx);
-    if (p >= C) p = C - 1;
-    longlong2 v;
-    v.x = (int64_t)__float_as_int(scores[(int64_t)row * C + p]);
-    v.y = idx + start;
+    const longlong2 v = shard_entry(cand, scores, local_final, n_sel, n_cand, row, j, C, Kl, start);
     const int64_t slot = (((int64_t)rank * rows + row) * Kl + j) * 16;
     for (int q = 0; q < world; q++) *reinterpret_cast<longlong2*>(peers.base[q] + gather_off + slot) = v;
   }
@@ -291,8 +303,18 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restri
 
 using namespace pk;
 
+static int counts_arg(const pk_tensor* t, int64_t bs, int64_t H, const char* name, const int32_t** out) {
+  *out = nullptr;
+  if (!t) return PK_OK;
+  PK_REQUIRE(t->data && t->dtype == PK_I32 && t->ndim == 2 && is_contig(t) && t->shape[0] == bs && t->shape[1] == H,
+             "%s must be contiguous i32 [bs,H]", name);
+  *out = (const int32_t*)t->data;
+  return PK_OK;
+}
+
 extern "C" int pk_shard_pack_topk(const pk_tensor* cand, const pk_tensor* scores, const pk_tensor* local_final,
-                                  int64_t start, const pk_tensor* packed, void* stream) {
+                                  int64_t start, const pk_tensor* n_sel, const pk_tensor* n_cand,
+                                  const pk_tensor* packed, void* stream) {
   PK_CHECK_TENSOR(cand, PK_I64, 3);
   PK_CHECK_TENSOR(scores, PK_F32, 3);
   PK_CHECK_TENSOR(local_final, PK_I64, 3);
@@ -306,9 +328,12 @@ extern "C" int pk_shard_pack_topk(const pk_tensor* cand, const pk_tensor* scores
   PK_REQUIRE(C >= 1 && C < (1LL << 31) && Kl < (1LL << 31) && bs * H < 65536, "sizes out of range");
   PK_REQUIRE((reinterpret_cast<uintptr_t>(packed->data) & 15) == 0, "packed must be 16-byte aligned");
   if (bs * H * Kl == 0) return PK_OK;
+  const int32_t *ns = nullptr, *nc = nullptr;
+  int rc;
+  if ((rc = counts_arg(n_sel, bs, H, "n_sel", &ns)) || (rc = counts_arg(n_cand, bs, H, "n_cand", &nc))) return rc;
   shard_pack_kernel<<<dim3((unsigned)((Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
       (const int64_t*)cand->data, (const float*)scores->data, (const int64_t*)local_final->data, (int64_t*)packed->data,
-      (int)C, (int)Kl, start);
+      (int)C, (int)Kl, start, ns, nc);
   return check_launch("shard_pack_topk");
 }
 
@@ -390,7 +415,8 @@ static int fill_peers(PeerSet* ps, const uint64_t* peer_bases, int world, int ra
 }
 
 extern "C" int pk_shard_exchange_topk(const pk_tensor* cand, const pk_tensor* scores, const pk_tensor* local_final,
-                                      int64_t start, const uint64_t* peer_bases, int world, int rank,
+                                      int64_t start, const pk_tensor* n_sel, const pk_tensor* n_cand,
+                                      const uint64_t* peer_bases, int world, int rank,
                                       int64_t gather_offset, int64_t flags_offset, void* control, void* stream) {
   PK_CHECK_TENSOR(cand, PK_I64, 3);
   PK_CHECK_TENSOR(scores, PK_F32, 3);
@@ -405,9 +431,11 @@ extern "C" int pk_shard_exchange_topk(const pk_tensor* cand, const pk_tensor* sc
   PeerSet ps;
   int rc;
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
+  const int32_t *ns = nullptr, *nc = nullptr;
+  if ((rc = counts_arg(n_sel, bs, H, "n_sel", &ns)) || (rc = counts_arg(n_cand, bs, H, "n_cand", &nc))) return rc;
   shard_pack_peer_kernel<<<dim3((unsigned)((Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
       (const int64_t*)cand->data, (const float*)scores->data, (const int64_t*)local_final->data, (int)C, (int)Kl, start, ps,
-      gather_offset, flags_offset, rank, world, (int)(bs * H), (PeerCtl*)control);
+      gather_offset, flags_offset, rank, world, (int)(bs * H), (PeerCtl*)control, ns, nc);
   return check_launch("shard_exchange_topk");
 }
 

@@ -8,11 +8,13 @@ cache on one device):
   retrieval path; `head_shard()` gives the slice.
 * The sequence (million-token contexts): the searchable zone is cut into equal contiguous chunks, one per
   rank, each with its codes / 4-bit records in its own HBM and its K/V rows in its own HBM (when they fit) or
-  pinned host memory.  Per layer and step every rank runs the local chain (collision -> candidates -> rerank ->
-  local top-K) with GLOBAL tier thresholds and the GLOBAL cluster histogram; the ranks exchange (fp32 score,
-  global key index) of their local lists and every rank selects the same global top-K; each rank attends only
-  the selected rows it owns (rank 0 also the window) and a second exchange of (partial output, log2 denominator)
-  gives every rank the exact softmax over the union.  `SequenceShardedCache` / `sequence_sharded_attend` run the
+  pinned host memory.  Per layer and step every rank counts collisions over its chunk with GLOBAL tier thresholds
+  and the GLOBAL cluster histogram; the ranks all-gather their count histograms, so every rank knows the global
+  threshold count and its share of the ties and keeps exactly its part of the single-GPU candidate set; after the
+  rerank the ranks exchange (fp32 score, global key index) of their local top-K lists and every rank selects the
+  same global top-K - the single-GPU selection, bit for bit; each rank attends only the selected rows it owns
+  (rank 0 also the window) and an exchange of (partial output, log2 denominator) gives every rank the exact softmax
+  over the union.  `SequenceShardedCache` / `sequence_sharded_attend` run the
   exchanges either as two small NCCL all-gathers with CUDA packing / unpacking kernels around them, or as
   stores into peer memory with flag words (`PeerExchange`).
 
@@ -41,14 +43,36 @@ def sequence_shard(n_keys: int, rank: int, world: int):
     return start, min(n_keys, start + per)
 
 
-def local_plan(n_total: int, world: int, collision_ratio: float, candidate_ratio: float, final_topk: int,
-               tier_ratios=(0.05, 0.15, 0.30, 0.50, 0.75, 1.0)):
-    """Launch parameters of one shard: tier thresholds from the GLOBAL zone length, a per-shard candidate budget of
-    ceil(C_total / world) and a local top-K of min(K, C_local)."""
+def global_plan(n_total: int, collision_ratio: float, candidate_ratio: float, final_topk: int,
+                tier_ratios=(0.05, 0.15, 0.30, 0.50, 0.75, 1.0)):
+    """Launch parameters shared by every shard: tier thresholds, candidate count and final K of the WHOLE zone,
+    exactly as a single GPU would use them (cache_hub/polar_cache.py:1221-1222, :1239-1240, :1300)."""
     tiers = [int(math.ceil(n_total * collision_ratio * r)) for r in tier_ratios]
     c_total = max(1, int(math.ceil(n_total * candidate_ratio)))
-    c_local = max(1, (c_total + world - 1) // world)
-    return tiers, c_local, min(final_topk, c_local)
+    return tiers, c_total, min(final_topk, c_total)
+
+
+def shard_candidate_plan(shard_hist: torch.Tensor, rank: int, c_total: int):
+    """What the selection kernel derives from the all-gathered count histograms (host-side mirror, any device):
+    shard_hist int [world,bs,H,256] = how many keys of every shard have each collision count.  Returns
+    (T [bs,H], ties [bs,H], n_cand [bs,H]): shard `rank` takes every key with count > T, and the first `ties` of its
+    keys with count == T in key order; the union over the shards is the single-GPU candidate set - the c_total keys
+    with the highest counts, ties going to the lowest key index - because the shards are contiguous and in key order."""
+    h = shard_hist.to(torch.int64)
+    total = h.sum(0)                                                   # [bs,H,256]
+    suffix = torch.flip(torch.cumsum(torch.flip(total, [-1]), -1), [-1])   # keys with count >= bin
+    T = (suffix >= c_total).to(torch.int64).sum(-1) - 1                # highest bin whose suffix reaches c_total
+    T = T.clamp_(min=0)
+    above = torch.gather(suffix, -1, (T + 1).clamp(max=255).unsqueeze(-1)).squeeze(-1)
+    above = torch.where(T >= 255, torch.zeros_like(above), above)
+    quota = c_total - above                                            # ties of count T taken over the whole zone
+    eq = torch.gather(h, -1, T.view(1, *T.shape, 1).expand(h.shape[0], *T.shape, 1)).squeeze(-1)   # [world,bs,H]
+    before = eq[:rank].sum(0)
+    ties = torch.minimum((quota - before).clamp(min=0), eq[rank])
+    mine = h[rank]
+    idx = torch.arange(256, device=h.device).view(1, 1, 256)
+    gt = torch.where(idx > T.unsqueeze(-1), mine, torch.zeros_like(mine)).sum(-1)
+    return T, ties, gt + ties
 
 
 def allreduce_cluster_counts(counts: torch.Tensor, group=None) -> torch.Tensor:
@@ -127,41 +151,58 @@ def merge_gathered_partials(gathered: torch.Tensor) -> torch.Tensor:
 def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global, store_k,
                             store_v, n_total, start, end, collision_ratio, candidate_ratio, final_topk,
                             window_k=None, window_v=None, n_window=0, group=None, n_window_dev=None, n_window_add=0,
-                            exchange=None):
+                            exchange=None, scratch=None, attn_scratch=None):
     """One layer, one decode step of the sequence-sharded form on this rank's shard [start, end) of a zone of
     n_total keys.  codebook / key_block_weight / key_4bit / store_* hold the shard only (local index = global -
     start); counts_global is the all-reduced cluster histogram.  The window rows are attended by the rank that
-    passes them (rank 0).  Returns (attention output identical on every rank, global top-K indices)."""
+    passes them (rank 0).
+
+    The selection is the single-GPU selection: every shard counts collisions with the global thresholds, the ranks
+    all-gather their 256-bin count histograms, and each takes the keys above the GLOBAL threshold count plus its
+    share of the ties in rank (= key) order, so the union of the shards' candidates is the single-GPU candidate set;
+    the global top-K of the shards' local top-K lists is then the single-GPU final selection.  Three small exchanges
+    per layer: histograms (1 KB per head), local top lists (16 B x K per head), partial attention results.
+    Returns (attention output identical on every rank, global top-K indices)."""
     from . import ops
     world = dist.get_world_size(group) if dist.is_initialized() else 1
-    tiers, c_local, k_local = local_plan(n_total, world, collision_ratio, candidate_ratio, final_topk)
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    tiers, c_total, k_final = global_plan(n_total, collision_ratio, candidate_ratio, final_topk)
     if world == 1:   # the whole zone is local: the plain chain, nothing to exchange
         final, _ = ops.retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global,
-                                tiers, c_local, k_local)
+                                tiers, c_total, k_final, scratch=scratch)
         return ops.sparse_attention(queries, window_k, window_v, n_window, store_k, store_v, final,
-                                    n_window_dev=n_window_dev, n_window_add=n_window_add), final
-    fin_local, ex = ops.retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global,
-                                 tiers, c_local, k_local, want=("cand", "scores_f32"))
+                                    n_window_dev=n_window_dev, n_window_add=n_window_add, scratch=attn_scratch), final
     bs, _, Hq, _ = queries.shape
     H, dev = codebook.shape[1], queries.device
-    if exchange is not None:   # both exchanges as stores into peer memory (no collective launch)
-        ops.shard_exchange_topk(ex["cand"], ex["scores_f32"], fin_local, start, exchange)
-        scores, indices = ops.shard_collect_topk(exchange, bs, H, k_local)
+    n_local = codebook.shape[3]
+    row = min(c_total, n_local)
+    bufs = {"cand": torch.empty(bs, H, row, dtype=torch.int64, device=dev),
+            "scores_f32": torch.empty(bs, H, row, dtype=torch.float32, device=dev)}
+    args = (queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global, c_total, k_final)
+    # phase 1: collision counts of the shard, and how many of its keys have each count
+    _, _, ex = ops.retrieve_ex(*args, tier_counts=tiers, phase=1, outputs=bufs, scratch=scratch)
+    hist_all = torch.empty(world * bs, H, 256, dtype=torch.int32, device=dev)
+    dist.all_gather_into_tensor(hist_all, ex["local_hist"], group=group)
+    # phase 2: candidates by the global threshold, rerank, local top-K
+    fin_local, n_sel, ex = ops.retrieve_ex(*args, tier_counts=tiers, phase=2, shard_hist=hist_all.view(world, bs, H, 256),
+                                           world=world, rank=rank, outputs=bufs, scratch=scratch)
+    n_cand = ex["n_cand"]
+    if exchange is not None:   # the two larger exchanges as stores into peer memory (no collective launch)
+        ops.shard_exchange_topk(ex["cand"], ex["scores_f32"], fin_local, start, exchange, n_sel=n_sel, n_cand=n_cand)
+        scores, indices = ops.shard_collect_topk(exchange, bs, H, k_final)
     else:
-        # exchange 1: (score, global index) of the local top list, one packed buffer, one all-gather
-        packed = ops.shard_pack_topk(ex["cand"], ex["scores_f32"], fin_local, start)
-        flat = torch.empty(world * bs, H, k_local, 2, dtype=torch.int64, device=dev)
+        packed = ops.shard_pack_topk(ex["cand"], ex["scores_f32"], fin_local, start, n_sel=n_sel, n_cand=n_cand)
+        flat = torch.empty(world * bs, H, k_final, 2, dtype=torch.int64, device=dev)
         dist.all_gather_into_tensor(flat, packed, group=group)          # output = inputs concatenated along dim 0
-        scores, indices = ops.shard_unpack_topk(flat.view(world, bs, H, k_local, 2))
-    final = ops.final_topk(scores, indices, min(final_topk, world * k_local))
+        scores, indices = ops.shard_unpack_topk(flat.view(world, bs, H, k_final, 2))
+    final = ops.final_topk(scores, indices, k_final)
     local, n_owned = ops.shard_owned_rows(final, start, end)
     lse = torch.empty(bs, Hq, dtype=torch.float32, device=dev)
     out = ops.sparse_attention(queries, window_k, window_v, n_window, store_k, store_v, local, n_sel=n_owned, lse=lse,
-                               n_window_dev=n_window_dev, n_window_add=n_window_add)
+                               n_window_dev=n_window_dev, n_window_add=n_window_add, scratch=attn_scratch)
     if exchange is not None:
         ops.shard_exchange_partial(out, lse, exchange)
         return ops.shard_collect_partial(exchange, bs, Hq), final
-    # exchange 2: (partial output, log2 denominator), one packed buffer, one all-gather
     part = ops.shard_pack_partial(out, lse)
     flat2 = torch.empty(world * bs, Hq, 129, dtype=torch.float32, device=dev)
     dist.all_gather_into_tensor(flat2, part, group=group)
@@ -313,11 +354,19 @@ class SequenceShardedCache:
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
         self.px = None
-        if exchange == "peer" and world > 1:   # the two per-layer exchanges as stores into peer memory
-            _, _, k_local = local_plan(n_total, world, collision_ratio, candidate_ratio, final_topk)
-            self.px = PeerExchange(1, num_kv_heads, num_heads, k_local, device, group)
+        if exchange == "peer" and world > 1:   # the two larger per-layer exchanges as stores into peer memory
+            _, _, k_final = global_plan(n_total, collision_ratio, candidate_ratio, final_topk)
+            self.px = PeerExchange(1, num_kv_heads, num_heads, k_final, device, group)
         self.device_positions = False     # window length read from a device word (captured steps)
         self._dev_state = torch.zeros(1, dtype=torch.int32, device=device)
+        # scratch of the chain and of the attention kernel, sized once for everything this shard can grow to: the
+        # addresses stay fixed, so captured decode steps remain valid
+        from . import ops
+        n_cap = max(self._n_local[0] + self.growth, 1)
+        n_all = n_total + ((max_new_length + interval - 1) // interval * interval + interval)
+        c_cap = min(n_cap, max(1, int(math.ceil(n_all * candidate_ratio))))
+        self._retrieve_scratch = ops.Scratch(device, ops.retrieve_scratch_bytes(1, num_kv_heads, n_cap, c_cap))
+        self._attn_scratch = ops.Scratch(device, ops.attention_scratch_bytes(1, num_heads, cap + final_topk))
 
     # the names the single-GPU cache uses for the same quantities
     @property
@@ -411,7 +460,8 @@ class SequenceShardedCache:
             window_v=self.window_v[layer_idx] if first else None,
             n_window=(self.window_capacity if self.device_positions else self._window_len[layer_idx]) if first else 0,
             group=self.group, n_window_dev=self._dev_state[0:1] if (first and self.device_positions) else None,
-            n_window_add=1 if (first and self.device_positions) else 0, exchange=self.px)
+            n_window_add=1 if (first and self.device_positions) else 0, exchange=self.px,
+            scratch=self._retrieve_scratch, attn_scratch=self._attn_scratch)
         self.last_topk_indices = final
         return out
 

@@ -399,14 +399,16 @@ def retrieve_ex(queries, signs, mag_centers, codebook, key_block_weight, key_4bi
 # --------------------------------------------------------------------------------------------------
 # sequence-sharded form: packing / unpacking around the two all-gathers
 # --------------------------------------------------------------------------------------------------
-def shard_pack_topk(cand, scores, local_final, start, packed=None):
-    """(cand, scores, local_final) -> packed i64 [bs,H,Kl,2]; see pk_shard_pack_topk."""
+def shard_pack_topk(cand, scores, local_final, start, packed=None, n_sel=None, n_cand=None):
+    """(cand, scores, local_final) -> packed i64 [bs,H,Kl,2]; n_sel / n_cand (i32 [bs,H]) give the valid entries of
+    local_final / cand rows; see pk_shard_pack_topk."""
     _require_cuda(cand, scores, local_final)
     bs, H, Kl = local_final.shape
     if packed is None:
         packed = torch.empty(bs, H, Kl, 2, dtype=torch.int64, device=cand.device)
-    d = [L.desc(t) for t in (cand, scores, local_final, packed)]
-    _call("pk_shard_pack_topk", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(start), L.ref(d[3]), L.stream_ptr(cand.device))
+    d = [L.desc(t) for t in (cand, scores, local_final, n_sel, n_cand, packed)]
+    _call("pk_shard_pack_topk", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(start), L.ref(d[3]), L.ref(d[4]), L.ref(d[5]),
+          L.stream_ptr(cand.device))
     return packed
 
 
@@ -453,13 +455,13 @@ def shard_merge_partial(gathered):
     return out
 
 
-def shard_exchange_topk(cand, scores, local_final, start, px):
+def shard_exchange_topk(cand, scores, local_final, start, px, n_sel=None, n_cand=None):
     """Pack this rank's local top list and store it into every peer's gather area; see pk_shard_exchange_topk.
     px: a dist.PeerExchange."""
     _require_cuda(cand, scores, local_final)
-    d = [L.desc(t) for t in (cand, scores, local_final)]
-    _call("pk_shard_exchange_topk", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(start), px.peer_array, px.world, px.rank,
-          px.gather1_off, px.flags1_off, px.ctl.data_ptr(), L.stream_ptr(cand.device))
+    d = [L.desc(t) for t in (cand, scores, local_final, n_sel, n_cand)]
+    _call("pk_shard_exchange_topk", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(start), L.ref(d[3]), L.ref(d[4]),
+          px.peer_array, px.world, px.rank, px.gather1_off, px.flags1_off, px.ctl.data_ptr(), L.stream_ptr(cand.device))
 
 
 def shard_collect_topk(px, bs, H, Kl):

@@ -1,6 +1,6 @@
-"""World-size-2 tests of the multi-GPU plumbing with gloo ranks on CPU: the exchange of local top lists, the
-partial-attention merge and the histogram all-reduce of the sequence-sharded form, against the same sharded
-formulation evaluated in one process by the oracle."""
+"""World-size-2 tests of the multi-GPU plumbing with gloo ranks on CPU: the exchange of count histograms and local top
+lists, the partial-attention merge and the histogram all-reduce of the sequence-sharded form.  The reference is the
+oracle's SINGLE-GPU selection over the whole zone: the sharded form must reproduce it bit for bit."""
 import os
 import socket
 
@@ -25,23 +25,63 @@ def _oracle_select(scores, indices, k):
     return O.final_topk(scores, indices, k)
 
 
-def _shard_result(O, rank, world, keys, vals, q, signs, cen, coll, cand_ratio, K, counts_global, span=None):
-    """One rank's part of the sharded formulation on the CPU; span = (start, end) when the chunks are not the equal
-    split (after flushes the last chunk has grown)."""
+def _shard_counts(O, span, keys, q, signs, coll, counts_global):
+    """Collision counts of one shard with the GLOBAL thresholds and cluster histogram, plus what the rerank needs."""
+    start, end = span
+    N, H = keys.shape[2], keys.shape[1]
+    cb, w, pk = O.encode(keys[:, :, start:end].contiguous(), signs)
+    qb, qn = O.query_prep(q, H, signs)
+    cnt = O.collision(O.cluster_rank(qb), counts_global, cb, O.tier_counts(N, coll))
+    return cnt, (pk, w, qb, qn)
+
+
+def _count_hist(cnt):
+    """int32 [bs,H,256]: how many keys of the shard have each collision count."""
+    bs, H, n = cnt.shape
+    h = torch.zeros(bs, H, 256, dtype=torch.int32)
+    h.scatter_add_(2, cnt.long(), torch.ones(bs, H, n, dtype=torch.int32))
+    return h
+
+
+def _shard_result(O, rank, spans, keys, q, signs, cen, coll, cand_ratio, K, counts_global, hist_all=None):
+    """One rank's part of the exact sharded selection on the CPU: candidates by the global threshold count and this
+    shard's share of the ties, rerank, local top-K; lists padded to K entries with (-inf, -1).  hist_all
+    [world,bs,H,256] is what the all-gather delivers; when None it is computed here from every shard."""
     from pariskv_b200 import dist as pkd
     N = keys.shape[2]
-    start, end = span if span is not None else pkd.sequence_shard(N, rank, world)
-    tiers, c_local, k_local = pkd.local_plan(N, world, coll, cand_ratio, K)
-    cb, w, pk = O.encode(keys[:, :, start:end].contiguous(), signs)
-    H = keys.shape[1]
-    qb, qn = O.query_prep(q, H, signs)
-    ids = O.cluster_rank(qb)
-    cnt = O.collision(ids, counts_global, cb, tiers)
-    cand = O.topk(cnt, c_local)
-    s32, _ = O.rerank(cand, pk, w, qb, qn, cen)
-    loc = O.final_topk(s32, cand, k_local)
-    sc = torch.gather(s32, 2, torch.searchsorted(cand, loc))
-    return sc, loc + start, (start, end), (cb,)
+    _, c_total, k_final = pkd.global_plan(N, coll, cand_ratio, K)
+    cnt, (pk, w, qb, qn) = _shard_counts(O, spans[rank], keys, q, signs, coll, counts_global)
+    if hist_all is None:
+        hist_all = torch.stack([_count_hist(_shard_counts(O, sp, keys, q, signs, coll, counts_global)[0]) for sp in spans])
+    T, ties, n_cand = pkd.shard_candidate_plan(hist_all, rank, c_total)
+    bs, H, n = cnt.shape
+    start = spans[rank][0]
+    sc_out = torch.full((bs, H, k_final), float("-inf"))
+    idx_out = torch.full((bs, H, k_final), -1, dtype=torch.int64)
+    for b in range(bs):
+        for h in range(H):
+            c = cnt[b, h]
+            eq = torch.nonzero(c == T[b, h]).flatten()[: int(ties[b, h])]
+            cand = torch.cat([torch.nonzero(c > T[b, h]).flatten(), eq]).sort().values
+            assert cand.numel() == int(n_cand[b, h])
+            if cand.numel() == 0:
+                continue
+            s32, _ = O.rerank(cand.view(1, 1, -1), pk[b:b + 1, h:h + 1], w[b:b + 1, h:h + 1], qb[b:b + 1, h:h + 1],
+                              qn[b:b + 1, h:h + 1], cen)
+            kl = min(k_final, cand.numel())
+            loc = O.final_topk(s32, cand.view(1, 1, -1), kl)[0, 0]
+            sc_out[b, h, :kl] = s32[0, 0][torch.searchsorted(cand, loc)]
+            idx_out[b, h, :kl] = loc + start
+    return sc_out, idx_out
+
+
+def _single_gpu_final(O, keys, q, signs, cen, coll, cand_ratio, K, counts_global):
+    """The reference: the whole zone on one device (cache_hub/polar_cache.py:1207-1304 restated by the oracle)."""
+    from pariskv_b200 import dist as pkd
+    N = keys.shape[2]
+    _, c_total, k_final = pkd.global_plan(N, coll, cand_ratio, K)
+    cb, w, pk = O.encode(keys, signs)
+    return O.retrieve(q, signs, cb, w, pk, counts_global, cen, coll, c_total, k_final)["final"]
 
 
 def _worker(rank, world, port, tmp):
@@ -66,13 +106,22 @@ def _worker(rank, world, port, tmp):
         pkd.allreduce_cluster_counts(counts)
         cb_all, _, _ = O.encode(keys, signs)
         assert torch.equal(counts, O.cluster_counts(cb_all))
-        # local chain, exchange, global selection
-        sc, gi, _, _ = _shard_result(O, rank, world, keys, vals, q, signs, cen, coll, cand_ratio, K, counts)
+        # local counts, exchange of the count histograms, candidates by the global threshold, exchange of the local
+        # top lists, global selection
+        spans = [pkd.sequence_shard(N, r, world) for r in range(world)]
+        mine = _count_hist(_shard_counts(O, spans[rank], keys, q, signs, coll, counts)[0])
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        hist_all = torch.stack(gathered)
+        sc, gi = _shard_result(O, rank, spans, keys, q, signs, cen, coll, cand_ratio, K, counts, hist_all=hist_all)
         final = pkd.merge_local_topk(sc, gi, K, select=_oracle_select)
-        # the same formulation evaluated serially
-        parts = [_shard_result(O, r, world, keys, vals, q, signs, cen, coll, cand_ratio, K, counts) for r in range(world)]
-        want = O.final_topk(torch.cat([p[0] for p in parts], -1), torch.cat([p[1] for p in parts], -1), K)
-        assert torch.equal(final, want)
+        # the reference: the single-GPU selection over the whole zone
+        want = _single_gpu_final(O, keys, q, signs, cen, coll, cand_ratio, K, counts)
+        assert torch.equal(final, want), "the sharded selection is not the single-GPU selection"
+        T, ties, n_cand = pkd.shard_candidate_plan(hist_all, rank, pkd.global_plan(N, coll, cand_ratio, K)[1])
+        tot = n_cand.clone()
+        dist.all_reduce(tot)
+        assert bool((tot == pkd.global_plan(N, coll, cand_ratio, K)[1]).all()), "shards' candidate counts must add up"
         assert bool((final[..., 1:] > final[..., :-1]).all())
         # every rank attends its own rows; partial results merge to attention over the union
         local, n_owned = pkd.owned_rows(final, start, end)
@@ -114,8 +163,8 @@ def test_head_and_sequence_shards():
     cover = [pkd.sequence_shard(1048508, r, 8) for r in range(8)]
     assert cover[0][0] == 0 and cover[-1][1] == 1048508
     assert all(cover[i][1] == cover[i + 1][0] for i in range(7))
-    tiers, c_local, k_local = pkd.local_plan(1048508, 8, 0.2, 0.1, 2048)
-    assert c_local == -(-104851 // 8) and k_local == 2048 and tiers[-1] == 209702
+    tiers, c_total, k_final = pkd.global_plan(1048508, 0.2, 0.1, 2048)
+    assert c_total == 104851 and k_final == 2048 and tiers[-1] == 209702
 
 
 def test_owned_rows_split():
@@ -132,7 +181,19 @@ def test_tier_thresholds_match_the_reference_arithmetic():
     from pariskv_b200 import dist as pkd
     want = [328, 984, 1967, 3277, 4916, 6554]
     assert list(O.tier_counts(32768, 0.2)) == want
-    tiers, c_local, k_local = pkd.local_plan(32768, 1, 0.2, 4096 / 32768, 256)
-    assert tiers == want and c_local == 4096 and k_local == 256
-    # per-shard budgets: ceil of the global candidate count over the ranks, the final K capped by it
-    assert pkd.local_plan(32768, 4, 0.2, 4096 / 32768, 2048)[1:] == (1024, 1024)
+    tiers, c_total, k_final = pkd.global_plan(32768, 0.2, 4096 / 32768, 256)
+    assert tiers == want and c_total == 4096 and k_final == 256
+
+
+def test_shard_candidate_plan_splits_ties_in_rank_order():
+    """Three shards; 5 candidates wanted; counts: two keys at 9, then four keys at 7 spread over the shards: the two 9s
+    are taken outright, three of the 7s in rank order (shard 0 has one, shard 1 two, shard 2 one -> 1, 2, 0)."""
+    from pariskv_b200 import dist as pkd
+    h = torch.zeros(3, 1, 1, 256, dtype=torch.int32)
+    h[0, 0, 0, 9], h[0, 0, 0, 7], h[0, 0, 0, 2] = 1, 1, 10
+    h[1, 0, 0, 7], h[1, 0, 0, 1] = 2, 10
+    h[2, 0, 0, 9], h[2, 0, 0, 7], h[2, 0, 0, 0] = 1, 1, 10
+    got = [pkd.shard_candidate_plan(h, r, 5) for r in range(3)]
+    assert [int(g[0]) for g in got] == [7, 7, 7]
+    assert [int(g[1]) for g in got] == [1, 2, 0]
+    assert [int(g[2]) for g in got] == [2, 2, 1]

@@ -8,7 +8,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from conftest import srht_signs, synth_keys, synth_queries
-from test_dist_gloo import _free_port, _shard_result
+from test_dist_gloo import _free_port, _single_gpu_final
 
 pytestmark = pytest.mark.gpu
 
@@ -45,9 +45,8 @@ def _worker(rank, world, port, tmp):
             q.to(dev), signs.to(dev), cen.to(dev), cb, w, pk, counts, sk, sv, N, start, end, coll, cand_ratio, K,
             window_k=wk.to(dev) if rank == 0 else None, window_v=wv.to(dev) if rank == 0 else None,
             n_window=40 if rank == 0 else 0)
-        parts = [_shard_result(O, r, world, keys, vals, q, signs, cen, coll, cand_ratio, K, counts.cpu()) for r in range(world)]
-        want = O.final_topk(torch.cat([p[0] for p in parts], -1), torch.cat([p[1] for p in parts], -1), K)
-        assert torch.equal(final.cpu(), want), "global selection differs from the sharded oracle"
+        want = _single_gpu_final(O, keys, q, signs, cen, coll, cand_ratio, K, counts.cpu())
+        assert torch.equal(final.cpu(), want), "the sharded selection is not the single-GPU selection"
         ref = O.attention(q, torch.cat([wk, O.gather(keys, want)], 2), torch.cat([wv, O.gather(vals, want)], 2))
         err = (out.float().cpu() - ref).abs().max().item()
         assert err <= 2e-2, err
@@ -58,7 +57,8 @@ def _worker(rank, world, port, tmp):
 
 def _cache_check(rank, world, dev, exchange="nccl"):
     """SequenceShardedCache: load two layers, decode across one flush of the update buffer (the flushed rows go to the
-    last rank's chunk, the histogram delta is all-reduced), attend; against the oracle's sharded formulation."""
+    last rank's chunk, the histogram delta is all-reduced), attend; against the oracle's SINGLE-GPU selection over the
+    whole zone."""
     from oracle import oracle as O
     from pariskv_b200 import dist as pkd
     g = torch.Generator().manual_seed(5)
@@ -101,12 +101,9 @@ def _cache_check(rank, world, dev, exchange="nccl"):
             data[l] = [keys, vals, wk, wv]
             N = keys.shape[2]
             assert cache.cpu_valid_end[l] == N
-            spans = [(a, b if r < world - 1 else N) for r, (a, b) in enumerate(spans0)]
             counts = O.cluster_counts(O.encode(keys, signs)[0])
             assert torch.equal(cache.counts[l].cpu(), counts)
-            parts = [_shard_result(O, r, world, keys, vals, q, signs, cen, 0.2, 0.1, K, counts, span=spans[r])
-                     for r in range(world)]
-            want = O.final_topk(torch.cat([p[0] for p in parts], -1), torch.cat([p[1] for p in parts], -1), K)
+            want = _single_gpu_final(O, keys, q, signs, cen, 0.2, 0.1, K, counts)
             assert torch.equal(cache.last_topk_indices.cpu(), want), (step, l)
             ref = O.attention(q, torch.cat([wk, O.gather(keys, want)], 2), torch.cat([wv, O.gather(vals, want)], 2))
             err = (out.float().cpu() - ref).abs().max().item()
