@@ -134,12 +134,11 @@ class DecoderHarness:
 
 
 class GraphedDecoder:
-    """Replays the decode step as a CUDA graph.  Between two flushes of the update buffer every launch
-    argument of the step is constant except the window position and the RoPE position, which the kernels
-    read from device words.  The zone length, the candidate count and the tier thresholds are launch arguments,
-    so there is one graph per zone length; graphs for the lengths that the coming flushes will produce can be
-    captured ahead of time (`precapture`), as a serving engine captures its graphs at start-up: capturing executes
-    nothing and only needs the launch arguments.  The step that flushes runs eagerly."""
+    """Replays the decode step as a CUDA graph.  The single-GPU cache keeps every position (window rows, zone length
+    per sample) in device words that its kernels read and advance themselves, flushes included, so ONE graph serves
+    the whole generation (one more if the run crosses from the short-sequence regime into retrieval).  The
+    sequence-sharded cache still passes its zone length as a launch argument: it gets one graph per zone length,
+    captured ahead of time (`precapture`), and runs the step that flushes eagerly."""
 
     def __init__(self, model, cache):
         self.model, self.cache = model, cache
@@ -156,6 +155,10 @@ class GraphedDecoder:
         self.side = torch.cuda.Stream(device=dev)
 
     def _zone_length(self):
+        """What the captured step depends on besides device words: nothing but the attention regime for the
+        single-GPU cache, the zone length for the sequence-sharded one."""
+        if hasattr(self.cache, "graph_key"):
+            return self.cache.graph_key()
         return getattr(self.cache, "cpu_valid_end", [0])[0]
 
     def _capture(self, n_zone, future=None):

@@ -247,6 +247,31 @@ int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* window_k, con
 int pk_append_kv(const pk_tensor* k_row, const pk_tensor* v_row, const pk_tensor* window_k,
                  const pk_tensor* window_v, int64_t pos, const pk_tensor* pos_dev, int64_t pos_add, void* stream);
 
+/* One decode token into the cache, with the key coded once, when it is appended, and the flush of a full update
+ * buffer inside the same launch: the row writes of polar_cache.decode_update_kv_cache (cache_hub/polar_cache.py:827-881)
+ * and the index update of _update_polar_index (:743-821, which codes a whole buffer at flush time, for all layers,
+ * and then blocks on the copy stream).  All positions live in `state` (int32, device):
+ *   state[0] rows in the window   state[1] arrival counter (zero)   state[2] flushes so far   state[3] error flag
+ *   state[4 + b] searchable keys of sample b
+ * so the launch arguments never change and a captured CUDA graph stays valid across flushes.
+ *   k_row/v_row    bf16 [bs,1,H,128]
+ *   window_k/_v    bf16 [bs,H,cap_w,128], cap_w = sink + local + interval; the row goes to window row state[0]
+ *   win_codes u8 [bs,H,cap_w,16], win_weight bf16 [bs,H,cap_w,16], win_4bit u8 [bs,H,cap_w,16,4], win_vnorm f32
+ *                  [bs,H,cap_w]: contiguous staging records of the window rows (codes, rerank weights, 4-bit codes, ||v||)
+ *   codebook / block_weight / packed_4bit: the zone records in the reference's logical shapes, stored key-major
+ *                  (as pk_encode_keys prefers); value_norm f32 [bs,H,cap_z] or NULL
+ *   store_kv       bf16 [bs,H,cap_s,2,128]: K row and V row of a zone key next to each other, device or pinned host
+ * When the appended row fills the window, rows [sink, sink + interval) are published: records -> zone records
+ * [n, n + interval), codes -> cluster_counts, K/V rows -> store rows, remaining rows slide down, state[0] =
+ * cap_w - interval, state[4 + b] += interval.  state[3] becomes 1 (and nothing is published) if the zone or the
+ * store has no room, or if state[0] is outside the window. */
+int pk_append_encode(const pk_tensor* k_row, const pk_tensor* v_row, const pk_tensor* signs,
+                     const pk_tensor* window_k, const pk_tensor* window_v, const pk_tensor* win_codes,
+                     const pk_tensor* win_weight, const pk_tensor* win_4bit, const pk_tensor* win_vnorm,
+                     const pk_tensor* codebook, const pk_tensor* block_weight, const pk_tensor* packed_4bit,
+                     const pk_tensor* value_norm, const pk_tensor* cluster_counts, const pk_tensor* store_kv,
+                     const pk_tensor* state, int64_t sink, int64_t interval, void* stream);
+
 /* ---- the whole retrieval chain in one call ------------------------------------------------------- */
 
 /* queries -> final top-K key indices for one layer and one decode step: the body of

@@ -74,6 +74,7 @@ SIGNATURES = {
     "pk_attention_workspace_bytes": (_I64, [_I64, _I64, _I64]),
     "pk_sparse_attention": (_INT, [TP, TP, TP, _I64, TP, _I64, TP, TP, TP, TP, _I64, _F32, TP, TP, _VP, _I64, _VP]),
     "pk_append_kv": (_INT, [TP, TP, TP, TP, _I64, TP, _I64, _VP]),
+    "pk_append_encode": (_INT, [TP] * 16 + [_I64, _I64, _VP]),
     "pk_retrieve_workspace_bytes": (_I64, [_I64, _I64, _I64, _I64]),
     "pk_retrieve": (_INT, [TP, TP, TP, TP, TP, TP, TP, _I64P, _INT, _I64, _I64, TP, TP, TP, TP, TP, TP, _VP, _I64,
                            _VP]),

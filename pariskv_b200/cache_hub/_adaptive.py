@@ -31,42 +31,23 @@ class AdaptiveKCache(_base_cache):
             raise ValueError("adaptive top-k supports at most 4096 rows per head")
         dev, bs, H = self.device, self.batch_size, self.kv_head
         self._attn_scale = 1.0 / math.sqrt(self.head_dim)
-        # ||v|| of the window rows and of the zone rows (zone-relative index), fp32
-        self._sl_vnorm_cache = [torch.zeros(bs, H, self.window_capacity, dtype=torch.float32, device=dev)
-                                for _ in range(self.layer_num)]
+        # ||v|| of the window rows and of the zone rows (zone-relative index), fp32.  The window norms are the staging
+        # array that the append kernel fills for every cache; the zone norms are published by its flush.
+        self._sl_vnorm_cache = self._win_vnorm
         self.value_norm_gpu = [torch.zeros(bs, H, self.zone_capacity, dtype=torch.float32, device=dev)
                                for _ in range(self.layer_num)]
         self.last_adaptive = None   # (adaptive_k, topk_indices, n_sel, sl_logits, cand, cand_scores) of the last compute
 
-    # ---- value norms follow every K/V write -------------------------------------------------------------
+    def _zone_vnorm(self, layer):
+        return self.value_norm_gpu[layer]
+
+    # ---- value norms of the prompt (decode rows are handled by the append kernel) -------------------------
     def _prefill_sample(self, k, v, layer, b, vs):
         super()._prefill_sample(k, v, layer, b, vs)
-        vn = torch.linalg.vector_norm(v[vs:].to(self.dtype).float(), dim=-1).transpose(0, 1)  # [H, P]
-        P = vn.shape[1]
-        N = self.cpu_valid_end[layer]
-        sink, local = self.sink_size, self.local_size
-        if N == 0:
-            n = self._window_len[layer]
-            self._sl_vnorm_cache[layer][b, :, :n] = vn[:, :n]
-            return
-        self._sl_vnorm_cache[layer][b, :, :sink] = vn[:, :sink]
-        self._sl_vnorm_cache[layer][b, :, sink:sink + local] = vn[:, P - local:]
-        self.value_norm_gpu[layer][b, :, :N] = vn[:, sink:sink + N]
-
-    def decode_update_kv_cache(self, key_states, value_states, layer_idx):
-        if self.device_positions:
-            raise RuntimeError("the adaptive-k variants track value norms on the host side of the step: run them eagerly")
-        pos = self._window_len[layer_idx]
-        self._sl_vnorm_cache[layer_idx][:, :, pos] = torch.linalg.vector_norm(value_states[:, 0].float(), dim=-1)
-        return super().decode_update_kv_cache(key_states, value_states, layer_idx)
-
-    def _flush(self, layer):
-        I, sink, local = self.dynamic_update_interval, self.sink_size, self.local_size
-        N = self.cpu_valid_end[layer]
-        vn = self._sl_vnorm_cache[layer]
-        self.value_norm_gpu[layer][:, :, N:N + I] = vn[:, :, sink:sink + I]
-        vn[:, :, sink:sink + local] = vn[:, :, sink + I:sink + I + local].clone()
-        super()._flush(layer)
+        N = self.zone_len[layer][b]
+        if N > 0:
+            vn = torch.linalg.vector_norm(v[vs:].to(self.dtype).float(), dim=-1).transpose(0, 1)  # [H, P]
+            self.value_norm_gpu[layer][b, :, :N] = vn[:, self.sink_size:self.sink_size + N]
 
     # ---- decode attention ---------------------------------------------------------------------------------
     def compute(self, queries, layer_idx):

@@ -80,7 +80,8 @@ int retrieve_impl(const pk_retrieve_args& a, cudaStream_t st) {
   const bool sharded = a.phase != 0;
   const bool varlen = a.kv_len != nullptr;
   PK_REQUIRE(!(sharded && varlen), "per-sample zone lengths and sharded selection cannot be combined");
-  if (!sharded) PK_REQUIRE(C <= N && K <= C, "need K <= C <= N (K=%lld C=%lld N=%lld)", (long long)K, (long long)C, (long long)N);
+  if (!sharded && !varlen) PK_REQUIRE(C <= N && K <= C, "need K <= C <= N (K=%lld C=%lld N=%lld)", (long long)K, (long long)C, (long long)N);
+  if (varlen) PK_REQUIRE(C <= N, "need C <= N (C=%lld N=%lld)", (long long)C, (long long)N);
   ChainQuery cq = {};
   SelectArgs sa = {};
   if (varlen) {

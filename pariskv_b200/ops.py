@@ -280,6 +280,16 @@ def append_kv(k_row, v_row, window_k, window_v, pos, pos_dev=None, pos_add=0):
           L.stream_ptr(window_k.device))
 
 
+def append_encode(k_row, v_row, signs, window_k, window_v, win_codes, win_weight, win_4bit, win_vnorm, codebook,
+                  block_weight, packed_4bit, value_norm, cluster_counts, store_kv, state, sink, interval):
+    """One decode token into the cache: window row, key coding, and the flush of a full update buffer, all positions
+    read from the device-side `state` words; see pk_append_encode."""
+    _require_cuda(k_row, v_row, window_k, window_v, state)
+    d = [L.desc(t) for t in (k_row, v_row, signs, window_k, window_v, win_codes, win_weight, win_4bit, win_vnorm, codebook,
+                             block_weight, packed_4bit, value_norm, cluster_counts, store_kv, state)]
+    _call("pk_append_encode", *[L.ref(x) for x in d], int(sink), int(interval), L.stream_ptr(window_k.device))
+
+
 def sparse_attention(queries, window_k, window_v, n_window, store_k=None, store_v=None, selected=None, n_sel=None,
                      index_offset=0, scale=None, out=None, n_window_dev=None, n_window_add=0, lse=None, scratch=None):
     """Decode attention over window rows [0, n_window) plus the selected rows of the K/V store (device or

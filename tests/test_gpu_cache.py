@@ -244,8 +244,9 @@ def test_long_generation_with_drifting_keys_one_kv_head(oracle):
 
 
 def test_graphed_decoder_with_precaptured_graphs_matches_eager():
-    """bench.GraphedDecoder: graphs for the zone lengths of the coming flushes are captured ahead of time; a run that
-    crosses three flushes must produce the same tokens as plain eager stepping (same weights, same cache content)."""
+    """bench.GraphedDecoder: ONE captured graph replayed across three flushes of the update buffer (the flush runs
+    inside the append launch, all positions are device words) must produce the same tokens as plain eager stepping
+    (same weights, same cache content)."""
     import bench
     cfg = dict(layers=2, hidden=256, q_heads=8, kv_heads=2, head_dim=128, ffn=512, vocab=997, rope_theta=1.0e6,
                context=2600, sink=4, local=16, interval=8, topk=32)
@@ -274,7 +275,7 @@ def test_graphed_decoder_with_precaptured_graphs_matches_eager():
     runner.tok.copy_(tok)
     runner.precapture(3)
     captured = runner.captures
-    assert captured == 4
+    assert captured == 1, "one graph must serve every zone length"
     for _ in range(steps - 2):
         runner.step()
         got.append(int(runner.nxt))
@@ -362,3 +363,40 @@ def test_attention_status_word_is_read_and_raised(oracle):
     out2 = cache.compute(q.to(DEV), 0)
     assert torch.equal(out, out2)
     cache.check_status()
+
+
+def test_per_query_head_retrieval_option(oracle):
+    """per_query_head_retrieval: every query head selects its own top-k from the keys of its KV head.  Oracle: the
+    same chain run with one "KV head" per query head (the KV head's codes repeated over the group, group size one)."""
+    g = torch.Generator().manual_seed(41)
+    bs, H, Hq, sink, local, I, topk, P = 2, 2, 8, 4, 16, 8, 32, 2300
+    G = Hq // H
+    from pariskv_b200.cache_hub.polar_cache import polar_cache
+    cache = polar_cache(valid_start=[0] * bs, layer_num=1, batch_size=bs, max_length=P + 32, num_key_value_heads=H, num_heads=Hq,
+                        head_dim=128, dtype=torch.bfloat16, layer_mapping={"0": DEV}, max_new_length=32, sink_size=sink,
+                        local_size=local, core=0, nprobe=0, cache_unit_size=0, cache_cluster_num=0, num_gpus=1, model_size=8,
+                        final_topk=topk, dynamic_update_interval=I, enable_offload=True, per_query_head_retrieval=True)
+    K = synth_keys(g, bs, H, P)
+    V = torch.randn(bs, H, P, 128, generator=g).to(torch.bfloat16)
+    cache.prefill_update_kv_cache(None, K.transpose(1, 2).contiguous().to(DEV), V.transpose(1, 2).contiguous().to(DEV), 0, 0)
+    nk = torch.randn(bs, H, 1, 128, generator=g).to(torch.bfloat16)
+    nv = torch.randn(bs, H, 1, 128, generator=g).to(torch.bfloat16)
+    cache.decode_update_kv_cache(nk.transpose(1, 2).contiguous().to(DEV), nv.transpose(1, 2).contiguous().to(DEV), 0)
+    q = (torch.randn(bs, 1, Hq, 128, generator=g) * 0.5).to(torch.bfloat16)
+    out = cache.compute(q.to(DEV), 0)
+    signs = cache.srht_diagonal_signs.cpu()
+    rep = lambda t: t.repeat_interleave(G, dim=1)          # KV-head tensors repeated per query head
+    zk, zv = K[:, :, sink:P - local].contiguous(), V[:, :, sink:P - local].contiguous()
+    cb, w, pk = oracle.encode(zk, signs)
+    N = zk.shape[2]
+    _, C, Kf = cache.retrieval_plan(N)
+    _, coll = cache._get_adaptive_ratios(N)
+    r = oracle.retrieve(q, signs, rep(cb), rep(w), rep(pk), rep(oracle.cluster_counts(cb)), cache._mag_centers.cpu(), coll, C, Kf)
+    assert torch.equal(cache.last_topk_indices.cpu(), r["final"]), "per-query-head selections differ from the oracle"
+    sel = r["final"]                                        # [bs, Hq, Kf]
+    heads_differ = any(not torch.equal(sel[0, 0], sel[0, j]) for j in range(1, G))
+    assert heads_differ, "query heads of one group should not all retrieve the same rows"
+    wk = torch.cat([rep(K[:, :, :sink]), rep(K[:, :, P - local:]), rep(nk), oracle.gather(rep(zk), sel)], 2)
+    wv = torch.cat([rep(V[:, :, :sink]), rep(V[:, :, P - local:]), rep(nv), oracle.gather(rep(zv), sel)], 2)
+    ref = oracle.attention(q, wk, wv)                      # Hq query heads over Hq "KV heads": group size one
+    assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
