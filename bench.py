@@ -100,25 +100,35 @@ class DecoderHarness:
         return self.reducer.reduce(partial, residual)
 
     def step(self, cache, token, pos_dev=None):
-        """One decode token through all layers; token: int64 [1] on the device.  Returns next token [1].
-        pos_dev (float32 [1] on the device) replaces the host-side position when the step is captured.
+        """One decode token per sequence through all layers; token: int64 [B] on the device.  Returns the next
+        tokens [B].  pos_dev (float32 [B] or [1] on the device) replaces the host-side position when the step is
+        captured or when the sequences of a batch stand at different positions.
         q and k share one RMS-norm and one rotate-half RoPE call per layer (stacked per-head weights)."""
         c = self.cfg
         Hq, Hk, D, Ff = self.Hq, self.Hk, c["head_dim"], self.Ff
-        ang = (pos_dev if pos_dev is not None else cache.context) * self._inv_freq
-        cos = torch.cos(ang).repeat(2).to(torch.bfloat16)          # [128]
-        sin = torch.sin(ang)
-        sin = torch.cat([-sin, sin]).to(torch.bfloat16)            # sign of rotate-half folded in
-        h = self.embed[token]                                      # [1, hidden]
+        B = token.shape[0]
+        pos = pos_dev if pos_dev is not None else float(cache.context)
+        if B == 1:
+            ang = pos * self._inv_freq
+            cos = torch.cos(ang).repeat(2).to(torch.bfloat16)          # [128]
+            sin = torch.sin(ang)
+            sin = torch.cat([-sin, sin]).to(torch.bfloat16)            # sign of rotate-half folded in
+        else:
+            ang = (pos.view(-1, 1) if torch.is_tensor(pos) else pos) * self._inv_freq.view(1, -1)
+            ang = ang.expand(B, -1)
+            cos = torch.cos(ang).repeat(1, 2).to(torch.bfloat16).view(B, 1, D)
+            sin = torch.sin(ang)
+            sin = torch.cat([-sin, sin], -1).to(torch.bfloat16).view(B, 1, D)
+        h = self.embed[token]                                      # [B, hidden]
         for l in range(c["layers"]):
             x = F.rms_norm(h, (c["hidden"],), self.ln1[l], 1e-6)
             qkv = F.linear(x, self.wqkv[l])
-            qk = F.rms_norm(qkv[:, :(Hq + Hk) * D].view(1, Hq + Hk, D), (D,), None, 1e-6) * self.qkn[l]
+            qk = F.rms_norm(qkv[:, :(Hq + Hk) * D].view(B, Hq + Hk, D), (D,), None, 1e-6) * self.qkn[l]
             qk = qk * cos + torch.roll(qk, 64, -1) * sin            # rotate-half RoPE
-            v = qkv[:, (Hq + Hk) * D:].view(1, 1, Hk, D)
-            cache.decode_update_kv_cache(qk[:, Hq:].view(1, 1, Hk, D), v, l)
-            attn = cache.compute(qk[:, :Hq].view(1, 1, Hq, D), l)
-            h = self._sum_over_ranks(F.linear(attn.view(1, Hq * D), self.wo[l]), h)
+            v = qkv[:, (Hq + Hk) * D:].view(B, 1, Hk, D)
+            cache.decode_update_kv_cache(qk[:, Hq:].view(B, 1, Hk, D), v, l)
+            attn = cache.compute(qk[:, :Hq].view(B, 1, Hq, D), l)
+            h = self._sum_over_ranks(F.linear(attn.view(B, Hq * D), self.wo[l]), h)
             x = F.rms_norm(h, (c["hidden"],), self.ln2[l], 1e-6)
             gu = F.linear(x, self.wgu[l])
             h = self._sum_over_ranks(F.linear(F.silu(gu[:, :Ff]) * gu[:, Ff:], self.wd[l]), h)
@@ -710,6 +720,117 @@ def prefill_mode(args, cfg, device):
         "offload_bytes": offload_bytes, "gpu_launches_per_pass": res[-1][2]}), flush=True)
 
 
+# --------------------------------------------------------------------------------------------------------
+# batched decode of sequences of different lengths, K/V resident in HBM
+# --------------------------------------------------------------------------------------------------------
+CFG_VARLEN = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256,
+                  rope_theta=5.0e5, sink=4, local=64, interval=128, batch=16, min_len=16384, max_len=32768,
+                  min_k=1024, max_k=4096, threshold=0.85)
+
+
+def varlen_mode(args, device):
+    """Llama-3-8B-shaped decoder, batch 16, context lengths uniform in [16384, 32768] (seeded), K/V resident in HBM,
+    adaptive-k selection with 1024 - 4096 rows per head.  The per-sequence zone lengths live in device words that the
+    kernels read, so the whole batched step is one captured graph."""
+    from pariskv_b200 import _lib
+    from pariskv_b200.cache_hub.polar_cache_adaptivek_varlen import polar_cache as varlen_cache
+    from pariskv_b200.cache_hub.polar_cache import polar_cache as plain_cache
+    cfg = dict(CFG_VARLEN)
+    debug = False
+    if args.layers:
+        cfg["layers"], debug = args.layers, True
+    if args.batch:
+        cfg["batch"], debug = args.batch, True
+    K, W = args.steps, max(args.warmup, 3)
+    B, H, Hq, Lyr = cfg["batch"], cfg["kv_heads"], cfg["q_heads"], cfg["layers"]
+    gl = torch.Generator().manual_seed(2024)
+    lens = torch.randint(cfg["min_len"], cfg["max_len"] + 1, (B,), generator=gl).tolist()
+    Pmax = max(lens)
+    max_new = W + K + 2 * cfg["interval"] + 8
+    adaptive = args.selection == "adaptive"
+    common = dict(valid_start=[Pmax - n for n in lens], layer_num=Lyr, batch_size=B, max_length=Pmax + max_new,
+                  num_key_value_heads=H, num_heads=Hq, head_dim=128, dtype=torch.bfloat16,
+                  layer_mapping={str(i): str(device) for i in range(Lyr)}, max_new_length=max_new, sink_size=cfg["sink"],
+                  local_size=cfg["local"], core=0, nprobe=0, cache_unit_size=0, cache_cluster_num=0, num_gpus=1,
+                  model_size=8, dynamic_update_interval=cfg["interval"], enable_offload=False)
+    t_setup = time.time()
+    if adaptive:
+        cache = varlen_cache(final_topk=cfg["max_k"], adaptive_topk_threshold=cfg["threshold"],
+                             adaptive_topk_min_k=cfg["min_k"], adaptive_topk_max_k=cfg["max_k"], **common)
+    else:
+        cache = plain_cache(final_topk=2048, **common)
+    model = DecoderHarness(cfg, device, seed=4321)
+    g = torch.Generator(device=device).manual_seed(17)
+    for l in range(Lyr):      # left-padded lockstep prefill: sample b occupies columns [Pmax - len_b, Pmax)
+        k, v = synth_kv(g, Pmax, H, device)
+        k, v = k.expand(B, -1, -1, -1), v.expand(B, -1, -1, -1)      # the same synthetic stream, cut at different lengths
+        cache.prefill_update_kv_cache(None, k, v, l, 0)
+        del k, v
+    torch.cuda.synchronize(device)
+    setup_s = time.time() - t_setup
+    token = torch.full((B,), 11, device=device, dtype=torch.int64)
+    pos = torch.tensor([float(n) for n in lens], device=device)
+    use_graph = not args.no_graph and not adaptive     # the adaptive variants size their window product on the host
+    for _ in range(2):
+        token = model.step(cache, token, pos)
+        pos += 1
+    graph = None
+    if use_graph:
+        tok_s, saved = token.clone(), cache.host_state()
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            graph.capture_begin()
+            out = model.step(cache, tok_s, pos)
+            tok_s.copy_(out)
+            pos += 1
+            graph.capture_end()
+        torch.cuda.current_stream().wait_stream(side)
+        cache.set_host_state(saved)
+
+    def advance():
+        nonlocal token
+        if graph is not None:
+            graph.replay()
+            cache.note_replayed_step()
+        else:
+            token = model.step(cache, token, pos)
+            pos.add_(1)
+
+    for _ in range(W):
+        advance()
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        advance()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    cache.check_status()
+    launches = (_lib.launch_count() - n0) if graph is None else K * Lyr * 4
+    line = {"metric": "decode_tokens_per_s", "value": B * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": K,
+            "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"batched decode, Llama-3-8B architecture, batch {B}, per-sequence context lengths uniform in "
+                                   f"[{cfg['min_len']}, {cfg['max_len']}] (seeded), K/V resident in HBM, "
+                                   + (f"adaptive-k selection {cfg['min_k']}-{cfg['max_k']} rows per head, threshold {cfg['threshold']}"
+                                      if adaptive else "top-k 2048 per KV head"),
+                       "layers": Lyr, "batch": B, "lengths_min_max": [min(lens), max(lens)],
+                       "l2": "inputs larger than L2: weights plus the codes of 16 sequences are streamed every step"},
+            "clocks": clocks, "gpu_launches": int(launches), "cuda_graph": {"used": graph is not None, "captures": 1 if graph else 0},
+            "setup_s": round(setup_s, 1), "zone_keys_min_max": [min(cache.zone_len[0]), max(cache.zone_len[0])],
+            "selection": args.selection}
+    if debug:
+        line["invalid"] = "debug run with reduced layers / batch"
+    print(json.dumps(line), flush=True)
+
+
 def kernels_mode(args, cfg, device):
     """Cache path only: per step and layer one K/V append and one compute() on a random query."""
     from pariskv_b200 import _lib
@@ -914,7 +1035,7 @@ def main():
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
     ap.add_argument("--stage-steps", type=int, default=16, help="extra steps with per-kernel event timing")
     ap.add_argument("--no-graph", action="store_true", help="run every step eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--mode", default="decode", choices=["decode", "replicas", "kernels", "ops", "seqshard", "prefill"],
+    ap.add_argument("--mode", default="decode", choices=["decode", "replicas", "kernels", "ops", "seqshard", "prefill", "varlen"],
                     help="decode: the benchmark; with N GPUs the same sequence with its KV heads split over the ranks "
                          "(tensor parallel, strong scaling).  replicas: one independent sequence per GPU.  kernels: only "
                          "the cache path (append, retrieval chain, attention) per layer, no model; a small profiling "
@@ -929,11 +1050,14 @@ def main():
     ap.add_argument("--only", default=None, help="--mode ops: run only the ops whose name contains this text")
     ap.add_argument("--store", default="auto", choices=["auto", "host", "hbm"],
                     help="--mode seqshard: where a shard's K/V rows live (auto: HBM when they fit, else pinned host)")
+    ap.add_argument("--selection", default="adaptive", choices=["adaptive", "topk"],
+                    help="--mode varlen: adaptive-k selection (1024 - 4096 rows per head) or a fixed top-k of 2048")
+    ap.add_argument("--batch", type=int, default=None, help="--mode varlen, debug only: smaller batch (marks the line invalid)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the line invalid)")
     ap.add_argument("--context", type=int, default=None, help="debug only: shorter context (marks the line invalid)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 64 if args.mode == "seqshard" else 256
+        args.steps = 64 if args.mode in ("seqshard", "varlen") else 256
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -970,6 +1094,9 @@ def main():
 
     if args.mode == "seqshard":
         seqshard_mode(args, device, rank, world, local_rank)
+        return
+    if args.mode == "varlen":
+        varlen_mode(args, device)
         return
     if args.mode == "kernels":
         kernels_mode(args, cfg, device)

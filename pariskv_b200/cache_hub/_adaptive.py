@@ -59,12 +59,19 @@ class AdaptiveKCache(_base_cache):
         if total < max(self.FULL_ATTENTION_THRESHOLD, self.steady_size + 2 * self.final_topk) or N <= 0:
             return super().compute(queries, layer_idx)
         wk, wv = self.unified_keys_gpu[layer_idx], self.unified_values_gpu[layer_idx]
-        tiers, C, _ = self.retrieval_plan(N)
-        _, ex = ops.retrieve(queries, self.srht_diagonal_signs, self._mag_centers,
-                             self.codebook_gpu[layer_idx][:, :, :, :N], self.key_block_weight_gpu[layer_idx][:, :, :, :N],
-                             self.key_4bit_packed_gpu[layer_idx][:, :, :, :N, :], self.cluster_key_counts_gpu[layer_idx],
-                             tiers, C, 0, want=("cand", "scores_f32", "query_avg"), scratch=self._retrieve_scratch)
-        cand, cand_scores = ex["cand"], ex["scores_f32"].to(torch.bfloat16)   # the reference ranks bf16 scores
+        # rows of the candidate lists are c_max long; a sample's own count follows from its zone length, read on the
+        # device, and the rest of its row carries score -inf (no weight in the adaptive selection)
+        st = self._layer_state[layer_idx]
+        _, _, ex = ops.retrieve_ex(queries, self.srht_diagonal_signs, self._mag_centers, self.codebook_gpu[layer_idx],
+                                   self.key_block_weight_gpu[layer_idx], self.key_4bit_packed_gpu[layer_idx],
+                                   self.cluster_key_counts_gpu[layer_idx], self._c_max, 0, kv_len=st[4:4 + self.batch_size],
+                                   schedule=self._zone_schedule, want=("cand", "scores_f32", "query_avg"),
+                                   scratch=self._retrieve_scratch)
+        cand, cand_scores = ex["cand"], ex["scores_f32"]
+        C = self.retrieval_plan(N)[1]          # candidates of the longest sample
+        if min(self.zone_len[layer_idx]) == N:  # equal lengths: the lists as the reference shapes them, [bs,H,C]
+            cand, cand_scores = cand[:, :, :C].contiguous(), cand_scores[:, :, :C].contiguous()
+        cand_scores = cand_scores.to(torch.bfloat16)   # the reference ranks bf16 scores
         # window logits: a small dense product, left to the library as the reference does
         sl_logits = torch.einsum("bhd,bhkd->bhk", ex["query_avg"], wk[:, :, :n_win]).to(torch.float32) * self._attn_scale
         K_out = min(self._max_k, C)

@@ -4,7 +4,7 @@ from types import SimpleNamespace
 
 import torch
 
-from ... import ops
+from ... import ops, torch_ops  # noqa: F401  (registers torch.ops.pariskv.*)
 
 
 def _adaptive_topk(sl_logits, cand_logits, sl_vnorm, cand_indices, cand_vnorm, threshold, K_out, adaptive_k,
@@ -28,5 +28,5 @@ def adaptive_topk_cuda(query_avg, sink_local_keys, sl_vnorm, cand_scores, cand_i
     K_out = min(int(topk_cap), cand_scores.shape[-1])
     # the sink/local logits are a small dense product: left to the library, as the reference does
     sl_logits = torch.einsum("bhd,bhkd->bhk", query_avg, sink_local_keys).to(torch.float32) * attn_scale
-    return ops.adaptive_topk(sl_logits.contiguous(), cand_scores, float(attn_scale), sl_vnorm, cand_indices, cand_vnorm,
-                             float(threshold), K_out)
+    return torch.ops.pariskv.adaptive_k_fused(sl_logits.contiguous(), cand_scores, float(attn_scale), sl_vnorm, cand_indices,
+                                              cand_vnorm, float(threshold), K_out)

@@ -4,7 +4,7 @@ from types import SimpleNamespace
 
 import torch
 
-from ... import ops
+from ... import ops, torch_ops  # noqa: F401  (registers torch.ops.pariskv.*)
 
 
 def _update_cache_cnt(sorted_cluster_ids, topk_cluster_cnt, code_book, cache_cnt):
@@ -17,8 +17,4 @@ def load_kernel_module(path="collision.cu", name="update_cache_cnt", **_):
 
 
 def update_cache_cnt_cuda(sorted_cluster_ids, topk_cluster_cnt, codebook) -> torch.Tensor:
-    code_book = codebook.transpose(-1, -2).contiguous()
-    bs, H, N, B = code_book.shape
-    cache_cnt = torch.empty(bs, H, N, dtype=torch.int32, device=codebook.device)
-    ops.collision(sorted_cluster_ids.contiguous(), topk_cluster_cnt.contiguous(), code_book, cache_cnt)
-    return cache_cnt
+    return torch.ops.pariskv.collision(sorted_cluster_ids, topk_cluster_cnt, codebook.transpose(-1, -2).contiguous())

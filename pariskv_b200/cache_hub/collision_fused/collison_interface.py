@@ -4,7 +4,7 @@ from types import SimpleNamespace
 
 import torch
 
-from ... import ops
+from ... import ops, torch_ops  # noqa: F401  (registers torch.ops.pariskv.*)
 
 
 def _update_cache_cnt(sorted_cluster_ids, cluster_key_counts, code_book, tier_counts, cache_cnt):
@@ -21,4 +21,4 @@ def load_kernel_module(path="collision.cu", name="update_cache_cnt", **_):
 def update_cache_cnt_cuda_interface(sorted_cluster_ids, cluster_key_counts, codebook, tier_counts) -> torch.Tensor:
     """sorted_cluster_ids i64|i32 [bs,H,B,NC], cluster_key_counts i32 [bs,H,B,NC], codebook u8 [bs,H,B,N] (any
     strides), tier_counts list[int] -> cache_cnt i32 [bs,H,N]."""
-    return ops.collision_fused(sorted_cluster_ids, cluster_key_counts, codebook, list(tier_counts))
+    return torch.ops.pariskv.collision_fused(sorted_cluster_ids, cluster_key_counts, codebook, [int(t) for t in tier_counts])

@@ -13,8 +13,8 @@ class polar_cache(AdaptiveKCache):
     def __init__(self, *args, collision_ratio=None, candidate_ratio=None, enable_recall: bool = False,
                  adaptive_topk_threshold: float = 0.85, adaptive_topk_min_k=None, adaptive_topk_max_k=None,
                  adaptive_topk_max_k_ratio: float = 0.1, **kwargs):
-        if not kwargs.get("enable_offload", True):
-            raise ValueError("the varlen adaptive-k cache supports enable_offload=True only, like the reference")
+        # the reference's class is offload-only (cache_hub/polar_cache_adaptivek_varlen.py:228-231); here the same
+        # kernels read the store from pinned host memory or from HBM, so enable_offload=False is allowed as well
         super().__init__(*args, **kwargs)
         max_k = int(adaptive_topk_max_k if adaptive_topk_max_k is not None else os.environ.get("ADAPTIVE_TOPK_MAX_K", "800"))
         min_k = int(adaptive_topk_min_k if adaptive_topk_min_k is not None else os.environ.get("ADAPTIVE_TOPK_MIN_K", "100"))

@@ -4,7 +4,7 @@ from types import SimpleNamespace
 
 import torch
 
-from ... import ops
+from ... import ops, torch_ops  # noqa: F401  (registers torch.ops.pariskv.*)
 
 
 def _partial_rerank(coarse_indices, key_4bit, key_block_weight, q_blocks, q_norm, mag_centers, B, m, approx_scores,
@@ -28,7 +28,9 @@ def partial_rerank_cuda(coarse_indices, key_4bit, key_block_weight, q_blocks, q_
     assert key_4bit.stride(-1) == 1
     assert B == 16 and m == 8, "only B = 16, m = 8 is supported"
     bs, H, C = coarse_indices.shape
-    v4b = torch.empty(bs, H, B, C, m, dtype=torch.bfloat16, device=coarse_indices.device) if want_v4b else None
+    if not want_v4b:
+        return torch.ops.pariskv.rerank(coarse_indices, key_4bit, key_block_weight, q_blocks, q_norm, mag_centers), None
+    v4b = torch.empty(bs, H, B, C, m, dtype=torch.bfloat16, device=coarse_indices.device)
     scores, _ = ops.rerank(coarse_indices, key_4bit, key_block_weight, q_blocks, q_norm, mag_centers, v4b=v4b)
     return scores, v4b
 

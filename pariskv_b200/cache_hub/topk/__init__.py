@@ -5,17 +5,17 @@ from types import SimpleNamespace
 
 import torch
 
-from ... import ops
+from ... import torch_ops  # noqa: F401  (registers torch.ops.pariskv.*)
 
 
 def _topk_2d(input, k):
     assert input.dim() == 2, "input must be 2D [B, L]"
-    return ops.topk(input, int(k))
+    return torch.ops.pariskv.topk(input, int(k))
 
 
 def _topk_3d(input, k):
     assert input.dim() == 3, "input must be 3D [bs, kv_heads, kv_len]"
-    return ops.topk(input, int(k))
+    return torch.ops.pariskv.topk(input, int(k))
 
 
 def load_radix_topk_ext(verbose: bool = False):
@@ -27,7 +27,7 @@ def bucket_topk(input: torch.Tensor, k: int) -> torch.Tensor:
     assert k > 0, f"k must be positive, got {k}"
     if input.dim() not in (2, 3):
         raise ValueError(f"input must be 2D or 3D, got {input.dim()}D")
-    return ops.topk(input, int(k))
+    return torch.ops.pariskv.topk(input, int(k))
 
 
 radix_topk = bucket_topk

@@ -606,7 +606,16 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
     p.scores_f32[row_base + out_pos + i] = s;
     p.cand_out[row_base + out_pos + i] = key;
   }
-  if (chunk == 0 && tid == 0 && p.n_cand_out) p.n_cand_out[bh] = (int32_t)C_here;
+  if (chunk == 0) {
+    if (tid == 0 && p.n_cand_out) p.n_cand_out[bh] = (int32_t)C_here;
+    // per-sample lengths: rows are longer than this sample's candidate list; the tail gets (score -inf, key 0), so a
+    // consumer that walks whole rows (the adaptive selection) gives those entries no weight
+    if (p.n_dev)
+      for (int64_t i = C_here + tid; i < p.C; i += SEL_THREADS) {
+        p.scores_f32[row_base + i] = -INFINITY;
+        p.cand_out[row_base + i] = 0;
+      }
+  }
   PK_MARK(4, mk);
   if (p.K <= 0) return;
 

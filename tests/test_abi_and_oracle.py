@@ -196,3 +196,37 @@ def test_host_gather_runs_on_cpu(oracle):
     idx[1, 2, 3] = 100
     with pytest.raises(RuntimeError, match="out of bounds"):
         ops.gather_kv_out_cpu(src, idx, out)
+
+
+def test_torch_ops_are_registered_with_schemas_and_shape_functions():
+    """The seven ops are torch custom ops (namespace pariskv): the dispatcher knows their schemas and, through the
+    fake implementations, their output shapes - checked here on meta tensors, no GPU involved."""
+    from pariskv_b200 import torch_ops
+    for name in torch_ops.OPS:
+        assert hasattr(torch.ops.pariskv, name), name
+    m = lambda *shape, dtype: torch.empty(*shape, dtype=dtype, device="meta")
+    bs, H, B, NC, N, C = 2, 3, 16, 256, 1000, 100
+    out = torch.ops.pariskv.collision_fused(m(bs, H, B, NC, dtype=torch.int64), m(bs, H, B, NC, dtype=torch.int32),
+                                            m(bs, H, B, N, dtype=torch.uint8), [10, 20, 30, 40, 50, 60])
+    assert out.shape == (bs, H, N) and out.dtype == torch.int32
+    out = torch.ops.pariskv.collision(m(bs, H, B, NC, dtype=torch.int32), m(bs, H, B, dtype=torch.int32),
+                                      m(bs, H, N, B, dtype=torch.int32))
+    assert out.shape == (bs, H, N) and out.dtype == torch.int32
+    out = torch.ops.pariskv.topk(m(bs, H, N, dtype=torch.int32), C)
+    assert out.shape == (bs, H, C) and out.dtype == torch.int64
+    out = torch.ops.pariskv.rerank(m(bs, H, C, dtype=torch.int64), m(bs, H, B, N, 4, dtype=torch.uint8),
+                                   m(bs, H, B, N, dtype=torch.bfloat16), m(bs, H, B, 8, dtype=torch.bfloat16),
+                                   m(bs, H, 1, dtype=torch.bfloat16), m(8, dtype=torch.bfloat16))
+    assert out.shape == (bs, H, C) and out.dtype == torch.bfloat16
+    k, idx = torch.ops.pariskv.adaptive_k_fused(m(bs, H, 68, dtype=torch.float32), m(bs, H, C, dtype=torch.bfloat16), 0.088,
+                                                m(bs, H, 68, dtype=torch.float32), m(bs, H, C, dtype=torch.int64),
+                                                m(bs, H, C, dtype=torch.float32), 0.9, 64)
+    assert k.shape == (bs, H) and idx.shape == (bs, H, 64) and idx.dtype == torch.int64
+    schema = str(torch.ops.pariskv.gather_trans.default._schema)
+    assert "Tensor(a!) dst_k" in schema and "Tensor(b!) dst_v" in schema
+    # the host-side gather runs through the registered op
+    src = torch.randn(1, 2, 50, 128).to(torch.bfloat16)
+    index = torch.randint(0, 50, (1, 2, 7))
+    out = torch.empty(1, 2, 7, 128, dtype=torch.bfloat16)
+    torch.ops.pariskv.gather(src, index, out)
+    assert torch.equal(out, torch.gather(src, 2, index[..., None].expand(1, 2, 7, 128)))

@@ -400,3 +400,85 @@ def test_per_query_head_retrieval_option(oracle):
     wv = torch.cat([rep(V[:, :, :sink]), rep(V[:, :, P - local:]), rep(nv), oracle.gather(rep(zv), sel)], 2)
     ref = oracle.attention(q, wk, wv)                      # Hq query heads over Hq "KV heads": group size one
     assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
+
+
+def test_batch_of_different_lengths_equals_single_sequences(oracle):
+    """Three samples of different lengths decoded as ONE batch (left-padded lockstep prefill, per-sample zone lengths
+    read on the device) across a flush: every step, every sample's retrieved indices and attention output must be
+    exactly what a batch-1 cache of that sample gives, and the indices must be the oracle's."""
+    g = torch.Generator().manual_seed(51)
+    H, Hq, sink, local, I, topk = 2, 8, 4, 16, 8, 48
+    lens = [2300, 3100, 2650]
+    bs, Pmax, steps = len(lens), max(lens), 12
+    Ks = [synth_keys(g, 1, H, n) for n in lens]
+    Vs = [torch.randn(1, H, n, 128, generator=g).to(torch.bfloat16) for n in lens]
+
+    def make(batch, starts):
+        from pariskv_b200.cache_hub.polar_cache import polar_cache
+        return polar_cache(valid_start=starts, layer_num=1, batch_size=batch, max_length=Pmax + 32, num_key_value_heads=H,
+                           num_heads=Hq, head_dim=128, dtype=torch.bfloat16, layer_mapping={"0": DEV}, max_new_length=32,
+                           sink_size=sink, local_size=local, core=0, nprobe=0, cache_unit_size=0, cache_cluster_num=0,
+                           num_gpus=1, model_size=8, final_topk=topk, dynamic_update_interval=I, enable_offload=True)
+
+    batched = make(bs, [Pmax - n for n in lens])
+    kp = torch.zeros(bs, Pmax, H, 128, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    for b, n in enumerate(lens):                     # left padding: sample b starts at column Pmax - n
+        kp[b, Pmax - n:] = Ks[b][0].transpose(0, 1)
+        vp[b, Pmax - n:] = Vs[b][0].transpose(0, 1)
+    batched.prefill_update_kv_cache(None, kp.to(DEV), vp.to(DEV), 0, 0)
+    singles = []
+    for b, n in enumerate(lens):
+        c = make(1, [0])
+        c.prefill_update_kv_cache(None, Ks[b].transpose(1, 2).contiguous().to(DEV), Vs[b].transpose(1, 2).contiguous().to(DEV), 0, 0)
+        singles.append(c)
+    assert batched.zone_len[0] == [n - sink - local for n in lens]
+    signs = batched.srht_diagonal_signs.cpu()
+    for t in range(steps):
+        nk = synth_keys(g, bs, H, 1).transpose(1, 2).contiguous()      # [bs,1,H,128]
+        nv = torch.randn(bs, 1, H, 128, generator=g).to(torch.bfloat16)
+        q = (torch.randn(bs, 1, Hq, 128, generator=g) * 0.5).to(torch.bfloat16)
+        batched.decode_update_kv_cache(nk.to(DEV), nv.to(DEV), 0)
+        out = batched.compute(q.to(DEV), 0)
+        for b, n in enumerate(lens):
+            Ks[b] = torch.cat([Ks[b], nk[b:b + 1].transpose(1, 2)], 2)
+            singles[b].decode_update_kv_cache(nk[b:b + 1].to(DEV), nv[b:b + 1].to(DEV), 0)
+            one = singles[b].compute(q[b:b + 1].to(DEV), 0)
+            assert torch.equal(out[b:b + 1], one), (t, b)
+            kb = int(batched.last_n_sel[b, 0])
+            assert kb == singles[b].last_topk_indices.shape[2] == topk
+            assert torch.equal(batched.last_topk_indices[b, :, :kb], singles[b].last_topk_indices[0]), (t, b)
+            if t in (0, steps - 1):                   # before and after the flush: the oracle on this sample's zone
+                N = batched.zone_len[0][b]
+                zk = Ks[b][:, :, sink:sink + N].contiguous()
+                cb, w, pk = oracle.encode(zk, signs)
+                _, C, Kf = batched.retrieval_plan(N)
+                _, coll = batched._get_adaptive_ratios(N)
+                r = oracle.retrieve(q[b:b + 1], signs, cb, w, pk, oracle.cluster_counts(cb), batched._mag_centers.cpu(), coll, C, Kf)
+                assert torch.equal(batched.last_topk_indices[b:b + 1, :, :Kf].cpu(), r["final"]), (t, b)
+    assert batched.zone_len[0] == [n - sink - local + I for n in lens], "one flush of the update buffer was expected"
+    batched.check_status()
+
+
+def test_append_reports_a_full_zone_through_its_status_word():
+    """A flush that finds no room in the zone publishes nothing and raises the layer's error word; the host-side
+    mirror refuses the step before it is launched.  Here the launch is forced through the op itself, with a state
+    that claims a zone already at capacity: every address stays valid, nothing faults."""
+    from pariskv_b200 import ops
+    cache = _make_cache(2300, 8, 1, 2, 8, 4, 16, 8, 32, False, 1)
+    g = torch.Generator().manual_seed(3)
+    K = synth_keys(g, 1, 2, 2300)
+    V = torch.randn(1, 2, 2300, 128, generator=g).to(torch.bfloat16)
+    cache.prefill_update_kv_cache(None, K.transpose(1, 2).contiguous().to(DEV), V.transpose(1, 2).contiguous().to(DEV), 0, 0)
+    st = cache._layer_state[0]
+    st[0] = cache.window_capacity - 1            # the next row fills the window ...
+    st[4] = cache.zone_capacity                  # ... and the zone claims to be full
+    row = torch.zeros(1, 1, 2, 128, dtype=torch.bfloat16, device=DEV)
+    ops.append_encode(row, row, cache.srht_diagonal_signs, cache.unified_keys_gpu[0], cache.unified_values_gpu[0],
+                      cache._win_codes[0], cache._win_weight[0], cache._win_4bit[0], cache._win_vnorm[0], cache.codebook_gpu[0],
+                      cache.key_block_weight_gpu[0], cache.key_4bit_packed_gpu[0], None, cache.cluster_key_counts_gpu[0],
+                      cache._store_kv[0], st, cache.sink_size, cache.dynamic_update_interval)
+    torch.cuda.synchronize()
+    assert st.tolist()[3] == 1 and st.tolist()[4] == cache.zone_capacity
+    with pytest.raises(RuntimeError, match="no room for a flush"):
+        cache.check_status()

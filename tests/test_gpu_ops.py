@@ -521,3 +521,26 @@ def test_mirror_rerank_fused_returns_ascending_indices(ops, oracle):
     for h in range(2):
         order = sorted(range(600), key=lambda i: (-float(s32[0, h, i]), i))[:100]
         assert sorted(int(cand[0, h, i]) for i in order) == fin[0, h].tolist()
+
+
+def test_torch_custom_ops_run_the_same_kernels(ops, oracle):
+    """torch.ops.pariskv.* (the registered custom ops the mirror modules call) give the bits of the direct calls."""
+    from pariskv_b200 import torch_ops  # noqa: F401
+    g = torch.Generator().manual_seed(8)
+    ids, counts, codes = _rand_collision_inputs(g, 1, 2, 16, 256, 3000)
+    tiers = [30, 90, 180, 300, 450, 600]
+    a = torch.ops.pariskv.collision_fused(ids.to(DEV), counts.to(DEV), codes.to(DEV), list(tiers))
+    assert torch.equal(a, ops.collision_fused(ids.to(DEV), counts.to(DEV), codes.to(DEV), tiers))
+    cand = torch.ops.pariskv.topk(a, 300)
+    assert torch.equal(cand, ops.topk(a, 300))
+    pk, w, qb, qn = (t.to(DEV) for t in _rerank_inputs(g, 1, 2, 3000))
+    cen = oracle.constants()[1].to(DEV)
+    s = torch.ops.pariskv.rerank(cand, pk, w, qb, qn, cen)
+    assert torch.equal(s, ops.rerank(cand, pk, w, qb, qn, cen)[0])
+    src_k = torch.randn(1, 2, 3000, 128, generator=g).to(torch.bfloat16).pin_memory()
+    src_v = torch.randn(1, 2, 3000, 128, generator=g).to(torch.bfloat16).pin_memory()
+    dk = torch.zeros(1, 2, 300, 128, dtype=torch.bfloat16, device=DEV)
+    dv = torch.zeros_like(dk)
+    torch.ops.pariskv.gather_trans(src_k, src_v, cand, dk, dv)
+    idx = cand.cpu()[..., None].expand(1, 2, 300, 128)
+    assert torch.equal(dk.cpu(), torch.gather(src_k, 2, idx)) and torch.equal(dv.cpu(), torch.gather(src_v, 2, idx))
