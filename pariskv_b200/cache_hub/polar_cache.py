@@ -230,10 +230,10 @@ class polar_cache(KV_Cache):
         return key_states[:, vs:], value_states[:, vs:]
 
     def _valid_start(self, b):
-        vs = self.valid_start
-        if isinstance(vs, (list, tuple)) or (torch.is_tensor(vs) and vs.dim() > 0):
-            return int(vs[b])
-        return int(vs)
+        vs = self.valid_start     # a number, or one per sample (list, tensor, numpy array: the reference passes the latter)
+        if getattr(vs, "ndim", None) == 0 or not hasattr(vs, "__len__"):
+            return int(vs)
+        return int(vs[b])
 
     def _prefill_sample(self, k, v, layer, b, vs):
         """k, v: [seq_len, H, 128] of one sample; tokens before `vs` are padding."""
