@@ -420,10 +420,6 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const ChainQuery& cq = p.q;
-#ifdef PK_PHASES
-  const bool mk = blockIdx.x == 1 && blockIdx.y == 0;
-#endif
-  PK_MARK(0, mk);
   if (cq.n_dev) pdl_wait();  // the zone length may have been written by the kernel just before this one
   const int64_t N = cq.n_dev ? min(max((int64_t)cq.n_dev[b], (int64_t)1), p.N) : p.N;
   const int64_t Nv = N + p.mis;
@@ -455,7 +451,6 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
   }
   pdl_wait();     // the code loads above do not depend on the kernel before this one; the query below does
   pdl_trigger();
-  PK_MARK(1, mk);
 
   // ---- prologue: query, cluster ranking, tier table ----
   {
@@ -503,7 +498,6 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
     *reinterpret_cast<int4*>(my + lane * 8) = c0;
     *reinterpret_cast<int4*>(my + lane * 8 + 4) = c1;
     __syncthreads();
-    PK_MARK(2, mk);
     const int n_tiers = (int)s_tiers[8];
     unsigned tier[8];
 #pragma unroll
@@ -551,11 +545,9 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
       excl += cnt[rr];
     }
     __syncthreads();  // the table is complete and the staging area is free again
-    PK_MARK(3, mk);
     for (int i = tid; i < 16 * 256; i += CC_THREADS) hist[i] = 0;
     __syncthreads();
   }
-  PK_MARK(4, mk);
 
   // a chunk covered in one pass gets two histograms (its halves), so the selection kernel can run two blocks on it
   const bool split = p.chunk_keys <= CC_PASS;
@@ -634,7 +626,6 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
     }
   }
   __syncthreads();
-  PK_MARK(5, mk);
   {
     const int half = tid >> 8, bin = tid & 255;
     if (half == 0 || split) {
@@ -646,7 +637,6 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
         p.chunk_hist[((int64_t)bh * p.n_hist + row) * 256 + bin] = t;
     }
   }
-  PK_MARK(6, mk);
 }
 
 // Unfused single-tier op: codes are int32 [bs,H,N,B] contiguous; one thread per key.
@@ -1021,8 +1011,3 @@ extern "C" int pk_collision_fused_static(const pk_tensor* sorted_cluster_ids, co
                             kStaticTableBytes, stream);
 }
 
-#ifdef PK_PHASES
-extern "C" int pk_debug_phases_collision(unsigned long long* out64) {
-  return cudaMemcpyFromSymbol(out64, pk::g_pk_phase, sizeof(unsigned long long) * 64) == cudaSuccess ? PK_OK : PK_ERR_CUDA;
-}
-#endif

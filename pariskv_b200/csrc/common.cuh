@@ -102,21 +102,6 @@ inline cudaError_t launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block,
 
 // ---- device side ----
 #ifdef __CUDACC__
-#ifdef PK_PHASES
-// Development aid (never part of a normal build): thread 0 of one chosen block stores the global timer at numbered
-// points of a kernel, so the phases of a single block can be laid out on a time line.
-static __device__ unsigned long long g_pk_phase[64];  // one copy per translation unit
-__device__ __forceinline__ void pk_mark(int i, bool on) {
-  if (on && threadIdx.x == 0) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_pk_phase[i] = t;
-  }
-}
-#define PK_MARK(i, on) pk::pk_mark(i, on)
-#else
-#define PK_MARK(i, on) ((void)0)
-#endif
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -245,7 +245,6 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
     mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, off));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
   }
-  PK_MARK(9, blockIdx.y == 0);
   float scale = (float)(FT_BINS - 1) / (mx - mn);
   if (!(scale > 0.0f) || !(scale < INFINITY)) return false;  // flat or non-finite range (the same for every thread)
   auto bin_of = [&](uint32_t u) -> unsigned {
@@ -253,9 +252,7 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
   };
   for (int i = tid; i < n; i += NT) atomicAdd(&hist[bin_of(raw[i])], 1u);
   __syncthreads();
-  PK_MARK(10, blockIdx.y == 0);
   block_threshold_bin<NT>(hist, FT_BINS, (unsigned)K, s_w, s_w + 2 * NW);
-  PK_MARK(11, blockIdx.y == 0);
   const unsigned T = s_w[2 * NW], above = s_w[2 * NW + 1], in_bin = s_w[2 * NW + 2];
   if (in_bin > (unsigned)FT_TIES) return false;
   const unsigned rem = (unsigned)K - above;  // taken from the threshold bin
@@ -270,7 +267,6 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
     flag[i] = f;
   }
   __syncthreads();
-  PK_MARK(12, blockIdx.y == 0);
   const int n_tie = (int)s_w[2 * NW + 3];
   for (int t = tid; t < n_tie; t += NT) {
     const uint2 me = tie[t];
@@ -282,7 +278,6 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
     flag[me.y] = rk < rem ? 1 : 0;
   }
   __syncthreads();
-  PK_MARK(13, blockIdx.y == 0);
   // ordered compaction: a contiguous span of positions per thread, one scan; the selected positions go to a list in
   // shared memory (over the histogram, K <= FT_BINS), so that the candidate ids are then fetched in one batch
   const int per = (n + NT - 1) / NT;
@@ -296,7 +291,6 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
     for (int i = i0; i < i1; i++)
       if (flag[i]) sel[pos++] = (unsigned)i;
     __syncthreads();
-    PK_MARK(14, blockIdx.y == 0);
     for (int base = tid; base < K; base += NT * 8) {
       int64_t cv[8];
 #pragma unroll
@@ -449,10 +443,6 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t bh = blockIdx.y, chunk = blockIdx.x;
   const int b = (int)(bh / a.H), h = (int)(bh % a.H);
-#ifdef PK_PHASES
-  const bool mk = blockIdx.x == 1 && blockIdx.y == 0;
-#endif
-  PK_MARK(0, mk);
   pdl_wait();  // counts, block histograms, query blocks and the zeroed arrival counters come from the collision kernel
   pdl_trigger();
   const int64_t N = p.n_dev ? min(max((int64_t)p.n_dev[b], (int64_t)1), p.N) : p.N;
@@ -504,7 +494,6 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
   }
   if (tid < 8) s_misc[tid] = 0;
   __syncthreads();
-  PK_MARK(1, mk);
   // threshold bin: suffix sums over 256 bins (8 warps x 32 bins)
   unsigned v = tid < 256 ? g_tot : 0u, incl = v;
 #pragma unroll
@@ -538,7 +527,6 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
   // candidates of this (batch, head) held by this shard
   const int64_t C_here = min((int64_t)s_misc[4] + (int64_t)min(tot[T], quota), p.C);
 
-  PK_MARK(2, mk);
   unsigned gt_run = 0, eq_run = 0;  // running counts over this chunk (all threads hold the same values)
   unsigned n_list = 0;
   for (int64_t t0 = v_begin; t0 < v_end; t0 += 16 * SEL_THREADS) {
@@ -593,7 +581,6 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
     __syncthreads();
   }
   n_list = gt_run + (min(eq_base + eq_run, quota) - min(eq_base, quota));
-  PK_MARK(3, mk);
   const int64_t row_base = bh * p.C;
   const int64_t out_pos = (int64_t)gt_base + min(eq_base, quota);
   const float qn = bf2f(a.q_norm[bh]);
@@ -616,7 +603,6 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
         p.cand_out[row_base + i] = 0;
       }
   }
-  PK_MARK(4, mk);
   if (p.K <= 0) return;
 
   // ---- the block that arrives last for this (batch, head) selects the final top-K ----
@@ -626,7 +612,6 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
   __syncthreads();
   if (!s_misc[5]) return;
   __threadfence();
-  PK_MARK(8, blockIdx.y == 0);
   const int K_here = (int)min(p.K, C_here);
   if (K_here > 0) {
     // shared memory of the final stage (over the candidate list, no longer needed):
@@ -649,7 +634,6 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
     if (p.n_sel_out) p.n_sel_out[bh] = K_here;
     p.counters[bh] = 0;
   }
-  PK_MARK(15, blockIdx.y == 0);
 }
 
 bool rerank_fast_layout(const RerankArgs& a) {
@@ -781,8 +765,3 @@ extern "C" int pk_rerank(const pk_tensor* coarse_indices, const pk_tensor* key_4
   return launch_rerank(a, bs * H, sbf, s32, v, (cudaStream_t)stream);
 }
 
-#ifdef PK_PHASES
-extern "C" int pk_debug_phases_select(unsigned long long* out64) {
-  return cudaMemcpyFromSymbol(out64, pk::g_pk_phase, sizeof(unsigned long long) * 64) == cudaSuccess ? PK_OK : PK_ERR_CUDA;
-}
-#endif
