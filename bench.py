@@ -1258,10 +1258,10 @@ def main():
     N = cache.cpu_valid_end[0]
     tiers, C, Kf = cache.retrieval_plan(N)
     n_rows = cfg["sink"] + cfg["local"] + cfg["interval"] // 2 + Kf
-    alg = {  # algorithmic bytes per launch (one layer, all KV heads): codes + counts; candidates; rows
+    alg = {  # algorithmic bytes per launch (one layer, this rank's KV heads): codes + counts; candidates (selection,
+        # rerank and final top-K are one launch); rows
         "collision": 20 * N * H,
-        "select_rerank": (4 * N + 8 * C + 106 * C) * H,
-        "final_topk": (10 * C + 8 * Kf) * H,
+        "select_rerank": (4 * N + 8 * C + 106 * C + 10 * C + 8 * Kf) * H,
         "attention": n_rows * 512 * H,
     }
     stages_out = {}
@@ -1275,12 +1275,13 @@ def main():
     retrieval_us = sum(stages_out.get(s, {}).get("avg_us", 0.0) for s in
                        ("query_prep", "rank_table", "collision", "select_rerank", "final_topk"))
     coll = stages_out.get("collision", {})
-    roofline = {"kernel": "collision_kernel (weighted multi-tier collision count)", "bound": "hbm",
+    roofline = {"kernel": "chain_collision_kernel (query preparation + cluster ranking + weighted multi-tier collision count)",
+                "bound": "hbm",
                 "achieved": coll.get("achieved_gbs"), "peak": peak, "unit": "GB/s",
                 "frac": round(coll["achieved_gbs"] / peak, 4) if coll else None, "peak_kind": f"of {peak_kind}",
-                # DRAM bytes of one launch from the ncu capture summarised under profiles/ (16.06 B per key and head
+                # DRAM bytes of one launch from the ncu capture summarised under profiles/ (16.19 B per key and head
                 # at N = 131004), scaled linearly to this run's N
-                "traffic": int(round(16.06 * N * H)), "algorithmic_bytes_per_launch": alg["collision"],
+                "traffic": int(round(16.19 * N * H)), "algorithmic_bytes_per_launch": alg["collision"],
                 # for context: the nominal HBM3e figure (the fraction that counts is the one of the measured peak)
                 "frac_of_nominal_8000_gbs": round(coll["achieved_gbs"] / 8000.0, 4) if coll else None}
     att = stages_out.get("attention", {})
