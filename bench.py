@@ -251,6 +251,26 @@ def synth_kv(gen, P, H, device):
     return z.to(torch.bfloat16), v.to(torch.bfloat16)
 
 
+class numa_scope:
+    """hostmem.near_device unless --no-numa was given; `.bound` says what was done."""
+
+    def __init__(self, device, args):
+        from pariskv_b200 import hostmem
+        self._cm = None if getattr(args, "no_numa", False) else hostmem.near_device(device)
+        self.bound = None
+
+    def __enter__(self):
+        if self._cm is not None:
+            self._cm.__enter__()
+            self.bound = self._cm.bound
+        return self
+
+    def __exit__(self, *exc):
+        if self._cm is not None:
+            self._cm.__exit__(*exc)
+        return False
+
+
 def build_cache(cfg, device, max_new, seed, offload=True, rank=0, world=1):
     """The cache of this rank: with world > 1 it holds KV heads [rank * H / world, (rank + 1) * H / world) of the same
     synthetic sequence (keys / values are drawn for all heads with the same generator, then sliced)."""
@@ -1045,6 +1065,8 @@ def main():
                          "all-reduces")
     ap.add_argument("--no-offload", action="store_true",
                     help="variant, not the benchmark configuration: keep the K/V rows in HBM instead of pinned host memory")
+    ap.add_argument("--no-numa", action="store_true",
+                    help="variant: do not place the pinned K/V store on the NUMA node of the GPU's host link")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
                     help="--mode seqshard: the two per-layer exchanges as NCCL all-gathers or as stores into peer memory")
     ap.add_argument("--only", default=None, help="--mode ops: run only the ops whose name contains this text")
@@ -1137,10 +1159,14 @@ def main():
                      "what": "rank r's retrieved indices == heads [r H/N, (r+1) H/N) of the oracle's single-GPU result "
                              "(bit for bit), attention within 2e-2, reduction over ranks == fp32 sum in rank order"}
         model = DecoderHarness(cfg, device, seed=1234, rank=rank, world=world, reducer=reducer)
-        cache = build_cache(cfg, device, max_new, seed=100, offload=not args.no_offload, rank=rank, world=world)
     else:
         model = DecoderHarness(cfg, device, seed=1234)
-        cache = build_cache(cfg, device, max_new, seed=100 + rank, offload=not args.no_offload)
+    # the K/V store is first touched on the CPUs of this GPU's NUMA node: its rows are then local to the GPU's link
+    with numa_scope(device, args) as numa:
+        if tp:
+            cache = build_cache(cfg, device, max_new, seed=100, offload=not args.no_offload, rank=rank, world=world)
+        else:
+            cache = build_cache(cfg, device, max_new, seed=100 + rank, offload=not args.no_offload)
     setup_s = time.time() - t_setup
     token = torch.tensor([11], device=device)
     use_graph = not args.no_graph
@@ -1286,7 +1312,8 @@ def main():
                 "frac_of_nominal_8000_gbs": round(coll["achieved_gbs"] / 8000.0, 4) if coll else None}
     att = stages_out.get("attention", {})
     # the host link's own rate in this run: one contiguous 512 MiB copy from pinned host memory by the copy engine
-    src = torch.empty(512 << 20, dtype=torch.uint8, pin_memory=True)
+    with numa_scope(device, args):
+        src = torch.empty(512 << 20, dtype=torch.uint8, pin_memory=True)
     dst = torch.empty(512 << 20, dtype=torch.uint8, device=device)
     dst.copy_(src, non_blocking=True)
     torch.cuda.synchronize(device)
@@ -1333,7 +1360,7 @@ def main():
         "cpu_baseline": cpu,
         "published_reference": {"decode_tok_s_128k_bs1": 41.10, "note": "hardware and model unstated by the reference"},
         "cuda_graph": {"used": use_graph, "captures": runner.captures},
-        "setup_s": round(setup_s, 1), "zone_keys_per_head": N, "candidates": C, "final_topk": Kf,
+        "setup_s": round(setup_s, 1), "host_numa": numa.bound, "zone_keys_per_head": N, "candidates": C, "final_topk": Kf,
         "kv_heads_per_rank": H,
     }
     if tp:

@@ -241,51 +241,67 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // tile maxima / scale factors are computed one tile per thread, then every thread sums its output
-  // dimension over the tiles with independent loads (no serial chain of L2 round trips)
-  float* s_f = obuf;            // scale factor per tile (reuses the merge buffer)
-  float* s_lt = obuf + 1024;    // l per tile
-  __shared__ float s_red[4];
-  for (int g = 0; g < p.G; g++) {
-    const int64_t bq = (int64_t)b * p.Hq + h * p.G + g;
-    const float* rec = p.ws + bq * p.n_tiles * ATT_REC;
-    float mloc = -INFINITY;
-    for (int64_t t = tid; t < p.n_tiles; t += ATT_THREADS) {
-      const float mt = __ldcg(rec + t * ATT_REC + 128);
-      s_f[t & 1023] = mt;
-      s_lt[t & 1023] = __ldcg(rec + t * ATT_REC + 129);
-      mloc = fmaxf(mloc, mt);
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
-    __syncthreads();
-    if ((tid & 31) == 0) s_red[tid >> 5] = mloc;
-    __syncthreads();
-    const float M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
-    for (int64_t t = tid; t < p.n_tiles; t += ATT_THREADS) {
-      const float mt = s_f[t & 1023];
-      s_f[t & 1023] = (mt == -INFINITY) ? 0.0f : exp2f(mt - M);
-    }
-    __syncthreads();
-    float L = 0.0f, O = 0.0f;
-    int64_t t = 0;
-    for (; t + 8 <= p.n_tiles; t += 8) {
-      float v[8];
-#pragma unroll
-      for (int i = 0; i < 8; i++) v[i] = __ldcg(rec + (t + i) * ATT_REC + tid);
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        O += v[i] * s_f[(t + i) & 1023];
-        L += s_lt[(t + i) & 1023] * s_f[(t + i) & 1023];
+  // Up to ATT_GQ query heads are merged at a time.  Warp g takes head g: it reads the tiles' (m, l), reduces the
+  // maximum and the denominator with shuffles and leaves one scale factor per tile in shared memory; after ONE
+  // block barrier every thread sums its output dimension over the tiles for all of these heads, the loads of
+  // several tiles and heads in flight together (no serial chain of L2 round trips, no barrier per head).
+  float* s_f = obuf;                    // [ATT_GQ][1024] scale factor per tile (reuses the merge buffer)
+  __shared__ float s_L[ATT_GQ], s_M[ATT_GQ];
+  static_assert(ATT_THREADS == 32 * ATT_GQ, "one warp per query head of a group");
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int qg = 0; qg < p.n_qgroups; qg++) {
+    const int n_heads = min(ATT_GQ, p.G - qg * ATT_GQ);
+    const int64_t bq0 = (int64_t)b * p.Hq + h * p.G + qg * ATT_GQ;
+    if (qg) __syncthreads();            // the scale factors of the previous group have been consumed
+    if (warp < n_heads) {
+      const float* rec = p.ws + (bq0 + warp) * p.n_tiles * ATT_REC;
+      float mloc = -INFINITY;
+      for (int64_t t = lane; t < p.n_tiles; t += 32) {
+        const float mt = __ldcg(rec + t * ATT_REC + 128);
+        s_f[warp * 1024 + t] = mt;
+        mloc = fmaxf(mloc, mt);
       }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
+      float L = 0.0f;
+      for (int64_t t = lane; t < p.n_tiles; t += 32) {
+        const float mt = s_f[warp * 1024 + t];
+        const float f = (mt == -INFINITY) ? 0.0f : exp2f(mt - mloc);
+        s_f[warp * 1024 + t] = f;
+        L += __ldcg(rec + t * ATT_REC + 129) * f;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
+      if (lane == 0) s_L[warp] = L, s_M[warp] = mloc;
     }
-    for (; t < p.n_tiles; t++) {
-      O += __ldcg(rec + t * ATT_REC + tid) * s_f[t & 1023];
-      L += s_lt[t & 1023] * s_f[t & 1023];
-    }
-    p.out[bq * 128 + tid] = f2bf(L > 0.0f ? O / L : 0.0f);
-    if (p.lse && tid == 0) p.lse[bq] = L > 0.0f ? M + log2f(L) : -INFINITY;
     __syncthreads();
+    float O[ATT_GQ];
+#pragma unroll
+    for (int g = 0; g < ATT_GQ; g++) O[g] = 0.0f;
+    const float* rec0 = p.ws + bq0 * p.n_tiles * ATT_REC + tid;
+    int64_t t = 0;
+    for (; t + 4 <= p.n_tiles; t += 4) {
+      float v[ATT_GQ][4];
+#pragma unroll
+      for (int g = 0; g < ATT_GQ; g++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) v[g][i] = g < n_heads ? __ldcg(rec0 + (g * p.n_tiles + t + i) * ATT_REC) : 0.0f;
+#pragma unroll
+      for (int g = 0; g < ATT_GQ; g++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) O[g] += v[g][i] * s_f[g * 1024 + t + i];
+    }
+    for (; t < p.n_tiles; t++)
+#pragma unroll
+      for (int g = 0; g < ATT_GQ; g++)
+        if (g < n_heads) O[g] += __ldcg(rec0 + (g * p.n_tiles + t) * ATT_REC) * s_f[g * 1024 + t];
+#pragma unroll
+    for (int g = 0; g < ATT_GQ; g++) {
+      if (g >= n_heads) continue;
+      const float L = s_L[g];
+      p.out[(bq0 + g) * 128 + tid] = f2bf(L > 0.0f ? O[g] / L : 0.0f);
+      if (p.lse && tid == 0) p.lse[bq0 + g] = L > 0.0f ? s_M[g] + log2f(L) : -INFINITY;
+    }
   }
 }
 

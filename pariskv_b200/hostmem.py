@@ -53,3 +53,57 @@ def _release(tensors):
 def release_on_collect(owner, tensors):
     """Unregister `tensors` (a list, kept alive by this call) when `owner` is garbage-collected."""
     return weakref.finalize(owner, _release, tensors)
+
+
+def _cpulist(text):
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def device_node_cpus(device):
+    """CPUs (allowed to this process) of the NUMA node that `device`'s PCIe link hangs off, with the node's number:
+    (node, cpus), or None when that cannot be told (no sysfs entry, a single-node host, none of the CPUs allowed)."""
+    import os
+    try:
+        prop = torch.cuda.get_device_properties(device)
+        addr = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{addr}/numa_node") as f:
+            node = int(f.read())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = _cpulist(f.read()) & os.sched_getaffinity(0)
+        return (node, cpus) if cpus else None
+    except (OSError, AttributeError, ValueError, RuntimeError):   # RuntimeError: no CUDA driver
+        return None
+
+
+class near_device:
+    """Context manager: inside it the calling thread runs on the CPUs of `device`'s NUMA node, so that host memory
+    first touched there (the K/V stores of `pinned_empty`) is local to the GPU's PCIe link.  Rows that a GPU fetches
+    from the other socket's memory cross the inter-socket link first, which costs bandwidth and latency on a path
+    that is host-link bound.  Build the cache inside; the previous affinity comes back on exit.  `.bound` is
+    {"node": n, "cpus": count} when the affinity was changed, else None.  No GPU setting is touched."""
+
+    def __init__(self, device):
+        self.device, self.bound, self._saved = device, None, None
+
+    def __enter__(self):
+        import os
+        found = device_node_cpus(self.device)
+        if found:
+            self._saved = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, found[1])
+            self.bound = {"node": found[0], "cpus": len(found[1])}
+        return self
+
+    def __exit__(self, *exc):
+        import os
+        if self._saved is not None:
+            os.sched_setaffinity(0, self._saved)
+        return False

@@ -230,3 +230,16 @@ def test_torch_ops_are_registered_with_schemas_and_shape_functions():
     out = torch.empty(1, 2, 7, 128, dtype=torch.bfloat16)
     torch.ops.pariskv.gather(src, index, out)
     assert torch.equal(out, torch.gather(src, 2, index[..., None].expand(1, 2, 7, 128)))
+
+
+def test_host_numa_helpers_without_a_gpu():
+    """The CPU-list parser, and the store-placement scope as a no-op where the GPU's node cannot be told."""
+    import os
+    from pariskv_b200 import hostmem
+    assert hostmem._cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert hostmem._cpulist("") == set()
+    before = os.sched_getaffinity(0)
+    import torch
+    with hostmem.near_device(torch.device("cuda", 0)) as scope:
+        assert scope.bound is None or scope.bound["cpus"] > 0
+    assert os.sched_getaffinity(0) == before
