@@ -94,45 +94,40 @@ class DecoderHarness:
         if world > 1:
             self._gathered = torch.empty(world, 2, dtype=torch.int64, device=device)
 
-    def _sum_over_ranks(self, partial, residual):
+    def _sum_norm(self, partial, residual, weight):
+        """(h, x): h = residual + the sum of `partial` over ranks, x = RMS-norm(h) * weight: one launch (with the
+        exchange inside it at world > 1, peer mode)."""
+        from pariskv_b200 import ops
         if self.world == 1:
-            return residual + partial
-        return self.reducer.reduce(partial, residual)
+            return ops.add_rmsnorm(partial, residual, weight, 1e-6)
+        return self.reducer.reduce_norm(partial, residual, weight, 1e-6)
 
     def step(self, cache, token, pos_dev=None):
         """One decode token per sequence through all layers; token: int64 [B] on the device.  Returns the next
         tokens [B].  pos_dev (float32 [B] or [1] on the device) replaces the host-side position when the step is
         captured or when the sequences of a batch stand at different positions.
-        q and k share one RMS-norm and one rotate-half RoPE call per layer (stacked per-head weights)."""
+        Between the projections (library GEMMs) a layer launches four elementwise kernels of this repository:
+        q/k norm + RoPE, residual add (+ reduction over ranks) + norm twice, and the gated activation."""
+        from pariskv_b200 import ops
         c = self.cfg
-        Hq, Hk, D, Ff = self.Hq, self.Hk, c["head_dim"], self.Ff
+        Hq, Hk, D, L = self.Hq, self.Hk, c["head_dim"], c["layers"]
         B = token.shape[0]
         pos = pos_dev if pos_dev is not None else float(cache.context)
-        if B == 1:
-            ang = pos * self._inv_freq
-            cos = torch.cos(ang).repeat(2).to(torch.bfloat16)          # [128]
-            sin = torch.sin(ang)
-            sin = torch.cat([-sin, sin]).to(torch.bfloat16)            # sign of rotate-half folded in
-        else:
-            ang = (pos.view(-1, 1) if torch.is_tensor(pos) else pos) * self._inv_freq.view(1, -1)
-            ang = ang.expand(B, -1)
-            cos = torch.cos(ang).repeat(1, 2).to(torch.bfloat16).view(B, 1, D)
-            sin = torch.sin(ang)
-            sin = torch.cat([-sin, sin], -1).to(torch.bfloat16).view(B, 1, D)
-        h = self.embed[token]                                      # [B, hidden]
-        for l in range(c["layers"]):
-            x = F.rms_norm(h, (c["hidden"],), self.ln1[l], 1e-6)
+        ang = (pos.view(-1, 1) if torch.is_tensor(pos) else pos) * self._inv_freq.view(1, -1)   # [1 or B, 64]
+        cos = torch.cos(ang).repeat(1, 2).to(torch.bfloat16).contiguous()                       # [1 or B, 128]
+        sin = torch.sin(ang)
+        sin = torch.cat([-sin, sin], -1).to(torch.bfloat16).contiguous()     # sign of rotate-half folded in
+        h, x = ops.add_rmsnorm(self.embed[token], None, self.ln1[0], 1e-6)   # [B, hidden]
+        for l in range(L):
             qkv = F.linear(x, self.wqkv[l])
-            qk = F.rms_norm(qkv[:, :(Hq + Hk) * D].view(B, Hq + Hk, D), (D,), None, 1e-6) * self.qkn[l]
-            qk = qk * cos + torch.roll(qk, 64, -1) * sin            # rotate-half RoPE
+            qk = ops.qk_norm_rope(qkv, self.qkn[l], cos, sin, 1e-6)            # [B, Hq + Hk, 128]
             v = qkv[:, (Hq + Hk) * D:].view(B, 1, Hk, D)
             cache.decode_update_kv_cache(qk[:, Hq:].view(B, 1, Hk, D), v, l)
             attn = cache.compute(qk[:, :Hq].view(B, 1, Hq, D), l)
-            h = self._sum_over_ranks(F.linear(attn.view(B, Hq * D), self.wo[l]), h)
-            x = F.rms_norm(h, (c["hidden"],), self.ln2[l], 1e-6)
-            gu = F.linear(x, self.wgu[l])
-            h = self._sum_over_ranks(F.linear(F.silu(gu[:, :Ff]) * gu[:, Ff:], self.wd[l]), h)
-        logits = F.linear(F.rms_norm(h, (c["hidden"],), self.lnf, 1e-6), self.lm_head)
+            h, x = self._sum_norm(F.linear(attn.view(B, Hq * D), self.wo[l]), h, self.ln2[l])
+            act = ops.silu_mul(F.linear(x, self.wgu[l]))
+            h, x = self._sum_norm(F.linear(act, self.wd[l]), h, self.ln1[l + 1] if l + 1 < L else self.lnf)
+        logits = F.linear(x, self.lm_head)
         if self.world == 1:
             return logits.argmax(-1)
         # vocabulary-parallel arg-max: every rank's (maximum, global index), the first maximum wins as in argmax
@@ -580,7 +575,13 @@ def tp_selfcheck(device, rank, world, reducer):
             ok = ok and torch.equal(got, want.to(torch.bfloat16).float())
         else:
             ok = ok and (got - want).abs().max().item() <= 0.25
-        cases += 1
+        # the form the decode step uses: the same reduction with the RMS-norm of the result from the same launch
+        wn = (1.0 + 0.1 * torch.randn(4096, generator=g)).to(torch.bfloat16)
+        h2, x2 = reducer.reduce_norm(parts[rank].clone().to(device), res.to(device), wn.to(device))
+        h2, x2 = h2.float().cpu(), x2.float().cpu()
+        xr = h2 * torch.rsqrt((h2 * h2).mean() + 1e-6) * wn.float()
+        ok = ok and (h2 - want).abs().max().item() <= 0.25 and (x2 - xr).abs().max().item() <= 2e-2 * max(1.0, xr.abs().max().item())
+        cases += 2
         flag = torch.tensor([1 if ok else 0], device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         ok = bool(flag.item())

@@ -429,7 +429,29 @@ int pk_shard_collect_partial(uint64_t local_base, int64_t gather_offset, int64_t
  * No counterpart in the reference. */
 int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residual, const pk_tensor* out,
                     const uint64_t* peer_bases, int world, int rank, int64_t gather_offset, int64_t area_bytes,
-                    int64_t flags_offset, void* control, void* stream);
+                    int64_t flags_offset, void* control, const pk_tensor* norm_weight, const pk_tensor* normed_out,
+                    double eps, void* stream);
+
+/* ---- decode glue: the elementwise steps of a decoder layer around the cache calls ----------------------- */
+
+/* One launch each, bf16, one token per sequence.  The reference takes these from its attention library
+ * (model_hub/qwen.py:381 silu_and_mul, :405 / :429 rmsnorm, :482 rotary embedding); they are part of this library
+ * because a decode step is launch-latency bound outside the host-link fetch.
+ *
+ * pk_qk_norm_rope: per-head RMS-norm (weight bf16 [heads,128], heads = q heads followed by KV heads) of the first
+ *   heads*128 columns of the fused q/k/v row qkv bf16 [B, >= heads*128] (unit inner stride), then rotate-half RoPE
+ *   with cos / sin bf16 [1 or B,128] (sin carries the sign: [-sin, sin]):  y = bf16(x * rstd * w),
+ *   out[b,h,d] = bf16(y[d] * cos[d] + y[d xor 64] * sin[d]);  out bf16 [B,heads,128].
+ * pk_add_rmsnorm: h_out = bf16(a + residual) (residual may be NULL), x_out = bf16(h_out * rstd(h_out) * weight);
+ *   a, residual, h_out, x_out bf16 [B,n], weight bf16 [n], n a multiple of 8.  h_out may alias residual or a.
+ * pk_silu_mul: out[b,i] = bf16( bf16(silu(gate_up[b,i])) * gate_up[b,F+i] );  gate_up bf16 [B,2F], out bf16 [B,F].
+ * pk_tp_allreduce with normed_out != NULL additionally writes normed_out = RMS-norm(out) * norm_weight (bf16 [n];
+ *   one row), so that a tensor-parallel layer needs no separate norm launch after a reduction. */
+int pk_qk_norm_rope(const pk_tensor* qkv, const pk_tensor* weight, const pk_tensor* cos, const pk_tensor* sin,
+                    const pk_tensor* out, double eps, void* stream);
+int pk_add_rmsnorm(const pk_tensor* a, const pk_tensor* residual, const pk_tensor* weight, const pk_tensor* h_out,
+                   const pk_tensor* x_out, double eps, void* stream);
+int pk_silu_mul(const pk_tensor* gate_up, const pk_tensor* out, void* stream);
 
 #ifdef __cplusplus
 }

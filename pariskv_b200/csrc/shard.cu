@@ -242,9 +242,12 @@ __global__ void __launch_bounds__(128) shard_merge_partial_peer_kernel(const flo
 __global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restrict__ partial, const uint4* __restrict__ residual,
                                                            uint4* __restrict__ out, int n16, PeerSet peers, int64_t gather_off,
                                                            int64_t area_bytes, int64_t flags_off, int rank, int world,
-                                                           PeerCtl* ctl) {
+                                                           PeerCtl* ctl, const uint4* __restrict__ norm_w,
+                                                           uint4* __restrict__ normed, float eps) {
   const int tid = threadIdx.x;
   __shared__ unsigned s_epoch;
+  __shared__ float s_part[16];
+  float ss = 0.0f;
   if (tid == 0) s_epoch = ctl->epoch + 1;
   __syncthreads();
   const unsigned epoch = s_epoch;
@@ -296,6 +299,31 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restri
     o.z = (uint32_t)f2bf(acc[4]) | ((uint32_t)f2bf(acc[5]) << 16);
     o.w = (uint32_t)f2bf(acc[6]) | ((uint32_t)f2bf(acc[7]) << 16);
     out[i] = o;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      const float r = bfround(acc[k]);
+      ss = fmaf(r, r, ss);
+    }
+  }
+  if (!normed) return;
+  // the RMS-norm of the reduced row, for the projection that follows: x = bf16(out * rsqrt(mean(out^2) + eps) * w)
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((tid & 31) == 0) s_part[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 16; k++) tot += s_part[k];
+  const float rstd = rsqrtf(tot / (float)(n16 * 8) + eps);
+  for (int i = tid; i < n16; i += blockDim.x) {   // every thread re-reads what it wrote itself
+    const uint4 v = out[i], wv = norm_w[i];
+    const uint32_t hw[4] = {v.x, v.y, v.z, v.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+      ow[k] = (uint32_t)f2bf(__uint_as_float(hw[k] << 16) * rstd * __uint_as_float(ww[k] << 16)) |
+              ((uint32_t)f2bf(__uint_as_float(hw[k] & 0xffff0000u) * rstd * __uint_as_float(ww[k] & 0xffff0000u)) << 16);
+    normed[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
   }
 }
 
@@ -489,10 +517,24 @@ extern "C" int pk_shard_collect_partial(uint64_t local_base, int64_t gather_offs
 
 extern "C" int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residual, const pk_tensor* out,
                                const uint64_t* peer_bases, int world, int rank, int64_t gather_offset, int64_t area_bytes,
-                               int64_t flags_offset, void* control, void* stream) {
+                               int64_t flags_offset, void* control, const pk_tensor* norm_weight,
+                               const pk_tensor* normed_out, double eps, void* stream) {
   PK_CHECK_TENSOR(partial, PK_BF16, 2);
   PK_CHECK_TENSOR(out, PK_BF16, 2);
   const int64_t n = numel(partial);
+  const uint4* nw = nullptr;
+  uint4* nout = nullptr;
+  if (normed_out) {
+    PK_CHECK_TENSOR(normed_out, PK_BF16, 2);
+    PK_CHECK_TENSOR(norm_weight, PK_BF16, 1);
+    PK_REQUIRE(partial->shape[0] == 1, "the fused RMS-norm takes one row (partial must be [1,n])");
+    PK_REQUIRE(is_contig(normed_out) && numel(normed_out) == n && is_contig(norm_weight) && numel(norm_weight) == n &&
+                   (reinterpret_cast<uintptr_t>(normed_out->data) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(norm_weight->data) & 15) == 0,
+               "normed_out / norm_weight must be contiguous bf16 of n elements, 16-byte aligned");
+    nw = (const uint4*)norm_weight->data;
+    nout = (uint4*)normed_out->data;
+  }
   PK_REQUIRE(is_contig(partial) && is_contig(out) && numel(out) == n && n >= 8 && n % 8 == 0 && n <= (1 << 20),
              "partial / out must be contiguous bf16 with the same number of elements, a multiple of 8, at most 2^20");
   PK_REQUIRE((reinterpret_cast<uintptr_t>(partial->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(out->data) & 15) == 0,
@@ -511,6 +553,7 @@ extern "C" int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residu
   int rc;
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
   tp_allreduce_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const uint4*)partial->data, res, (uint4*)out->data, (int)(n / 8), ps,
-                                                           gather_offset, area_bytes, flags_offset, rank, world, (PeerCtl*)control);
+                                                           gather_offset, area_bytes, flags_offset, rank, world, (PeerCtl*)control,
+                                                           nw, nout, (float)eps);
   return check_launch("tp_allreduce");
 }

@@ -253,6 +253,16 @@ class TPReducer:
         from . import ops
         return ops.tp_allreduce(partial.contiguous(), residual.contiguous(), self)
 
+    def reduce_norm(self, partial, residual, weight, eps=1e-6):
+        """(h, x): h = residual + sum over ranks of partial, x = RMS-norm(h) * weight.  In peer mode one launch does
+        the exchange, the sum and the norm; otherwise the collective is followed by one add + norm launch."""
+        from . import ops
+        if self.mode == "peer":
+            return ops.tp_allreduce(partial.contiguous(), residual.contiguous(), self, norm_weight=weight, eps=eps)
+        if self.mode == "nccl":
+            dist.all_reduce(partial, group=self.group)
+        return ops.add_rmsnorm(partial, residual, weight, eps)
+
     def check(self):
         """Raise if a bounded wait ran out (host synchronisation: call it outside the decode loop)."""
         if self.mode == "peer" and int(self.ctl.cpu()[2]):

@@ -501,13 +501,49 @@ def shard_collect_partial(px, bs, Hq):
     return out
 
 
-def tp_allreduce(partial, residual, px, out=None):
+def tp_allreduce(partial, residual, px, out=None, norm_weight=None, eps=1e-6):
     """out = residual + sum over ranks of partial, one launch over peer memory; px: a dist.TPReducer in peer mode.
-    See pk_tp_allreduce."""
+    With norm_weight (bf16 [n]) the same launch also writes RMS-norm(out) * norm_weight and (out, normed) is
+    returned.  See pk_tp_allreduce."""
     _require_cuda(partial, residual)
     if out is None:
         out = torch.empty_like(partial)
     d = [L.desc(t) for t in (partial, residual, out)]
+    normed = torch.empty_like(partial) if norm_weight is not None else None
+    dn = [L.desc(t) for t in (norm_weight, normed)] if norm_weight is not None else None
     _call("pk_tp_allreduce", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), px.peer_array, px.world, px.rank, 0, px.area_bytes,
-          px.flags_off, px.ctl.data_ptr(), L.stream_ptr(partial.device))
+          px.flags_off, px.ctl.data_ptr(), L.ref(dn[0]) if dn else None, L.ref(dn[1]) if dn else None, float(eps),
+          L.stream_ptr(partial.device))
+    return out if norm_weight is None else (out, normed)
+
+
+def qk_norm_rope(qkv, weight, cos, sin, eps=1e-6, out=None):
+    """Per-head RMS-norm and rotate-half RoPE of the q and k heads of a fused q/k/v row in one launch.
+    qkv bf16 [B, >= heads*128]; weight bf16 [heads,128]; cos / sin bf16 [1 or B,128] (sin = [-sin, sin]).
+    Returns bf16 [B, heads, 128].  See pk_qk_norm_rope."""
+    _require_cuda(qkv, weight, cos, sin)
+    B, heads = qkv.shape[0], weight.shape[0]
+    if out is None:
+        out = torch.empty(B, heads, 128, dtype=torch.bfloat16, device=qkv.device)
+    d = [L.desc(t) for t in (qkv, weight, cos, sin, out)]
+    _call("pk_qk_norm_rope", *[L.ref(x) for x in d], float(eps), L.stream_ptr(qkv.device))
+    return out
+
+
+def add_rmsnorm(a, residual, weight, eps=1e-6):
+    """h = a + residual (residual may be None), x = RMS-norm(h) * weight, one launch.  Returns (h, x).
+    See pk_add_rmsnorm."""
+    _require_cuda(a, weight)
+    h, x = torch.empty_like(a), torch.empty_like(a)
+    d = [L.desc(t) if t is not None else None for t in (a, residual, weight, h, x)]
+    _call("pk_add_rmsnorm", *[L.ref(t) if t is not None else None for t in d], float(eps), L.stream_ptr(a.device))
+    return h, x
+
+
+def silu_mul(gate_up):
+    """silu(gate_up[:, :F]) * gate_up[:, F:], one launch.  See pk_silu_mul."""
+    _require_cuda(gate_up)
+    out = torch.empty(gate_up.shape[0], gate_up.shape[1] // 2, dtype=torch.bfloat16, device=gate_up.device)
+    d = [L.desc(gate_up), L.desc(out)]
+    _call("pk_silu_mul", L.ref(d[0]), L.ref(d[1]), L.stream_ptr(gate_up.device))
     return out

@@ -208,6 +208,14 @@ def _tp_worker(rank, world, port):
                     assert torch.equal(got, want.to(torch.bfloat16).float()), (mode, it)
                 else:
                     assert (got - want).abs().max().item() <= 0.25, (mode, it)
+                if it % 3 == 0:       # the same reduction with the RMS-norm of the result written by the same launch
+                    wn = (1.0 + 0.1 * torch.randn(4096, generator=g)).to(torch.bfloat16)
+                    h, x = red.reduce_norm(parts[rank].clone().to(dev), res.to(dev), wn.to(dev))
+                    h, x = h.float().cpu(), x.float().cpu()
+                    if mode == "peer":
+                        assert torch.equal(h, got), (mode, it)
+                    ref = h * torch.rsqrt((h * h).mean() + 1e-6) * wn.float()
+                    assert (x - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item()), (mode, it)
             red.check()
             torch.cuda.synchronize()
             dist.barrier()

@@ -544,3 +544,50 @@ def test_torch_custom_ops_run_the_same_kernels(ops, oracle):
     torch.ops.pariskv.gather_trans(src_k, src_v, cand, dk, dv)
     idx = cand.cpu()[..., None].expand(1, 2, 300, 128)
     assert torch.equal(dk.cpu(), torch.gather(src_k, 2, idx)) and torch.equal(dv.cpu(), torch.gather(src_v, 2, idx))
+
+
+# ---- decode glue: the elementwise steps of a decoder layer ---------------------------------------------------------
+@pytest.mark.parametrize("B,Hq,Hk", [(1, 32, 8), (3, 4, 1), (16, 32, 8)])
+def test_qk_norm_rope_against_fp32(ops, B, Hq, Hk):
+    """y = x * rsqrt(mean(x^2) + eps) * w per head, then rotate-half RoPE; fp32 torch reference, bf16 tolerance."""
+    g = torch.Generator().manual_seed(B * 100 + Hq)
+    heads = Hq + Hk
+    qkv = torch.randn(B, (heads + Hk) * 128, generator=g).to(torch.bfloat16)
+    w = (1.0 + 0.2 * torch.randn(heads, 128, generator=g)).to(torch.bfloat16)
+    ang = torch.rand(B, 64, generator=g) * 6.28
+    cos = torch.cos(ang).repeat(1, 2).to(torch.bfloat16)
+    sin = torch.cat([-torch.sin(ang), torch.sin(ang)], -1).to(torch.bfloat16)
+    for cs in ((cos, sin), (cos[:1].contiguous(), sin[:1].contiguous())):
+        out = ops.qk_norm_rope(qkv.to(DEV), w.to(DEV), cs[0].to(DEV), cs[1].to(DEV), 1e-6)
+        x = qkv[:, :heads * 128].float().view(B, heads, 128)
+        y = (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * w.float()).to(torch.bfloat16).float()
+        ref = y * cs[0].float().view(-1, 1, 128) + torch.roll(y, 64, -1) * cs[1].float().view(-1, 1, 128)
+        assert out.shape == (B, heads, 128)
+        assert (out.float().cpu() - ref).abs().max().item() <= 3e-2
+
+
+@pytest.mark.parametrize("B,n", [(1, 4096), (5, 1024), (2, 8192), (1, 40)])
+def test_add_rmsnorm_and_silu_mul_against_fp32(ops, B, n):
+    g = torch.Generator().manual_seed(n + B)
+    a = torch.randn(B, n, generator=g).to(torch.bfloat16)
+    r = torch.randn(B, n, generator=g).to(torch.bfloat16)
+    w = (1.0 + 0.2 * torch.randn(n, generator=g)).to(torch.bfloat16)
+    for res in (r, None):
+        h, x = ops.add_rmsnorm(a.to(DEV), None if res is None else res.to(DEV), w.to(DEV), 1e-6)
+        hr = (a.float() + (0 if res is None else res.float())).to(torch.bfloat16)
+        assert torch.equal(h.cpu(), hr)          # one bf16 rounding of an exact fp32 sum
+        xr = hr.float() * torch.rsqrt((hr.float() ** 2).mean(-1, keepdim=True) + 1e-6) * w.float()
+        assert (x.float().cpu() - xr).abs().max().item() <= 2e-2 * max(1.0, xr.abs().max().item())
+    gu = torch.randn(B, 2 * n, generator=g).to(torch.bfloat16)
+    act = ops.silu_mul(gu.to(DEV))
+    ref = torch.nn.functional.silu(gu[:, :n].float()) * gu[:, n:].float()
+    assert act.shape == (B, n)
+    assert (act.float().cpu() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_glue_argument_errors(ops):
+    with pytest.raises(Exception):
+        ops.silu_mul(torch.zeros(1, 20, dtype=torch.bfloat16, device=DEV))       # F = 10 is not a multiple of 8
+    with pytest.raises(Exception):
+        ops.add_rmsnorm(torch.zeros(1, 64, dtype=torch.bfloat16, device=DEV), None,
+                        torch.zeros(32, dtype=torch.bfloat16, device=DEV))
