@@ -128,7 +128,7 @@ class DecoderHarness:
             act = ops.silu_mul(F.linear(x, self.wgu[l]))
             h, x = self._sum_norm(F.linear(act, self.wd[l]), h, self.ln1[l + 1] if l + 1 < L else self.lnf)
         logits = F.linear(x, self.lm_head)
-        if self.world == 1:
+        if self.world == 1 or getattr(self.reducer, "mode", None) == "none":
             return logits.argmax(-1)
         # vocabulary-parallel arg-max: every rank's (maximum, global index), the first maximum wins as in argmax
         m, i = logits.float().max(-1)
@@ -244,6 +244,15 @@ def synth_kv(gen, P, H, device):
     z *= torch.exp(0.5 * torch.randn(1, P, H, 1, generator=gen, device=device, dtype=torch.float32))
     v = torch.randn(1, P, H, 128, generator=gen, device=device, dtype=torch.float32)
     return z.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
+class TPReducer_none:
+    """Stands in for dist.TPReducer where one rank's share is timed alone: the sum over ranks is the local add."""
+    mode = "none"
+
+    def reduce_norm(self, partial, residual, weight, eps=1e-6):
+        from pariskv_b200 import ops
+        return ops.add_rmsnorm(partial, residual, weight, eps)
 
 
 class numa_scope:
@@ -1066,6 +1075,9 @@ def main():
                          "all-reduces")
     ap.add_argument("--no-offload", action="store_true",
                     help="variant, not the benchmark configuration: keep the K/V rows in HBM instead of pinned host memory")
+    ap.add_argument("--tp-share", type=int, default=1,
+                    help="variant (N = 1 only): time rank 0's share of a tensor-parallel step over this many ranks on one "
+                         "GPU, the reductions replaced by local adds: what a rank costs before any communication")
     ap.add_argument("--no-numa", action="store_true",
                     help="variant: do not place the pinned K/V store on the NUMA node of the GPU's host link")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
@@ -1160,12 +1172,17 @@ def main():
                      "what": "rank r's retrieved indices == heads [r H/N, (r+1) H/N) of the oracle's single-GPU result "
                              "(bit for bit), attention within 2e-2, reduction over ranks == fp32 sum in rank order"}
         model = DecoderHarness(cfg, device, seed=1234, rank=rank, world=world, reducer=reducer)
+    elif args.tp_share > 1:
+        # variant: rank 0's share of an N-way tensor-parallel step on ONE GPU, reductions replaced by local adds
+        model = DecoderHarness(cfg, device, seed=1234, rank=0, world=args.tp_share, reducer=TPReducer_none())
     else:
         model = DecoderHarness(cfg, device, seed=1234)
     # the K/V store is first touched on the CPUs of this GPU's NUMA node: its rows are then local to the GPU's link
     with numa_scope(device, args) as numa:
         if tp:
             cache = build_cache(cfg, device, max_new, seed=100, offload=not args.no_offload, rank=rank, world=world)
+        elif args.tp_share > 1:
+            cache = build_cache(cfg, device, max_new, seed=100, offload=not args.no_offload, rank=0, world=args.tp_share)
         else:
             cache = build_cache(cfg, device, max_new, seed=100 + rank, offload=not args.no_offload)
     setup_s = time.time() - t_setup
@@ -1371,6 +1388,8 @@ def main():
             line["invalid"] = "the world-N self-check against the oracle failed"
     if debug:
         line["invalid"] = "debug run with reduced layers/context"
+    if args.tp_share > 1:
+        line["invalid"] = f"variant: one rank's share of a {args.tp_share}-way tensor-parallel step, no communication"
     if args.no_offload:
         line["invalid"] = "variant: K/V rows resident in HBM; the benchmark configuration keeps them in pinned host memory"
     print(json.dumps(line), flush=True)

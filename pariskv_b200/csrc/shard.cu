@@ -259,19 +259,20 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restri
   }
   __threadfence_system();
   __syncthreads();
-  if (tid == 0) {
-    for (int q = 0; q < world; q++) st_release_sys(reinterpret_cast<unsigned*>(peers.base[q] + flags_off) + rank, epoch);
-    ctl->epoch = epoch;
+  // thread q publishes to peer q and waits for peer q's flag: the `world` stores and the `world` waits run side by
+  // side instead of one after the other (each release store orders the block's data stores, which every thread
+  // fenced before the barrier, ahead of the flag)
+  if (tid < world) {
+    st_release_sys(reinterpret_cast<unsigned*>(peers.base[tid] + flags_off) + rank, epoch);
+    if (tid == 0) ctl->epoch = epoch;
     const unsigned* flags = reinterpret_cast<const unsigned*>(peers.base[rank] + flags_off);
-    for (int r = 0; r < world; r++) {
-      long long polls = 0;
-      while ((int)(ld_acquire_sys(flags + r) - epoch) < 0) {
-        if (++polls > SHARD_WAIT_POLLS) {
-          atomicExch(&ctl->status, 1u);
-          break;
-        }
-        __nanosleep(100);
+    long long polls = 0;
+    while ((int)(ld_acquire_sys(flags + tid) - epoch) < 0) {
+      if (++polls > SHARD_WAIT_POLLS) {
+        atomicExch(&ctl->status, 1u);
+        break;
       }
+      __nanosleep(40);
     }
   }
   __syncthreads();
