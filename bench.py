@@ -1146,7 +1146,7 @@ def main():
     tp = world > 1 and args.mode == "decode"          # one sequence, KV heads split over the ranks
     if tp and (cfg["kv_heads"] % world or cfg["q_heads"] % world):
         raise SystemExit(f"{cfg['kv_heads']} KV heads do not split over {world} ranks")
-    max_new = W + 2 * K + S + 2 * cfg["interval"] + 8
+    max_new = W + 2 * K + 2 * S + 2 * cfg["interval"] + 16
     # pinned host memory for the K/V store: refuse early rather than drive the box out of memory
     need_gb = (1 if tp else world) * 2 * cfg["layers"] * cfg["kv_heads"] * (cfg["context"] + max_new + cfg["interval"]) * 256 / 1e9
     try:
@@ -1251,7 +1251,23 @@ def main():
     ms_e2e = f0.elapsed_time(f1)
 
     # ---- per-kernel event timing on extra steps (not part of either headline number) ----
-    stage = {}
+    # Inside the graph: a second capture of the same step with timing on brackets every launch of this library with
+    # external event-record nodes, which each replay stamps, so a stage is timed where it runs, between its neighbours
+    # in the replayed step.  Then the same stages on eager steps (launch overhead included), for comparison.
+    stage, stage_eager, probe = {}, {}, None
+    if S > 0 and use_graph:
+        _lib.timing_enable(True)
+        probe = GraphedDecoder(model, cache)
+        probe.tok.copy_(runner.tok)
+        for i in range(S + 1):
+            probe.step()                    # the first call captures (event nodes included) and replays
+            torch.cuda.synchronize(device)
+            if i:
+                for name, (tot_ms, cnt) in _lib.timing_read_graph().items():
+                    a = stage.get(name, (0.0, 0))
+                    stage[name] = (a[0] + tot_ms, a[1] + cnt)
+        _lib.timing_enable(False)
+        runner.tok.copy_(probe.tok)
     if S > 0:
         _lib.timing_enable(True)
         cache.device_positions = False
@@ -1259,8 +1275,10 @@ def main():
         for _ in range(S):
             token = model.step(cache, token)
         torch.cuda.synchronize(device)
-        stage = _lib.timing_read()
+        stage_eager = _lib.timing_read()
         _lib.timing_enable(False)
+        if not stage:
+            stage = stage_eager
 
     att_us_ranks = None
     if world > 1:
@@ -1283,6 +1301,8 @@ def main():
             return
         import gc
         runner.release()
+        if probe is not None:
+            probe.release()
         gc.collect()
         barrier()
         sys.stdout.flush()
@@ -1318,6 +1338,7 @@ def main():
         stages_out[name] = ent
     retrieval_us = sum(stages_out.get(s, {}).get("avg_us", 0.0) for s in
                        ("query_prep", "rank_table", "collision", "select_rerank", "final_topk"))
+    stages_eager_us = {name: round(tot_ms * 1e3 / cnt, 3) for name, (tot_ms, cnt) in stage_eager.items()}
     coll = stages_out.get("collision", {})
     roofline = {"kernel": "chain_collision_kernel (query preparation + cluster ranking + weighted multi-tier collision count)",
                 "bound": "hbm",
@@ -1374,6 +1395,9 @@ def main():
                 "ms_per_step": ms_e2e / K},
         "gpu_launches": int(launches),
         "roofline": roofline, "host_link": host_link, "stages": stages_out,
+        "stage_timing": ("CUDA events recorded as nodes of the replayed step graph" if probe is not None
+                         else "CUDA events around eager launches"),
+        "stages_eager_us": stages_eager_us,
         "retrieval_us_per_step_per_layer": round(retrieval_us, 2),
         "cpu_baseline": cpu,
         "published_reference": {"decode_tok_s_128k_bs1": 41.10, "note": "hardware and model unstated by the reference"},

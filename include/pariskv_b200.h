@@ -55,9 +55,16 @@ int64_t pk_launch_count(void);
  * decode path is bracketed by CUDA events on its own stream.  pk_timing_read waits for the recorded
  * events, sums elapsed milliseconds and launch counts per stage (stage ids: 0 query prep, 1 cluster
  * ranking/table, 2 collision, 3 select+rerank, 4 final top-k, 5 attention tiles, 6 attention merge,
- * 7 encode, 8 stand-alone top-k, 9 stand-alone rerank, 10 UVA gather, 11 cluster histogram, 12 row append) and clears the record. */
+ * 7 encode, 8 stand-alone top-k, 9 stand-alone rerank, 10 UVA gather, 11 cluster histogram, 12 row append,
+ * 13 decode glue, 14 tensor-parallel reduce) and clears the record. */
 int pk_timing_enable(int on);
 int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages);
+/* Launches issued INTO A STREAM CAPTURE while timing is enabled are bracketed by external event-record nodes, which
+ * every replay of the captured graph stamps again: pk_timing_read_graph waits for them and sums, per stage, what the
+ * LAST replay measured (all graphs captured with timing on; it clears nothing).  pk_timing_clear_graph destroys those
+ * events: call it only after the graphs that record them are gone. */
+int pk_timing_read_graph(double* ms_per_stage, int64_t* spans_per_stage, int n_stages);
+int pk_timing_clear_graph(void);
 
 /* Process-wide option, no counterpart in the reference: launch the kernels of the decode chain with programmatic
  * dependent launch (a kernel's prologue may overlap the tail of its predecessor).  Off by default: with the decode

@@ -55,6 +55,8 @@ SIGNATURES = {
     "pk_set_pdl": (_INT, [_INT]),
     "pk_timing_enable": (_INT, [_INT]),
     "pk_timing_read": (_INT, [ctypes.POINTER(ctypes.c_double), _I64P, _INT]),
+    "pk_timing_read_graph": (_INT, [ctypes.POINTER(ctypes.c_double), _I64P, _INT]),
+    "pk_timing_clear_graph": (_INT, []),
     "pk_encode_keys": (_INT, [TP, TP, TP, TP, TP, TP, _VP]),
     "pk_count_clusters": (_INT, [TP, TP, _INT, _VP]),
     "pk_query_prep": (_INT, [TP, TP, TP, TP, TP, _VP]),
@@ -181,7 +183,7 @@ def launch_count() -> int:
 
 
 STAGES = ["query_prep", "rank_table", "collision", "select_rerank", "final_topk", "attention", "attention_merge",
-          "encode", "topk", "rerank", "uva_gather", "count_clusters", "append"]
+          "encode", "topk", "rerank", "uva_gather", "count_clusters", "append", "glue", "tp_reduce"]
 
 
 def timing_enable(on: bool):
@@ -195,3 +197,16 @@ def timing_read():
     cnt = (ctypes.c_int64 * n)()
     check(load().pk_timing_read(ms, cnt, n))
     return {STAGES[i]: (float(ms[i]), int(cnt[i])) for i in range(n) if cnt[i]}
+
+
+def timing_read_graph():
+    """-> {stage: (total_ms, launches)} of the last replay of the graphs captured while timing was enabled."""
+    n = len(STAGES)
+    ms = (ctypes.c_double * n)()
+    cnt = (ctypes.c_int64 * n)()
+    check(load().pk_timing_read_graph(ms, cnt, n))
+    return {STAGES[i]: (float(ms[i]), int(cnt[i])) for i in range(n) if cnt[i]}
+
+
+def timing_clear_graph():
+    check(load().pk_timing_clear_graph())

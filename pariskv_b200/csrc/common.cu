@@ -34,6 +34,7 @@ constexpr int kMaxSpans = 1 << 16;
 std::mutex g_tmu;
 bool g_timing = false;
 std::vector<Span> g_spans;       // recorded since the last read
+std::vector<Span> g_graph_spans; // recorded into a stream capture: re-recorded by every replay of that graph
 std::vector<cudaEvent_t> g_pool; // reusable events
 cudaEvent_t take_event() {
   if (!g_pool.empty()) { cudaEvent_t e = g_pool.back(); g_pool.pop_back(); return e; }
@@ -43,18 +44,35 @@ cudaEvent_t take_event() {
 }
 }  // namespace
 
-StageTimer::StageTimer(int stage, cudaStream_t st) : stage_(stage), st_(st), a_(nullptr), on_(false) {
+// Inside a stream capture the events are recorded as EXTERNAL event nodes (cudaEventRecordExternal): they become
+// part of the graph and every replay stamps them, so a stage can be timed where it actually runs, between its
+// neighbours inside the replayed step.
+StageTimer::StageTimer(int stage, cudaStream_t st) : stage_(stage), st_(st), a_(nullptr), on_(false), cap_(false) {
   if (!g_timing) return;
   std::lock_guard<std::mutex> lk(g_tmu);
-  if ((int)g_spans.size() >= kMaxSpans) return;
-  a_ = take_event();
-  if (a_ && cudaEventRecord(a_, st_) == cudaSuccess) on_ = true;
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st_, &cs) != cudaSuccess) return;
+  cap_ = cs == cudaStreamCaptureStatusActive;
+  if ((int)(cap_ ? g_graph_spans.size() : g_spans.size()) >= kMaxSpans) return;
+  if (cap_) {
+    if (cudaEventCreate(&a_) != cudaSuccess) return;   // owned by the graph's span list, not by the pool
+  } else {
+    a_ = take_event();
+  }
+  if (a_ && cudaEventRecordWithFlags(a_, st_, cap_ ? cudaEventRecordExternal : cudaEventRecordDefault) == cudaSuccess)
+    on_ = true;
 }
 StageTimer::~StageTimer() {
   if (!on_) return;
   std::lock_guard<std::mutex> lk(g_tmu);
-  cudaEvent_t b = take_event();
-  if (b && cudaEventRecord(b, st_) == cudaSuccess) g_spans.push_back({stage_, a_, b});
+  cudaEvent_t b = nullptr;
+  if (cap_) {
+    if (cudaEventCreate(&b) != cudaSuccess) return;
+  } else {
+    b = take_event();
+  }
+  if (b && cudaEventRecordWithFlags(b, st_, cap_ ? cudaEventRecordExternal : cudaEventRecordDefault) == cudaSuccess)
+    (cap_ ? g_graph_spans : g_spans).push_back({stage_, a_, b});
 }
 
 static std::atomic<int> g_pdl{0};  // off unless asked for: measured neutral when the step is replayed as a graph
@@ -116,6 +134,30 @@ int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages)
     pk::g_pool.push_back(s.b);
   }
   pk::g_spans.clear();
+  return PK_OK;
+}
+
+int pk_timing_read_graph(double* ms_per_stage, int64_t* spans_per_stage, int n_stages) {
+  std::lock_guard<std::mutex> lk(pk::g_tmu);
+  for (int i = 0; i < n_stages; i++) ms_per_stage[i] = 0.0, spans_per_stage[i] = 0;
+  for (auto& s : pk::g_graph_spans) {
+    float ms = 0.0f;
+    if (cudaEventSynchronize(s.b) == cudaSuccess && cudaEventElapsedTime(&ms, s.a, s.b) == cudaSuccess &&
+        s.stage >= 0 && s.stage < n_stages) {
+      ms_per_stage[s.stage] += ms;
+      spans_per_stage[s.stage] += 1;
+    }
+  }
+  return PK_OK;
+}
+
+int pk_timing_clear_graph(void) {
+  std::lock_guard<std::mutex> lk(pk::g_tmu);
+  for (auto& s : pk::g_graph_spans) {
+    cudaEventDestroy(s.a);
+    cudaEventDestroy(s.b);
+  }
+  pk::g_graph_spans.clear();
   return PK_OK;
 }
 }

@@ -152,6 +152,7 @@ extern "C" int pk_qk_norm_rope(const pk_tensor* qkv, const pk_tensor* weight, co
   const int64_t n_warps = B * heads;
   if (n_warps == 0) return PK_OK;
   PK_REQUIRE(heads < (1 << 20) && n_warps < (1LL << 31), "sizes out of range");
+  StageTimer timer(ST_GLUE, (cudaStream_t)stream);
   qk_norm_rope_kernel<<<(unsigned)((n_warps + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
       (const uint16_t*)qkv->data, qkv->stride[0], (const uint16_t*)weight->data, (const uint16_t*)cos->data,
       (const uint16_t*)sin->data, cos->shape[0] == 1 ? 0 : 128, (uint16_t*)out->data, (int)heads, n_warps, (float)eps);
@@ -180,6 +181,7 @@ extern "C" int pk_add_rmsnorm(const pk_tensor* a, const pk_tensor* residual, con
   PK_REQUIRE(aligned16(a->data) && aligned16(weight->data) && aligned16(h_out->data) && aligned16(x_out->data),
              "tensors must be 16-byte aligned");
   if (B * n == 0) return PK_OK;
+  StageTimer timer(ST_GLUE, (cudaStream_t)stream);
   add_rmsnorm_kernel<<<(unsigned)B, 512, 0, (cudaStream_t)stream>>>((const uint16_t*)a->data, r, (const uint16_t*)weight->data,
                                                                      (uint16_t*)h_out->data, (uint16_t*)x_out->data, (int)n,
                                                                      (float)eps);
@@ -195,6 +197,7 @@ extern "C" int pk_silu_mul(const pk_tensor* gate_up, const pk_tensor* out, void*
   PK_REQUIRE(F % 8 == 0 && F < (1 << 30) && B < 65536, "F must be a multiple of 8, B < 65536");
   PK_REQUIRE(aligned16(gate_up->data) && aligned16(out->data), "tensors must be 16-byte aligned");
   if (B * F == 0) return PK_OK;
+  StageTimer timer(ST_GLUE, (cudaStream_t)stream);
   silu_mul_kernel<<<dim3((unsigned)((F / 8 + 255) / 256), (unsigned)B), 256, 0, (cudaStream_t)stream>>>(
       (const uint16_t*)gate_up->data, (uint16_t*)out->data, (int)F);
   return check_launch("silu_mul");

@@ -553,6 +553,7 @@ extern "C" int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residu
   PeerSet ps;
   int rc;
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
+  StageTimer timer(ST_REDUCE, (cudaStream_t)stream);
   tp_allreduce_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const uint4*)partial->data, res, (uint4*)out->data, (int)(n / 8), ps,
                                                            gather_offset, area_bytes, flags_offset, rank, world, (PeerCtl*)control,
                                                            nw, nout, (float)eps);

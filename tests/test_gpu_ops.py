@@ -591,3 +591,34 @@ def test_glue_argument_errors(ops):
     with pytest.raises(Exception):
         ops.add_rmsnorm(torch.zeros(1, 64, dtype=torch.bfloat16, device=DEV), None,
                         torch.zeros(32, dtype=torch.bfloat16, device=DEV))
+
+
+def test_stage_timing_inside_a_replayed_graph(ops):
+    """Launches captured while timing is on are bracketed by event nodes that every replay stamps again."""
+    from pariskv_b200 import _lib
+    gu = torch.randn(4, 2 * 4096, device=DEV).to(torch.bfloat16)
+    ops.silu_mul(gu)                                   # first use outside the capture
+    torch.cuda.synchronize()
+    _lib.timing_clear_graph()
+    _lib.timing_enable(True)
+    try:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g.capture_begin()
+            out = ops.silu_mul(gu)
+            out2 = ops.silu_mul(gu)
+            g.capture_end()
+        torch.cuda.current_stream().wait_stream(side)
+    finally:
+        _lib.timing_enable(False)
+    for _ in range(3):
+        g.replay()
+        torch.cuda.synchronize()
+        got = _lib.timing_read_graph()
+        assert got["glue"][1] == 2 and 0.0 < got["glue"][0] < 50.0      # two launches, milliseconds
+    assert torch.equal(out, out2)
+    del g
+    _lib.timing_clear_graph()
+    assert _lib.timing_read_graph() == {}
