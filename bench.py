@@ -952,7 +952,7 @@ def seqshard_mode(args, device, rank, world, local_rank):
     model = DecoderHarness(cfg, device, seed=1234)
     cache = SequenceShardedCache(Lyr, H, cfg["q_heads"], n_total, cfg["sink"], cfg["local"], cfg["interval"],
                                  cfg["topk"], device, rank, world, store=args.store, exchange=args.exchange,
-                                 max_new_length=W + K + 8)
+                                 max_new_length=W + K + 8 + (args.stage_steps if args.stage_steps is not None else 8))
     for l in range(Lyr):
         ks, vs = [], []
         for b in range(start // SHARD_BLOCK, (max(end, start + 1) - 1) // SHARD_BLOCK + 1):
@@ -1009,6 +1009,38 @@ def seqshard_mode(args, device, rank, world, local_rank):
     last = (runner.tok if use_graph else token).clone()
     if cache.px is not None:
         cache.px.check()
+    # per-stage event timing on a few eager steps (not part of the headline number): every launch of this library,
+    # per rank; what is left of an eager step is the dense part (library GEMVs) and, with --exchange nccl, the
+    # collectives.  The receiving kernels of the peer exchange contain the wait for the slowest rank.
+    S = args.stage_steps if args.stage_steps is not None else 8
+    stage_ranks, eager_ms = None, None
+    if S > 0:
+        token = last.clone()
+        barrier()
+        _lib.timing_enable(True)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(S):
+            token = model.step(cache, token)
+        s1.record()
+        torch.cuda.synchronize(device)
+        st = _lib.timing_read()
+        _lib.timing_enable(False)
+        eager_ms = s0.elapsed_time(s1) / S
+        names = list(_lib.STAGES)
+        mine = torch.tensor([st[n][0] * 1e3 / (S * Lyr) if n in st else 0.0 for n in names] + [eager_ms * 1e3 / Lyr],
+                            device=device, dtype=torch.float64)
+        allr = torch.empty(world, mine.numel(), device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_gather_into_tensor(allr, mine.view(1, -1))
+        else:
+            allr.copy_(mine.view(1, -1))
+        allr = allr.cpu()
+        stage_ranks = {n: [round(float(allr[r, i]), 2) for r in range(world)] for i, n in enumerate(names)
+                       if float(allr[:, i].max()) > 0.0}
+        stage_ranks["eager_layer_total"] = [round(float(allr[r, -1]), 2) for r in range(world)]
+        if cache.px is not None:
+            cache.px.check()
     agree = True
     if world > 1:
         t = torch.tensor([ms], device=device, dtype=torch.float64)
@@ -1034,6 +1066,9 @@ def seqshard_mode(args, device, rank, world, local_rank):
             "setup_s": round(setup_s, 1), "zone_keys_per_head": n_total, "shard_keys_per_head": end - start,
             "candidates_total": c_total, "final_topk": k_final,
             "selection": "exact: global threshold count from all-gathered count histograms, ties in rank order",
+            "stage_us_per_layer_per_rank": stage_ranks,
+            "stage_timing": "CUDA events around eager launches of this library, microseconds per layer summed over a "
+                            "stage's launches, one entry per rank; eager_layer_total = eager step / layers",
         }
         if debug:
             line["invalid"] = "debug run with reduced layers/context"
@@ -1063,7 +1098,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-baseline-seconds", type=float, default=12.0)
-    ap.add_argument("--stage-steps", type=int, default=16, help="extra steps with per-kernel event timing")
+    ap.add_argument("--stage-steps", type=int, default=None,
+                    help="extra steps with per-kernel event timing (default 16; 8 for --mode seqshard)")
     ap.add_argument("--no-graph", action="store_true", help="run every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--mode", default="decode", choices=["decode", "replicas", "kernels", "ops", "seqshard", "prefill", "varlen"],
                     help="decode: the benchmark; with N GPUs the same sequence with its KV heads split over the ranks "
@@ -1142,7 +1178,7 @@ def main():
     if args.mode == "prefill":
         prefill_mode(args, cfg, device)
         return
-    K, W, S = args.steps, args.warmup, args.stage_steps
+    K, W, S = args.steps, args.warmup, (16 if args.stage_steps is None else args.stage_steps)
     tp = world > 1 and args.mode == "decode"          # one sequence, KV heads split over the ranks
     if tp and (cfg["kv_heads"] % world or cfg["q_heads"] % world):
         raise SystemExit(f"{cfg['kv_heads']} KV heads do not split over {world} ranks")

@@ -839,6 +839,7 @@ __global__ void __launch_bounds__(256) hist_reduce_kernel(const uint32_t* __rest
 
 int launch_hist_reduce(const uint32_t* chunk_hist, int64_t bs_h, int64_t n_chunks, int64_t chunk_keys, int mis, int H,
                        int64_t N, const int32_t* n_dev, uint32_t* local_hist, cudaStream_t st) {
+  StageTimer tm(ST_HIST_REDUCE, st);
   launch_chain(hist_reduce_kernel, dim3((unsigned)bs_h), dim3(256), 0, st, chunk_hist, n_chunks, chunk_keys, mis, H, N,
                n_dev, local_hist);
   return check_launch("shard histogram");

@@ -360,6 +360,7 @@ extern "C" int pk_shard_pack_topk(const pk_tensor* cand, const pk_tensor* scores
   const int32_t *ns = nullptr, *nc = nullptr;
   int rc;
   if ((rc = counts_arg(n_sel, bs, H, "n_sel", &ns)) || (rc = counts_arg(n_cand, bs, H, "n_cand", &nc))) return rc;
+  StageTimer timer(ST_SHARD_SEND, (cudaStream_t)stream);
   shard_pack_kernel<<<dim3((unsigned)((Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
       (const int64_t*)cand->data, (const float*)scores->data, (const int64_t*)local_final->data, (int64_t*)packed->data,
       (int)C, (int)Kl, start, ns, nc);
@@ -380,6 +381,7 @@ extern "C" int pk_shard_unpack_topk(const pk_tensor* gathered, const pk_tensor* 
   PK_REQUIRE(world * Kl < (1LL << 31) && bs * H < 65536, "sizes out of range");
   PK_REQUIRE((reinterpret_cast<uintptr_t>(gathered->data) & 15) == 0, "gathered must be 16-byte aligned");
   if (numel(gathered) == 0) return PK_OK;
+  StageTimer timer(ST_SHARD_RECV, (cudaStream_t)stream);
   shard_unpack_kernel<<<dim3((unsigned)((world * Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
       (const int64_t*)gathered->data, (float*)scores->data, (int64_t*)indices->data, (int)world, (int)(bs * H), (int)Kl);
   return check_launch("shard_unpack_topk");
@@ -397,6 +399,7 @@ extern "C" int pk_shard_owned_rows(const pk_tensor* final_indices, int64_t start
              "local must be [bs,H,K] and n_owned [bs,H]");
   PK_REQUIRE(start <= end && K < (1LL << 31), "bad shard range");
   if (bs * H == 0) return PK_OK;
+  StageTimer timer(ST_SHARD_OWNED, (cudaStream_t)stream);
   shard_owned_kernel<<<(unsigned)(bs * H), 256, 0, (cudaStream_t)stream>>>(
       (const int64_t*)final_indices->data, (int64_t*)local->data, (int32_t*)n_owned->data, (int)K, start, end);
   return check_launch("shard_owned_rows");
@@ -412,6 +415,7 @@ extern "C" int pk_shard_pack_partial(const pk_tensor* out, const pk_tensor* lse,
   PK_REQUIRE(packed->shape[0] == bs && packed->shape[1] == Hq && packed->shape[2] == 129 && is_contig(packed),
              "packed must be contiguous [bs,Hq,129]");
   if (bs * Hq == 0) return PK_OK;
+  StageTimer timer(ST_SHARD_SEND, (cudaStream_t)stream);
   shard_pack_partial_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)out->data, (const float*)lse->data, (float*)packed->data);
   return check_launch("shard_pack_partial");
@@ -426,6 +430,7 @@ extern "C" int pk_shard_merge_partial(const pk_tensor* gathered, const pk_tensor
              "out must be contiguous [bs,1,Hq,128]");
   PK_REQUIRE(world >= 1 && world <= 1024, "world size out of range");
   if (bs * Hq == 0) return PK_OK;
+  StageTimer timer(ST_SHARD_RECV, (cudaStream_t)stream);
   shard_merge_partial_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
       (const float*)gathered->data, (__nv_bfloat16*)out->data, (int)world, (int)(bs * Hq));
   return check_launch("shard_merge_partial");
@@ -462,6 +467,7 @@ extern "C" int pk_shard_exchange_topk(const pk_tensor* cand, const pk_tensor* sc
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
   const int32_t *ns = nullptr, *nc = nullptr;
   if ((rc = counts_arg(n_sel, bs, H, "n_sel", &ns)) || (rc = counts_arg(n_cand, bs, H, "n_cand", &nc))) return rc;
+  StageTimer timer(ST_SHARD_SEND, (cudaStream_t)stream);
   shard_pack_peer_kernel<<<dim3((unsigned)((Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
       (const int64_t*)cand->data, (const float*)scores->data, (const int64_t*)local_final->data, (int)C, (int)Kl, start, ps,
       gather_offset, flags_offset, rank, world, (int)(bs * H), (PeerCtl*)control, ns, nc);
@@ -479,6 +485,7 @@ extern "C" int pk_shard_collect_topk(uint64_t local_base, int64_t gather_offset,
              "scores / indices must be contiguous [bs,H,world*Kl]");
   PK_REQUIRE(local_base != 0 && control != nullptr && gather_offset % 16 == 0 && flags_offset % 4 == 0, "buffer or offsets invalid");
   char* base = reinterpret_cast<char*>(local_base);
+  StageTimer timer(ST_SHARD_RECV, (cudaStream_t)stream);
   shard_unpack_peer_kernel<<<dim3((unsigned)((world * Kl + 255) / 256), (unsigned)(bs * H)), 256, 0, (cudaStream_t)stream>>>(
       (const int64_t*)(base + gather_offset), (const unsigned*)(base + flags_offset), (PeerCtl*)control, (float*)scores->data,
       (int64_t*)indices->data, world, (int)(bs * H), (int)Kl);
@@ -496,6 +503,7 @@ extern "C" int pk_shard_exchange_partial(const pk_tensor* out, const pk_tensor* 
   PeerSet ps;
   int rc;
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
+  StageTimer timer(ST_SHARD_SEND, (cudaStream_t)stream);
   shard_pack_partial_peer_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)out->data, (const float*)lse->data, ps, gather_offset, flags_offset, rank, world, (int)(bs * Hq),
       (PeerCtl*)control);
@@ -510,6 +518,7 @@ extern "C" int pk_shard_collect_partial(uint64_t local_base, int64_t gather_offs
   PK_REQUIRE(world >= 1 && world <= 16 && local_base != 0 && control != nullptr && gather_offset % 16 == 0 && flags_offset % 4 == 0,
              "buffer or offsets invalid");
   char* base = reinterpret_cast<char*>(local_base);
+  StageTimer timer(ST_SHARD_RECV, (cudaStream_t)stream);
   shard_merge_partial_peer_kernel<<<(unsigned)(bs * Hq), 128, 0, (cudaStream_t)stream>>>(
       (const float*)(base + gather_offset), (const unsigned*)(base + flags_offset), (PeerCtl*)control,
       (__nv_bfloat16*)out->data, world, (int)(bs * Hq));
