@@ -55,13 +55,24 @@ class DecoderHarness:
     ranks' local maxima.  Weights are drawn in full with the same generator on every rank and then sliced, so the
     model is the same for every world size."""
 
-    def __init__(self, cfg, device, seed, rank=0, world=1, reducer=None):
+    def __init__(self, cfg, device, seed, rank=0, world=1, reducer=None, gather_heads=False):
         g = torch.Generator(device=device).manual_seed(seed)
         L, Hd, Hq, Hk, D, Ff, V = (cfg[k] for k in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "ffn", "vocab"))
         if Hq % world or Hk % world or Ff % world or V % world:
             raise ValueError(f"heads ({Hq}/{Hk}), ffn ({Ff}) and vocabulary ({V}) must split evenly over {world} ranks")
         self.cfg, self.device, self.rank, self.world, self.reducer = cfg, device, rank, world, reducer
         self.Hq, self.Hk, self.Ff, self.V = Hq // world, Hk // world, Ff // world, V // world
+        # gather_heads: the cache behind this model wants ALL heads on every rank (it is sharded along the sequence):
+        # the ranks' q/k/v rows are all-gathered after the projection, the norm / RoPE and the cache calls run on all
+        # heads, and the output projection takes this rank's slice of the attention output
+        self.gather_heads = bool(gather_heads) and world > 1
+        if self.gather_heads:
+            per = (self.Hq + 2 * self.Hk) * D     # one rank's [q_r | k_r | v_r]
+            src = []
+            for lo, n in ((0, self.Hq * D), (self.Hq * D, self.Hk * D), ((self.Hq + self.Hk) * D, self.Hk * D)):
+                for r in range(world):
+                    src.append(torch.arange(r * per + lo, r * per + lo + n))
+            self._perm = torch.cat(src).to(device)   # gathered [r][q_r|k_r|v_r] -> [q of all heads | k | v]
 
         def w(*shape, std=0.02):
             return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
@@ -88,7 +99,8 @@ class DecoderHarness:
         self.ln1 = [ones(Hd) for _ in range(L)]
         self.ln2 = [ones(Hd) for _ in range(L)]
         # per-head-dim norm weights of q and k (Qwen3), stacked so both are applied in one multiply
-        self.qkn = [torch.cat([ones(D).expand(self.Hq, D), ones(D).expand(self.Hk, D)]).contiguous() for _ in range(L)]
+        nq, nk = (Hq, Hk) if self.gather_heads else (self.Hq, self.Hk)
+        self.qkn = [torch.cat([ones(D).expand(nq, D), ones(D).expand(nk, D)]).contiguous() for _ in range(L)]
         self.lnf = ones(Hd)
         self._inv_freq = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, D, 2, device=device, dtype=torch.float32) / D))
         if world > 1:
@@ -110,7 +122,8 @@ class DecoderHarness:
         q/k norm + RoPE, residual add (+ reduction over ranks) + norm twice, and the gated activation."""
         from pariskv_b200 import ops
         c = self.cfg
-        Hq, Hk, D, L = self.Hq, self.Hk, c["head_dim"], c["layers"]
+        D, L = c["head_dim"], c["layers"]
+        Hq, Hk = (c["q_heads"], c["kv_heads"]) if self.gather_heads else (self.Hq, self.Hk)   # heads the cache sees
         B = token.shape[0]
         pos = pos_dev if pos_dev is not None else float(cache.context)
         ang = (pos.view(-1, 1) if torch.is_tensor(pos) else pos) * self._inv_freq.view(1, -1)   # [1 or B, 64]
@@ -120,14 +133,19 @@ class DecoderHarness:
         h, x = ops.add_rmsnorm(self.embed[token], None, self.ln1[0], 1e-6)   # [B, hidden]
         for l in range(L):
             qkv = F.linear(x, self.wqkv[l])
+            if self.gather_heads:     # all heads on every rank: [q_r | k_r | v_r] of every rank -> [q | k | v]
+                qkv = self.reducer.all_gather(qkv).view(-1)[self._perm].view(1, -1)
             qk = ops.qk_norm_rope(qkv, self.qkn[l], cos, sin, 1e-6)            # [B, Hq + Hk, 128]
             v = qkv[:, (Hq + Hk) * D:].view(B, 1, Hk, D)
             cache.decode_update_kv_cache(qk[:, Hq:].view(B, 1, Hk, D), v, l)
-            attn = cache.compute(qk[:, :Hq].view(B, 1, Hq, D), l)
-            h, x = self._sum_norm(F.linear(attn.view(B, Hq * D), self.wo[l]), h, self.ln2[l])
+            attn = cache.compute(qk[:, :Hq].view(B, 1, Hq, D), l).view(B, Hq * D)
+            if self.gather_heads:     # row-parallel output projection: this rank's q heads
+                attn = attn[:, self.rank * self.Hq * D:(self.rank + 1) * self.Hq * D]
+            h, x = self._sum_norm(F.linear(attn, self.wo[l]), h, self.ln2[l])
             act = ops.silu_mul(F.linear(x, self.wgu[l]))
             h, x = self._sum_norm(F.linear(act, self.wd[l]), h, self.ln1[l + 1] if l + 1 < L else self.lnf)
         logits = F.linear(x, self.lm_head)
+        self.last_logits = logits          # this rank's slice of the vocabulary (kept for checks)
         if self.world == 1 or getattr(self.reducer, "mode", None) == "none":
             return logits.argmax(-1)
         # vocabulary-parallel arg-max: every rank's (maximum, global index), the first maximum wins as in argmax
@@ -919,7 +937,8 @@ def synth_block(layer, block, n, H, device, seed):
 def seqshard_mode(args, device, rank, world, local_rank):
     """One decode sequence whose zone is split into `world` contiguous chunks: per-rank retrieval over the local
     chunk, all-gather of the local top lists, attention over the owned rows, merge through the softmax
-    denominators.  The dense part of the model is replicated on every rank."""
+    denominators.  The dense part of the model is tensor-parallel over the same ranks (--dense tp, the default: the
+    q/k/v rows of all heads are all-gathered for the cache, the output and MLP projections reduced) or replicated."""
     from pariskv_b200 import _lib
     from pariskv_b200.dist import SequenceShardedCache, sequence_shard
     cfg = dict(CFG_1M)
@@ -949,7 +968,17 @@ def seqshard_mode(args, device, rank, world, local_rank):
             dist.destroy_process_group()
         return
     t_setup = time.time()
-    model = DecoderHarness(cfg, device, seed=1234)
+    reducer = None
+    if world > 1 and args.dense == "tp":
+        # the dense layers tensor-parallel (heads / MLP columns / vocabulary split over the ranks) while the cache is
+        # sharded along the sequence: one all-gather of the q/k/v rows and two reductions per layer on top of the
+        # cache's three exchanges
+        from pariskv_b200.dist import TPReducer
+        row = max(cfg["hidden"], (cfg["q_heads"] + 2 * cfg["kv_heads"]) * cfg["head_dim"])   # the gathered q/k/v row
+        reducer = TPReducer(row, device, mode="peer" if args.exchange == "peer" else "nccl")
+        model = DecoderHarness(cfg, device, seed=1234, rank=rank, world=world, reducer=reducer, gather_heads=True)
+    else:
+        model = DecoderHarness(cfg, device, seed=1234)
     cache = SequenceShardedCache(Lyr, H, cfg["q_heads"], n_total, cfg["sink"], cfg["local"], cfg["interval"],
                                  cfg["topk"], device, rank, world, store=args.store, exchange=args.exchange,
                                  max_new_length=W + K + 8 + (args.stage_steps if args.stage_steps is not None else 8))
@@ -1009,6 +1038,8 @@ def seqshard_mode(args, device, rank, world, local_rank):
     last = (runner.tok if use_graph else token).clone()
     if cache.px is not None:
         cache.px.check()
+    if reducer is not None:
+        reducer.check()
     # per-stage event timing on a few eager steps (not part of the headline number): every launch of this library,
     # per rank; what is left of an eager step is the dense part (library GEMVs) and, with --exchange nccl, the
     # collectives.  The receiving kernels of the peer exchange contain the wait for the slowest rank.
@@ -1058,7 +1089,7 @@ def seqshard_mode(args, device, rank, world, local_rank):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"Llama-3-8B-shaped decoder, one sequence of {cfg['context']} tokens, bs 1, top-k "
                                    f"{cfg['topk']}, zone of {n_total} keys per head split into {world} contiguous "
-                                   f"chunk(s); dense layers replicated; K/V rows in {'HBM' if cache.store == 'hbm' else 'pinned host memory'}",
+                                   f"chunk(s); dense layers {'tensor-parallel' if reducer is not None else 'replicated'}; K/V rows in {'HBM' if cache.store == 'hbm' else 'pinned host memory'}",
                        "layers": Lyr, "kv_heads": H, "q_heads": cfg["q_heads"], "parallelism": f"sp{world}",
                        "l2": "per-step working set (codes of all layers) exceeds L2"},
             "clocks": clocks, "gpu_launches": int(launches), "ranks_agree": agree, "exchange": args.exchange,
@@ -1116,6 +1147,8 @@ def main():
                          "GPU, the reductions replaced by local adds: what a rank costs before any communication")
     ap.add_argument("--no-numa", action="store_true",
                     help="variant: do not place the pinned K/V store on the NUMA node of the GPU's host link")
+    ap.add_argument("--dense", default="tp", choices=["tp", "replicated"],
+                    help="--mode seqshard: the dense layers split over the ranks (tensor parallel) or replicated")
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
                     help="--mode seqshard: the two per-layer exchanges as NCCL all-gathers or as stores into peer memory")
     ap.add_argument("--only", default=None, help="--mode ops: run only the ops whose name contains this text")

@@ -440,6 +440,12 @@ int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residual, const p
                     int64_t flags_offset, void* control, const pk_tensor* norm_weight, const pk_tensor* normed_out,
                     double eps, void* stream);
 
+/* The all-gather on the same buffers, flags and control block (it counts as one exchange in the common sequence):
+ * out bf16 [1, world*n] = the ranks' part bf16 [1,n] in rank order.  A model whose dense layers are tensor-parallel
+ * while its cache is sharded along the sequence gathers the q/k/v rows of all heads with it. */
+int pk_tp_allgather(const pk_tensor* part, const pk_tensor* out, const uint64_t* peer_bases, int world, int rank,
+                    int64_t gather_offset, int64_t area_bytes, int64_t flags_offset, void* control, void* stream);
+
 /* ---- decode glue: the elementwise steps of a decoder layer around the cache calls ----------------------- */
 
 /* One launch each, bf16, one token per sequence.  The reference takes these from its attention library

@@ -92,6 +92,7 @@ SIGNATURES = {
     "pk_shard_exchange_partial": (_INT, [TP, TP, _U64P, _INT, _INT, _I64, _I64, _VP, _VP]),
     "pk_shard_collect_partial": (_INT, [_U64, _I64, _I64, _VP, _INT, TP, _VP]),
     "pk_tp_allreduce": (_INT, [TP, TP, TP, _U64P, _INT, _INT, _I64, _I64, _I64, _VP, TP, TP, ctypes.c_double, _VP]),
+    "pk_tp_allgather": (_INT, [TP, TP, _U64P, _INT, _INT, _I64, _I64, _I64, _VP, _VP]),
     "pk_qk_norm_rope": (_INT, [TP, TP, TP, TP, TP, ctypes.c_double, _VP]),
     "pk_add_rmsnorm": (_INT, [TP, TP, TP, TP, TP, ctypes.c_double, _VP]),
     "pk_silu_mul": (_INT, [TP, TP, _VP]),

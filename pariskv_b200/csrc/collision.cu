@@ -424,6 +424,11 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
   const int64_t N = cq.n_dev ? min(max((int64_t)cq.n_dev[b], (int64_t)1), p.N) : p.N;
   const int64_t Nv = N + p.mis;
   const int64_t v_begin = (int64_t)blockIdx.x * p.chunk_keys;
+  if (cq.zero_area) {  // every block clears its slice of the next kernel's value histogram, also beyond a short zone
+    const int per = (cq.zero_area_words + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int lo = (int)blockIdx.x * per, hi = min(cq.zero_area_words, lo + per);
+    for (int i = lo + tid; i < hi; i += CC_THREADS) cq.zero_area[(int64_t)bh * cq.zero_area_words + i] = 0u;
+  }
   if (v_begin >= Nv) return;  // beyond this sample's zone (whole block, before any barrier)
   const int64_t v_end = min(Nv, v_begin + p.chunk_keys);
   const uint8_t* base = p.codes + b * p.c_b + h * p.c_h - p.mis * p.c_l;

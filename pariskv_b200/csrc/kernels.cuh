@@ -59,6 +59,8 @@ struct ChainQuery {
   pk_zone_schedule sched;     // thresholds = zone_tiers(sched, n_dev[b]) when n_dev is set
   long long n_plan;           // > 0: thresholds from this zone length instead (a shard of a longer zone)
   unsigned* zero_words;       // [bs*H] words set to zero here (arrival counters of the selection kernel), or null
+  unsigned* zero_area;        // [bs*H][zero_area_words] set to zero here (the selection kernel's value histogram), or null
+  int zero_area_words;
 };
 int launch_collision(const pk_tensor* codebook, const uint32_t* lut, int32_t* out_i32, cudaStream_t st);
 int chain_layout(const pk_tensor* codebook, int* layout);
@@ -107,6 +109,9 @@ struct SelectArgs {
   int64_t C;                     // row stride (and capacity) of cand_out / scores_f32
   int64_t C_want;                // candidates wanted per head over the whole zone, all shards together (n_dev == null)
   int64_t K;                     // final top-K; 0 = stop after the rerank
+  int fill_tail;                 // rows may be longer than the candidate list: the tail gets (score -inf, key 0)
+  unsigned* val_hist;            // [bs*H][select_value_bins()] zero at launch, or null: histogram of the scores' top
+                                 // key bits, filled while the scores are computed; long rows select their top-K from it
   const int32_t* n_dev;          // [bs] searchable keys per sample, or null
   pk_zone_schedule sched;        // candidates = zone_candidates(sched, n_dev[b]) when n_dev is set
   const uint32_t* shard_hist;    // [world][bs*H][256] histograms of every shard (exact sequence-sharded selection)
@@ -119,6 +124,7 @@ struct SelectArgs {
   unsigned* counters;            // [bs*H] arrival counters, zero at launch (K > 0)
 };
 int64_t select_smem_bytes(int64_t chunk_keys, int64_t C, int64_t K);
+int64_t select_value_bins();     // words per (batch, head) of SelectArgs::val_hist
 int64_t select_final_max_row();  // longest score row whose final top-K the selection kernel finishes entirely in shared memory
 int launch_select_rerank(const RerankArgs& a, int64_t bs_h, const SelectArgs& s, cudaStream_t st);
 

@@ -118,6 +118,7 @@ struct SelParams {
   SelectArgs s;
   int small_cap;  // longest row that the all-in-shared-memory final selection takes (a multiple of 16)
   int key_cache;  // words of the shared-memory key cache of the general final selection
+  int bitmap_words;  // words of the position bitmap of the histogram-based final selection (tie list behind it)
 };
 
 // ---- final top-K of one (batch, head) by one block ------------------------------------------------------------------
@@ -308,6 +309,123 @@ __device__ bool final_select_cached(const float* __restrict__ scores, const int6
       for (int j = 0; j < 8; j++)
         if (i + j < i1 && flag[i + j]) out[pos++] = cv[j];
     }
+  }
+  return true;
+}
+
+// Long rows.  While the scores were computed, every block added them to a histogram over the top VH_BITS bits of the
+// ordered key (sign, exponent, five mantissa bits) in global memory, so the block that finishes last starts with the
+// threshold bin in hand: it reads the histogram once (32 bins per thread, highest bins first), then walks the row
+// twice with coalesced loads, sixteen in flight per thread: once to collect the threshold bin's elements, which are
+// ranked among themselves (value descending, position ascending) and marked in a position bitmap, once to emit the
+// selected positions in order.  A warp covers 1024 consecutive positions per round; lane g receives, by ballot, the
+// mask of positions [32 g, 32 g + 32) and owns them in the block-wide scan.
+// Returns false (nothing written) when the threshold bin holds more than FT_TIES elements.
+constexpr int VH_BITS = 14;
+constexpr int VH_BINS = 1 << VH_BITS;
+constexpr int VH_SHIFT = 32 - VH_BITS;
+
+template <int NT>
+__device__ bool final_select_hist(const float* __restrict__ scores, const int64_t* __restrict__ cand, int n, int K,
+                                  int64_t* __restrict__ out, const unsigned* __restrict__ vhist, unsigned* bitmap,
+                                  uint2* tie, unsigned* s_w, unsigned long long* s_scan) {
+  static_assert(VH_BINS == NT * 32, "32 histogram bins per thread");
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // ---- threshold bin: thread 0 holds the highest 32 bins ----
+  const int top = VH_BINS - 32 * (tid + 1);
+  unsigned sum = 0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(vhist + top) + j);
+    sum += v.x + v.y + v.z + v.w;
+  }
+  unsigned long long total;
+  const unsigned before = (unsigned)block_scan_excl<NT>((unsigned long long)sum, s_scan, &total);
+  if (tid == 0) s_w[3] = 0;  // tie counter
+  {  // the K-th largest lies in the 32 bins of exactly one thread; its warp looks at them together, lane l at bin 31 - l
+    const bool has = before < (unsigned)K && (unsigned)K <= before + sum;
+    const unsigned who = __ballot_sync(0xffffffffu, has);
+    if (who) {
+      const int f = __ffs(who) - 1;
+      const int ftop = __shfl_sync(0xffffffffu, top, f);
+      const unsigned fbefore = __shfl_sync(0xffffffffu, before, f);
+      const unsigned cj = __ldcg(vhist + ftop + 31 - lane);
+      unsigned incl = cj;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const unsigned o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += o;
+      }
+      const unsigned hit = __ballot_sync(0xffffffffu, fbefore + incl >= (unsigned)K);
+      if (hit && lane == __ffs(hit) - 1) s_w[0] = (unsigned)(ftop + 31 - lane), s_w[1] = fbefore + incl - cj, s_w[2] = cj;
+    }
+  }
+  const int n_words = (n + 31) >> 5;
+  for (int i = tid; i < n_words; i += NT) bitmap[i] = 0;
+  __syncthreads();
+  const unsigned T = s_w[0], above = s_w[1], in_bin = s_w[2];
+  if ((unsigned)total < (unsigned)K || in_bin > (unsigned)FT_TIES) return false;  // (an inconsistent histogram too)
+  const unsigned rem = (unsigned)K - above;
+  // ---- the threshold bin's elements ----
+  for (int base = tid; base < n; base += NT * 16) {
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) v[j] = base + j * NT < n ? __ldcg(scores + base + j * NT) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+      const int i = base + j * NT;
+      const unsigned k = ord_key(v[j]);
+      if (i < n && (k >> VH_SHIFT) == T) {
+        const unsigned at = atomicAdd(&s_w[3], 1u);
+        if (at < (unsigned)FT_TIES) tie[at] = make_uint2(k, (unsigned)i);
+      }
+    }
+  }
+  __syncthreads();
+  const int n_tie = (int)min(s_w[3], (unsigned)FT_TIES);
+  for (int t = tid; t < n_tie; t += NT) {
+    const uint2 me = tie[t];
+    unsigned rk = 0;
+    for (int j = 0; j < n_tie; j++) {
+      const uint2 o = tie[j];
+      rk += (o.x > me.x || (o.x == me.x && o.y < me.y)) ? 1u : 0u;
+    }
+    if (rk < rem) atomicOr(&bitmap[me.y >> 5], 1u << (me.y & 31));
+  }
+  __syncthreads();
+  // ---- ordered emission ----
+  unsigned long long run = 0;
+  for (int rb = 0; rb < n; rb += NT * 32) {
+    const int wb = rb + warp * 1024;
+    unsigned mine = 0;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      float v[16];
+#pragma unroll
+      for (int g = 0; g < 16; g++) {
+        const int pos = wb + (half * 16 + g) * 32 + lane;
+        v[g] = pos < n ? __ldcg(scores + pos) : 0.0f;
+      }
+#pragma unroll
+      for (int g = 0; g < 16; g++) {
+        const int pos = wb + (half * 16 + g) * 32 + lane;
+        const bool gt = pos < n && (ord_key(v[g]) >> VH_SHIFT) > T;
+        const unsigned m = __ballot_sync(0xffffffffu, gt);
+        if (lane == half * 16 + g) mine = m;
+      }
+    }
+    const int gbase = wb + lane * 32;  // this lane's 32 positions
+    unsigned take = mine | (gbase < n ? bitmap[gbase >> 5] : 0u);
+    unsigned long long tot_round;
+    unsigned o = (unsigned)(run + block_scan_excl<NT>((unsigned long long)__popc(take), s_scan, &tot_round));
+    while (take) {
+      const int j = __ffs(take) - 1;
+      take &= take - 1;
+      if (o < (unsigned)K) out[o] = __ldcg(cand + gbase + j);
+      o++;
+    }
+    run += tot_round;
+    __syncthreads();
   }
   return true;
 }
@@ -592,12 +710,13 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
     const float s = rerank_one<FAST>(sm, a, k4, w, key, qn, lane, nullptr, 0);
     p.scores_f32[row_base + out_pos + i] = s;
     p.cand_out[row_base + out_pos + i] = key;
+    if (p.val_hist) atomicAdd(p.val_hist + bh * VH_BINS + (ord_key(s) >> VH_SHIFT), 1u);
   }
   if (chunk == 0) {
     if (tid == 0 && p.n_cand_out) p.n_cand_out[bh] = (int32_t)C_here;
-    // per-sample lengths: rows are longer than this sample's candidate list; the tail gets (score -inf, key 0), so a
-    // consumer that walks whole rows (the adaptive selection) gives those entries no weight
-    if (p.n_dev)
+    // per-sample lengths or shards: rows are longer than this candidate list; the tail gets (score -inf, key 0), so
+    // a consumer that walks whole rows (the adaptive selection, a separate top-K launch) gives those entries no weight
+    if (p.fill_tail)
       for (int64_t i = C_here + tid; i < p.C; i += SEL_THREADS) {
         p.scores_f32[row_base + i] = -INFINITY;
         p.cand_out[row_base + i] = 0;
@@ -624,6 +743,14 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
       uint2* tie = reinterpret_cast<uint2*>(flag + pp.small_cap);
       done = final_select_cached<SEL_THREADS>(p.scores_f32 + row_base, p.cand_out + row_base, (int)C_here, K_here,
                                               p.final_out + bh * p.K, keys, hist, flag, tie, s_warp, s_scan);
+      __syncthreads();
+    }
+    if (!done && p.val_hist && (C_here + 31) / 32 <= pp.bitmap_words) {
+      unsigned* bitmap = reinterpret_cast<unsigned*>(list);
+      uint2* tie = reinterpret_cast<uint2*>(bitmap + pp.bitmap_words);
+      done = final_select_hist<SEL_THREADS>(p.scores_f32 + row_base, p.cand_out + row_base, (int)C_here, K_here,
+                                            p.final_out + bh * p.K, p.val_hist + bh * VH_BINS, bitmap, tie, s_warp,
+                                            s_scan);
       __syncthreads();
     }
     if (!done)
@@ -678,6 +805,7 @@ inline int64_t final_small_cap(int64_t C) { return (C < FT_KEYS_MAX ? (C + 15) /
 }  // namespace
 
 int64_t select_final_max_row() { return FT_KEYS_MAX; }
+int64_t select_value_bins() { return VH_BINS; }
 
 int64_t select_smem_bytes(int64_t chunk_keys, int64_t C, int64_t K) {
   int64_t body = chunk_keys * (int64_t)sizeof(int);  // the chunk's candidate list
@@ -695,6 +823,7 @@ int launch_select_rerank(const RerankArgs& a, int64_t bs_h, const SelectArgs& sa
   const int64_t smem = select_smem_bytes(sa.chunk_keys, sa.C, sa.K);
   p.small_cap = sa.K > 0 ? (int)final_small_cap(sa.C) : 0;
   p.key_cache = sa.K > 0 ? (int)((smem - (int64_t)sizeof(RerankSmem)) / 4 - FT_BINS) : 0;
+  p.bitmap_words = sa.K > 0 ? (int)((smem - (int64_t)sizeof(RerankSmem) - (int64_t)FT_TIES * 8) / 4) : 0;
   if (sa.C >= (1ll << 31) || sa.N >= (1ll << 31)) return fail(PK_ERR_ARG, "zone too long for the selection kernel");
   dim3 grid((unsigned)sa.n_chunks, (unsigned)bs_h);
   const bool fast = rerank_fast_layout(a);

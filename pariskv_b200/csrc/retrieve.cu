@@ -11,7 +11,7 @@ namespace {
 inline int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
 
 struct RetrieveLayout {
-  int64_t q_blocks, q_norm, counters, counts, hist, scores, cand, topk, topk_bytes, total;
+  int64_t q_blocks, q_norm, counters, counts, hist, scores, cand, vhist, topk, topk_bytes, total;
   int64_t u8_stride, n_chunks_max;
 };
 
@@ -34,6 +34,8 @@ RetrieveLayout make_layout(int64_t bs, int64_t H, int64_t N, int64_t C) {
   l.hist = off, off += align256(bh * l.n_chunks_max * 256 * 4);
   l.scores = off, off += align256(bh * C * 4);
   l.cand = off, off += align256(bh * C * 8);
+  // value histogram of the final selection: long rows only
+  l.vhist = off, off += C > select_final_max_row() ? align256(bh * select_value_bins() * 4) : 0;
   l.topk_bytes = topk_scratch_bytes(bh, C, 2048);   // long rows only; the size does not depend on K
   l.topk = off, off += align256(l.topk_bytes);
   l.total = off;
@@ -175,6 +177,8 @@ int retrieve_impl(const pk_retrieve_args& a, cudaStream_t st) {
     cq.q_blocks = qb, cq.q_norm = qn, cq.query_avg = qa;
     cq.counts = (const int32_t*)counts_t->data;
     cq.zero_words = counters;
+    if (K > 0 && row > select_final_max_row() && (varlen || sharded || n_sel))
+      cq.zero_area = (unsigned*)(ws + lay.vhist), cq.zero_area_words = (int)select_value_bins();
     if ((rc = launch_chain_collision(codebook, cq, counts, lay.u8_stride, hist, &mis, &chunk_keys, &n_chunks, st)))
       return rc;
     if (n_chunks > lay.n_chunks_max) return fail(PK_ERR_WORKSPACE, "internal: histogram workspace undersized");
@@ -203,21 +207,24 @@ int retrieve_impl(const pk_retrieve_args& a, cudaStream_t st) {
     sa.shard_hist = (const uint32_t*)a.shard_hist->data, sa.world = a.world, sa.rank = a.rank;
   }
   sa.cand_out = cd, sa.scores_f32 = sc;
-  // Long score rows with a fixed length (no per-sample lengths, no shards): the final top-K runs as the two-pass
-  // selection over many blocks, which is faster than one block walking a row of 100 K scores.
-  const bool separate_final = K > 0 && !varlen && !sharded && !n_sel && row > select_final_max_row();
+  // Long score rows.  Full rows of a fixed length (no per-sample lengths, no shards): the final top-K runs as the
+  // two-pass selection over many blocks after the selection kernel (measured faster at 100 K scores per row than one
+  // block per head).  Rows whose length is only known on the device: every block of the selection kernel adds its
+  // scores to a histogram of their top key bits, which the collision kernel cleared (phase 2 finds it cleared by
+  // phase 1), and the last block of a (batch, head) selects from it - still one launch.
+  sa.fill_tail = varlen;
+  const bool long_rows = K > 0 && row > select_final_max_row();
+  const bool separate_final = long_rows && !varlen && !sharded && !n_sel;
+  sa.val_hist = long_rows && !separate_final ? (unsigned*)(ws + lay.vhist) : nullptr;
   if (separate_final) sa.K = 0;
   sa.final_out = K > 0 ? (int64_t*)a.final_indices->data : nullptr;
   sa.n_sel_out = n_sel, sa.n_cand_out = n_cand, sa.counters = counters;
   ra.cand = nullptr;
   ra.q_blocks = qb, ra.q_norm = qn, ra.centers = (const uint16_t*)a.mag_centers->data;
   ra.C = row;
-  if ((rc = launch_select_rerank(ra, bh, sa, st))) return rc;
-  if (!separate_final) return PK_OK;
-  if ((rc = launch_topk(sc, true, bh, row, row, K, (int64_t*)a.final_indices->data, cd, row, 0, st, ST_FINAL_TOPK,
-                        lay.topk_bytes ? ws + lay.topk : nullptr, lay.topk_bytes)))
-    return rc;
-  return PK_OK;
+  if ((rc = launch_select_rerank(ra, bh, sa, st)) || !separate_final) return rc;
+  return launch_topk(sc, true, bh, row, row, K, (int64_t*)a.final_indices->data, cd, row, 0, st, ST_FINAL_TOPK,
+                     lay.topk_bytes ? ws + lay.topk : nullptr, lay.topk_bytes);
 }
 }  // namespace
 

@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restri
                                                            uint4* __restrict__ out, int n16, PeerSet peers, int64_t gather_off,
                                                            int64_t area_bytes, int64_t flags_off, int rank, int world,
                                                            PeerCtl* ctl, const uint4* __restrict__ norm_w,
-                                                           uint4* __restrict__ normed, float eps) {
+                                                           uint4* __restrict__ normed, float eps, int gather_only) {
   const int tid = threadIdx.x;
   __shared__ unsigned s_epoch;
   __shared__ float s_part[16];
@@ -277,6 +277,10 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restri
   }
   __syncthreads();
   const uint4* mine = reinterpret_cast<const uint4*>(peers.base[rank] + area);
+  if (gather_only) {  // all-gather: the slots of the area in rank order are the result
+    for (int i = tid; i < n16 * world; i += blockDim.x) out[i] = __ldcg(mine + i);
+    return;
+  }
   for (int i = tid; i < n16; i += blockDim.x) {
     float acc[8];
     {
@@ -565,6 +569,29 @@ extern "C" int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residu
   StageTimer timer(ST_REDUCE, (cudaStream_t)stream);
   tp_allreduce_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const uint4*)partial->data, res, (uint4*)out->data, (int)(n / 8), ps,
                                                            gather_offset, area_bytes, flags_offset, rank, world, (PeerCtl*)control,
-                                                           nw, nout, (float)eps);
+                                                           nw, nout, (float)eps, 0);
   return check_launch("tp_allreduce");
+}
+
+extern "C" int pk_tp_allgather(const pk_tensor* part, const pk_tensor* out, const uint64_t* peer_bases, int world, int rank,
+                               int64_t gather_offset, int64_t area_bytes, int64_t flags_offset, void* control,
+                               void* stream) {
+  PK_CHECK_TENSOR(part, PK_BF16, 2);
+  PK_CHECK_TENSOR(out, PK_BF16, 2);
+  const int64_t n = numel(part);
+  PK_REQUIRE(is_contig(part) && is_contig(out) && numel(out) == n * world && n >= 8 && n % 8 == 0 && n <= (1 << 20),
+             "part must be contiguous bf16 of n elements (a multiple of 8, at most 2^20), out of world x n");
+  PK_REQUIRE((reinterpret_cast<uintptr_t>(part->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(out->data) & 15) == 0,
+             "part / out must be 16-byte aligned");
+  PK_REQUIRE(control != nullptr && gather_offset >= 0 && gather_offset % 16 == 0 && flags_offset >= 0 && flags_offset % 4 == 0 &&
+                 area_bytes >= (int64_t)world * n * 2 && area_bytes % 16 == 0,
+             "control block, offsets or area size invalid (one area holds world x n bf16; two areas follow each other)");
+  PeerSet ps;
+  int rc;
+  if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
+  StageTimer timer(ST_REDUCE, (cudaStream_t)stream);
+  tp_allreduce_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const uint4*)part->data, nullptr, (uint4*)out->data, (int)(n / 8), ps,
+                                                           gather_offset, area_bytes, flags_offset, rank, world, (PeerCtl*)control,
+                                                           nullptr, nullptr, 0.0f, 1);
+  return check_launch("tp_allgather");
 }

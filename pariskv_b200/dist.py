@@ -263,6 +263,19 @@ class TPReducer:
             dist.all_reduce(partial, group=self.group)
         return ops.add_rmsnorm(partial, residual, weight, eps)
 
+    def all_gather(self, part):
+        """part: bf16 [1, m] (m * world <= n) -> bf16 [1, world * m], the ranks' parts in rank order."""
+        if self.mode == "none":
+            return part
+        if part.numel() * self.world > self.n:
+            raise ValueError("the gathered row must fit the reducer's row length")
+        if self.mode == "nccl":
+            out = torch.empty(1, self.world * part.numel(), dtype=part.dtype, device=part.device)
+            dist.all_gather_into_tensor(out.view(self.world, -1), part.contiguous(), group=self.group)
+            return out
+        from . import ops
+        return ops.tp_allgather(part.contiguous(), self)
+
     def check(self):
         """Raise if a bounded wait ran out (host synchronisation: call it outside the decode loop)."""
         if self.mode == "peer" and int(self.ctl.cpu()[2]):

@@ -517,6 +517,18 @@ def tp_allreduce(partial, residual, px, out=None, norm_weight=None, eps=1e-6):
     return out if norm_weight is None else (out, normed)
 
 
+def tp_allgather(part, px, out=None):
+    """out [1, world*n] = every rank's part [1, n] in rank order, one launch over peer memory; px: a dist.TPReducer
+    in peer mode.  See pk_tp_allgather."""
+    _require_cuda(part)
+    if out is None:
+        out = torch.empty(1, px.world * part.numel(), dtype=torch.bfloat16, device=part.device)
+    d = [L.desc(part), L.desc(out)]
+    _call("pk_tp_allgather", L.ref(d[0]), L.ref(d[1]), px.peer_array, px.world, px.rank, 0, px.area_bytes, px.flags_off,
+          px.ctl.data_ptr(), L.stream_ptr(part.device))
+    return out
+
+
 def qk_norm_rope(qkv, weight, cos, sin, eps=1e-6, out=None):
     """Per-head RMS-norm and rotate-half RoPE of the q and k heads of a fused q/k/v row in one launch.
     qkv bf16 [B, >= heads*128]; weight bf16 [heads,128]; cos / sin bf16 [1 or B,128] (sin = [-sin, sin]).

@@ -49,7 +49,8 @@ def test_device_plan_matches_host_arithmetic(schedule):
         assert lib.pk_zone_max_candidates(ctypes.byref(schedule), N) == want
 
 
-@pytest.mark.parametrize("lens,K", [((4099, 33000, 9000), 256), ((700, 120, 4999), 64), ((31000, 31000), 2048)])
+@pytest.mark.parametrize("lens,K", [((4099, 33000, 9000), 256), ((700, 120, 4999), 64), ((31000, 31000), 2048),
+                                    ((200000, 90000), 2048)])   # the last: candidate rows long enough for the separate top-K
 def test_varlen_batch_equals_single_sequences_and_oracle(ops, oracle, schedule, lens, K):
     """A batch whose samples have different zone lengths (device i32 [bs]) gives, per sample, exactly what a batch-1
     call on that sample gives with host-side thresholds — and what the oracle gives."""
@@ -86,7 +87,8 @@ def test_varlen_batch_equals_single_sequences_and_oracle(ops, oracle, schedule, 
         assert torch.equal(fin[b, :, :Kb].cpu(), ref["final"][0])
 
 
-@pytest.mark.parametrize("N,K,world", [(40000, 512, 4), (9001, 256, 3), (131004, 2048, 8)])
+@pytest.mark.parametrize("N,K,world", [(40000, 512, 4), (9001, 256, 3), (131004, 2048, 8), (400000, 2048, 2),
+                                       (300000, 1024, 3)])   # the last two: shard rows beyond the in-block final stage
 def test_sharded_phases_reproduce_single_gpu_selection(ops, oracle, N, K, world):
     """W contiguous shards, each run through phase 1 / phase 2 with the gathered histograms: the union of the shards'
     candidate lists IS the single-GPU candidate list, and the top-K of the shards' local top lists IS the single-GPU

@@ -226,3 +226,59 @@ def _tp_worker(rank, world, port):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_tensor_parallel_reduce_on_two_gpus():
     mp.spawn(_tp_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+class _EchoCache:
+    """Stands in for a cache that wants all heads on every rank: attention output = the (normed, rotated) queries."""
+    context = 300
+
+    def decode_update_kv_cache(self, k, v, layer):
+        self.kv_shape = (tuple(k.shape), tuple(v.shape))
+
+    def compute(self, q, layer):
+        return q
+
+
+def _hybrid_worker(rank, world, port):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import bench
+        from pariskv_b200.dist import TPReducer
+        cfg = dict(layers=3, hidden=512, q_heads=8, kv_heads=4, head_dim=128, ffn=1024, vocab=2048, rope_theta=1e4)
+        single = bench.DecoderHarness(cfg, dev, seed=21)
+        tok = torch.tensor([17], device=dev)
+        single.step(_EchoCache(), tok)
+        want = single.last_logits.float()
+        Vr = cfg["vocab"] // world
+        for mode in ("peer", "nccl"):
+            red = TPReducer((cfg["q_heads"] + 2 * cfg["kv_heads"]) * 128, dev, mode=mode)
+            model = bench.DecoderHarness(cfg, dev, seed=21, rank=rank, world=world, reducer=red, gather_heads=True)
+            cache = _EchoCache()
+            nxt = model.step(cache, tok)
+            got = model.last_logits.float()
+            # the cache saw ALL heads; the logits are this rank's slice of the single-GPU logits (bf16 rounding of the
+            # split sums aside); the arg-max over the ranks' slices is the same token on every rank
+            assert cache.kv_shape == ((1, 1, 4, 128), (1, 1, 4, 128))
+            ref = want[:, rank * Vr:(rank + 1) * Vr]
+            assert (got - ref).abs().max().item() <= 0.05 * max(1.0, ref.abs().max().item()), mode
+            toks = torch.empty(world, dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(toks, nxt)
+            assert bool((toks == toks[0]).all())
+            red.check()
+            torch.cuda.synchronize()
+            dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_dense_layers_with_all_heads_gathered_on_two_gpus():
+    """The harness form used with the sequence-sharded cache: q/k/v rows all-gathered (peer kernel or NCCL), output
+    and MLP projections reduced; against the single-GPU harness with the same weights."""
+    mp.spawn(_hybrid_worker, args=(2, _free_port()), nprocs=2, join=True)
