@@ -65,6 +65,7 @@ class DecoderHarness:
         # gather_heads: the cache behind this model wants ALL heads on every rank (it is sharded along the sequence):
         # the ranks' q/k/v rows are all-gathered after the projection, the norm / RoPE and the cache calls run on all
         # heads, and the output projection takes this rank's slice of the attention output
+        self.own_gemv = True    # False: every projection through the library GEMM (bench.py --gemv cublas)
         self.gather_heads = bool(gather_heads) and world > 1
         if self.gather_heads:
             per = (self.Hq + 2 * self.Hk) * D     # one rank's [q_r | k_r | v_r]
@@ -131,8 +132,12 @@ class DecoderHarness:
         sin = torch.sin(ang)
         sin = torch.cat([-sin, sin], -1).to(torch.bfloat16).contiguous()     # sign of rotate-half folded in
         h, x = ops.add_rmsnorm(self.embed[token], None, self.ln1[0], 1e-6)   # [B, hidden]
+        # one token: the projections are matrix-vector products streamed by this library's kernel (the gate / up pair
+        # with the activation in its epilogue); batches go through the library GEMM
+        own = B == 1 and self.own_gemv
+        lin = (lambda t, w: ops.gemv(w, t)) if own else F.linear
         for l in range(L):
-            qkv = F.linear(x, self.wqkv[l])
+            qkv = lin(x, self.wqkv[l])
             if self.gather_heads:     # all heads on every rank: [q_r | k_r | v_r] of every rank -> [q | k | v]
                 qkv = self.reducer.all_gather(qkv).view(-1)[self._perm].view(1, -1)
             qk = ops.qk_norm_rope(qkv, self.qkn[l], cos, sin, 1e-6)            # [B, Hq + Hk, 128]
@@ -141,10 +146,10 @@ class DecoderHarness:
             attn = cache.compute(qk[:, :Hq].view(B, 1, Hq, D), l).view(B, Hq * D)
             if self.gather_heads:     # row-parallel output projection: this rank's q heads
                 attn = attn[:, self.rank * self.Hq * D:(self.rank + 1) * self.Hq * D]
-            h, x = self._sum_norm(F.linear(attn, self.wo[l]), h, self.ln2[l])
-            act = ops.silu_mul(F.linear(x, self.wgu[l]))
-            h, x = self._sum_norm(F.linear(act, self.wd[l]), h, self.ln1[l + 1] if l + 1 < L else self.lnf)
-        logits = F.linear(x, self.lm_head)
+            h, x = self._sum_norm(lin(attn, self.wo[l]), h, self.ln2[l])
+            act = ops.gemv(self.wgu[l], x, gated=True) if own else ops.silu_mul(F.linear(x, self.wgu[l]))
+            h, x = self._sum_norm(lin(act, self.wd[l]), h, self.ln1[l + 1] if l + 1 < L else self.lnf)
+        logits = lin(x, self.lm_head)
         self.last_logits = logits          # this rank's slice of the vocabulary (kept for checks)
         if self.world == 1 or getattr(self.reducer, "mode", None) == "none":
             return logits.argmax(-1)
@@ -1145,6 +1150,9 @@ def main():
     ap.add_argument("--tp-share", type=int, default=1,
                     help="variant (N = 1 only): time rank 0's share of a tensor-parallel step over this many ranks on one "
                          "GPU, the reductions replaced by local adds: what a rank costs before any communication")
+    ap.add_argument("--gemv", default="own", choices=["own", "cublas"],
+                    help="variant: the one-token projections through this library's streaming matrix-vector kernel "
+                         "(default) or through the library GEMM")
     ap.add_argument("--no-numa", action="store_true",
                     help="variant: do not place the pinned K/V store on the NUMA node of the GPU's host link")
     ap.add_argument("--dense", default="tp", choices=["tp", "replicated"],
@@ -1246,6 +1254,7 @@ def main():
         model = DecoderHarness(cfg, device, seed=1234, rank=0, world=args.tp_share, reducer=TPReducer_none())
     else:
         model = DecoderHarness(cfg, device, seed=1234)
+    model.own_gemv = args.gemv == "own"
     # the K/V store is first touched on the CPUs of this GPU's NUMA node: its rows are then local to the GPU's link
     with numa_scope(device, args) as numa:
         if tp:
@@ -1471,7 +1480,7 @@ def main():
         "cpu_baseline": cpu,
         "published_reference": {"decode_tok_s_128k_bs1": 41.10, "note": "hardware and model unstated by the reference"},
         "cuda_graph": {"used": use_graph, "captures": runner.captures},
-        "setup_s": round(setup_s, 1), "host_numa": numa.bound, "zone_keys_per_head": N, "candidates": C, "final_topk": Kf,
+        "setup_s": round(setup_s, 1), "host_numa": numa.bound, "gemv": args.gemv, "zone_keys_per_head": N, "candidates": C, "final_topk": Kf,
         "kv_heads_per_rank": H,
     }
     if tp:

@@ -57,7 +57,7 @@ int64_t pk_launch_count(void);
  * ranking/table, 2 collision, 3 select+rerank, 4 final top-k, 5 attention tiles, 6 attention merge,
  * 7 encode, 8 stand-alone top-k, 9 stand-alone rerank, 10 UVA gather, 11 cluster histogram, 12 row append,
  * 13 decode glue, 14 tensor-parallel reduce, 15 shard pack / send, 16 shard receive / merge, 17 shard owned rows,
- * 18 shard count-histogram reduce) and clears the record. */
+ * 18 shard count-histogram reduce, 19 matrix-vector product) and clears the record. */
 int pk_timing_enable(int on);
 int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages);
 /* Launches issued INTO A STREAM CAPTURE while timing is enabled are bracketed by external event-record nodes, which
@@ -466,6 +466,10 @@ int pk_qk_norm_rope(const pk_tensor* qkv, const pk_tensor* weight, const pk_tens
 int pk_add_rmsnorm(const pk_tensor* a, const pk_tensor* residual, const pk_tensor* weight, const pk_tensor* h_out,
                    const pk_tensor* x_out, double eps, void* stream);
 int pk_silu_mul(const pk_tensor* gate_up, const pk_tensor* out, void* stream);
+/* pk_gemv: out[1,O] = x[1,I] * weight[O,I]^T (bf16, fp32 accumulation), one token; HBM-bound streaming kernel, two rows
+ *   per warp.  gated != 0: weight is a stacked [gate; up] matrix of O = 2F rows and out[1,F] = silu(gate x) * (up x),
+ *   rounded like pk_silu_mul after a separate product.  I a multiple of 8, at most 24576. */
+int pk_gemv(const pk_tensor* weight, const pk_tensor* x, const pk_tensor* out, int gated, void* stream);
 
 #ifdef __cplusplus
 }

@@ -96,6 +96,7 @@ SIGNATURES = {
     "pk_qk_norm_rope": (_INT, [TP, TP, TP, TP, TP, ctypes.c_double, _VP]),
     "pk_add_rmsnorm": (_INT, [TP, TP, TP, TP, TP, ctypes.c_double, _VP]),
     "pk_silu_mul": (_INT, [TP, TP, _VP]),
+    "pk_gemv": (_INT, [TP, TP, TP, _INT, _VP]),
 }
 
 _lib = None
@@ -185,7 +186,7 @@ def launch_count() -> int:
 
 STAGES = ["query_prep", "rank_table", "collision", "select_rerank", "final_topk", "attention", "attention_merge",
           "encode", "topk", "rerank", "uva_gather", "count_clusters", "append", "glue", "tp_reduce",
-          "shard_send", "shard_recv", "shard_owned", "hist_reduce"]
+          "shard_send", "shard_recv", "shard_owned", "hist_reduce", "gemv"]
 
 
 def timing_enable(on: bool):

@@ -202,3 +202,98 @@ extern "C" int pk_silu_mul(const pk_tensor* gate_up, const pk_tensor* out, void*
       (const uint16_t*)gate_up->data, (uint16_t*)out->data, (int)F);
   return check_launch("silu_mul");
 }
+
+// ---- matrix-vector products of a decode step (one token): y = W x, W bf16 [O, I] row-major, fp32 accumulation ------
+// HBM-bound: a warp takes two rows, every lane keeps sixteen 16-byte streaming loads in flight, x sits in shared memory.
+// GATED: the rows are (o, o + F) of a stacked [gate; up] matrix and the output is silu(gate) * up, rounded like the
+// separate launches would (bf16 after the product, after silu, after the multiply).
+namespace pk {
+namespace {
+
+__device__ __forceinline__ void unpack8(const uint4 v, float* f) {
+  f[0] = __uint_as_float(v.x << 16), f[1] = __uint_as_float(v.x & 0xffff0000u);
+  f[2] = __uint_as_float(v.y << 16), f[3] = __uint_as_float(v.y & 0xffff0000u);
+  f[4] = __uint_as_float(v.z << 16), f[5] = __uint_as_float(v.z & 0xffff0000u);
+  f[6] = __uint_as_float(v.w << 16), f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+constexpr int GV_THREADS = 256;
+constexpr int GV_UNROLL = 8;
+
+template <bool GATED>
+__global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const uint16_t* __restrict__ W, const uint16_t* __restrict__ x,
+                                                          uint16_t* __restrict__ out, int O, int I, int F) {
+  extern __shared__ __align__(16) unsigned char gv_smem[];
+  uint4* xs = reinterpret_cast<uint4*>(gv_smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nchunk = I >> 3;
+  for (int c = tid; c < nchunk; c += GV_THREADS) xs[c] = __ldg(reinterpret_cast<const uint4*>(x) + c);
+  __syncthreads();
+  const int n_pairs = GATED ? F : (O + 1) / 2;
+  const int p = blockIdx.x * (GV_THREADS / 32) + warp;
+  if (p >= n_pairs) return;
+  const int r0 = GATED ? p : 2 * p, r1 = GATED ? p + F : 2 * p + 1;
+  const bool has1 = r1 < O;
+  const uint4* w0 = reinterpret_cast<const uint4*>(W + (int64_t)r0 * I);
+  const uint4* w1 = reinterpret_cast<const uint4*>(W + (int64_t)(has1 ? r1 : r0) * I);
+  float acc0 = 0.0f, acc1 = 0.0f;
+  for (int c0 = lane; c0 < nchunk; c0 += 32 * GV_UNROLL) {
+    uint4 a[GV_UNROLL], b[GV_UNROLL];
+#pragma unroll
+    for (int u = 0; u < GV_UNROLL; u++) {
+      const int c = c0 + 32 * u;
+      a[u] = c < nchunk ? __ldcs(w0 + c) : make_uint4(0, 0, 0, 0);
+      b[u] = c < nchunk ? __ldcs(w1 + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < GV_UNROLL; u++) {
+      const int c = c0 + 32 * u;
+      if (c < nchunk) {
+        float xf[8], af[8], bf[8];
+        unpack8(xs[c], xf);
+        unpack8(a[u], af);
+        unpack8(b[u], bf);
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc0 = fmaf(af[k], xf[k], acc0), acc1 = fmaf(bf[k], xf[k], acc1);
+      }
+    }
+  }
+  acc0 = warp_sum(acc0);
+  acc1 = warp_sum(acc1);
+  if (lane == 0) {
+    if (GATED) {
+      const float g = bfround(acc0), uu = bfround(acc1);
+      out[p] = f2bf(bfround(g / (1.0f + __expf(-g))) * uu);
+    } else {
+      out[r0] = f2bf(acc0);
+      if (has1) out[r1] = f2bf(acc1);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace pk
+
+extern "C" int pk_gemv(const pk_tensor* weight, const pk_tensor* x, const pk_tensor* out, int gated, void* stream) {
+  PK_CHECK_TENSOR(weight, PK_BF16, 2);
+  PK_CHECK_TENSOR(x, PK_BF16, 2);
+  PK_CHECK_TENSOR(out, PK_BF16, 2);
+  const int64_t O = weight->shape[0], I = weight->shape[1];
+  PK_REQUIRE(is_contig(weight) && is_contig(x) && is_contig(out) && x->shape[0] == 1 && x->shape[1] == I && out->shape[0] == 1,
+             "weight must be contiguous bf16 [O,I], x [1,I], out [1,O] (or [1,O/2] when gated)");
+  PK_REQUIRE(I % 8 == 0 && I >= 8 && I <= 24576 && O >= 1 && O < (1LL << 30), "I must be a multiple of 8, at most 24576");
+  PK_REQUIRE(gated ? (O % 2 == 0 && out->shape[1] == O / 2) : out->shape[1] == O,
+             "out must have O columns (O/2 when gated, with O even)");
+  PK_REQUIRE(aligned16(weight->data) && aligned16(x->data), "weight and x must be 16-byte aligned");
+  const int64_t pairs = gated ? O / 2 : (O + 1) / 2;
+  const unsigned grid = (unsigned)((pairs + GV_THREADS / 32 - 1) / (GV_THREADS / 32));
+  const size_t smem = (size_t)I * 2;
+  StageTimer timer(ST_GEMV, (cudaStream_t)stream);
+  if (gated)
+    gemv_kernel<true><<<grid, GV_THREADS, smem, (cudaStream_t)stream>>>((const uint16_t*)weight->data, (const uint16_t*)x->data,
+                                                                       (uint16_t*)out->data, (int)O, (int)I, (int)(O / 2));
+  else
+    gemv_kernel<false><<<grid, GV_THREADS, smem, (cudaStream_t)stream>>>((const uint16_t*)weight->data, (const uint16_t*)x->data,
+                                                                        (uint16_t*)out->data, (int)O, (int)I, 0);
+  return check_launch("gemv");
+}

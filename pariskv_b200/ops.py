@@ -559,3 +559,14 @@ def silu_mul(gate_up):
     d = [L.desc(gate_up), L.desc(out)]
     _call("pk_silu_mul", L.ref(d[0]), L.ref(d[1]), L.stream_ptr(gate_up.device))
     return out
+
+
+def gemv(weight, x, gated=False):
+    """x [1, I] @ weight[O, I]^T -> [1, O] (bf16, fp32 accumulation) for one token; gated: weight = [gate; up] stacked,
+    result [1, O/2] = silu(gate x) * (up x).  See pk_gemv."""
+    _require_cuda(weight, x)
+    O = weight.shape[0]
+    out = torch.empty(1, O // 2 if gated else O, dtype=torch.bfloat16, device=x.device)
+    d = [L.desc(weight), L.desc(x), L.desc(out)]
+    _call("pk_gemv", L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), int(bool(gated)), L.stream_ptr(x.device))
+    return out

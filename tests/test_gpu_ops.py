@@ -622,3 +622,22 @@ def test_stage_timing_inside_a_replayed_graph(ops):
     del g
     _lib.timing_clear_graph()
     assert _lib.timing_read_graph() == {}
+
+
+@pytest.mark.parametrize("O,I", [(6144, 4096), (4096, 12288), (1001, 520), (2, 8)])
+def test_gemv_against_fp32(ops, O, I):
+    """One-token projection: fp32 accumulation, one bf16 rounding; plain and gated ([gate; up] stacked, silu in the
+    epilogue, rounded like the separate launches)."""
+    g = torch.Generator().manual_seed(O + I)
+    W = (torch.randn(O, I, generator=g) * 0.05).to(torch.bfloat16)
+    x = torch.randn(1, I, generator=g).to(torch.bfloat16)
+    y = ops.gemv(W.to(DEV), x.to(DEV))
+    ref = x.float() @ W.float().t()
+    assert y.shape == (1, O)
+    assert (y.float().cpu() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+    if O % 2 == 0:
+        act = ops.gemv(W.to(DEV), x.to(DEV), gated=True)
+        gu = ref.to(torch.bfloat16).float()
+        want = torch.nn.functional.silu(gu[:, :O // 2]).to(torch.bfloat16).float() * gu[:, O // 2:]
+        assert act.shape == (1, O // 2)
+        assert (act.float().cpu() - want).abs().max().item() <= 3e-2 * max(1.0, want.abs().max().item())
