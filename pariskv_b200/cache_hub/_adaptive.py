@@ -37,6 +37,8 @@ class AdaptiveKCache(_base_cache):
         self.value_norm_gpu = [torch.zeros(bs, H, self.zone_capacity, dtype=torch.float32, device=dev)
                                for _ in range(self.layer_num)]
         self.last_adaptive = None   # (adaptive_k, topk_indices, n_sel, sl_logits, cand, cand_scores) of the last compute
+        self.fixed_shapes = False   # True: capacity-shaped tensors on eager steps too (what a stream capture uses)
+        self._row_ids = torch.arange(self.window_capacity, device=dev, dtype=torch.int32)
 
     def _zone_vnorm(self, layer):
         return self.value_norm_gpu[layer]
@@ -69,23 +71,42 @@ class AdaptiveKCache(_base_cache):
                                    scratch=self._retrieve_scratch)
         cand, cand_scores = ex["cand"], ex["scores_f32"]
         C = self.retrieval_plan(N)[1]          # candidates of the longest sample
-        if min(self.zone_len[layer_idx]) == N:  # equal lengths: the lists as the reference shapes them, [bs,H,C]
-            cand, cand_scores = cand[:, :, :C].contiguous(), cand_scores[:, :, :C].contiguous()
+        # Shapes that follow the host's view of the lengths (the reference's shapes) on eager steps; inside a stream
+        # capture, or with fixed_shapes set, every shape is a capacity and the lengths act on the device only: window
+        # rows beyond the filled part get logit -inf, candidate rows keep their -inf tail, and a head never attends
+        # more rows than it has candidates.  Both forms attend the same rows.
+        fixed = self.fixed_shapes or torch.cuda.is_current_stream_capturing()
+        equal = min(self.zone_len[layer_idx]) == N
+        if fixed:
+            n_rows, C = self.window_capacity, cand.shape[2]
+        else:
+            n_rows = n_win
+            if equal:   # equal lengths: the lists as the reference shapes them, [bs,H,C]
+                cand, cand_scores = cand[:, :, :C].contiguous(), cand_scores[:, :, :C].contiguous()
         cand_scores = cand_scores.to(torch.bfloat16)   # the reference ranks bf16 scores
         # window logits: a small dense product, left to the library as the reference does
-        sl_logits = torch.einsum("bhd,bhkd->bhk", ex["query_avg"], wk[:, :, :n_win]).to(torch.float32) * self._attn_scale
+        sl_logits = torch.einsum("bhd,bhkd->bhk", ex["query_avg"], wk[:, :, :n_rows]).to(torch.float32) * self._attn_scale
+        if fixed:
+            sl_logits = sl_logits.masked_fill(self._row_ids[:n_rows] >= st[0], float("-inf"))
         K_out = min(self._max_k, C)
         min_k = min(self._min_k, K_out)
         adaptive_k, topk = ops.adaptive_topk(sl_logits.contiguous(), cand_scores, self._attn_scale,
-                                             self._sl_vnorm_cache[layer_idx][:, :, :n_win], cand, None,
+                                             self._sl_vnorm_cache[layer_idx][:, :, :n_rows], cand, None,
                                              self.adaptive_topk_threshold, K_out,
                                              value_norm=self.value_norm_gpu[layer_idx], sink_size=0,
                                              min_k=max(1, min_k), max_k=max(1, K_out))
+        if fixed or not equal:   # rows longer than a sample's candidate list: its count caps what the head attends
+            adaptive_k = torch.minimum(adaptive_k, ex["n_cand"].to(adaptive_k.dtype))
         if self._per_head:
             n_sel = adaptive_k.to(torch.int32)
         else:  # dense variant: every head attends the first max-over-heads rows of its own ranking
             n_sel = adaptive_k.max().to(torch.int32).expand_as(adaptive_k).contiguous()
+            if fixed or not equal:
+                n_sel = torch.minimum(n_sel, ex["n_cand"])
         self.last_adaptive = (adaptive_k, topk, n_sel, sl_logits, cand, cand_scores)
         self.last_topk_indices = topk
+        if fixed:
+            return self._attend(queries, wk, wv, self.window_capacity, self._store_k[layer_idx], self._store_v[layer_idx],
+                                topk, n_sel=n_sel, n_window_dev=st[0:1], n_window_add=0)
         return self._attend(queries, wk, wv, n_win, self._store_k[layer_idx], self._store_v[layer_idx], topk,
                             n_sel=n_sel)

@@ -88,3 +88,64 @@ def test_adaptive_cache_matches_oracle(oracle, kind, extra, bs):
                 tol = max(2e-2, ref.abs().max().item() * 2.0 ** -8)
                 assert (out[sb, :, g0:g1].float().cpu() - ref).abs().max().item() <= tol, (t, b, h)
     assert cache.cpu_valid_end[0] == P - sink - local + I
+
+
+@pytest.mark.parametrize("kind,extra", [("dense", dict(adaptive_topk_threshold=0.9, adaptive_topk_max_k=256)),
+                                        ("varlen", dict(adaptive_topk_threshold=0.85, adaptive_topk_min_k=20,
+                                                        adaptive_topk_max_k=200))])
+def test_adaptive_cache_replays_under_one_graph(kind, extra):
+    """Append + adaptive compute captured ONCE and replayed over a flush of the update buffer gives, step for step, the
+    rows (per-head counts, benefit order) and the attention output of eager stepping on a twin cache: inside a capture
+    every shape is a capacity and the lengths act through device words only."""
+    g = torch.Generator().manual_seed(11)
+    bs, H, Hq, sink, local, I, P, steps = 2, 2, 8, 4, 16, 8, 2400, 19
+    twins = [_make(kind, P, bs, H, Hq, sink, local, I, **extra) for _ in range(2)]
+    K = synth_keys(g, bs, H, P)
+    V = (torch.randn(bs, H, P, 128, generator=g) * torch.exp(0.5 * torch.randn(bs, H, P, 1, generator=g))).to(torch.bfloat16)
+    for c in twins:
+        c.prefill_update_kv_cache(None, K.transpose(1, 2).contiguous().to(DEV), V.transpose(1, 2).contiguous().to(DEV), 0, 0)
+    eager, graphed = twins
+    k_in = torch.zeros(bs, 1, H, 128, dtype=torch.bfloat16, device=DEV)
+    v_in = torch.zeros_like(k_in)
+    q_in = torch.zeros(bs, 1, Hq, 128, dtype=torch.bfloat16, device=DEV)
+    graph, out_g, captured = None, None, 0
+    for t in range(steps):
+        nk = synth_keys(g, bs, H, 1).transpose(1, 2).contiguous()
+        nv = torch.randn(bs, 1, H, 128, generator=g).to(torch.bfloat16)
+        pick = torch.randint(sink, P - local, (bs, H), generator=g)
+        qk = torch.stack([torch.stack([K[b, h, pick[b, h]].float() for h in range(H)]) for b in range(bs)])
+        q = (qk / qk.norm(dim=-1, keepdim=True) * 6.0).unsqueeze(2).expand(bs, H, Hq // H, 128)
+        q = (q + 0.3 * torch.randn(bs, H, Hq // H, 128, generator=g)).reshape(bs, 1, Hq, 128).to(torch.bfloat16)
+        k_in.copy_(nk), v_in.copy_(nv), q_in.copy_(q)
+        eager.decode_update_kv_cache(k_in, v_in, 0)
+        want = eager.compute(q_in, 0).clone()
+        ak_e, topk_e, nsel_e = (x.clone() for x in eager.last_adaptive[:3])
+        if t < 2:      # first steps eagerly on both (first-use set-up outside the capture)
+            graphed.decode_update_kv_cache(k_in, v_in, 0)
+            got = graphed.compute(q_in, 0)
+        else:
+            if graph is None:
+                torch.cuda.synchronize()
+                saved = graphed.host_state()
+                graph = torch.cuda.CUDAGraph()
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    graph.capture_begin()
+                    graphed.decode_update_kv_cache(k_in, v_in, 0)
+                    out_g = graphed.compute(q_in, 0)
+                    graph.capture_end()
+                torch.cuda.current_stream().wait_stream(side)
+                graphed.set_host_state(saved)   # the capture ran the host bookkeeping of one step without executing it
+                captured += 1
+            graph.replay()
+            graphed.note_replayed_step()
+            got = out_g
+        ak_g, topk_g, nsel_g = graphed.last_adaptive[:3]
+        assert torch.equal(nsel_g, nsel_e), t
+        for b in range(bs):
+            for h in range(H):
+                n = int(nsel_e[b, h])
+                assert torch.equal(topk_g[b, h, :n], topk_e[b, h, :n]), (t, b, h)
+        assert torch.equal(got, want), t
+    assert captured == 1 and eager.cpu_valid_end[0] > P - local - sink      # at least one flush was replayed
