@@ -328,7 +328,8 @@ constexpr int VH_SHIFT = 32 - VH_BITS;
 template <int NT>
 __device__ bool final_select_hist(const float* __restrict__ scores, const int64_t* __restrict__ cand, int n, int K,
                                   int64_t* __restrict__ out, const unsigned* __restrict__ vhist, unsigned* bitmap,
-                                  uint2* tie, unsigned* s_w, unsigned long long* s_scan) {
+                                  uint2* tie, unsigned* sel /*K words or null*/, unsigned* s_w,
+                                  unsigned long long* s_scan) {
   static_assert(VH_BINS == NT * 32, "32 histogram bins per thread");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // ---- threshold bin: thread 0 holds the highest 32 bins ----
@@ -418,14 +419,27 @@ __device__ bool final_select_hist(const float* __restrict__ scores, const int64_
     unsigned take = mine | (gbase < n ? bitmap[gbase >> 5] : 0u);
     unsigned long long tot_round;
     unsigned o = (unsigned)(run + block_scan_excl<NT>((unsigned long long)__popc(take), s_scan, &tot_round));
-    while (take) {
+    while (take) {  // positions first (shared memory); the candidate ids are fetched afterwards, many loads in flight
       const int j = __ffs(take) - 1;
       take &= take - 1;
-      if (o < (unsigned)K) out[o] = __ldcg(cand + gbase + j);
+      if (o < (unsigned)K) {
+        if (sel) sel[o] = (unsigned)(gbase + j);
+        else out[o] = __ldcg(cand + gbase + j);
+      }
       o++;
     }
     run += tot_round;
     __syncthreads();
+  }
+  if (sel) {
+    for (int base = tid; base < K; base += NT * 8) {
+      int64_t cv[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) cv[j] = base + j * NT < K ? __ldcg(cand + sel[base + j * NT]) : 0;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        if (base + j * NT < K) out[base + j * NT] = cv[j];
+    }
   }
   return true;
 }
@@ -748,8 +762,11 @@ __global__ void __launch_bounds__(SEL_THREADS, FAST ? 2 : 1) select_rerank_kerne
     if (!done && p.val_hist && (C_here + 31) / 32 <= pp.bitmap_words) {
       unsigned* bitmap = reinterpret_cast<unsigned*>(list);
       uint2* tie = reinterpret_cast<uint2*>(bitmap + pp.bitmap_words);
+      // the position list sits in the unused upper part of the bitmap area when there is room for it
+      const int n_words = (int)((C_here + 31) / 32);
+      unsigned* sel = n_words + K_here <= pp.bitmap_words ? bitmap + n_words : nullptr;
       done = final_select_hist<SEL_THREADS>(p.scores_f32 + row_base, p.cand_out + row_base, (int)C_here, K_here,
-                                            p.final_out + bh * p.K, p.val_hist + bh * VH_BINS, bitmap, tie, s_warp,
+                                            p.final_out + bh * p.K, p.val_hist + bh * VH_BINS, bitmap, tie, sel, s_warp,
                                             s_scan);
       __syncthreads();
     }
