@@ -1155,6 +1155,9 @@ def main():
     ap.add_argument("--gemv", default="own", choices=["own", "cublas"],
                     help="variant: the one-token projections through this library's streaming matrix-vector kernel "
                          "(default) or through the library GEMM")
+    ap.add_argument("--pdl", default="on", choices=["on", "off"],
+                    help="programmatic dependent launch between the kernels of this library (a kernel's prologue, e.g. "
+                         "the first weight loads of a projection, runs under the tail of its predecessor)")
     ap.add_argument("--no-numa", action="store_true",
                     help="variant: do not place the pinned K/V store on the NUMA node of the GPU's host link")
     ap.add_argument("--dense", default="tp", choices=["tp", "replicated"],
@@ -1200,6 +1203,7 @@ def main():
     from pariskv_b200.build import build
     build()
     _lib.load()
+    _lib.set_pdl(args.pdl == "on")
 
     def barrier():
         if world > 1:
@@ -1482,7 +1486,7 @@ def main():
         "cpu_baseline": cpu,
         "published_reference": {"decode_tok_s_128k_bs1": 41.10, "note": "hardware and model unstated by the reference"},
         "cuda_graph": {"used": use_graph, "captures": runner.captures},
-        "setup_s": round(setup_s, 1), "host_numa": numa.bound, "gemv": args.gemv, "zone_keys_per_head": N, "candidates": C, "final_topk": Kf,
+        "setup_s": round(setup_s, 1), "host_numa": numa.bound, "gemv": args.gemv, "pdl": args.pdl, "zone_keys_per_head": N, "candidates": C, "final_topk": Kf,
         "kv_heads_per_rank": H,
     }
     if tp:

@@ -67,9 +67,12 @@ int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages)
 int pk_timing_read_graph(double* ms_per_stage, int64_t* spans_per_stage, int n_stages);
 int pk_timing_clear_graph(void);
 
-/* Process-wide option, no counterpart in the reference: launch the kernels of the decode chain with programmatic
- * dependent launch (a kernel's prologue may overlap the tail of its predecessor).  Off by default: with the decode
- * step replayed as a CUDA graph it measured neutral on B200. */
+/* Process-wide option, no counterpart in the reference: launch the kernels of this library with programmatic
+ * dependent launch.  A kernel may then be scheduled while its predecessor on the stream still runs; it does only
+ * what does not depend on earlier kernels (the collision kernel its first code loads, a projection its first weight
+ * loads) and then waits for the predecessor to complete, and every kernel releases its successor only after its own
+ * wait, so completion is transitive along the stream.  Off by default; with the decode step replayed as a CUDA graph
+ * it measured +1.9 % tokens/s at the 128K configuration on B200. */
 int pk_set_pdl(int on);
 
 /* ---- (a) key coding ---------------------------------------------------------------------- */

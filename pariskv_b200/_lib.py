@@ -189,6 +189,11 @@ STAGES = ["query_prep", "rank_table", "collision", "select_rerank", "final_topk"
           "shard_send", "shard_recv", "shard_owned", "hist_reduce", "gemv"]
 
 
+def set_pdl(on: bool):
+    """Launch the kernels of a decode step with programmatic dependent launch (see pk_set_pdl)."""
+    check(load().pk_set_pdl(int(bool(on))))
+
+
 def timing_enable(on: bool):
     check(load().pk_timing_enable(int(bool(on))))
 

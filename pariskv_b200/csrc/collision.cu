@@ -424,12 +424,20 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
   const int64_t N = cq.n_dev ? min(max((int64_t)cq.n_dev[b], (int64_t)1), p.N) : p.N;
   const int64_t Nv = N + p.mis;
   const int64_t v_begin = (int64_t)blockIdx.x * p.chunk_keys;
-  if (cq.zero_area) {  // every block clears its slice of the next kernel's value histogram, also beyond a short zone
+  // every block clears its slice of the next kernel's value histogram, also a block beyond a short zone; a write, so
+  // it comes after the wait for the kernels before this one
+  auto clear_slice = [&]() {
+    if (!cq.zero_area) return;
     const int per = (cq.zero_area_words + (int)gridDim.x - 1) / (int)gridDim.x;
     const int lo = (int)blockIdx.x * per, hi = min(cq.zero_area_words, lo + per);
     for (int i = lo + tid; i < hi; i += CC_THREADS) cq.zero_area[(int64_t)bh * cq.zero_area_words + i] = 0u;
+  };
+  if (v_begin >= Nv) {  // beyond this sample's zone (whole block, before any barrier)
+    pdl_wait();
+    pdl_trigger();
+    clear_slice();
+    return;
   }
-  if (v_begin >= Nv) return;  // beyond this sample's zone (whole block, before any barrier)
   const int64_t v_end = min(Nv, v_begin + p.chunk_keys);
   const uint8_t* base = p.codes + b * p.c_b + h * p.c_h - p.mis * p.c_l;
   uint8_t* out8 = p.out_u8 + (int64_t)bh * p.u8_stride;
@@ -456,6 +464,7 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
   }
   pdl_wait();     // the code loads above do not depend on the kernel before this one; the query below does
   pdl_trigger();
+  clear_slice();
 
   // ---- prologue: query, cluster ranking, tier table ----
   {

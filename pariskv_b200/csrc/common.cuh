@@ -70,8 +70,9 @@ inline int elem_size(int dtype) {
 // may be scheduled while its predecessor is still running, does the part of its prologue that does not read the
 // predecessor's output, and then blocks in pdl_wait() until the predecessor has completed and flushed.  Every
 // kernel signals pdl_trigger() only AFTER its own pdl_wait(), so completion is transitive along the chain.
-// Without the launch attribute both instructions do nothing.  The attribute is set only after pk_set_pdl(1):
-// with the decode step replayed as a CUDA graph it measured neutral on B200.
+// Without the launch attribute both instructions do nothing.  The attribute is set only after pk_set_pdl(1).
+// EVERY kernel launched through launch_chain() must call pdl_wait() before it reads or writes anything an earlier
+// kernel may touch: a kernel that skipped the wait would break the chain for its successors.
 bool pdl_enabled();
 
 // Per-device "done once" flags for settings that belong to a device (cudaFuncSetAttribute opt-ins): bit d is set

@@ -212,6 +212,8 @@ __global__ void __launch_bounds__(256) append_encode_kernel(AppendParams p) {
   const int64_t bh = blockIdx.x;
   const int b = (int)(bh / p.H), h = (int)(bh % p.H);
   __shared__ int s_last;
+  pdl_wait();     // the rows to append and the state words come from the kernels before this one
+  pdl_trigger();
   const int pos = p.state[0];
   const int64_t N = p.state[4 + b];
   uint16_t* wk = p.wk + b * p.w_b + h * p.w_h;

@@ -23,6 +23,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kernel(const uint16_t* __res
                                                            const uint16_t* __restrict__ w, const uint16_t* __restrict__ cosv,
                                                            const uint16_t* __restrict__ sinv, int64_t cs_stride,
                                                            uint16_t* __restrict__ out, int heads, int64_t n_warps, float eps) {
+  pdl_wait();
+  pdl_trigger();
   const int64_t wid = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (wid >= n_warps) return;
   const int lane = threadIdx.x & 31;
@@ -60,6 +62,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_kernel(const uint16_t* __res
 __global__ void __launch_bounds__(512) add_rmsnorm_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ r,
                                                           const uint16_t* __restrict__ w, uint16_t* __restrict__ h_out,
                                                           uint16_t* __restrict__ x_out, int n, float eps) {
+  pdl_wait();
+  pdl_trigger();
   const int tid = threadIdx.x;
   const int64_t base = (int64_t)blockIdx.x * n;
   __shared__ float s_part[16];
@@ -107,6 +111,8 @@ __global__ void __launch_bounds__(512) add_rmsnorm_kernel(const uint16_t* __rest
 
 // out[row][i] = bf16( bf16(silu(g[row][i])) * u[row][i] ), g = gu[row][0:F], u = gu[row][F:2F]
 __global__ void __launch_bounds__(256) silu_mul_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ out, int F) {
+  pdl_wait();
+  pdl_trigger();
   const int64_t row = blockIdx.y;
   const int i = (blockIdx.x * 256 + threadIdx.x) * 8;
   if (i >= F) return;
@@ -153,7 +159,7 @@ extern "C" int pk_qk_norm_rope(const pk_tensor* qkv, const pk_tensor* weight, co
   if (n_warps == 0) return PK_OK;
   PK_REQUIRE(heads < (1 << 20) && n_warps < (1LL << 31), "sizes out of range");
   StageTimer timer(ST_GLUE, (cudaStream_t)stream);
-  qk_norm_rope_kernel<<<(unsigned)((n_warps + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
+  launch_chain(qk_norm_rope_kernel, dim3((unsigned)((n_warps + 3) / 4)), dim3(128), 0, (cudaStream_t)stream,
       (const uint16_t*)qkv->data, qkv->stride[0], (const uint16_t*)weight->data, (const uint16_t*)cos->data,
       (const uint16_t*)sin->data, cos->shape[0] == 1 ? 0 : 128, (uint16_t*)out->data, (int)heads, n_warps, (float)eps);
   return check_launch("qk_norm_rope");
@@ -182,9 +188,8 @@ extern "C" int pk_add_rmsnorm(const pk_tensor* a, const pk_tensor* residual, con
              "tensors must be 16-byte aligned");
   if (B * n == 0) return PK_OK;
   StageTimer timer(ST_GLUE, (cudaStream_t)stream);
-  add_rmsnorm_kernel<<<(unsigned)B, 512, 0, (cudaStream_t)stream>>>((const uint16_t*)a->data, r, (const uint16_t*)weight->data,
-                                                                     (uint16_t*)h_out->data, (uint16_t*)x_out->data, (int)n,
-                                                                     (float)eps);
+  launch_chain(add_rmsnorm_kernel, dim3((unsigned)B), dim3(512), 0, (cudaStream_t)stream, (const uint16_t*)a->data, r,
+               (const uint16_t*)weight->data, (uint16_t*)h_out->data, (uint16_t*)x_out->data, (int)n, (float)eps);
   return check_launch("add_rmsnorm");
 }
 
@@ -198,8 +203,8 @@ extern "C" int pk_silu_mul(const pk_tensor* gate_up, const pk_tensor* out, void*
   PK_REQUIRE(aligned16(gate_up->data) && aligned16(out->data), "tensors must be 16-byte aligned");
   if (B * F == 0) return PK_OK;
   StageTimer timer(ST_GLUE, (cudaStream_t)stream);
-  silu_mul_kernel<<<dim3((unsigned)((F / 8 + 255) / 256), (unsigned)B), 256, 0, (cudaStream_t)stream>>>(
-      (const uint16_t*)gate_up->data, (uint16_t*)out->data, (int)F);
+  launch_chain(silu_mul_kernel, dim3((unsigned)((F / 8 + 255) / 256), (unsigned)B), dim3(256), 0, (cudaStream_t)stream,
+               (const uint16_t*)gate_up->data, (uint16_t*)out->data, (int)F);
   return check_launch("silu_mul");
 }
 
@@ -227,24 +232,33 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const uint16_t* __rest
   uint4* xs = reinterpret_cast<uint4*>(gv_smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nchunk = I >> 3;
-  for (int c = tid; c < nchunk; c += GV_THREADS) xs[c] = __ldg(reinterpret_cast<const uint4*>(x) + c);
-  __syncthreads();
   const int n_pairs = GATED ? F : (O + 1) / 2;
   const int p = blockIdx.x * (GV_THREADS / 32) + warp;
-  if (p >= n_pairs) return;
+  const bool live = p < n_pairs;
   const int r0 = GATED ? p : 2 * p, r1 = GATED ? p + F : 2 * p + 1;
-  const bool has1 = r1 < O;
-  const uint4* w0 = reinterpret_cast<const uint4*>(W + (int64_t)r0 * I);
-  const uint4* w1 = reinterpret_cast<const uint4*>(W + (int64_t)(has1 ? r1 : r0) * I);
-  float acc0 = 0.0f, acc1 = 0.0f;
-  for (int c0 = lane; c0 < nchunk; c0 += 32 * GV_UNROLL) {
-    uint4 a[GV_UNROLL], b[GV_UNROLL];
+  const bool has1 = live && r1 < O;
+  const uint4* w0 = reinterpret_cast<const uint4*>(W + (int64_t)(live ? r0 : 0) * I);
+  const uint4* w1 = reinterpret_cast<const uint4*>(W + (int64_t)(has1 ? r1 : (live ? r0 : 0)) * I);
+  // The weights never change: the first batch of their loads is issued before the wait for the kernel that produces
+  // x, so with programmatic dependent launch the stream of weights starts under the tail of that kernel.
+  uint4 a[GV_UNROLL], b[GV_UNROLL];
+  auto load_batch = [&](int c0) {
 #pragma unroll
     for (int u = 0; u < GV_UNROLL; u++) {
       const int c = c0 + 32 * u;
-      a[u] = c < nchunk ? __ldcs(w0 + c) : make_uint4(0, 0, 0, 0);
-      b[u] = c < nchunk ? __ldcs(w1 + c) : make_uint4(0, 0, 0, 0);
+      a[u] = (live && c < nchunk) ? __ldcs(w0 + c) : make_uint4(0, 0, 0, 0);
+      b[u] = (live && c < nchunk) ? __ldcs(w1 + c) : make_uint4(0, 0, 0, 0);
     }
+  };
+  load_batch(lane);
+  pdl_wait();
+  pdl_trigger();
+  for (int c = tid; c < nchunk; c += GV_THREADS) xs[c] = __ldg(reinterpret_cast<const uint4*>(x) + c);
+  __syncthreads();
+  if (!live) return;
+  float acc0 = 0.0f, acc1 = 0.0f;
+  for (int base = 0; base < nchunk; base += 32 * GV_UNROLL) {   // warp-uniform trip count
+    const int c0 = base + lane;
 #pragma unroll
     for (int u = 0; u < GV_UNROLL; u++) {
       const int c = c0 + 32 * u;
@@ -257,6 +271,7 @@ __global__ void __launch_bounds__(GV_THREADS) gemv_kernel(const uint16_t* __rest
         for (int k = 0; k < 8; k++) acc0 = fmaf(af[k], xf[k], acc0), acc1 = fmaf(bf[k], xf[k], acc1);
       }
     }
+    if (base + 32 * GV_UNROLL < nchunk) load_batch(c0 + 32 * GV_UNROLL);
   }
   acc0 = warp_sum(acc0);
   acc1 = warp_sum(acc1);
@@ -290,10 +305,10 @@ extern "C" int pk_gemv(const pk_tensor* weight, const pk_tensor* x, const pk_ten
   const size_t smem = (size_t)I * 2;
   StageTimer timer(ST_GEMV, (cudaStream_t)stream);
   if (gated)
-    gemv_kernel<true><<<grid, GV_THREADS, smem, (cudaStream_t)stream>>>((const uint16_t*)weight->data, (const uint16_t*)x->data,
-                                                                       (uint16_t*)out->data, (int)O, (int)I, (int)(O / 2));
+    launch_chain(gemv_kernel<true>, dim3(grid), dim3(GV_THREADS), smem, (cudaStream_t)stream, (const uint16_t*)weight->data,
+                 (const uint16_t*)x->data, (uint16_t*)out->data, (int)O, (int)I, (int)(O / 2));
   else
-    gemv_kernel<false><<<grid, GV_THREADS, smem, (cudaStream_t)stream>>>((const uint16_t*)weight->data, (const uint16_t*)x->data,
-                                                                        (uint16_t*)out->data, (int)O, (int)I, 0);
+    launch_chain(gemv_kernel<false>, dim3(grid), dim3(GV_THREADS), smem, (cudaStream_t)stream, (const uint16_t*)weight->data,
+                 (const uint16_t*)x->data, (uint16_t*)out->data, (int)O, (int)I, 0);
   return check_launch("gemv");
 }

@@ -845,7 +845,9 @@ int launch_select_rerank(const RerankArgs& a, int64_t bs_h, const SelectArgs& sa
   dim3 grid((unsigned)sa.n_chunks, (unsigned)bs_h);
   const bool fast = rerank_fast_layout(a);
   auto kern = fast ? select_rerank_kernel<true> : select_rerank_kernel<false>;
-  if (smem > 48 * 1024) {  // an opt-in per device: set on every launch that needs it
+  // dynamic + static shared memory above 48 KB is an opt-in per device: set on every launch that may need it (the
+  // kernel's static part is a few KB, so the margin is taken generously)
+  if (smem > 40 * 1024) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return check_launch("select_rerank smem");
   }

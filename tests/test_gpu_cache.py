@@ -243,11 +243,15 @@ def test_long_generation_with_drifting_keys_one_kv_head(oracle):
     assert torch.equal(cache.cluster_key_counts_gpu[0].cpu(), oracle.cluster_counts(cb))
 
 
-def test_graphed_decoder_with_precaptured_graphs_matches_eager():
+@pytest.mark.parametrize("pdl", [False, True])
+def test_graphed_decoder_with_precaptured_graphs_matches_eager(pdl):
     """bench.GraphedDecoder: ONE captured graph replayed across three flushes of the update buffer (the flush runs
     inside the append launch, all positions are device words) must produce the same tokens as plain eager stepping
-    (same weights, same cache content)."""
+    (same weights, same cache content).  With programmatic dependent launch on, every kernel of the step may start
+    under the tail of its predecessor, captured and eager alike; the tokens must not change."""
     import bench
+    from pariskv_b200 import _lib
+    _lib.set_pdl(False)
     cfg = dict(layers=2, hidden=256, q_heads=8, kv_heads=2, head_dim=128, ffn=512, vocab=997, rope_theta=1.0e6,
                context=2600, sink=4, local=16, interval=8, topk=32)
     dev = torch.device(DEV)
@@ -266,6 +270,14 @@ def test_graphed_decoder_with_precaptured_graphs_matches_eager():
     assert cache.cpu_valid_end[0] == 2600 - 20 + 3 * 8
 
     cache = fresh()
+    _lib.set_pdl(pdl)
+    if pdl:      # eager stepping with dependent launch as well
+        tok, again = torch.tensor([3], device=dev), []
+        for _ in range(steps):
+            tok = model.step(cache, tok)
+            again.append(int(tok))
+        assert again == eager
+        cache = fresh()
     runner = bench.GraphedDecoder(model, cache)
     tok = torch.tensor([3], device=dev)
     got = []
@@ -279,6 +291,7 @@ def test_graphed_decoder_with_precaptured_graphs_matches_eager():
     for _ in range(steps - 2):
         runner.step()
         got.append(int(runner.nxt))
+    _lib.set_pdl(False)
     assert got == eager
     assert runner.captures == captured, "a graph was captured inside the run although all lengths were prepared"
     assert cache.cpu_valid_end[0] == 2600 - 20 + 3 * 8 and cache.context == 2600 + steps
