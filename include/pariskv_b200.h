@@ -432,11 +432,14 @@ int pk_shard_collect_partial(uint64_t local_base, int64_t gather_offset, int64_t
  * projections; at decode time that is one short vector, and this entry point does it in ONE launch over peer memory:
  *   out = residual + sum over ranks of partial          (bf16 [1,n] each, fp32 accumulation in rank order, so the
  *                                                        result is bit-identical on every rank)
+ * Every 32-bit data word travels with the exchange number in one 8-byte store into the receiver's gather area, so a
+ * slot that shows the expected number carries its data: no separate flag words, one NVLink store latency per exchange.
  * Layout of every rank's symmetric buffer (peer_bases[r] as seen from this process): two gather areas of area_bytes
- * (>= world * n * 2) each, one after the other from gather_offset, used alternately, and `world` u32 flag words at
- * flags_offset, zero before the first use; `control` = 16 bytes of LOCAL device memory (exchange number, unused,
- * status, pad), zero before the first use.  All ranks must issue the same sequence of reductions.  The wait is
- * bounded (about a second); on expiry control[2] becomes 1 and the result is invalid.  One rank per GPU.
+ * (>= world * n * 4: world x n/2 eight-byte slots) each, one after the other from gather_offset, used alternately,
+ * ZERO before the first use (flags_offset is kept in the signature and ignored); `control` = 16 bytes of LOCAL device
+ * memory (exchange number, unused, status, pad), zero before the first use.  n <= 8192.  All ranks must issue the same
+ * sequence of exchanges.  The wait is bounded (about a second); on expiry control[2] becomes 1 and the result is
+ * invalid.  One rank per GPU.
  * No counterpart in the reference. */
 int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residual, const pk_tensor* out,
                     const uint64_t* peer_bases, int world, int rank, int64_t gather_offset, int64_t area_bytes,

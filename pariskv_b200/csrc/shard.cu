@@ -231,86 +231,104 @@ __global__ void __launch_bounds__(128) shard_merge_partial_peer_kernel(const flo
   out[(int64_t)row * 128 + d] = __float2bfloat16(den > 0.f ? acc / den : 0.f);
 }
 
-// ---- row-parallel reduce of a tensor-parallel layer over peer memory, one launch ---------------------------------
-// out = residual + sum over ranks of partial, for one short vector (the [1, hidden] output of a row-parallel
-// projection at decode time).  One block: every thread stores its 16 bytes of this rank's partial into slot `rank` of
-// EVERY peer's gather area, the block publishes the exchange number into word `rank` of every peer's flags, waits
-// (bounded) until its own flag words carry that number, then sums the `world` slots of its own area in rank order in
-// fp32, so every rank computes bit-identical results.  Consecutive reductions alternate between two gather areas
-// (exchange number parity): a rank can reach the reduction after the next one only after every peer has published
-// the next one, i.e. has finished reading this one.
-__global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restrict__ partial, const uint4* __restrict__ residual,
-                                                           uint4* __restrict__ out, int n16, PeerSet peers, int64_t gather_off,
-                                                           int64_t area_bytes, int64_t flags_off, int rank, int world,
-                                                           PeerCtl* ctl, const uint4* __restrict__ norm_w,
-                                                           uint4* __restrict__ normed, float eps, int gather_only) {
+// ---- tensor-parallel reduction / all-gather of one short row over peer memory, one launch ------------------------
+// Every 32-bit data word (two bf16) travels with the exchange number in ONE 8-byte store {data, number} into the
+// receiver's gather area, slot [source rank][word].  An aligned 8-byte store is single-copy atomic, so a receiver that
+// reads the number it expects in a slot has that slot's data with it: no separate flag words, no fence between data
+// and flag, and the exchange costs one NVLink store latency plus the polling.  Each thread owns words t, t + 512, ...:
+// it stores them into every peer's area, then polls its own words of every source (bounded), sums the `world`
+// contributions in rank order in fp32 (bit-identical results on every rank), and optionally the block takes the
+// RMS-norm of the reduced row.  Consecutive exchanges alternate between two gather areas (exchange number parity): a
+// rank can send exchange k + 2 only after it completed k + 1, for which every peer had to send k + 1, i.e. had finished
+// reading k; so a slot of area (k & 1) is never overwritten before its reader is done with it.
+__device__ __forceinline__ void st_slot(unsigned long long* p, unsigned data, unsigned tag) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_slot(const unsigned long long* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+constexpr int TP_THREADS = 512;
+constexpr int TP_WORDS_MAX = 8;   // words per thread: rows of up to 8192 bf16
+constexpr int TP_WORLD_MAX = 16;
+
+__global__ void __launch_bounds__(TP_THREADS) tp_allreduce_kernel(const unsigned* __restrict__ partial,
+                                                                  const unsigned* __restrict__ residual,
+                                                                  unsigned* __restrict__ out, int n32, PeerSet peers,
+                                                                  int64_t gather_off, int64_t area_bytes, int rank, int world,
+                                                                  PeerCtl* ctl, const unsigned* __restrict__ norm_w,
+                                                                  unsigned* __restrict__ normed, float eps, int gather_only) {
   const int tid = threadIdx.x;
   __shared__ unsigned s_epoch;
-  __shared__ float s_part[16];
-  float ss = 0.0f;
+  __shared__ float s_part[TP_THREADS / 32];
   if (tid == 0) s_epoch = ctl->epoch + 1;
   __syncthreads();
   const unsigned epoch = s_epoch;
+  if (tid == 0) ctl->epoch = epoch;
   const int64_t area = gather_off + (int64_t)(epoch & 1u) * area_bytes;
-  for (int i = tid; i < n16; i += blockDim.x) {
-    const uint4 v = partial[i];
-    for (int q = 0; q < world; q++)
-      reinterpret_cast<uint4*>(peers.base[q] + area)[(int64_t)rank * n16 + i] = v;
+  // ---- send ----
+#pragma unroll
+  for (int k = 0; k < TP_WORDS_MAX; k++) {
+    const int w = tid + k * TP_THREADS;
+    if (w < n32) {
+      const unsigned v = partial[w];
+      for (int q = 0; q < world; q++)
+        st_slot(reinterpret_cast<unsigned long long*>(peers.base[q] + area) + (int64_t)rank * n32 + w, v, epoch);
+    }
   }
-  __threadfence_system();
-  __syncthreads();
-  // thread q publishes to peer q and waits for peer q's flag: the `world` stores and the `world` waits run side by
-  // side instead of one after the other (each release store orders the block's data stores, which every thread
-  // fenced before the barrier, ahead of the flag)
-  if (tid < world) {
-    st_release_sys(reinterpret_cast<unsigned*>(peers.base[tid] + flags_off) + rank, epoch);
-    if (tid == 0) ctl->epoch = epoch;
-    const unsigned* flags = reinterpret_cast<const unsigned*>(peers.base[rank] + flags_off);
+  // ---- receive: my words of every source, in rank order ----
+  const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(peers.base[rank] + area);
+  float ss = 0.0f;
+  bool late = false;
+#pragma unroll
+  for (int k = 0; k < TP_WORDS_MAX; k++) {
+    const int w = tid + k * TP_THREADS;
+    if (w >= n32) continue;
+    float lo = 0.0f, hi = 0.0f;
+    if (!gather_only && residual) {
+      const unsigned r = residual[w];
+      lo = __uint_as_float(r << 16), hi = __uint_as_float(r & 0xffff0000u);
+    }
+    // one sweep loads this word's slot of every source back to back (all loads in flight), then looks at the numbers;
+    // sweeps repeat (bounded) until every source's store has landed
+    uint2 v[TP_WORLD_MAX];
     long long polls = 0;
-    while ((int)(ld_acquire_sys(flags + tid) - epoch) < 0) {
+    for (;;) {
+#pragma unroll
+      for (int r = 0; r < TP_WORLD_MAX; r++)
+        if (r < world) v[r] = ld_slot(mine + (int64_t)r * n32 + w);
+      bool all = true;
+#pragma unroll
+      for (int r = 0; r < TP_WORLD_MAX; r++)
+        if (r < world) all = all && v[r].y == epoch;
+      if (all) break;
       if (++polls > SHARD_WAIT_POLLS) {
-        atomicExch(&ctl->status, 1u);
+        late = true;
         break;
       }
-      __nanosleep(40);
+      __nanosleep(20);
     }
-  }
-  __syncthreads();
-  const uint4* mine = reinterpret_cast<const uint4*>(peers.base[rank] + area);
-  if (gather_only) {  // all-gather: the slots of the area in rank order are the result
-    for (int i = tid; i < n16 * world; i += blockDim.x) out[i] = __ldcg(mine + i);
-    return;
-  }
-  for (int i = tid; i < n16; i += blockDim.x) {
-    float acc[8];
-    {
-      const uint4 v = residual ? residual[i] : make_uint4(0, 0, 0, 0);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int k = 0; k < 4; k++) acc[2 * k] = __uint_as_float(w[k] << 16), acc[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
-    }
-    for (int r = 0; r < world; r++) {
-      const uint4 v = __ldcg(mine + (int64_t)r * n16 + i);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int k = 0; k < 4; k++) {
-        acc[2 * k] = __fadd_rn(acc[2 * k], __uint_as_float(w[k] << 16));
-        acc[2 * k + 1] = __fadd_rn(acc[2 * k + 1], __uint_as_float(w[k] & 0xffff0000u));
+    for (int r = 0; r < TP_WORLD_MAX; r++) {
+      if (r >= world) continue;
+      if (gather_only) {
+        out[(int64_t)r * n32 + w] = v[r].x;
+      } else {
+        lo = __fadd_rn(lo, __uint_as_float(v[r].x << 16));
+        hi = __fadd_rn(hi, __uint_as_float(v[r].x & 0xffff0000u));
       }
     }
-    uint4 o;
-    o.x = (uint32_t)f2bf(acc[0]) | ((uint32_t)f2bf(acc[1]) << 16);
-    o.y = (uint32_t)f2bf(acc[2]) | ((uint32_t)f2bf(acc[3]) << 16);
-    o.z = (uint32_t)f2bf(acc[4]) | ((uint32_t)f2bf(acc[5]) << 16);
-    o.w = (uint32_t)f2bf(acc[6]) | ((uint32_t)f2bf(acc[7]) << 16);
-    out[i] = o;
-#pragma unroll
-    for (int k = 0; k < 8; k++) {
-      const float r = bfround(acc[k]);
-      ss = fmaf(r, r, ss);
+    if (!gather_only) {
+      const unsigned o = (unsigned)f2bf(lo) | ((unsigned)f2bf(hi) << 16);
+      out[w] = o;
+      const float a = __uint_as_float(o << 16), b = __uint_as_float(o & 0xffff0000u);
+      ss = fmaf(a, a, fmaf(b, b, ss));
     }
   }
-  if (!normed) return;
+  if (late) atomicExch(&ctl->status, 1u);
+  if (gather_only || !normed) return;
   // the RMS-norm of the reduced row, for the projection that follows: x = bf16(out * rsqrt(mean(out^2) + eps) * w)
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
@@ -318,17 +336,16 @@ __global__ void __launch_bounds__(512) tp_allreduce_kernel(const uint4* __restri
   __syncthreads();
   float tot = 0.0f;
 #pragma unroll
-  for (int k = 0; k < 16; k++) tot += s_part[k];
-  const float rstd = rsqrtf(tot / (float)(n16 * 8) + eps);
-  for (int i = tid; i < n16; i += blockDim.x) {   // every thread re-reads what it wrote itself
-    const uint4 v = out[i], wv = norm_w[i];
-    const uint32_t hw[4] = {v.x, v.y, v.z, v.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
-    uint32_t ow[4];
+  for (int k = 0; k < TP_THREADS / 32; k++) tot += s_part[k];
+  const float rstd = rsqrtf(tot / (float)(n32 * 2) + eps);
 #pragma unroll
-    for (int k = 0; k < 4; k++)
-      ow[k] = (uint32_t)f2bf(__uint_as_float(hw[k] << 16) * rstd * __uint_as_float(ww[k] << 16)) |
-              ((uint32_t)f2bf(__uint_as_float(hw[k] & 0xffff0000u) * rstd * __uint_as_float(ww[k] & 0xffff0000u)) << 16);
-    normed[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  for (int k = 0; k < TP_WORDS_MAX; k++) {   // every thread re-reads what it wrote itself
+    const int w = tid + k * TP_THREADS;
+    if (w < n32) {
+      const unsigned h = out[w], g = norm_w[w];
+      normed[w] = (unsigned)f2bf(__uint_as_float(h << 16) * rstd * __uint_as_float(g << 16)) |
+                  ((unsigned)f2bf(__uint_as_float(h & 0xffff0000u) * rstd * __uint_as_float(g & 0xffff0000u)) << 16);
+    }
   }
 }
 
@@ -549,8 +566,9 @@ extern "C" int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residu
     nw = (const uint4*)norm_weight->data;
     nout = (uint4*)normed_out->data;
   }
-  PK_REQUIRE(is_contig(partial) && is_contig(out) && numel(out) == n && n >= 8 && n % 8 == 0 && n <= (1 << 20),
-             "partial / out must be contiguous bf16 with the same number of elements, a multiple of 8, at most 2^20");
+  PK_REQUIRE(is_contig(partial) && is_contig(out) && numel(out) == n && n >= 8 && n % 8 == 0 &&
+                 n <= 2 * TP_THREADS * TP_WORDS_MAX,
+             "partial / out must be contiguous bf16 with the same number of elements, a multiple of 8, at most 8192");
   PK_REQUIRE((reinterpret_cast<uintptr_t>(partial->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(out->data) & 15) == 0,
              "partial / out must be 16-byte aligned");
   const uint4* res = nullptr;
@@ -561,15 +579,17 @@ extern "C" int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residu
     res = (const uint4*)residual->data;
   }
   PK_REQUIRE(control != nullptr && gather_offset >= 0 && gather_offset % 16 == 0 && flags_offset >= 0 && flags_offset % 4 == 0 &&
-                 area_bytes >= (int64_t)world * n * 2 && area_bytes % 16 == 0,
-             "control block, offsets or area size invalid (one area holds world x n bf16; two areas follow each other)");
+                 area_bytes >= (int64_t)world * n * 4 && area_bytes % 16 == 0,
+             "control block, offsets or area size invalid (one area holds world x n/2 eight-byte slots; two areas follow "
+             "each other)");
   PeerSet ps;
   int rc;
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
   StageTimer timer(ST_REDUCE, (cudaStream_t)stream);
-  tp_allreduce_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const uint4*)partial->data, res, (uint4*)out->data, (int)(n / 8), ps,
-                                                           gather_offset, area_bytes, flags_offset, rank, world, (PeerCtl*)control,
-                                                           nw, nout, (float)eps, 0);
+  tp_allreduce_kernel<<<1, TP_THREADS, 0, (cudaStream_t)stream>>>((const unsigned*)partial->data, (const unsigned*)res,
+                                                                  (unsigned*)out->data, (int)(n / 2), ps, gather_offset, area_bytes,
+                                                                  rank, world, (PeerCtl*)control, (const unsigned*)nw,
+                                                                  (unsigned*)nout, (float)eps, 0);
   return check_launch("tp_allreduce");
 }
 
@@ -579,19 +599,21 @@ extern "C" int pk_tp_allgather(const pk_tensor* part, const pk_tensor* out, cons
   PK_CHECK_TENSOR(part, PK_BF16, 2);
   PK_CHECK_TENSOR(out, PK_BF16, 2);
   const int64_t n = numel(part);
-  PK_REQUIRE(is_contig(part) && is_contig(out) && numel(out) == n * world && n >= 8 && n % 8 == 0 && n <= (1 << 20),
-             "part must be contiguous bf16 of n elements (a multiple of 8, at most 2^20), out of world x n");
+  PK_REQUIRE(is_contig(part) && is_contig(out) && numel(out) == n * world && n >= 8 && n % 8 == 0 &&
+                 n <= 2 * TP_THREADS * TP_WORDS_MAX,
+             "part must be contiguous bf16 of n elements (a multiple of 8, at most 8192), out of world x n");
   PK_REQUIRE((reinterpret_cast<uintptr_t>(part->data) & 15) == 0 && (reinterpret_cast<uintptr_t>(out->data) & 15) == 0,
              "part / out must be 16-byte aligned");
   PK_REQUIRE(control != nullptr && gather_offset >= 0 && gather_offset % 16 == 0 && flags_offset >= 0 && flags_offset % 4 == 0 &&
-                 area_bytes >= (int64_t)world * n * 2 && area_bytes % 16 == 0,
-             "control block, offsets or area size invalid (one area holds world x n bf16; two areas follow each other)");
+                 area_bytes >= (int64_t)world * n * 4 && area_bytes % 16 == 0,
+             "control block, offsets or area size invalid (one area holds world x n/2 eight-byte slots; two areas follow "
+             "each other)");
   PeerSet ps;
   int rc;
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
   StageTimer timer(ST_REDUCE, (cudaStream_t)stream);
-  tp_allreduce_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const uint4*)part->data, nullptr, (uint4*)out->data, (int)(n / 8), ps,
-                                                           gather_offset, area_bytes, flags_offset, rank, world, (PeerCtl*)control,
-                                                           nullptr, nullptr, 0.0f, 1);
+  tp_allreduce_kernel<<<1, TP_THREADS, 0, (cudaStream_t)stream>>>((const unsigned*)part->data, nullptr, (unsigned*)out->data,
+                                                                  (int)(n / 2), ps, gather_offset, area_bytes, rank, world,
+                                                                  (PeerCtl*)control, nullptr, nullptr, 0.0f, 1);
   return check_launch("tp_allgather");
 }

@@ -214,8 +214,9 @@ class TPReducer:
     ranks of partial, for bf16 vectors of n elements.  With KV heads split over ranks (head_shard) this is the only
     exchange the model needs; the retrieval path itself has none.
 
-    mode "peer": one launch over peer memory (pk_tp_allreduce): stores into every peer's symmetric buffer, flag
-    words, fp32 sum in rank order, bit-identical on every rank; no NVLink multicast objects are created.
+    mode "peer": one launch over peer memory (pk_tp_allreduce): every data word goes into every peer's symmetric
+    buffer together with the exchange number in one 8-byte store, the receiver polls its slots (bounded), fp32 sum in
+    rank order, bit-identical on every rank; no NVLink multicast objects are created.
     mode "nccl": torch.distributed.all_reduce followed by the residual add.  A single rank needs neither."""
 
     def __init__(self, n, device, group=None, mode="peer"):
@@ -233,7 +234,7 @@ class TPReducer:
             from . import _lib
             if self.world > 16:
                 raise ValueError("at most 16 ranks")
-            self.area_bytes = (self.world * self.n * 2 + 255) // 256 * 256
+            self.area_bytes = (self.world * self.n * 4 + 255) // 256 * 256    # 8-byte slots: {two bf16, exchange number}
             self.flags_off = 2 * self.area_bytes
             self.buf = symm.empty(self.flags_off + 256, dtype=torch.uint8, device=device)
             self.buf.zero_()
