@@ -318,6 +318,7 @@ def build_cache(cfg, device, max_new, seed, offload=True, rank=0, world=1):
         cache.prefill_update_kv_cache(None, k[:, :, mine].contiguous(), v[:, :, mine].contiguous(), l, 0)
         del k, v
     torch.cuda.synchronize(device)
+    cache.queries_precede_append = True    # the harness makes q and k in one launch, before the append
     return cache
 
 

@@ -366,6 +366,11 @@ typedef struct pk_retrieve_args {
   const pk_tensor* query_avg;
   void* workspace;
   int64_t workspace_bytes;
+  int32_t queries_settled; /* nonzero: `queries` were complete before the kernel launched just before this call STARTED
+                              (another launch, e.g. pk_append_encode, sits between their producer and this call).  With
+                              pk_set_pdl(1) the collision kernel then prepares the query and ranks the clusters before it
+                              waits for that kernel.  Zero is always safe. */
+  int32_t reserved;
 } pk_retrieve_args;
 int pk_retrieve_ex(const pk_retrieve_args* args, void* stream);
 /* Largest candidate count the schedule gives for any zone length in 1..N. */

@@ -39,7 +39,8 @@ class PkRetrieveArgs(ctypes.Structure):
                 ("kv_len", TP), ("schedule", ctypes.POINTER(PkZoneSchedule)), ("local_hist", TP), ("shard_hist", TP),
                 ("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("final_indices", TP), ("n_sel", TP),
                 ("cand", TP), ("n_cand", TP), ("scores_f32", TP), ("q_blocks", TP), ("q_norm", TP),
-                ("query_avg", TP), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64)]
+                ("query_avg", TP), ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64),
+                ("queries_settled", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
 _I64, _INT, _F32, _VP = ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_void_p

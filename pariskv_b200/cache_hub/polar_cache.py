@@ -166,6 +166,8 @@ class polar_cache(KV_Cache):
         rows = (bs * H, self.group_size) if self.per_query_head_retrieval else (bs, H)
         self._retrieve_scratch = ops.Scratch(dev, ops.retrieve_scratch_bytes(rows[0], rows[1], max(self.zone_capacity, 1), self._c_max))
         self._attn_rows_max = self.window_capacity + max(self.final_topk, self._max_selected_rows())
+        self.queries_precede_append = False   # see compute(): set by callers that make q and k in one kernel
+        self._appended_layer = None
         self._attn_scratch = ops.Scratch(dev, ops.attention_scratch_bytes(bs, num_heads, self._attn_rows_max))
 
     def _max_selected_rows(self):
@@ -325,6 +327,7 @@ class polar_cache(KV_Cache):
                           self.key_4bit_packed_gpu[l], self._zone_vnorm(l), self.cluster_key_counts_gpu[l],
                           self._store_kv[l], self._layer_state[l], self.sink_size, self.dynamic_update_interval)
         self._mirror_append(l)
+        self._appended_layer = l
         if l == 0:
             self.context += 1
         return None, None
@@ -394,11 +397,16 @@ class polar_cache(KV_Cache):
             return self._attend(queries, wk, wv, n_win, sk, sv, sel)
         if self.per_query_head_retrieval:
             return self._compute_per_query_head(queries, l)
+        # A caller whose queries are made BEFORE it calls decode_update_kv_cache (one kernel makes q and k) says so with
+        # queries_precede_append: the append launch of this layer then sits between that kernel and this call, and the
+        # collision kernel may prepare the query before it waits for the append (matters with dependent launch only).
+        settled = self.queries_precede_append and self._appended_layer == l
+        self._appended_layer = None
         final, n_sel, _ = ops.retrieve_ex(queries, self.srht_diagonal_signs, self._mag_centers, self.codebook_gpu[l],
                                           self.key_block_weight_gpu[l], self.key_4bit_packed_gpu[l],
                                           self.cluster_key_counts_gpu[l], self._c_max, self.final_topk,
                                           kv_len=st[4:4 + self.batch_size], schedule=self._zone_schedule,
-                                          scratch=self._retrieve_scratch)
+                                          scratch=self._retrieve_scratch, queries_settled=settled)
         self._remember_selection(final, n_sel, l)
         # window rows and zone rows per head are read on the device
         return self._attend(queries, wk, wv, self.window_capacity, sk, sv, final, n_sel=n_sel,

@@ -420,6 +420,53 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
   const ChainQuery& cq = p.q;
+  // ---- query part of the prologue: warp 0 averages, normalises and rotates the query; then every warp scores the 256
+  // clusters of its subspace and sorts them (registers only).  It reads nothing but the queries and the signs, so where
+  // the caller vouches that those were complete before the PREVIOUS kernel on the stream started (cq.early_query: e.g.
+  // the append launch sits in between), it runs before the wait for that kernel, under its tail.
+  float qx[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qavg[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qn = 0.0f;
+  unsigned key[8];
+  auto query_part = [&]() {
+    if (warp == 0) {
+      const uint16_t* q = cq.queries + ((int64_t)b * cq.Hq + (int64_t)h * p.G) * 128 + 4 * lane;
+      float sg[4], acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      unpack4(__ldg(reinterpret_cast<const uint2*>(cq.signs + 4 * lane)), sg);
+      for (int g = 0; g < p.G; g++) {  // fp32 sum over the group, g ascending
+        float v[4];
+        unpack4(__ldg(reinterpret_cast<const uint2*>(q + g * 128)), v);
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[i] = __fadd_rn(acc[i], v[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) qx[i] = qavg[i] = bfround(__fmul_rn(acc[i], p.inv_g));
+      qn = rotate4(qx, sg, lane);
+#pragma unroll
+      for (int i = 0; i < 4; i++) s_q[4 * lane + i] = qx[i];
+    }
+    __syncthreads();
+    // register r of a lane starts with cluster c = 32 * r + lane: the first five terms of the score (bits 0..4 of c)
+    // are the lane's, the last three (bits 5..7) the register's; the sum is taken in the order j = 0..7
+    float qv[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) qv[j] = s_q[warp * 8 + j];
+    float s5 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 5; j++) s5 = __fadd_rn(s5, ((lane >> j) & 1) ? qv[j] : -qv[j]);
+#pragma unroll
+    for (int rr = 0; rr < 8; rr++) {
+      float sc = s5;
+#pragma unroll
+      for (int j = 5; j < 8; j++) sc = __fadd_rn(sc, ((rr >> (j - 5)) & 1) ? qv[j] : -qv[j]);
+      // order of (score descending, id ascending) as one unsigned compare; -0 counts as +0 like a float compare
+      unsigned bits = f2bf(sc);
+      if (bits == 0x8000u) bits = 0u;
+      const unsigned ord = (bits & 0x8000u) ? (~bits & 0xFFFFu) : (bits | 0x8000u);
+      key[rr] = (ord << 8) | (unsigned)(255 - (32 * rr + lane));
+    }
+    warp_sort_desc_256(key, lane);
+  };
+  const bool early = cq.early_query != 0;
+  if (early) query_part();
   if (cq.n_dev) pdl_wait();  // the zone length may have been written by the kernel just before this one
   const int64_t N = cq.n_dev ? min(max((int64_t)cq.n_dev[b], (int64_t)1), p.N) : p.N;
   const int64_t Nv = N + p.mis;
@@ -473,29 +520,15 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
     // cluster sizes of this warp's subspace: 8 consecutive clusters per lane
     const int4* cp = reinterpret_cast<const int4*>(cq.counts + ((int64_t)bh * 16 + sub) * 256 + lane * 8);
     const int4 c0 = __ldg(cp), c1 = __ldg(cp + 1);
-    if (warp == 0) {
-      const uint16_t* q = cq.queries + ((int64_t)b * cq.Hq + (int64_t)h * p.G) * 128 + 4 * lane;
-      float x[4], sg[4], acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      unpack4(__ldg(reinterpret_cast<const uint2*>(cq.signs + 4 * lane)), sg);
-      for (int g = 0; g < p.G; g++) {  // fp32 sum over the group, g ascending
-        float v[4];
-        unpack4(__ldg(reinterpret_cast<const uint2*>(q + g * 128)), v);
-#pragma unroll
-        for (int i = 0; i < 4; i++) acc[i] = __fadd_rn(acc[i], v[i]);
-      }
-#pragma unroll
-      for (int i = 0; i < 4; i++) x[i] = bfround(__fmul_rn(acc[i], p.inv_g));
-      if (publish && cq.query_avg)
+    if (!early) query_part();   // (its barrier also orders s_q before the reads below)
+    if (warp == 0 && publish) {
+      if (cq.query_avg)
         *reinterpret_cast<uint2*>(cq.query_avg + (int64_t)bh * 128 + 4 * lane) =
-            make_uint2((uint32_t)f2bf(x[0]) | ((uint32_t)f2bf(x[1]) << 16), (uint32_t)f2bf(x[2]) | ((uint32_t)f2bf(x[3]) << 16));
-      const float n = rotate4(x, sg, lane);
-#pragma unroll
-      for (int i = 0; i < 4; i++) s_q[4 * lane + i] = x[i];
-      if (publish) {
-        *reinterpret_cast<uint2*>(cq.q_blocks + (int64_t)bh * 128 + 4 * lane) =
-            make_uint2((uint32_t)f2bf(x[0]) | ((uint32_t)f2bf(x[1]) << 16), (uint32_t)f2bf(x[2]) | ((uint32_t)f2bf(x[3]) << 16));
-        if (lane == 0) cq.q_norm[bh] = f2bf(n);
-      }
+            make_uint2((uint32_t)f2bf(qavg[0]) | ((uint32_t)f2bf(qavg[1]) << 16),
+                       (uint32_t)f2bf(qavg[2]) | ((uint32_t)f2bf(qavg[3]) << 16));
+      *reinterpret_cast<uint2*>(cq.q_blocks + (int64_t)bh * 128 + 4 * lane) =
+          make_uint2((uint32_t)f2bf(qx[0]) | ((uint32_t)f2bf(qx[1]) << 16), (uint32_t)f2bf(qx[2]) | ((uint32_t)f2bf(qx[3]) << 16));
+      if (lane == 0) cq.q_norm[bh] = f2bf(qn);
     }
     if (tid == 32) {  // thresholds of this sample
       if (cq.n_dev || cq.n_plan > 0) {
@@ -516,27 +549,6 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
     unsigned tier[8];
 #pragma unroll
     for (int t = 0; t < 8; t++) tier[t] = t < n_tiers ? s_tiers[t] : 0u;
-    // register r of a lane starts with cluster c = 32 * r + lane: the first five terms of the score (bits 0..4 of c)
-    // are the lane's, the last three (bits 5..7) the register's; the sum is taken in the order j = 0..7
-    float qv[8];
-#pragma unroll
-    for (int j = 0; j < 8; j++) qv[j] = s_q[sub * 8 + j];
-    float s5 = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 5; j++) s5 = __fadd_rn(s5, ((lane >> j) & 1) ? qv[j] : -qv[j]);
-    unsigned key[8];
-#pragma unroll
-    for (int rr = 0; rr < 8; rr++) {
-      float sc = s5;
-#pragma unroll
-      for (int j = 5; j < 8; j++) sc = __fadd_rn(sc, ((rr >> (j - 5)) & 1) ? qv[j] : -qv[j]);
-      // order of (score descending, id ascending) as one unsigned compare; -0 counts as +0 like a float compare
-      unsigned bits = f2bf(sc);
-      if (bits == 0x8000u) bits = 0u;
-      const unsigned ord = (bits & 0x8000u) ? (~bits & 0xFFFFu) : (bits | 0x8000u);
-      key[rr] = (ord << 8) | (unsigned)(255 - (32 * rr + lane));
-    }
-    warp_sort_desc_256(key, lane);
     unsigned cnt[8], run = 0;
 #pragma unroll
     for (int rr = 0; rr < 8; rr++) {

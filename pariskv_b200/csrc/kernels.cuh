@@ -59,6 +59,7 @@ struct ChainQuery {
   pk_zone_schedule sched;     // thresholds = zone_tiers(sched, n_dev[b]) when n_dev is set
   long long n_plan;           // > 0: thresholds from this zone length instead (a shard of a longer zone)
   unsigned* zero_words;       // [bs*H] words set to zero here (arrival counters of the selection kernel), or null
+  int early_query;            // the queries were complete before the previous kernel on the stream started
   unsigned* zero_area;        // [bs*H][zero_area_words] set to zero here (the selection kernel's value histogram), or null
   int zero_area_words;
 };

@@ -177,6 +177,7 @@ int retrieve_impl(const pk_retrieve_args& a, cudaStream_t st) {
     cq.q_blocks = qb, cq.q_norm = qn, cq.query_avg = qa;
     cq.counts = (const int32_t*)counts_t->data;
     cq.zero_words = counters;
+    cq.early_query = a.queries_settled != 0;
     if (K > 0 && row > select_final_max_row() && (varlen || sharded || n_sel))
       cq.zero_area = (unsigned*)(ws + lay.vhist), cq.zero_area_words = (int)select_value_bins();
     if ((rc = launch_chain_collision(codebook, cq, counts, lay.u8_stride, hist, &mis, &chunk_keys, &n_chunks, st)))

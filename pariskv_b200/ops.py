@@ -348,11 +348,13 @@ def retrieve(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, 
 
 def retrieve_ex(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, cluster_key_counts, C, K,
                 tier_counts=None, kv_len=None, schedule=None, phase=0, local_hist=None, shard_hist=None, world=1,
-                rank=0, final_indices=None, n_sel=None, n_cand=None, want=(), outputs=None, scratch=None):
+                rank=0, final_indices=None, n_sel=None, n_cand=None, want=(), outputs=None, scratch=None,
+                queries_settled=False):
     """The retrieval chain with per-sample zone lengths read on the device (`kv_len` i32 [bs] + `schedule`, a
     _lib.zone_schedule) or in its two-phase form for a zone sharded over ranks (phase 1 -> local_hist; phase 2 with
     the all-gathered shard_hist); see pk_retrieve_ex.  `outputs` may hold preallocated tensors for the names in
-    `want` (reused between the two phases).  Returns (final_indices, n_sel, extras dict)."""
+    `want` (reused between the two phases).  queries_settled: the queries were complete before the launch just before
+    this call started (see pk_retrieve_args).  Returns (final_indices, n_sel, extras dict)."""
     _require_cuda(queries, codebook, key_block_weight, key_4bit, cluster_key_counts)
     bs, H, B, N = codebook.shape
     dev = codebook.device
@@ -400,6 +402,7 @@ def retrieve_ex(queries, signs, mag_centers, codebook, key_block_weight, key_4bi
         a.schedule = ctypes.pointer(schedule)
     a.phase, a.C, a.K, a.world, a.rank = int(phase), int(C), int(K), int(world), int(rank)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.queries_settled = 1 if queries_settled else 0
     _call("pk_retrieve_ex", ctypes.byref(a), L.stream_ptr(dev))
     extras["n_cand"] = n_cand
     extras["local_hist"] = local_hist

@@ -178,3 +178,39 @@ def test_final_selection_with_ties_and_flat_scores(ops):
     assert torch.equal(ex["cand"][0, 0].cpu(), torch.arange(C))
     assert torch.equal(fin[0, 0].cpu(), torch.arange(K))
     assert float(ex["scores_f32"].max() - ex["scores_f32"].min()) == 0.0
+
+
+def test_early_query_preparation_gives_the_same_chain(ops, schedule):
+    """queries_settled only moves the query preparation and the cluster sort ahead of the kernel's dependency wait:
+    candidates, scores and final indices are bit-identical, with dependent launch on or off."""
+    from pariskv_b200 import _lib
+    g = torch.Generator().manual_seed(404)
+    lens = (33000, 12000)
+    bs, H, Nmax = len(lens), 2, max(lens)
+    keys = synth_keys(g, bs, H, Nmax)
+    q = synth_queries(g, keys, 4).to(DEV)
+    signs = srht_signs().to(DEV)
+    cen = torch.tensor([0.0420, 0.1266, 0.2130, 0.3025, 0.3973, 0.5001, 0.6169, 0.7633], dtype=torch.bfloat16, device=DEV)
+    counts = torch.zeros(bs, H, 16, 256, dtype=torch.int32, device=DEV)
+    cb, w, pk = ops.alloc_key_metadata(bs, H, Nmax, DEV)
+    for b, n in enumerate(lens):
+        ops.encode_keys(keys[b:b + 1, :, :n].to(DEV), signs, cb[b:b + 1, :, :, :n], w[b:b + 1, :, :, :n],
+                        pk[b:b + 1, :, :, :n, :], cluster_counts=counts[b:b + 1])
+    kv_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    import ctypes
+    Cmax = int(_lib.load().pk_zone_max_candidates(ctypes.byref(schedule), Nmax))
+    outs = []
+    try:
+        for pdl in (False, True):
+            _lib.set_pdl(pdl)
+            for settled in (False, True):
+                fin, n_sel, ex = ops.retrieve_ex(q, signs, cen, cb, w, pk, counts, Cmax, 512, kv_len=kv_len,
+                                                 schedule=schedule, want=("cand", "scores_f32", "q_blocks", "q_norm"),
+                                                 queries_settled=settled)
+                outs.append((fin.clone(), n_sel.clone(), ex["cand"].clone(), ex["scores_f32"].clone(),
+                             ex["q_blocks"].clone(), ex["q_norm"].clone()))
+    finally:
+        _lib.set_pdl(False)
+    for o in outs[1:]:
+        for a, b in zip(outs[0], o):
+            assert torch.equal(a, b)
