@@ -426,7 +426,7 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
   // the append launch sits in between), it runs before the wait for that kernel, under its tail.
   float qx[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qavg[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qn = 0.0f;
   unsigned key[8];
-  auto query_part = [&]() {
+  auto prepare_query = [&]() {
     if (warp == 0) {
       const uint16_t* q = cq.queries + ((int64_t)b * cq.Hq + (int64_t)h * p.G) * 128 + 4 * lane;
       float sg[4], acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -443,7 +443,8 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
 #pragma unroll
       for (int i = 0; i < 4; i++) s_q[4 * lane + i] = qx[i];
     }
-    __syncthreads();
+  };
+  auto rank_clusters = [&]() {   // after a barrier behind prepare_query()
     // register r of a lane starts with cluster c = 32 * r + lane: the first five terms of the score (bits 0..4 of c)
     // are the lane's, the last three (bits 5..7) the register's; the sum is taken in the order j = 0..7
     float qv[8];
@@ -466,7 +467,11 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
     warp_sort_desc_256(key, lane);
   };
   const bool early = cq.early_query != 0;
-  if (early) query_part();
+  if (early) {
+    prepare_query();
+    __syncthreads();
+    rank_clusters();
+  }
   if (cq.n_dev) pdl_wait();  // the zone length may have been written by the kernel just before this one
   const int64_t N = cq.n_dev ? min(max((int64_t)cq.n_dev[b], (int64_t)1), p.N) : p.N;
   const int64_t Nv = N + p.mis;
@@ -520,7 +525,7 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
     // cluster sizes of this warp's subspace: 8 consecutive clusters per lane
     const int4* cp = reinterpret_cast<const int4*>(cq.counts + ((int64_t)bh * 16 + sub) * 256 + lane * 8);
     const int4 c0 = __ldg(cp), c1 = __ldg(cp + 1);
-    if (!early) query_part();   // (its barrier also orders s_q before the reads below)
+    if (!early) prepare_query();
     if (warp == 0 && publish) {
       if (cq.query_avg)
         *reinterpret_cast<uint2*>(cq.query_avg + (int64_t)bh * 128 + 4 * lane) =
@@ -545,6 +550,7 @@ __global__ void __launch_bounds__(CC_THREADS, 1) chain_collision_kernel(CollPara
     *reinterpret_cast<int4*>(my + lane * 8) = c0;
     *reinterpret_cast<int4*>(my + lane * 8 + 4) = c1;
     __syncthreads();
+    if (!early) rank_clusters();
     const int n_tiers = (int)s_tiers[8];
     unsigned tier[8];
 #pragma unroll
