@@ -1046,6 +1046,7 @@ def seqshard_mode(args, device, rank, world, local_rank):
     last = (runner.tok if use_graph else token).clone()
     if cache.px is not None:
         cache.px.check()
+        cache.hist_gather.check()
     if reducer is not None:
         reducer.check()
     # per-stage event timing on a few eager steps (not part of the headline number): every launch of this library,

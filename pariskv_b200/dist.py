@@ -151,7 +151,7 @@ def merge_gathered_partials(gathered: torch.Tensor) -> torch.Tensor:
 def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global, store_k,
                             store_v, n_total, start, end, collision_ratio, candidate_ratio, final_topk,
                             window_k=None, window_v=None, n_window=0, group=None, n_window_dev=None, n_window_add=0,
-                            exchange=None, scratch=None, attn_scratch=None):
+                            exchange=None, scratch=None, attn_scratch=None, hist_gather=None):
     """One layer, one decode step of the sequence-sharded form on this rank's shard [start, end) of a zone of
     n_total keys.  codebook / key_block_weight / key_4bit / store_* hold the shard only (local index = global -
     start); counts_global is the all-reduced cluster histogram.  The window rows are attended by the rank that
@@ -162,6 +162,8 @@ def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_wei
     share of the ties in rank (= key) order, so the union of the shards' candidates is the single-GPU candidate set;
     the global top-K of the shards' local top-K lists is then the single-GPU final selection.  Three small exchanges
     per layer: histograms (1 KB per head), local top lists (16 B x K per head), partial attention results.
+    exchange (a PeerExchange) turns the two larger exchanges into stores into peer memory, hist_gather (a TPReducer in
+    peer mode with room for bs*H*512 elements) the histogram all-gather too; without them they are NCCL collectives.
     Returns (attention output identical on every rank, global top-K indices)."""
     from . import ops
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -181,8 +183,11 @@ def sequence_sharded_attend(queries, signs, mag_centers, codebook, key_block_wei
     args = (queries, signs, mag_centers, codebook, key_block_weight, key_4bit, counts_global, c_total, k_final)
     # phase 1: collision counts of the shard, and how many of its keys have each count
     _, _, ex = ops.retrieve_ex(*args, tier_counts=tiers, phase=1, outputs=bufs, scratch=scratch)
-    hist_all = torch.empty(world * bs, H, 256, dtype=torch.int32, device=dev)
-    dist.all_gather_into_tensor(hist_all, ex["local_hist"], group=group)
+    if hist_gather is not None:   # over peer memory: the gather kernel moves 32-bit words, whatever they hold
+        hist_all = hist_gather.all_gather(ex["local_hist"].view(torch.bfloat16).view(1, -1)).view(torch.int32)
+    else:
+        hist_all = torch.empty(world * bs, H, 256, dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(hist_all, ex["local_hist"], group=group)
     # phase 2: candidates by the global threshold, rerank, local top-K
     fin_local, n_sel, ex = ops.retrieve_ex(*args, tier_counts=tiers, phase=2, shard_hist=hist_all.view(world, bs, H, 256),
                                            world=world, rank=rank, outputs=bufs, scratch=scratch)
@@ -265,11 +270,11 @@ class TPReducer:
         return ops.add_rmsnorm(partial, residual, weight, eps)
 
     def all_gather(self, part):
-        """part: bf16 [1, m] (m * world <= n) -> bf16 [1, world * m], the ranks' parts in rank order."""
+        """part: bf16 [1, m] (m <= n) -> bf16 [1, world * m], the ranks' parts in rank order."""
         if self.mode == "none":
             return part
-        if part.numel() * self.world > self.n:
-            raise ValueError("the gathered row must fit the reducer's row length")
+        if part.numel() > self.n:
+            raise ValueError("a rank's part must fit the reducer's row length")
         if self.mode == "nccl":
             out = torch.empty(1, self.world * part.numel(), dtype=part.dtype, device=part.device)
             dist.all_gather_into_tensor(out.view(self.world, -1), part.contiguous(), group=self.group)
@@ -377,10 +382,12 @@ class SequenceShardedCache:
         self.store = store
         if exchange not in ("nccl", "peer"):
             raise ValueError("exchange must be 'nccl' or 'peer'")
-        self.px = None
+        self.px, self.hist_gather = None, None
         if exchange == "peer" and world > 1:   # the two larger per-layer exchanges as stores into peer memory
             _, _, k_final = global_plan(n_total, collision_ratio, candidate_ratio, final_topk)
             self.px = PeerExchange(1, num_kv_heads, num_heads, k_final, device, group)
+            # the count histograms ([H,256] i32 per rank) travel through the short-row gather kernel as raw words
+            self.hist_gather = TPReducer(num_kv_heads * 512, device, group, mode="peer")
         self.device_positions = False     # window length read from a device word (captured steps)
         self._dev_state = torch.zeros(1, dtype=torch.int32, device=device)
         # scratch of the chain and of the attention kernel, sized once for everything this shard can grow to: the
@@ -485,7 +492,7 @@ class SequenceShardedCache:
             n_window=(self.window_capacity if self.device_positions else self._window_len[layer_idx]) if first else 0,
             group=self.group, n_window_dev=self._dev_state[0:1] if (first and self.device_positions) else None,
             n_window_add=1 if (first and self.device_positions) else 0, exchange=self.px,
-            scratch=self._retrieve_scratch, attn_scratch=self._attn_scratch)
+            scratch=self._retrieve_scratch, attn_scratch=self._attn_scratch, hist_gather=self.hist_gather)
         self.last_topk_indices = final
         return out
 
