@@ -304,7 +304,9 @@ __global__ void __launch_bounds__(TP_THREADS) tp_allreduce_kernel(const unsigned
       for (int r = 0; r < TP_WORLD_MAX; r++)
         if (r < world) all = all && v[r].y == epoch;
       if (all) break;
-      if (++polls > SHARD_WAIT_POLLS) {
+      // one full budget per thread and launch: after a first expiry the remaining words get a token budget, so a
+      // launch whose peer never arrives still ends after about a second
+      if (++polls > (late ? 1000 : SHARD_WAIT_POLLS)) {
         late = true;
         break;
       }

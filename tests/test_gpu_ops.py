@@ -487,6 +487,48 @@ def test_peer_exchange_wait_runs_out_and_reports():
     assert int(indices.abs().sum()) == 0 and float(scores.abs().sum()) == 0.0   # the zeroed gather area, unpacked
 
 
+def test_tp_reduce_wait_runs_out_and_reports():
+    """The one-launch reduction over peer memory with a peer that never sends: two local buffers stand for the two
+    ranks' gather areas, this "rank 0" stores into both and then waits for rank 1's slots, which nobody fills.  The
+    wait is bounded: the launch ends after about a second with the status word raised, the context stays usable, and
+    the same exchange with rank 1's slots filled in by hand returns the right sum at once."""
+    import time
+    from pariskv_b200 import _lib as L
+    world, n = 2, 512
+    area = world * n * 4
+    mine = torch.zeros(2 * area, dtype=torch.uint8, device=DEV)       # rank 0's two gather areas
+    other = torch.zeros(2 * area, dtype=torch.uint8, device=DEV)      # rank 1's (only written to)
+    ctl = torch.zeros(4, dtype=torch.int32, device=DEV)
+    part = torch.randn(1, n).to(torch.bfloat16).to(DEV)
+    res = torch.randn(1, n).to(torch.bfloat16).to(DEV)
+    out = torch.empty_like(part)
+    bases = L.u64_array([mine.data_ptr(), other.data_ptr()])
+    d = [L.desc(part), L.desc(res), L.desc(out)]
+
+    def call():
+        rc = L.load().pk_tp_allreduce(L.ref(d[0]), L.ref(d[1]), L.ref(d[2]), bases, world, 0, 0, area, 0, ctl.data_ptr(),
+                                      None, None, 1e-6, L.stream_ptr(torch.device(DEV)))
+        assert rc == 0
+        torch.cuda.synchronize()
+
+    t0 = time.time()
+    call()                                                            # exchange 1 -> area 1
+    waited = time.time() - t0
+    assert int(ctl[2]) == 1, "the expired wait was not reported"
+    assert 0.05 < waited < 20.0, waited
+    # exchange 2 -> area 0: fill rank 1's slots {two bf16, exchange number} by hand, then the launch returns at once
+    ctl[2] = 0
+    theirs = torch.randn(1, n).to(torch.bfloat16).to(DEV)
+    slots = mine.view(torch.int32).view(2, world, n // 2, 2)          # [area][source rank][word]{data, number}
+    slots[0, 1, :, 0] = theirs.view(torch.int32).view(-1)
+    slots[0, 1, :, 1] = 2
+    t0 = time.time()
+    call()
+    assert time.time() - t0 < 0.5 and int(ctl[2]) == 0
+    want = (res.float() + part.float() + theirs.float()).to(torch.bfloat16)
+    assert torch.equal(out, want)
+
+
 def test_mirror_rerank_v4b_is_optional_and_correct(ops, oracle):
     """Documented difference from the reference wrapper (cache_hub/rerank/rerank.py:214-263): the debug tensor v4b
     is produced only on request.  Without want_v4b the second return value is None; with it the tensor holds the
