@@ -104,8 +104,7 @@ class DecoderHarness:
         self.qkn = [torch.cat([ones(D).expand(nq, D), ones(D).expand(nk, D)]).contiguous() for _ in range(L)]
         self.lnf = ones(Hd)
         self._inv_freq = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, D, 2, device=device, dtype=torch.float32) / D))
-        if world > 1:
-            self._gathered = torch.empty(world, 2, dtype=torch.int64, device=device)
+        self._gathered = {}     # batch size -> [world, B, 2] buffer of the vocabulary-parallel arg-max
 
     def _sum_norm(self, partial, residual, weight):
         """(h, x): h = residual + the sum of `partial` over ranks, x = RMS-norm(h) * weight: one launch (with the
@@ -154,11 +153,14 @@ class DecoderHarness:
         if self.world == 1 or getattr(self.reducer, "mode", None) == "none":
             return logits.argmax(-1)
         # vocabulary-parallel arg-max: every rank's (maximum, global index), the first maximum wins as in argmax
-        m, i = logits.float().max(-1)
-        mine = torch.stack([m.view(torch.int32).to(torch.int64), i + self.rank * self.V], -1)   # [1, 2]
-        dist.all_gather_into_tensor(self._gathered, mine)
-        best = self._gathered[:, 0].to(torch.int32).view(torch.float32).argmax()
-        return self._gathered[:, 1].gather(0, best.view(1))
+        m, i = logits.float().max(-1)                                                           # [B]
+        mine = torch.stack([m.view(torch.int32).to(torch.int64), i + self.rank * self.V], -1)   # [B, 2]
+        if B not in self._gathered:
+            self._gathered[B] = torch.empty(self.world, B, 2, dtype=torch.int64, device=self.device)
+        got = self._gathered[B]
+        dist.all_gather_into_tensor(got, mine)
+        best = got[:, :, 0].to(torch.int32).view(torch.float32).argmax(0)      # the lowest rank wins a tie
+        return got[:, :, 1].gather(0, best.view(1, B)).view(B)
 
 
 class GraphedDecoder:
@@ -782,10 +784,12 @@ CFG_VARLEN = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, 
                   min_k=1024, max_k=4096, threshold=0.85)
 
 
-def varlen_mode(args, device):
+def varlen_mode(args, device, rank=0, world=1):
     """Llama-3-8B-shaped decoder, batch 16, context lengths uniform in [16384, 32768] (seeded), K/V resident in HBM,
     adaptive-k selection with 1024 - 4096 rows per head.  The per-sequence zone lengths live in device words that the
-    kernels read, so the whole batched step is one captured graph."""
+    kernels read, so the whole batched step is one captured graph.  With several ranks the KV heads (and the dense
+    layers) are split over them like in the decode benchmark; the reductions of the [batch, hidden] rows are NCCL
+    all-reduces."""
     from pariskv_b200 import _lib
     from pariskv_b200.cache_hub.polar_cache_adaptivek_varlen import polar_cache as varlen_cache
     from pariskv_b200.cache_hub.polar_cache import polar_cache as plain_cache
@@ -796,11 +800,16 @@ def varlen_mode(args, device):
     if args.batch:
         cfg["batch"], debug = args.batch, True
     K, W = args.steps, max(args.warmup, 3)
-    B, H, Hq, Lyr = cfg["batch"], cfg["kv_heads"], cfg["q_heads"], cfg["layers"]
+    B, Lyr = cfg["batch"], cfg["layers"]
+    if cfg["kv_heads"] % world or cfg["q_heads"] % world:
+        raise SystemExit(f"{cfg['kv_heads']} KV heads do not split over {world} ranks")
+    H, Hq = cfg["kv_heads"] // world, cfg["q_heads"] // world       # heads of this rank
+    from pariskv_b200.dist import head_shard
+    mine = head_shard(cfg["kv_heads"], rank, world)
     gl = torch.Generator().manual_seed(2024)
     lens = torch.randint(cfg["min_len"], cfg["max_len"] + 1, (B,), generator=gl).tolist()
     Pmax = max(lens)
-    max_new = W + K + 2 * cfg["interval"] + 8
+    max_new = W + K + 2 * cfg["interval"] + 16
     adaptive = args.selection == "adaptive"
     common = dict(valid_start=[Pmax - n for n in lens], layer_num=Lyr, batch_size=B, max_length=Pmax + max_new,
                   num_key_value_heads=H, num_heads=Hq, head_dim=128, dtype=torch.bfloat16,
@@ -813,10 +822,17 @@ def varlen_mode(args, device):
                              adaptive_topk_min_k=cfg["min_k"], adaptive_topk_max_k=cfg["max_k"], **common)
     else:
         cache = plain_cache(final_topk=2048, **common)
-    model = DecoderHarness(cfg, device, seed=4321)
+    reducer = None
+    if world > 1:
+        from pariskv_b200.dist import TPReducer
+        reducer = TPReducer(cfg["hidden"], device, mode="nccl")     # rows of a whole batch: the collective
+        model = DecoderHarness(cfg, device, seed=4321, rank=rank, world=world, reducer=reducer)
+    else:
+        model = DecoderHarness(cfg, device, seed=4321)
     g = torch.Generator(device=device).manual_seed(17)
     for l in range(Lyr):      # left-padded lockstep prefill: sample b occupies columns [Pmax - len_b, Pmax)
-        k, v = synth_kv(g, Pmax, H, device)
+        k, v = synth_kv(g, Pmax, cfg["kv_heads"], device)            # all heads with the same generator, then sliced
+        k, v = k[:, :, mine].contiguous(), v[:, :, mine].contiguous()
         k, v = k.expand(B, -1, -1, -1), v.expand(B, -1, -1, -1)      # the same synthetic stream, cut at different lengths
         cache.prefill_update_kv_cache(None, k, v, l, 0)
         del k, v
@@ -854,23 +870,70 @@ def varlen_mode(args, device):
             token = model.step(cache, token, pos)
             pos.add_(1)
 
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
     for _ in range(W):
         advance()
-    torch.cuda.synchronize(device)
-    sampler = ClockSampler(0)
+    barrier()
+    sampler = ClockSampler(device.index or 0)
     sampler.start()
     n0 = _lib.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
     e0.record()
     for _ in range(K):
         advance()
     e1.record()
-    torch.cuda.synchronize(device)
+    barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop()
     cache.check_status()
     launches = (_lib.launch_count() - n0) if graph is None else K * per_replay
-    line = {"metric": "decode_tokens_per_s", "value": B * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": K,
+    # per-stage event timing on a few eager steps (not part of the headline number)
+    S = 4 if args.stage_steps is None else args.stage_steps
+    stages_us = {}
+    if S > 0:
+        tok_e = (tok_s if graph is not None else token).clone()
+        _lib.timing_enable(True)
+        for _ in range(S):
+            tok_e = model.step(cache, tok_e, pos)
+            pos.add_(1)
+        torch.cuda.synchronize(device)
+        stages_us = {k: round(v[0] * 1e3 / (S * Lyr), 2) for k, v in _lib.timing_read().items()}
+        _lib.timing_enable(False)
+    agree = True
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        last = (tok_s if graph is not None else token).clone()
+        toks = torch.empty(world, B, dtype=torch.int64, device=device)
+        dist.all_gather_into_tensor(toks, last)
+        agree = bool((toks == toks[0:1]).all().item())
+
+    def teardown():
+        if world == 1:
+            return
+        import gc
+        nonlocal graph
+        graph = None            # a graph that holds captured collectives must be gone before the communicator
+        gc.collect()
+        barrier()
+        sys.stdout.flush()
+        guard = threading.Timer(30.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
+        dist.destroy_process_group()
+        guard.cancel()
+        os._exit(0)
+
+    if rank != 0:
+        teardown()
+        return
+    line = {"metric": "decode_tokens_per_s", "value": B * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"batched decode, Llama-3-8B architecture, batch {B}, per-sequence context lengths uniform in "
@@ -878,13 +941,21 @@ def varlen_mode(args, device):
                                    + (f"adaptive-k selection {cfg['min_k']}-{cfg['max_k']} rows per head, threshold {cfg['threshold']}"
                                       if adaptive else "top-k 2048 per KV head"),
                        "layers": Lyr, "batch": B, "lengths_min_max": [min(lens), max(lens)],
+                       "sharding": "single GPU" if world == 1 else
+                                   f"KV heads H/N per GPU (TP): {H} KV / {Hq} query heads per rank, NCCL all-reduces of "
+                                   f"[batch, hidden]",
+                       "parallelism": "single" if world == 1 else f"tp{world}",
                        "l2": "inputs larger than L2: weights plus the codes of 16 sequences are streamed every step"},
             "clocks": clocks, "gpu_launches": int(launches), "cuda_graph": {"used": graph is not None, "captures": 1 if graph else 0},
             "setup_s": round(setup_s, 1), "zone_keys_min_max": [min(cache.zone_len[0]), max(cache.zone_len[0])],
-            "selection": args.selection}
+            "selection": args.selection, "ranks_agree": agree,
+            "stage_us_per_layer": stages_us,
+            "stage_timing": "CUDA events around eager launches of this library (rank 0), microseconds per layer summed "
+                            "over a stage's launches; every launch carries ~4.5 us of event overhead"}
     if debug:
         line["invalid"] = "debug run with reduced layers / batch"
     print(json.dumps(line), flush=True)
+    teardown()
 
 
 def kernels_mode(args, cfg, device):
@@ -1216,7 +1287,7 @@ def main():
         seqshard_mode(args, device, rank, world, local_rank)
         return
     if args.mode == "varlen":
-        varlen_mode(args, device)
+        varlen_mode(args, device, rank, world)
         return
     if args.mode == "kernels":
         kernels_mode(args, cfg, device)

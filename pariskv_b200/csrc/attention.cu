@@ -2,13 +2,13 @@
 //
 // Per (batch, KV head) the attended rows are the first n_window rows of the GPU window
 // ([sink | local | update buffer]) followed by the K selected rows of the big K/V store, which may
-// live in pinned host memory.  The rows are cut into tiles of 64; one block per (tile, KV head, batch)
-// stages its tile with TMA bulk copies (cp.async.bulk, one 256-byte copy per K row and per V row,
-// completion counted on an mbarrier), so a whole grid keeps megabytes outstanding on the host link.
-// 16 groups of 8 lanes then run an online softmax over the staged rows for the query heads that share
-// the KV head (four at a time), and write partial (m, l, o) records.  The block that finishes last for a
-// (batch, KV head) merges the tiles and writes the output: one launch, no second kernel, no waiting on
-// other blocks.  Scores are kept in the log2 domain.
+// live in pinned host memory.  The rows are cut into tiles of 64; a block takes one tile, or several consecutive
+// ones that it streams through two staging buffers, and stages a tile with TMA bulk copies (cp.async.bulk, one
+// 512-byte copy per selected key where its K and V rows are adjacent, completion counted on an mbarrier), so a whole
+// grid keeps megabytes outstanding on the host link.  16 groups of 8 lanes then run an online softmax over the staged
+// rows for the query heads that share the KV head (four at a time), and the block writes one partial (m, l, o) record.
+// The block that finishes last for a (batch, KV head) merges the partials and writes the output: one launch, no
+// second kernel, no waiting on other blocks.  Scores are kept in the log2 domain.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -38,11 +38,11 @@ struct AttParams {
   const int32_t* n_sel;   // [bs*H] or null
   int64_t K, index_offset;
   int H, Hq, G, n_qgroups;
-  int64_t n_tiles;
+  int tiles_per_block;    // consecutive tiles of a (batch, KV head) that one block streams; the grid has ceil(tiles / it) groups
   float scale_log2;
   unsigned* counters;     // [bs*H] arrival counters, zero between calls
   int* status;            // set to 1 if a copy barrier was never completed
-  float* ws;              // [bs*Hq][n_tiles][ATT_REC]
+  float* ws;              // [bs*Hq][groups][ATT_REC]
   uint16_t* out;          // [bs][Hq][128]
   float* lse;             // optional [bs][Hq]: log2 of the softmax denominator (scaled scores, log2 domain)
 };
@@ -69,36 +69,58 @@ __device__ __forceinline__ bool mbar_wait(unsigned mb, unsigned parity, int limi
   return done != 0;
 }
 
-__global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams p) {
+__device__ __forceinline__ void mbar_arrive(unsigned mb) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mb) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(unsigned mb, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mb), "r"(bytes) : "memory");
+}
+
+// One block takes `tiles_per_block` consecutive tiles of a (batch, KV head) and streams them through two staging
+// buffers: while the online softmax runs over tile j, the copies of tile j + 1 are in flight.  With few tiles in the
+// whole launch (one sequence) every block has one tile and all copies of the launch are outstanding at once, which is
+// what the host link wants; with many (a batch of sequences, rows in HBM) a block amortises its fixed costs - index
+// loads, the partial record, the fence and the arrival - over its tiles and the grid is a single wave.
+__global__ void __launch_bounds__(ATT_THREADS, 3) sparse_attention_kernel(AttParams p) {
   extern __shared__ __align__(128) unsigned char dyn[];
-  uint16_t* KVs = reinterpret_cast<uint16_t*>(dyn);                          // [64][2][128]: K row, V row of a key
-  float* obuf = reinterpret_cast<float*>(dyn + 2 * ATT_TILE * 256);          // [16][4][128]
-  __shared__ __align__(8) unsigned long long mbar;
+  uint16_t* KVs = reinterpret_cast<uint16_t*>(dyn);                          // [2 buffers][64][2][128]: K row, V row of a key
+  float* obuf = reinterpret_cast<float*>(dyn + 2 * ATT_TILE * 256);          // [16][4][128], over the SECOND buffer:
+                                                                             // used when that buffer is idle
+  __shared__ __align__(8) unsigned long long mbar[2];
   __shared__ float s_m[16][ATT_GQ], s_l[16][ATT_GQ];
-  __shared__ unsigned char s_valid[ATT_TILE];
+  __shared__ unsigned char s_valid[2][ATT_TILE];
   __shared__ int s_last;
   const int tid = threadIdx.x;
-  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.y, b = blockIdx.z;
   const int64_t bh = (int64_t)b * p.H + h;
-  const unsigned mb = (unsigned)__cvta_generic_to_shared(&mbar);
+  const int n_groups = (int)gridDim.x, tpb = p.tiles_per_block;
+  const int t_first = (int)blockIdx.x * tpb;
+  const unsigned mb0 = (unsigned)__cvta_generic_to_shared(&mbar[0]);
   pdl_wait();  // the selected indices and the per-head row counts come from the kernels before this one
   const int64_t n_sel = p.n_sel ? min((int64_t)p.n_sel[bh], p.K) : p.K;
   const int64_t n_window =
       p.n_window_dev ? min(p.n_window, max((int64_t)0, (int64_t)p.n_window_dev[0] + p.n_window_add)) : p.n_window;
   const int64_t n_rows = n_window + n_sel;
-  const int64_t r0 = (int64_t)tile * ATT_TILE;
-  const int n_tile = (int)max((int64_t)0, min((int64_t)ATT_TILE, n_rows - r0));
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mb0), "r"(ATT_THREADS) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mb0 + 8), "r"(ATT_THREADS) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
 
-  // ---- stage the tile: thread t copies row t/2, K for even t and V for odd t; where the store keeps the V row of
-  // a key right behind its K row, the even thread fetches both with one 512-byte copy (half as many requests on the
-  // host link) ----
-  {
+  // ---- stage a tile: thread t copies row t/2, K for even t and V for odd t; where the store keeps the V row of a
+  // key right behind its K row, the even thread fetches both with one 512-byte copy (half as many requests on the
+  // host link).  Every thread arrives on the tile's barrier exactly once, the copying ones with their byte count ----
+  auto tile_rows = [&](int t) -> int {
+    return (int)max((int64_t)0, min((int64_t)ATT_TILE, n_rows - (int64_t)t * ATT_TILE));
+  };
+  auto issue = [&](int t, int buf) {
     const int i = tid >> 1;
     const bool is_v = tid & 1;
     const uint16_t* src = nullptr;
-    bool ok = i < n_tile, paired = false;
+    bool ok = i < tile_rows(t), paired = false;
     if (ok) {
-      const int64_t r = r0 + i;
+      const int64_t r = (int64_t)t * ATT_TILE + i;
       if (r < n_window) {
         src = (is_v ? p.wv : p.wk) + b * p.w_b + h * p.w_h + r * p.w_l;
       } else {
@@ -108,19 +130,12 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
         src = ((is_v && !paired) ? p.sv : p.sk) + b * p.s_b + h * p.s_h + (ok ? row : 0) * p.s_l;
       }
     }
-    if (tid == 0) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mb) : "memory");
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (!is_v && i < ATT_TILE) s_valid[i] = ok;
-    const int n_single = __syncthreads_count(ok && !paired);
-    const int n_double = __syncthreads_count(ok && paired && !is_v);
-    if (tid == 0)
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mb), "r"(n_single * 256 + n_double * 512)
-                   : "memory");
-    __syncthreads();
+    if (!is_v) s_valid[buf][i] = ok;
+    const unsigned mb = mb0 + 8 * buf;
     if (ok && !(paired && is_v)) {
-      const unsigned dst = (unsigned)__cvta_generic_to_shared(KVs + i * 256 + ((is_v && !paired) ? 128 : 0));
+      const unsigned dst =
+          (unsigned)__cvta_generic_to_shared(KVs + buf * (ATT_TILE * 256) + i * 256 + ((is_v && !paired) ? 128 : 0));
+      mbar_arrive_expect(mb, paired ? 512u : 256u);
       if (paired)
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];" ::"r"(dst),
                      "l"(src), "r"(mb)
@@ -129,20 +144,16 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 256, [%2];" ::"r"(dst),
                      "l"(src), "r"(mb)
                      : "memory");
+    } else {
+      mbar_arrive(mb);
     }
-  }
-  const int s = tid & 7, grp = tid >> 3;
-  // The copies never completed: report it, give them one more bounded chance to land, and go on with an EMPTY
-  // tile (partials m = -inf, l = 0), so that this block still arrives on the counter of its (batch, KV head), the
-  // merge runs and the counter returns to zero.  The host must treat a raised status word as fatal.
-  const bool landed = __syncthreads_and(mbar_wait(mb, 0, ATT_WAIT_LIMIT));
-  if (!landed) {
-    if (tid == 0) atomicExch(p.status, 1);
-    mbar_wait(mb, 0, ATT_WAIT_LIMIT);
-  }
-  const int n_live = landed ? n_tile : 0;
+  };
+  issue(t_first, 0);
 
-  for (int qg = 0; qg < p.n_qgroups; qg++) {
+  const int s = tid & 7, grp = tid >> 3;
+  bool dead = false;  // a copy barrier never completed: reported, the remaining tiles count as empty
+  for (int qg = 0; qg < p.n_qgroups; qg++) {  // more than one pass only for more than four query heads per KV head,
+                                              // and then a block has a single tile, which stays staged
     const int n_heads = min(ATT_GQ, p.G - qg * ATT_GQ);
     float qf[ATT_GQ][16];
 #pragma unroll
@@ -165,45 +176,64 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
 #pragma unroll
       for (int i = 0; i < 16; i++) o[g][i] = 0.0f;
     }
-    for (int i = grp; i < ATT_TILE; i += 16) {  // uniform trip count per warp: shuffles need all lanes
-      const bool live = i < n_live && s_valid[i];
-      float kf[16], vf[16];
-      if (live) {
-        const uint4* kp = reinterpret_cast<const uint4*>(KVs + i * 256 + 16 * s);
-        const uint4* vp = reinterpret_cast<const uint4*>(KVs + i * 256 + 128 + 16 * s);
-        unpack8f(kp[0], kf);
-        unpack8f(kp[1], kf + 8);
-        unpack8f(vp[0], vf);
-        unpack8f(vp[1], vf + 8);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; j++) kf[j] = 0.0f, vf[j] = 0.0f;
-      }
-#pragma unroll
-      for (int g = 0; g < ATT_GQ; g++) {
-        float d = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 16; j++) d = fmaf(kf[j], qf[g][j], d);
-        d += __shfl_xor_sync(0xffffffffu, d, 1);
-        d += __shfl_xor_sync(0xffffffffu, d, 2);
-        d += __shfl_xor_sync(0xffffffffu, d, 4);
-        if (live) {
-          const float sc = d * p.scale_log2;
-          const float mn = fmaxf(m[g], sc);
-          const float corr = exp2f(m[g] - mn);  // m = -inf on the first row gives 0
-          const float pr = exp2f(sc - mn);
-          lsum[g] = lsum[g] * corr + pr;
-#pragma unroll
-          for (int j = 0; j < 16; j++) o[g][j] = o[g][j] * corr + pr * vf[j];
-          m[g] = mn;
+    for (int j = 0; j < tpb; j++) {
+      const int buf = j & 1;
+      if (qg == 0) {
+        if (j + 1 < tpb && !dead) issue(t_first + j + 1, buf ^ 1);  // its buffer was released by the barrier below
+        // The copies never completed: report it, give them (and those of the tile just issued) one more bounded
+        // chance to land, and go on with EMPTY tiles (partials m = -inf, l = 0), so that this block still arrives on
+        // the counter of its (batch, KV head), the merge runs and the counter returns to zero.  The host must treat a
+        // raised status word as fatal.
+        if (!dead && !__syncthreads_and(mbar_wait(mb0 + 8 * buf, (unsigned)((j >> 1) & 1), ATT_WAIT_LIMIT))) {
+          if (tid == 0) atomicExch(p.status, 1);
+          mbar_wait(mb0 + 8 * buf, (unsigned)((j >> 1) & 1), ATT_WAIT_LIMIT);
+          if (j + 1 < tpb) mbar_wait(mb0 + 8 * (buf ^ 1), (unsigned)(((j + 1) >> 1) & 1), ATT_WAIT_LIMIT);
+          dead = true;
         }
       }
+      const int n_live = dead ? 0 : tile_rows(t_first + j);
+      const uint16_t* tile = KVs + buf * (ATT_TILE * 256);
+      for (int i = grp; i < ATT_TILE; i += 16) {  // uniform trip count per warp: shuffles need all lanes
+        const bool live = i < n_live && s_valid[buf][i];
+        float kf[16], vf[16];
+        if (live) {
+          const uint4* kp = reinterpret_cast<const uint4*>(tile + i * 256 + 16 * s);
+          const uint4* vp = reinterpret_cast<const uint4*>(tile + i * 256 + 128 + 16 * s);
+          unpack8f(kp[0], kf);
+          unpack8f(kp[1], kf + 8);
+          unpack8f(vp[0], vf);
+          unpack8f(vp[1], vf + 8);
+        } else {
+#pragma unroll
+          for (int jj = 0; jj < 16; jj++) kf[jj] = 0.0f, vf[jj] = 0.0f;
+        }
+#pragma unroll
+        for (int g = 0; g < ATT_GQ; g++) {
+          float d = 0.0f;
+#pragma unroll
+          for (int jj = 0; jj < 16; jj++) d = fmaf(kf[jj], qf[g][jj], d);
+          d += __shfl_xor_sync(0xffffffffu, d, 1);
+          d += __shfl_xor_sync(0xffffffffu, d, 2);
+          d += __shfl_xor_sync(0xffffffffu, d, 4);
+          if (live) {
+            const float sc = d * p.scale_log2;
+            const float mn = fmaxf(m[g], sc);
+            const float corr = exp2f(m[g] - mn);  // m = -inf on the first row gives 0
+            const float pr = exp2f(sc - mn);
+            lsum[g] = lsum[g] * corr + pr;
+#pragma unroll
+            for (int jj = 0; jj < 16; jj++) o[g][jj] = o[g][jj] * corr + pr * vf[jj];
+            m[g] = mn;
+          }
+        }
+      }
+      __syncthreads();  // the tile has been consumed: its buffer may be refilled (and, after the last tile or between
+                        // passes, obuf / s_m / s_l are free)
     }
-    __syncthreads();  // obuf / s_m / s_l of the previous pass have been consumed
 #pragma unroll
     for (int g = 0; g < ATT_GQ; g++) {
 #pragma unroll
-      for (int j = 0; j < 16; j++) obuf[(grp * ATT_GQ + g) * 128 + 16 * s + j] = o[g][j];
+      for (int jj = 0; jj < 16; jj++) obuf[(grp * ATT_GQ + g) * 128 + 16 * s + jj] = o[g][jj];
       if (s == 0) {
         s_m[grp][g] = m[g];
         s_l[grp][g] = lsum[g];
@@ -221,13 +251,14 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
         L += s_l[t][g] * f;
         O += obuf[(t * ATT_GQ + g) * 128 + tid] * f;
       }
-      float* rec = p.ws + (((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * p.n_tiles + tile) * ATT_REC;
+      float* rec = p.ws + (((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * n_groups + blockIdx.x) * ATT_REC;
       __stcg(rec + tid, O);
       if (tid == 0) {
         __stcg(rec + 128, M);
         __stcg(rec + 129, L);
       }
     }
+    __syncthreads();  // obuf / s_m / s_l have been consumed before the next pass writes them
   }
 
   // ---- the block that arrives last for this (batch, KV head) merges all tiles ----
@@ -235,7 +266,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
   __syncthreads();
   if (tid == 0) {
     const unsigned prev = atomicAdd(p.counters + bh, 1u);
-    s_last = prev + 1 == (unsigned)p.n_tiles;
+    s_last = prev + 1 == (unsigned)n_groups;
     if (s_last) p.counters[bh] = 0;  // ready for the next call on this stream
   }
   __syncthreads();
@@ -254,9 +285,9 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
     const int64_t bq0 = (int64_t)b * p.Hq + h * p.G + qg * ATT_GQ;
     if (qg) __syncthreads();            // the scale factors of the previous group have been consumed
     if (warp < n_heads) {
-      const float* rec = p.ws + (bq0 + warp) * p.n_tiles * ATT_REC;
+      const float* rec = p.ws + (bq0 + warp) * n_groups * ATT_REC;
       float mloc = -INFINITY;
-      for (int64_t t = lane; t < p.n_tiles; t += 32) {
+      for (int64_t t = lane; t < n_groups; t += 32) {
         const float mt = __ldcg(rec + t * ATT_REC + 128);
         s_f[warp * 1024 + t] = mt;
         mloc = fmaxf(mloc, mt);
@@ -264,7 +295,7 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
       float L = 0.0f;
-      for (int64_t t = lane; t < p.n_tiles; t += 32) {
+      for (int64_t t = lane; t < n_groups; t += 32) {
         const float mt = s_f[warp * 1024 + t];
         const float f = (mt == -INFINITY) ? 0.0f : exp2f(mt - mloc);
         s_f[warp * 1024 + t] = f;
@@ -278,23 +309,23 @@ __global__ void __launch_bounds__(ATT_THREADS) sparse_attention_kernel(AttParams
     float O[ATT_GQ];
 #pragma unroll
     for (int g = 0; g < ATT_GQ; g++) O[g] = 0.0f;
-    const float* rec0 = p.ws + bq0 * p.n_tiles * ATT_REC + tid;
+    const float* rec0 = p.ws + bq0 * n_groups * ATT_REC + tid;
     int64_t t = 0;
-    for (; t + 4 <= p.n_tiles; t += 4) {
+    for (; t + 4 <= n_groups; t += 4) {
       float v[ATT_GQ][4];
 #pragma unroll
       for (int g = 0; g < ATT_GQ; g++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) v[g][i] = g < n_heads ? __ldcg(rec0 + (g * p.n_tiles + t + i) * ATT_REC) : 0.0f;
+        for (int i = 0; i < 4; i++) v[g][i] = g < n_heads ? __ldcg(rec0 + (g * n_groups + t + i) * ATT_REC) : 0.0f;
 #pragma unroll
       for (int g = 0; g < ATT_GQ; g++)
 #pragma unroll
         for (int i = 0; i < 4; i++) O[g] += v[g][i] * s_f[g * 1024 + t + i];
     }
-    for (; t < p.n_tiles; t++)
+    for (; t < n_groups; t++)
 #pragma unroll
       for (int g = 0; g < ATT_GQ; g++)
-        if (g < n_heads) O[g] += __ldcg(rec0 + (g * p.n_tiles + t) * ATT_REC) * s_f[g * 1024 + t];
+        if (g < n_heads) O[g] += __ldcg(rec0 + (g * n_groups + t) * ATT_REC) * s_f[g * 1024 + t];
 #pragma unroll
     for (int g = 0; g < ATT_GQ; g++) {
       if (g >= n_heads) continue;
@@ -406,7 +437,16 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
   p.K = K, p.index_offset = index_offset;
   p.H = (int)H, p.Hq = (int)Hq, p.G = (int)(Hq / H);
   p.n_qgroups = (p.G + ATT_GQ - 1) / ATT_GQ;
-  p.n_tiles = n_tiles;
+  // Blocks per (batch, KV head): all the tiles when the launch is small (every copy of the launch outstanding at once),
+  // otherwise as many as give ONE wave of three blocks per SM, each streaming several tiles.  More than four query
+  // heads per KV head need the staged tile for several passes: one tile per block then.
+  int64_t groups = n_tiles;
+  if (p.n_qgroups == 1) {
+    const int64_t fit = (int64_t)sm_count() * 3 / (H * bs);
+    groups = fit < 1 ? 1 : (fit < n_tiles ? fit : n_tiles);
+  }
+  p.tiles_per_block = (int)((n_tiles + groups - 1) / groups);
+  groups = (n_tiles + p.tiles_per_block - 1) / p.tiles_per_block;
   p.scale_log2 = scale * 1.4426950408889634f;
   PK_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 15) == 0, "workspace must be 16-byte aligned");
   p.counters = (unsigned*)workspace;
@@ -426,7 +466,7 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
       return check_launch("sparse_attention smem");
     mark_on_device(smem_attr, bit);
   }
-  dim3 grid((unsigned)n_tiles, (unsigned)H, (unsigned)bs);
+  dim3 grid((unsigned)groups, (unsigned)H, (unsigned)bs);
   StageTimer tm(ST_ATTENTION, st);
   launch_chain(sparse_attention_kernel, grid, dim3(ATT_THREADS), (size_t)kSmem, st, p);
   return check_launch("sparse_attention");
