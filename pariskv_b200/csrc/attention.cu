@@ -20,6 +20,9 @@ constexpr int ATT_TILE = 64;
 constexpr int ATT_GQ = 4;       // query heads per pass
 constexpr int ATT_REC = 132;    // floats per partial: o[128], m, l, pad, pad
 constexpr int ATT_WAIT_LIMIT = 4000000;  // polls of the copy barrier before giving up
+// Elements (bf16) between two staged rows [K 128 | V 128 | pad].  The tensor-core form pads a row by 16 bytes, so that
+// the eight rows of an 8x8 fragment fall into eight different groups of four banks.
+template <bool MMA> struct AttRow { static constexpr int stride = MMA ? 264 : 256; };
 
 struct AttParams {
   const uint16_t* q;  // [bs][Hq][128]
@@ -81,10 +84,19 @@ __device__ __forceinline__ void mbar_arrive_expect(unsigned mb, unsigned bytes) 
 // whole launch (one sequence) every block has one tile and all copies of the launch are outstanding at once, which is
 // what the host link wants; with many (a batch of sequences, rows in HBM) a block amortises its fixed costs - index
 // loads, the partial record, the fence and the arrival - over its tiles and the grid is a single wave.
+//
+// MMA: the scores and the weighted sum of a tile run on the tensor cores (mma.sync m16n8k16, bf16 in, fp32 out) in the
+// arrangement of a flash-attention step with the query heads of the KV head as the 16 rows of the A operand (at most
+// eight are real): a warp takes 16 rows of the tile, S[head][row] = Q K^T is two n-tiles of eight k-steps, its C
+// fragments ARE the A fragments of P for O[head][dim] += P V (sixteen n-tiles over the 128 dims), V^T comes from
+// ldmatrix.trans.  The probabilities are rounded to bf16 for the second product, as the reference's attention
+// library does.
+template <bool MMA>
 __global__ void __launch_bounds__(ATT_THREADS, 3) sparse_attention_kernel(AttParams p) {
+  constexpr int RS = AttRow<MMA>::stride;  // elements per staged row
   extern __shared__ __align__(128) unsigned char dyn[];
-  uint16_t* KVs = reinterpret_cast<uint16_t*>(dyn);                          // [2 buffers][64][2][128]: K row, V row of a key
-  float* obuf = reinterpret_cast<float*>(dyn + 2 * ATT_TILE * 256);          // [16][4][128], over the SECOND buffer:
+  uint16_t* KVs = reinterpret_cast<uint16_t*>(dyn);                          // [2 buffers][64][RS]: K row, V row of a key
+  float* obuf = reinterpret_cast<float*>(dyn + 2 * ATT_TILE * RS);           // [16][4][128], over the SECOND buffer:
                                                                              // used when that buffer is idle
   __shared__ __align__(8) unsigned long long mbar[2];
   __shared__ float s_m[16][ATT_GQ], s_l[16][ATT_GQ];
@@ -134,7 +146,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 3) sparse_attention_kernel(AttPar
     const unsigned mb = mb0 + 8 * buf;
     if (ok && !(paired && is_v)) {
       const unsigned dst =
-          (unsigned)__cvta_generic_to_shared(KVs + buf * (ATT_TILE * 256) + i * 256 + ((is_v && !paired) ? 128 : 0));
+          (unsigned)__cvta_generic_to_shared(KVs + buf * (ATT_TILE * RS) + i * RS + ((is_v && !paired) ? 128 : 0));
       mbar_arrive_expect(mb, paired ? 512u : 256u);
       if (paired)
         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], 512, [%2];" ::"r"(dst),
@@ -145,108 +157,41 @@ __global__ void __launch_bounds__(ATT_THREADS, 3) sparse_attention_kernel(AttPar
                      "l"(src), "r"(mb)
                      : "memory");
     } else {
+      if (MMA && !ok) {  // a row without a copy is an operand of the matrix products all the same: make it zero
+        uint4* z = reinterpret_cast<uint4*>(KVs + buf * (ATT_TILE * RS) + i * RS + (is_v ? 128 : 0));
+#pragma unroll
+        for (int k = 0; k < 16; k++) z[k] = make_uint4(0, 0, 0, 0);
+      }
       mbar_arrive(mb);
     }
   };
   issue(t_first, 0);
 
-  const int s = tid & 7, grp = tid >> 3;
   bool dead = false;  // a copy barrier never completed: reported, the remaining tiles count as empty
-  for (int qg = 0; qg < p.n_qgroups; qg++) {  // more than one pass only for more than four query heads per KV head,
-                                              // and then a block has a single tile, which stays staged
-    const int n_heads = min(ATT_GQ, p.G - qg * ATT_GQ);
-    float qf[ATT_GQ][16];
-#pragma unroll
-    for (int g = 0; g < ATT_GQ; g++) {
-      if (g < n_heads) {
-        const uint4* qp =
-            reinterpret_cast<const uint4*>(p.q + ((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * 128 + 16 * s);
-        unpack8f(__ldg(qp), qf[g]);
-        unpack8f(__ldg(qp + 1), qf[g] + 8);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; i++) qf[g][i] = 0.0f;
-      }
+  // Called by every thread once per tile j of the block: starts the copies of tile j + 1 (its buffer was released by
+  // the barrier that ends tile j - 1), waits for tile j, returns its live rows.
+  // The copies never completed: report it, give them (and those of the tile just issued) one more bounded chance to
+  // land, and go on with EMPTY tiles (partials m = -inf, l = 0), so that this block still arrives on the counter of
+  // its (batch, KV head), the merge runs and the counter returns to zero.  The host must treat a raised status word
+  // as fatal.
+  auto acquire = [&](int j) -> int {
+    const int buf = j & 1;
+    if (j + 1 < tpb && !dead) issue(t_first + j + 1, buf ^ 1);
+    if (!dead && !__syncthreads_and(mbar_wait(mb0 + 8 * buf, (unsigned)((j >> 1) & 1), ATT_WAIT_LIMIT))) {
+      if (tid == 0) atomicExch(p.status, 1);
+      mbar_wait(mb0 + 8 * buf, (unsigned)((j >> 1) & 1), ATT_WAIT_LIMIT);
+      if (j + 1 < tpb) mbar_wait(mb0 + 8 * (buf ^ 1), (unsigned)(((j + 1) >> 1) & 1), ATT_WAIT_LIMIT);
+      dead = true;
     }
-    float m[ATT_GQ], lsum[ATT_GQ], o[ATT_GQ][16];
-#pragma unroll
-    for (int g = 0; g < ATT_GQ; g++) {
-      m[g] = -INFINITY;
-      lsum[g] = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 16; i++) o[g][i] = 0.0f;
-    }
-    for (int j = 0; j < tpb; j++) {
-      const int buf = j & 1;
-      if (qg == 0) {
-        if (j + 1 < tpb && !dead) issue(t_first + j + 1, buf ^ 1);  // its buffer was released by the barrier below
-        // The copies never completed: report it, give them (and those of the tile just issued) one more bounded
-        // chance to land, and go on with EMPTY tiles (partials m = -inf, l = 0), so that this block still arrives on
-        // the counter of its (batch, KV head), the merge runs and the counter returns to zero.  The host must treat a
-        // raised status word as fatal.
-        if (!dead && !__syncthreads_and(mbar_wait(mb0 + 8 * buf, (unsigned)((j >> 1) & 1), ATT_WAIT_LIMIT))) {
-          if (tid == 0) atomicExch(p.status, 1);
-          mbar_wait(mb0 + 8 * buf, (unsigned)((j >> 1) & 1), ATT_WAIT_LIMIT);
-          if (j + 1 < tpb) mbar_wait(mb0 + 8 * (buf ^ 1), (unsigned)(((j + 1) >> 1) & 1), ATT_WAIT_LIMIT);
-          dead = true;
-        }
-      }
-      const int n_live = dead ? 0 : tile_rows(t_first + j);
-      const uint16_t* tile = KVs + buf * (ATT_TILE * 256);
-      for (int i = grp; i < ATT_TILE; i += 16) {  // uniform trip count per warp: shuffles need all lanes
-        const bool live = i < n_live && s_valid[buf][i];
-        float kf[16], vf[16];
-        if (live) {
-          const uint4* kp = reinterpret_cast<const uint4*>(tile + i * 256 + 16 * s);
-          const uint4* vp = reinterpret_cast<const uint4*>(tile + i * 256 + 128 + 16 * s);
-          unpack8f(kp[0], kf);
-          unpack8f(kp[1], kf + 8);
-          unpack8f(vp[0], vf);
-          unpack8f(vp[1], vf + 8);
-        } else {
-#pragma unroll
-          for (int jj = 0; jj < 16; jj++) kf[jj] = 0.0f, vf[jj] = 0.0f;
-        }
-#pragma unroll
-        for (int g = 0; g < ATT_GQ; g++) {
-          float d = 0.0f;
-#pragma unroll
-          for (int jj = 0; jj < 16; jj++) d = fmaf(kf[jj], qf[g][jj], d);
-          d += __shfl_xor_sync(0xffffffffu, d, 1);
-          d += __shfl_xor_sync(0xffffffffu, d, 2);
-          d += __shfl_xor_sync(0xffffffffu, d, 4);
-          if (live) {
-            const float sc = d * p.scale_log2;
-            const float mn = fmaxf(m[g], sc);
-            const float corr = exp2f(m[g] - mn);  // m = -inf on the first row gives 0
-            const float pr = exp2f(sc - mn);
-            lsum[g] = lsum[g] * corr + pr;
-#pragma unroll
-            for (int jj = 0; jj < 16; jj++) o[g][jj] = o[g][jj] * corr + pr * vf[jj];
-            m[g] = mn;
-          }
-        }
-      }
-      __syncthreads();  // the tile has been consumed: its buffer may be refilled (and, after the last tile or between
-                        // passes, obuf / s_m / s_l are free)
-    }
-#pragma unroll
-    for (int g = 0; g < ATT_GQ; g++) {
-#pragma unroll
-      for (int jj = 0; jj < 16; jj++) obuf[(grp * ATT_GQ + g) * 128 + 16 * s + jj] = o[g][jj];
-      if (s == 0) {
-        s_m[grp][g] = m[g];
-        s_l[grp][g] = lsum[g];
-      }
-    }
-    __syncthreads();
+    return dead ? 0 : tile_rows(t_first + j);
+  };
+  // Partial record of this block for up to ATT_GQ query heads from the groups' (m, l, o) in shared memory.
+  auto block_partial = [&](int qg, int n_heads, int n_grp) {
     for (int g = 0; g < n_heads; g++) {
       float M = -INFINITY;
-#pragma unroll
-      for (int t = 0; t < 16; t++) M = fmaxf(M, s_m[t][g]);
+      for (int t = 0; t < n_grp; t++) M = fmaxf(M, s_m[t][g]);
       float L = 0.0f, O = 0.0f;
-#pragma unroll
-      for (int t = 0; t < 16; t++) {
+      for (int t = 0; t < n_grp; t++) {
         const float f = (s_m[t][g] == -INFINITY) ? 0.0f : exp2f(s_m[t][g] - M);
         L += s_l[t][g] * f;
         O += obuf[(t * ATT_GQ + g) * 128 + tid] * f;
@@ -258,7 +203,195 @@ __global__ void __launch_bounds__(ATT_THREADS, 3) sparse_attention_kernel(AttPar
         __stcg(rec + 129, L);
       }
     }
-    __syncthreads();  // obuf / s_m / s_l have been consumed before the next pass writes them
+  };
+
+  if constexpr (MMA) {
+    // ---- tensor-core form: one pass, at most ATT_GQ query heads per KV head ----
+    const int lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+    const bool head_ok = g < p.G;
+    uint32_t qa[8][2];  // A fragments of Q for the eight k-steps: rows g (a0, a2); rows g + 8 are zero (a1, a3)
+    {
+      const uint32_t* qrow = reinterpret_cast<const uint32_t*>(p.q + ((int64_t)b * p.Hq + h * p.G + (head_ok ? g : 0)) * 128);
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        qa[k][0] = head_ok ? __ldg(qrow + 8 * k + t) : 0u;
+        qa[k][1] = head_ok ? __ldg(qrow + 8 * k + 4 + t) : 0u;
+      }
+    }
+    float oacc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; n++) oacc[n][0] = oacc[n][1] = oacc[n][2] = oacc[n][3] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;  // head g; l is this lane's share, summed over the four lanes at the end
+    const int r0 = warp * 16;               // this warp's rows of every tile
+    for (int j = 0; j < tpb; j++) {
+      const int buf = j & 1;
+      const int n_live = acquire(j);
+      const uint16_t* tile = KVs + buf * (ATT_TILE * RS);
+      if (r0 < n_live) {  // warp-uniform
+        // S[head][row] = Q K^T over the warp's 16 rows: two n-tiles of eight rows
+        float sc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+          sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.0f;
+          const uint32_t* krow = reinterpret_cast<const uint32_t*>(tile + (r0 + nt * 8 + g) * RS);
+#pragma unroll
+          for (int k = 0; k < 8; k++) {
+            const uint32_t b0 = krow[8 * k + t], b1 = krow[8 * k + 4 + t];
+            asm volatile(
+                "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                : "+f"(sc[nt][0]), "+f"(sc[nt][1]), "+f"(sc[nt][2]), "+f"(sc[nt][3])
+                : "r"(qa[k][0]), "r"(0u), "r"(qa[k][1]), "r"(0u), "r"(b0), "r"(b1));
+          }
+        }
+        // online softmax of head g over the rows this lane holds: n-tile nt, columns 2t and 2t + 1
+        float v[2][2], mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const int row = r0 + nt * 8 + 2 * t + e;
+            const bool live = row < n_live && s_valid[buf][row];
+            v[nt][e] = live ? sc[nt][e] * p.scale_log2 : -INFINITY;
+            mx = fmaxf(mx, v[nt][e]);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const bool none = m_new == -INFINITY;  // no live row so far
+        const float corr = none ? 1.0f : exp2f(m_run - m_new);
+        float pr[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) pr[nt][e] = none ? 0.0f : exp2f(v[nt][e] - m_new);
+        l_run = l_run * corr + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
+        m_run = m_new;
+#pragma unroll
+        for (int n = 0; n < 16; n++) oacc[n][0] *= corr, oacc[n][1] *= corr;
+        // P as the A operand of the second product (bf16): rows g hold the probabilities, rows g + 8 are zero
+        uint32_t pa0, pa2;
+        {
+          const __nv_bfloat162 x0 = __floats2bfloat162_rn(pr[0][0], pr[0][1]), x1 = __floats2bfloat162_rn(pr[1][0], pr[1][1]);
+          pa0 = *reinterpret_cast<const uint32_t*>(&x0), pa2 = *reinterpret_cast<const uint32_t*>(&x1);
+        }
+        // O[head][dim] += P V: sixteen n-tiles of eight dims, two per ldmatrix (V^T fragments)
+        const int mi = lane >> 3;
+        const uint16_t* vrow = tile + (r0 + (mi & 1) * 8 + (lane & 7)) * RS + 128 + (mi >> 1) * 8;
+#pragma unroll
+        for (int np = 0; np < 8; np++) {
+          uint32_t b0, b1, b2, b3;
+          const unsigned addr = (unsigned)__cvta_generic_to_shared(vrow + np * 16);
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                       : "r"(addr));
+          asm volatile(
+              "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+              : "+f"(oacc[2 * np][0]), "+f"(oacc[2 * np][1]), "+f"(oacc[2 * np][2]), "+f"(oacc[2 * np][3])
+              : "r"(pa0), "r"(0u), "r"(pa2), "r"(0u), "r"(b0), "r"(b1));
+          asm volatile(
+              "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+              : "+f"(oacc[2 * np + 1][0]), "+f"(oacc[2 * np + 1][1]), "+f"(oacc[2 * np + 1][2]), "+f"(oacc[2 * np + 1][3])
+              : "r"(pa0), "r"(0u), "r"(pa2), "r"(0u), "r"(b2), "r"(b3));
+        }
+      }
+      __syncthreads();  // the tile has been consumed: its buffer may be refilled (after the last tile obuf is free)
+    }
+    // the four warps are the groups of the block-level merge
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (g < ATT_GQ) {
+#pragma unroll
+      for (int n = 0; n < 16; n++) {
+        obuf[(warp * ATT_GQ + g) * 128 + 8 * n + 2 * t] = oacc[n][0];
+        obuf[(warp * ATT_GQ + g) * 128 + 8 * n + 2 * t + 1] = oacc[n][1];
+      }
+      if (t == 0) {
+        s_m[warp][g] = head_ok ? m_run : -INFINITY;
+        s_l[warp][g] = head_ok ? l_run : 0.0f;
+      }
+    }
+    __syncthreads();
+    block_partial(0, min(ATT_GQ, p.G), ATT_THREADS / 32);
+  } else {
+    const int s = tid & 7, grp = tid >> 3;
+    for (int qg = 0; qg < p.n_qgroups; qg++) {  // more than one pass only for more than four query heads per KV head,
+                                                // and then a block has a single tile, which stays staged
+      const int n_heads = min(ATT_GQ, p.G - qg * ATT_GQ);
+      float qf[ATT_GQ][16];
+#pragma unroll
+      for (int g = 0; g < ATT_GQ; g++) {
+        if (g < n_heads) {
+          const uint4* qp =
+              reinterpret_cast<const uint4*>(p.q + ((int64_t)b * p.Hq + h * p.G + qg * ATT_GQ + g) * 128 + 16 * s);
+          unpack8f(__ldg(qp), qf[g]);
+          unpack8f(__ldg(qp + 1), qf[g] + 8);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; i++) qf[g][i] = 0.0f;
+        }
+      }
+      float m[ATT_GQ], lsum[ATT_GQ], o[ATT_GQ][16];
+#pragma unroll
+      for (int g = 0; g < ATT_GQ; g++) {
+        m[g] = -INFINITY;
+        lsum[g] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i++) o[g][i] = 0.0f;
+      }
+      for (int j = 0; j < tpb; j++) {
+        const int buf = j & 1;
+        const int n_live = qg == 0 ? acquire(j) : (dead ? 0 : tile_rows(t_first + j));
+        const uint16_t* tile = KVs + buf * (ATT_TILE * RS);
+        for (int i = grp; i < ATT_TILE; i += 16) {  // uniform trip count per warp: shuffles need all lanes
+          const bool live = i < n_live && s_valid[buf][i];
+          float kf[16], vf[16];
+          if (live) {
+            const uint4* kp = reinterpret_cast<const uint4*>(tile + i * RS + 16 * s);
+            const uint4* vp = reinterpret_cast<const uint4*>(tile + i * RS + 128 + 16 * s);
+            unpack8f(kp[0], kf);
+            unpack8f(kp[1], kf + 8);
+            unpack8f(vp[0], vf);
+            unpack8f(vp[1], vf + 8);
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 16; jj++) kf[jj] = 0.0f, vf[jj] = 0.0f;
+          }
+#pragma unroll
+          for (int g = 0; g < ATT_GQ; g++) {
+            float d = 0.0f;
+#pragma unroll
+            for (int jj = 0; jj < 16; jj++) d = fmaf(kf[jj], qf[g][jj], d);
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            if (live) {
+              const float sc = d * p.scale_log2;
+              const float mn = fmaxf(m[g], sc);
+              const float corr = exp2f(m[g] - mn);  // m = -inf on the first row gives 0
+              const float pr = exp2f(sc - mn);
+              lsum[g] = lsum[g] * corr + pr;
+#pragma unroll
+              for (int jj = 0; jj < 16; jj++) o[g][jj] = o[g][jj] * corr + pr * vf[jj];
+              m[g] = mn;
+            }
+          }
+        }
+        __syncthreads();  // the tile has been consumed: its buffer may be refilled (and, after the last tile or
+                          // between passes, obuf / s_m / s_l are free)
+      }
+#pragma unroll
+      for (int g = 0; g < ATT_GQ; g++) {
+#pragma unroll
+        for (int jj = 0; jj < 16; jj++) obuf[(grp * ATT_GQ + g) * 128 + 16 * s + jj] = o[g][jj];
+        if (s == 0) {
+          s_m[grp][g] = m[g];
+          s_l[grp][g] = lsum[g];
+        }
+      }
+      __syncthreads();
+      block_partial(qg, n_heads, 16);
+      __syncthreads();  // obuf / s_m / s_l have been consumed before the next pass writes them
+    }
   }
 
   // ---- the block that arrives last for this (batch, KV head) merges all tiles ----
@@ -459,15 +592,19 @@ extern "C" int pk_sparse_attention(const pk_tensor* queries, const pk_tensor* wi
     p.lse = (float*)lse->data;
   }
   cudaStream_t st = (cudaStream_t)stream;
-  constexpr int kSmem = 2 * ATT_TILE * 256 + 16 * ATT_GQ * 128 * 4;
-  static PerDevice smem_attr;  // the opt-in to more than 48 KB of dynamic shared memory is per device
-  if (const unsigned long long bit = first_on_device(smem_attr)) {
-    if (cudaFuncSetAttribute(sparse_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) != cudaSuccess)
-      return check_launch("sparse_attention smem");
-    mark_on_device(smem_attr, bit);
+  // at most ATT_GQ query heads per KV head: scores and weighted sum on the tensor cores; more: the scalar form in passes
+  const bool mma = p.G <= ATT_GQ;
+  const int smem = 2 * ATT_TILE * (mma ? AttRow<true>::stride : AttRow<false>::stride) * 2;   // two staging buffers
+  static PerDevice smem_attr[2];  // the opt-in to more than 48 KB of dynamic shared memory is per kernel and device
+  if (const unsigned long long bit = first_on_device(smem_attr[mma])) {
+    const cudaError_t e = mma ? cudaFuncSetAttribute(sparse_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                              : cudaFuncSetAttribute(sparse_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return check_launch("sparse_attention smem");
+    mark_on_device(smem_attr[mma], bit);
   }
   dim3 grid((unsigned)groups, (unsigned)H, (unsigned)bs);
   StageTimer tm(ST_ATTENTION, st);
-  launch_chain(sparse_attention_kernel, grid, dim3(ATT_THREADS), (size_t)kSmem, st, p);
+  if (mma) launch_chain(sparse_attention_kernel<true>, grid, dim3(ATT_THREADS), (size_t)smem, st, p);
+  else launch_chain(sparse_attention_kernel<false>, grid, dim3(ATT_THREADS), (size_t)smem, st, p);
   return check_launch("sparse_attention");
 }
