@@ -118,8 +118,10 @@ class DecoderHarness:
         """One decode token per sequence through all layers; token: int64 [B] on the device.  Returns the next
         tokens [B].  pos_dev (float32 [B] or [1] on the device) replaces the host-side position when the step is
         captured or when the sequences of a batch stand at different positions.
-        Between the projections (library GEMMs) a layer launches four elementwise kernels of this repository:
-        q/k norm + RoPE, residual add (+ reduction over ranks) + norm twice, and the gated activation."""
+        With one token a layer is twelve launches of this repository's library: the four of the cache path, four
+        projections (streaming matrix-vector kernel; the gate / up pair with the activation in its epilogue) and the
+        elementwise glue (q/k norm + RoPE, residual add (+ reduction over ranks) + norm twice).  Batches go through
+        the library GEMM and a separate activation launch."""
         from pariskv_b200 import ops
         c = self.cfg
         D, L = c["head_dim"], c["layers"]
