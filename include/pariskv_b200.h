@@ -57,7 +57,7 @@ int64_t pk_launch_count(void);
  * ranking/table, 2 collision, 3 select+rerank, 4 final top-k, 5 attention tiles, 6 attention merge,
  * 7 encode, 8 stand-alone top-k, 9 stand-alone rerank, 10 UVA gather, 11 cluster histogram, 12 row append,
  * 13 decode glue, 14 tensor-parallel reduce, 15 shard pack / send, 16 shard receive / merge, 17 shard owned rows,
- * 18 shard count-histogram reduce, 19 matrix-vector product) and clears the record. */
+ * 18 shard count-histogram reduce, 19 matrix-vector product, 20 adaptive-k selection) and clears the record. */
 int pk_timing_enable(int on);
 int pk_timing_read(double* ms_per_stage, int64_t* spans_per_stage, int n_stages);
 /* Launches issued INTO A STREAM CAPTURE while timing is enabled are bracketed by external event-record nodes, which

@@ -187,7 +187,7 @@ def launch_count() -> int:
 
 STAGES = ["query_prep", "rank_table", "collision", "select_rerank", "final_topk", "attention", "attention_merge",
           "encode", "topk", "rerank", "uva_gather", "count_clusters", "append", "glue", "tp_reduce",
-          "shard_send", "shard_recv", "shard_owned", "hist_reduce", "gemv"]
+          "shard_send", "shard_recv", "shard_owned", "hist_reduce", "gemv", "adaptive_topk"]
 
 
 def set_pdl(on: bool):

@@ -327,6 +327,7 @@ extern "C" int pk_adaptive_topk(const pk_tensor* sl_logits, const pk_tensor* can
     if (cudaFuncSetAttribute(adaptive_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return check_launch("adaptive_topk smem");
   }
+  StageTimer timer(ST_ADAPTIVE, (cudaStream_t)stream);
   adaptive_topk_kernel<<<(unsigned)(bs * H), AK_THREADS, smem, (cudaStream_t)stream>>>(p);
   return check_launch("adaptive_topk");
 }

@@ -17,7 +17,7 @@ int sm_count();
 enum Stage { ST_QUERY_PREP = 0, ST_RANK = 1, ST_COLLISION = 2, ST_SELECT_RERANK = 3, ST_FINAL_TOPK = 4,
              ST_ATTENTION = 5, ST_ATTENTION_MERGE = 6, ST_ENCODE = 7, ST_TOPK = 8, ST_RERANK = 9, ST_GATHER = 10,
              ST_COUNT = 11, ST_APPEND = 12, ST_GLUE = 13, ST_REDUCE = 14, ST_SHARD_SEND = 15, ST_SHARD_RECV = 16,
-             ST_SHARD_OWNED = 17, ST_HIST_REDUCE = 18, ST_GEMV = 19 };
+             ST_SHARD_OWNED = 17, ST_HIST_REDUCE = 18, ST_GEMV = 19, ST_ADAPTIVE = 20 };
 // Records one event before and one after the launches issued during its lifetime, on the launch stream.
 class StageTimer {
  public:
