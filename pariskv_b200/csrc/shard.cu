@@ -263,6 +263,8 @@ __global__ void __launch_bounds__(TP_THREADS) tp_allreduce_kernel(const unsigned
   const int tid = threadIdx.x;
   __shared__ unsigned s_epoch;
   __shared__ float s_part[TP_THREADS / 32];
+  pdl_wait();     // the partial row comes from the kernel before this one
+  pdl_trigger();
   if (tid == 0) s_epoch = ctl->epoch + 1;
   __syncthreads();
   const unsigned epoch = s_epoch;
@@ -588,10 +590,9 @@ extern "C" int pk_tp_allreduce(const pk_tensor* partial, const pk_tensor* residu
   int rc;
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
   StageTimer timer(ST_REDUCE, (cudaStream_t)stream);
-  tp_allreduce_kernel<<<1, TP_THREADS, 0, (cudaStream_t)stream>>>((const unsigned*)partial->data, (const unsigned*)res,
-                                                                  (unsigned*)out->data, (int)(n / 2), ps, gather_offset, area_bytes,
-                                                                  rank, world, (PeerCtl*)control, (const unsigned*)nw,
-                                                                  (unsigned*)nout, (float)eps, 0);
+  launch_chain(tp_allreduce_kernel, dim3(1), dim3(TP_THREADS), 0, (cudaStream_t)stream, (const unsigned*)partial->data,
+               (const unsigned*)res, (unsigned*)out->data, (int)(n / 2), ps, gather_offset, area_bytes, rank, world,
+               (PeerCtl*)control, (const unsigned*)nw, (unsigned*)nout, (float)eps, 0);
   return check_launch("tp_allreduce");
 }
 
@@ -614,8 +615,8 @@ extern "C" int pk_tp_allgather(const pk_tensor* part, const pk_tensor* out, cons
   int rc;
   if ((rc = fill_peers(&ps, peer_bases, world, rank))) return rc;
   StageTimer timer(ST_REDUCE, (cudaStream_t)stream);
-  tp_allreduce_kernel<<<1, TP_THREADS, 0, (cudaStream_t)stream>>>((const unsigned*)part->data, nullptr, (unsigned*)out->data,
-                                                                  (int)(n / 2), ps, gather_offset, area_bytes, rank, world,
-                                                                  (PeerCtl*)control, nullptr, nullptr, 0.0f, 1);
+  launch_chain(tp_allreduce_kernel, dim3(1), dim3(TP_THREADS), 0, (cudaStream_t)stream, (const unsigned*)part->data,
+               (const unsigned*)nullptr, (unsigned*)out->data, (int)(n / 2), ps, gather_offset, area_bytes, rank, world,
+               (PeerCtl*)control, (const unsigned*)nullptr, (unsigned*)nullptr, 0.0f, 1);
   return check_launch("tp_allgather");
 }
